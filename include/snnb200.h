@@ -1,0 +1,173 @@
+/*
+ * snnb200 — C ABI of the B200 (sm_100a) fused temporal SNN kernels.
+ *
+ * Every entry point replaces one Triton launcher (and the backend function in
+ * front of it) of pengjh0111/triton-snn-fusion; the reference item is cited
+ * above each declaration as <file>:<lines> inside that project.
+ *
+ * Conventions shared by all entry points
+ *   - plain device pointers, sizes and scalars; no torch types;
+ *   - the caller owns every buffer; nothing is allocated, nothing is
+ *     synchronised, no mutable global state is kept, so calls are re-entrant
+ *     and may be issued on any stream (`stream` is a cudaStream_t passed as
+ *     void*; NULL = the legacy default stream);
+ *   - return value: SNNB_OK or an SNNB_ERR_* code; the text of the last error
+ *     on the calling thread is returned by snnb_last_error();
+ *   - activations are dense channels-last ("NHWC") unless a layout argument
+ *     says otherwise: a frame is [B][H][W][C] with C innermost, a sequence is
+ *     T such frames `x_t_stride` elements apart;
+ *   - LIF update (reference runtime/snn_custom_ops.py:384-409), all in fp32
+ *     without FMA contraction:
+ *         h = (tau <= 1) ? v + x : v + (x - v) / tau
+ *         s = (h >= v_th)
+ *         v = (v_reset >= 0) ? (s ? v_reset : h)      hard reset
+ *                            : h - s * v_th           soft reset
+ *     `v_init == NULL` means a zero initial membrane (the reference's 0-dim
+ *     tensor convention, runtime/snn_custom_ops.py:378-381);
+ *   - dtypes are snnb_dtype values. `spike_dtype` may be the activation dtype
+ *     (drop-in: 0.0 / 1.0) or SNNB_U8 (0 / 1 bytes). `v_dtype` is the dtype of
+ *     both v_init and v_out: the activation dtype (drop-in) or SNNB_F32.
+ */
+#ifndef SNNB200_H_
+#define SNNB200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SNNB_OK 0
+#define SNNB_ERR_INVALID 1     /* bad argument (null pointer, size, alignment) */
+#define SNNB_ERR_UNSUPPORTED 2 /* valid request this build has no kernel for   */
+#define SNNB_ERR_CUDA 3        /* a CUDA runtime / driver call failed          */
+
+typedef enum snnb_dtype { SNNB_F32 = 0, SNNB_BF16 = 1, SNNB_F16 = 2, SNNB_U8 = 3 } snnb_dtype;
+typedef enum snnb_layout { SNNB_NCHW = 0, SNNB_NHWC = 1 } snnb_layout;
+
+/* Which conv / linear implementation to use. AUTO picks the tcgen05 path when
+ * the shape qualifies (16-bit activations, Cin a multiple of 64, see
+ * snnb_conv_lif) and the CUDA-core path otherwise. */
+typedef enum snnb_path { SNNB_PATH_AUTO = 0, SNNB_PATH_SIMT = 1, SNNB_PATH_TCGEN05 = 2 } snnb_path;
+
+/* Library version (major*10000 + minor*100 + patch). */
+int snnb_version(void);
+
+/* Text of the last error raised on the calling thread ("" if none). */
+const char *snnb_last_error(void);
+
+/* Reads and clears the device-side status word that the tcgen05 kernels set
+ * when one of their bounded mbarrier waits gives up. Synchronises the device.
+ * 0 = no kernel reported a problem. Diagnostic only; never called on the hot
+ * path. */
+int snnb_device_status(int *status_out);
+
+/*
+ * Standalone temporal LIF scan.
+ * Replaces run_triton_fused_temporal_lif_state
+ * (runtime/triton_temporal_lif_backend.py:57-117) and
+ * _fused_temporal_lif_state_kernel / run_fused_temporal_lif_state_kernel
+ * (kernels/generated_temporal_lif_kernel.py:53-154).
+ *   x_seq  [T][n]  activation dtype     spikes [T][n] spike_dtype
+ *   v_init [n] or NULL, v_out [n]       v_dtype
+ * Any T >= 1 (the reference only takes 1,2,4,8,16). Spikes are bit-exact
+ * against the fp32 reference loop.
+ */
+int snnb_lif_scan(const void *x_seq, const void *v_init, void *spikes, void *v_out,
+                  int T, int64_t n, int x_dtype, int spike_dtype, int v_dtype,
+                  float v_th, float v_reset, float tau, void *stream);
+
+/*
+ * LIF -> global average pool -> linear tail, summed over T, one kernel.
+ * Replaces run_triton_fused_temporal_lif_avgpool_linear
+ * (runtime/triton_temporal_lif_avgpool_linear_backend.py:58-108) and the two
+ * kernels + launcher of kernels/generated_temporal_lif_avgpool_linear_kernel.py:8-209.
+ *   x_seq [T][N][C][HW] (SNNB_NCHW) or [T][N][HW][C] (SNNB_NHWC), dtype
+ *   fc_w [K][C], fc_b [K] or NULL, dtype
+ *   out_sum [N][K] dtype   = sum_t ( W * mean_hw(spike_t) + b )
+ *   v_init / v_out as x_seq[0], v_dtype
+ */
+int snnb_lif_avgpool_linear(const void *x_seq, const void *v_init, const void *fc_w,
+                            const void *fc_b, void *out_sum, void *v_out,
+                            int T, int N, int C, int HW, int K, int layout,
+                            int dtype, int v_dtype,
+                            float v_th, float v_reset, float tau, void *stream);
+
+/*
+ * 3x3 depthwise conv (BN folded into w, b) + optional residual + LIF over T.
+ * Replaces the depthwise kernels emitted by
+ * kernels/benchmark_conv_lif_temporal_general.py:713-817 and the backend
+ * run_triton_fused_temporal_depthwise_conv_lif_state
+ * (runtime/triton_convlif_backend.py:473-510, :513-598).
+ *   x_seq [T][B][H][W][C] (frames x_t_stride elements apart; 0 = one frame
+ *   reused for every step), w [C][3][3] (the torch [C,1,3,3] tensor), b [C],
+ *   residual NULL or [T][B][Ho][Wo][C], spikes [T][B][Ho][Wo][C],
+ *   v_init/v_out [B][Ho][Wo][C]; stride 1 or 2, padding 1.
+ */
+int snnb_dwconv3x3_lif(const void *x_seq, int64_t x_t_stride, const void *w, const void *b,
+                       const void *residual, const void *v_init, void *spikes, void *v_out,
+                       int T, int B, int C, int H, int W, int stride,
+                       int dtype, int spike_dtype, int v_dtype,
+                       float v_th, float v_reset, float tau, void *stream);
+
+/*
+ * Dense conv (groups = 1, BN folded into w, b) + optional residual + LIF over T.
+ * Replaces the regular / pointwise / residual kernels emitted by
+ * kernels/benchmark_conv_lif_temporal_general.py:561-710 (+ :685-703 residual),
+ * their launchers (:971-1323) and the backends
+ * run_triton_fused_temporal_conv_lif_state / _pointwise_ / _conv_add_ /
+ * _packed_out (runtime/triton_convlif_backend.py:393-817).
+ *   x_seq [T][B][H][W][Cin], frames x_t_stride elements apart (0 = the same
+ *   frame at every step: the conv is evaluated once and only the LIF runs T
+ *   times), w [Cout][KH][KW][Cin] (the torch weight in channels_last memory
+ *   format), b [Cout], residual NULL or [T][B][Ho][Wo][Cout],
+ *   spikes [T][B][Ho][Wo][Cout], v_init/v_out [B][Ho][Wo][Cout].
+ * `lif` = 0 turns the LIF off: `spikes` then receives conv + bias (+ residual)
+ * in the activation dtype for every t and v_init / v_out are ignored (used for
+ * the BN-folded shortcut convs that feed a residual input).
+ * path: SNNB_PATH_TCGEN05 needs dtype bf16/f16, Cin % 64 == 0, Cout % 16 == 0,
+ * (KH,KW,stride,pad) in {(1,1,1|2,0), (3,3,1|2,1)} and T*min(Cout,128)-column
+ * accumulators that fit TMEM (T <= 16); anything else runs on SNNB_PATH_SIMT.
+ */
+int snnb_conv_lif(const void *x_seq, int64_t x_t_stride, const void *w, const void *b,
+                  const void *residual, const void *v_init, void *spikes, void *v_out,
+                  int T, int B, int Cin, int H, int W, int Cout, int KH, int KW,
+                  int stride, int pad, int lif,
+                  int dtype, int spike_dtype, int v_dtype,
+                  float v_th, float v_reset, float tau, int path, void *stream);
+
+/*
+ * Temporal linear + LIF.
+ * Replaces run_triton_fused_temporal_linear_lif_state{,_packed,_packed_out}
+ * (runtime/triton_temporal_linear_lif_backend.py:74-274) and
+ * _fused_temporal_linear_lif_state_kernel + launcher
+ * (kernels/generated_temporal_linear_lif_kernel.py:91-363).
+ *   x_seq [T][M][K] (x_t_stride elements apart), w [N][K], b [N] or NULL,
+ *   spikes [T][M][N], v_init/v_out [M][N].
+ * The tcgen05 path needs dtype bf16/f16 and K % 64 == 0, N % 16 == 0.
+ */
+int snnb_linear_lif(const void *x_seq, int64_t x_t_stride, const void *w, const void *b,
+                    const void *v_init, void *spikes, void *v_out,
+                    int T, int M, int K, int N,
+                    int dtype, int spike_dtype, int v_dtype,
+                    float v_th, float v_reset, float tau, int path, void *stream);
+
+/*
+ * Stateless neighbours of the fused ops inside a spiking ResNet, so that a
+ * whole network runs on this library's channels-last layout. In the reference
+ * these stay ordinary aten ops applied to flatten(0,1) of the spike stack
+ * (compiler/fx_spatial_batching.py:799-879).
+ */
+/* NCHW <-> NHWC of `frames` frames [C][HW] <-> [HW][C]. */
+int snnb_nchw_to_nhwc(const void *src, void *dst, int64_t frames, int C, int HW, int dtype, void *stream);
+int snnb_nhwc_to_nchw(const void *src, void *dst, int64_t frames, int C, int HW, int dtype, void *stream);
+/* max_pool2d(kernel 3, stride 2, padding 1) over `frames` NHWC frames. */
+int snnb_maxpool3x3s2(const void *x, void *y, int64_t frames, int H, int W, int C, int dtype, void *stream);
+/* out[n][k] = (1/T) sum_t ( fc_w . mean_hw x[t][n] + fc_b ), x NHWC [T][N][HW][C], out fp32. */
+int snnb_avgpool_linear_mean(const void *x_seq, const void *fc_w, const void *fc_b, float *out,
+                             int T, int N, int C, int HW, int K, int dtype, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SNNB200_H_ */
