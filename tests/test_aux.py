@@ -1,0 +1,59 @@
+"""Stateless channels-last helpers against torch on the CPU."""
+import pytest
+import torch
+import torch.nn.functional as F
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _lib():
+    from triton_snn_fusion_b200 import _lib
+    return _lib
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("shape", [(5, 3, 7, 9), (2, 64, 14, 14), (1, 33, 1, 1)])
+def test_layout_round_trip(dtype, shape):
+    L = _lib()
+    F_, C, H, W = shape
+    x = torch.randn(shape).to(dtype)
+    xd = x.to(DEV)
+    y = torch.empty(F_, H, W, C, dtype=dtype, device=DEV)
+    L.check(L.lib.snnb_nchw_to_nhwc(xd.data_ptr(), y.data_ptr(), F_, C, H * W, L.dtype_code(dtype), None), "t")
+    assert torch.equal(y.cpu(), x.permute(0, 2, 3, 1).contiguous())
+    back = torch.empty_like(xd)
+    L.check(L.lib.snnb_nhwc_to_nchw(y.data_ptr(), back.data_ptr(), F_, C, H * W, L.dtype_code(dtype), None), "t")
+    assert torch.equal(back.cpu(), x)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("shape", [(3, 64, 16, 16), (2, 6, 9, 7), (1, 8, 112, 112)])
+def test_maxpool(dtype, shape):
+    L = _lib()
+    F_, C, H, W = shape
+    x = (torch.rand(shape) < 0.3).to(dtype)
+    ref = F.max_pool2d(x.float(), 3, 2, 1)
+    xd = x.permute(0, 2, 3, 1).contiguous().to(DEV)
+    Ho, Wo = ref.shape[2], ref.shape[3]
+    y = torch.empty(F_, Ho, Wo, C, dtype=dtype, device=DEV)
+    L.check(L.lib.snnb_maxpool3x3s2(xd.data_ptr(), y.data_ptr(), F_, H, W, C, L.dtype_code(dtype), None), "maxpool")
+    assert torch.equal(y.cpu().float().permute(0, 3, 1, 2), ref)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_avgpool_linear_mean(dtype):
+    L = _lib()
+    T, N, C, H, W, K = 4, 6, 512, 7, 7, 1000
+    torch.manual_seed(0)
+    x = (torch.rand(T, N, C, H, W) < 0.2).to(dtype)
+    w = (torch.randn(K, C) * 0.05).to(dtype)
+    b = (torch.randn(K) * 0.05).to(dtype)
+    ref = torch.stack([F.linear(F.adaptive_avg_pool2d(x[t].float(), 1).flatten(1), w.float(), b.float())
+                       for t in range(T)]).mean(0)
+    xd = x.permute(0, 1, 3, 4, 2).contiguous().to(DEV)
+    out = torch.empty(N, K, device=DEV)
+    wd, bd = w.to(DEV), b.to(DEV)  # keep the device copies alive across the call
+    L.check(L.lib.snnb_avgpool_linear_mean(xd.data_ptr(), wd.data_ptr(), bd.data_ptr(), out.data_ptr(),
+                                           T, N, C, H * W, K, L.dtype_code(dtype), None), "head")
+    torch.testing.assert_close(out.cpu(), ref, rtol=1e-4, atol=1e-5)

@@ -1,0 +1,186 @@
+// Stateless channels-last helpers around the fused ops: layout transposes, the 3x3/s2
+// max pool after a ResNet stem, and the avgpool + linear head averaged over T.
+#include "common.cuh"
+
+namespace snnb {
+namespace {
+
+// [frames][R][Ccols] -> [frames][Ccols][R] for 2- or 4-byte elements (32x32 smem tiles).
+template <typename E>
+__global__ void transpose_kernel(const E *__restrict__ src, E *__restrict__ dst, int R, int Cc) {
+  __shared__ E tile[32][33];
+  const int64_t f = blockIdx.z;
+  const E *s = src + f * (int64_t)R * Cc;
+  E *d = dst + f * (int64_t)R * Cc;
+  const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+  for (int i = threadIdx.y; i < 32; i += 8) {
+    const int r = r0 + i, c = c0 + threadIdx.x;
+    if (r < R && c < Cc) tile[i][threadIdx.x] = s[(int64_t)r * Cc + c];
+  }
+  __syncthreads();
+  for (int i = threadIdx.y; i < 32; i += 8) {
+    const int c = c0 + i, r = r0 + threadIdx.x;
+    if (r < R && c < Cc) d[(int64_t)c * R + r] = tile[threadIdx.x][i];
+  }
+}
+
+int transpose(const void *src, void *dst, int64_t frames, int R, int Cc, int dtype, cudaStream_t st, const char *what) {
+  if (!src || !dst) return fail(SNNB_ERR_INVALID, "%s: null pointer", what);
+  if (frames < 0 || R < 1 || Cc < 1) return fail(SNNB_ERR_INVALID, "%s: bad sizes", what);
+  if (!is_act_dtype(dtype) && dtype != SNNB_U8) return fail(SNNB_ERR_INVALID, "%s: unsupported dtype", what);
+  if (frames == 0) return SNNB_OK;
+  const dim3 block(32, 8);
+  const unsigned gx = (Cc + 31) / 32, gy = (R + 31) / 32;
+  for (int64_t f0 = 0; f0 < frames; f0 += 65535) {
+    const unsigned nf = (unsigned)((frames - f0) < 65535 ? (frames - f0) : 65535);
+    const dim3 grid(gx, gy, nf);
+    const int64_t off = f0 * (int64_t)R * Cc;
+    const int es = dtype_size(dtype);
+    if (es == 4) transpose_kernel<uint32_t><<<grid, block, 0, st>>>(static_cast<const uint32_t *>(src) + off, static_cast<uint32_t *>(dst) + off, R, Cc);
+    else if (es == 2) transpose_kernel<uint16_t><<<grid, block, 0, st>>>(static_cast<const uint16_t *>(src) + off, static_cast<uint16_t *>(dst) + off, R, Cc);
+    else transpose_kernel<uint8_t><<<grid, block, 0, st>>>(static_cast<const uint8_t *>(src) + off, static_cast<uint8_t *>(dst) + off, R, Cc);
+  }
+  SNNB_CHECK_LAUNCH(what);
+  return SNNB_OK;
+}
+
+template <typename XT, int VEC>
+__global__ void __launch_bounds__(256)
+maxpool3x3s2_kernel(const XT *__restrict__ x, XT *__restrict__ y, int64_t frames, int H, int W, int C, int Ho, int Wo) {
+  const int CV = C / VEC;
+  const int64_t total = frames * Ho * Wo * CV;
+  int64_t idx = (int64_t)blockIdx.x * 256 + threadIdx.x;
+  if (idx >= total) return;
+  const int cv = (int)(idx % CV); idx /= CV;
+  const int wo = (int)(idx % Wo); idx /= Wo;
+  const int ho = (int)(idx % Ho);
+  const int64_t f = idx / Ho;
+  float m[VEC];
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) m[i] = -INFINITY;
+  const XT *xf = x + f * (int64_t)H * W * C + cv * VEC;
+#pragma unroll
+  for (int r = 0; r < 3; ++r) {
+    const int hi = ho * 2 - 1 + r;
+    if (hi < 0 || hi >= H) continue;
+#pragma unroll
+    for (int c = 0; c < 3; ++c) {
+      const int wi = wo * 2 - 1 + c;
+      if (wi < 0 || wi >= W) continue;
+      float v[VEC];
+      load_pack<XT, VEC>(xf + ((int64_t)hi * W + wi) * C, v);
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) m[i] = fmaxf(m[i], v[i]);
+    }
+  }
+  store_pack<XT, VEC, false>(y + ((f * Ho + ho) * (int64_t)Wo + wo) * C + cv * VEC, m);
+}
+
+template <typename XT>
+int maxpool(const void *x, void *y, int64_t frames, int H, int W, int C, cudaStream_t st) {
+  const int Ho = (H + 2 - 3) / 2 + 1, Wo = (W + 2 - 3) / 2 + 1;
+  constexpr int V = 16 / sizeof(XT);
+  const bool vec = (C % V == 0) && aligned16(x) && aligned16(y);
+  const int64_t total = frames * Ho * Wo * (vec ? C / V : C);
+  const int64_t blocks = (total + 255) / 256;
+  if (blocks > 0x7fffffffLL) return fail(SNNB_ERR_INVALID, "maxpool3x3s2: problem too large");
+  if (blocks == 0) return SNNB_OK;
+  if (vec) maxpool3x3s2_kernel<XT, V><<<(unsigned)blocks, 256, 0, st>>>(static_cast<const XT *>(x), static_cast<XT *>(y), frames, H, W, C, Ho, Wo);
+  else maxpool3x3s2_kernel<XT, 1><<<(unsigned)blocks, 256, 0, st>>>(static_cast<const XT *>(x), static_cast<XT *>(y), frames, H, W, C, Ho, Wo);
+  SNNB_CHECK_LAUNCH("maxpool3x3s2");
+  return SNNB_OK;
+}
+
+// One CTA per group of SB samples: channel sums over (t, pixel) into shared memory, then a
+// warp-per-class mat-vec for the SB samples with the fc row read once.
+constexpr int SB = 4;
+template <typename XT>
+__global__ void __launch_bounds__(256)
+avgpool_linear_mean_kernel(const XT *__restrict__ x, const XT *__restrict__ w, const XT *__restrict__ b,
+                           float *__restrict__ out, int T, int N, int C, int HW, int K) {
+  extern __shared__ float sums[];  // [SB][C]
+  const int n0 = blockIdx.x * SB;
+  const int ns = min(SB, N - n0);
+  const int tid = threadIdx.x;
+  const int64_t frame = (int64_t)N * HW * C;
+  for (int i = tid; i < ns * C; i += 256) {
+    const int s = i / C, c = i % C;
+    float a = 0.f;
+    for (int t = 0; t < T; ++t) {
+      const XT *px = x + (int64_t)t * frame + (int64_t)(n0 + s) * HW * C + c;
+      for (int p = 0; p < HW; ++p) a += DT<XT>::to_f(px[(int64_t)p * C]);
+    }
+    sums[s * C + c] = a;
+  }
+  __syncthreads();
+  const int warp = tid / 32, lane = tid % 32;
+  const float scale = 1.0f / ((float)T * (float)HW);
+  for (int k = warp; k < K; k += 8) {
+    float acc[SB];
+#pragma unroll
+    for (int s = 0; s < SB; ++s) acc[s] = 0.f;
+    const XT *wk = w + (int64_t)k * C;
+    for (int c = lane; c < C; c += 32) {
+      const float wv = DT<XT>::to_f(wk[c]);
+#pragma unroll
+      for (int s = 0; s < SB; ++s)
+        if (s < ns) acc[s] = fmaf(wv, sums[s * C + c], acc[s]);
+    }
+    const float bk = b != nullptr ? DT<XT>::to_f(b[k]) : 0.f;
+#pragma unroll
+    for (int s = 0; s < SB; ++s) {
+      float a = acc[s];
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) a += __shfl_xor_sync(0xffffffffu, a, off);
+      if (lane == 0 && s < ns) out[(int64_t)(n0 + s) * K + k] = a * scale + bk;
+    }
+  }
+}
+
+template <typename XT>
+int head(const void *x, const void *w, const void *b, float *out, int T, int N, int C, int HW, int K, cudaStream_t st) {
+  const size_t smem = (size_t)SB * C * sizeof(float);
+  if (smem > 48 * 1024) return fail(SNNB_ERR_UNSUPPORTED, "avgpool_linear_mean: C=%d too large", C);
+  avgpool_linear_mean_kernel<XT><<<(N + SB - 1) / SB, 256, smem, st>>>(
+      static_cast<const XT *>(x), static_cast<const XT *>(w), static_cast<const XT *>(b), out, T, N, C, HW, K);
+  SNNB_CHECK_LAUNCH("avgpool_linear_mean");
+  return SNNB_OK;
+}
+
+}  // namespace
+}  // namespace snnb
+
+extern "C" int snnb_nchw_to_nhwc(const void *src, void *dst, int64_t frames, int C, int HW, int dtype, void *stream) {
+  return snnb::transpose(src, dst, frames, C, HW, dtype, static_cast<cudaStream_t>(stream), "nchw_to_nhwc");
+}
+
+extern "C" int snnb_nhwc_to_nchw(const void *src, void *dst, int64_t frames, int C, int HW, int dtype, void *stream) {
+  return snnb::transpose(src, dst, frames, HW, C, dtype, static_cast<cudaStream_t>(stream), "nhwc_to_nchw");
+}
+
+extern "C" int snnb_maxpool3x3s2(const void *x, void *y, int64_t frames, int H, int W, int C, int dtype, void *stream) {
+  using namespace snnb;
+  SNNB_CHECK_ARG(x && y, "maxpool3x3s2: null pointer");
+  SNNB_CHECK_ARG(frames >= 0 && H >= 1 && W >= 1 && C >= 1, "maxpool3x3s2: bad sizes");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (dtype) {
+    case SNNB_F32: return maxpool<float>(x, y, frames, H, W, C, st);
+    case SNNB_BF16: return maxpool<__nv_bfloat16>(x, y, frames, H, W, C, st);
+    case SNNB_F16: return maxpool<__half>(x, y, frames, H, W, C, st);
+    default: return fail(SNNB_ERR_INVALID, "maxpool3x3s2: unsupported dtype %d", dtype);
+  }
+}
+
+extern "C" int snnb_avgpool_linear_mean(const void *x_seq, const void *fc_w, const void *fc_b, float *out,
+                                        int T, int N, int C, int HW, int K, int dtype, void *stream) {
+  using namespace snnb;
+  SNNB_CHECK_ARG(x_seq && fc_w && out, "avgpool_linear_mean: null pointer");
+  SNNB_CHECK_ARG(T >= 1 && N >= 1 && C >= 1 && HW >= 1 && K >= 1, "avgpool_linear_mean: sizes must be positive");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (dtype) {
+    case SNNB_F32: return head<float>(x_seq, fc_w, fc_b, out, T, N, C, HW, K, st);
+    case SNNB_BF16: return head<__nv_bfloat16>(x_seq, fc_w, fc_b, out, T, N, C, HW, K, st);
+    case SNNB_F16: return head<__half>(x_seq, fc_w, fc_b, out, T, N, C, HW, K, st);
+    default: return fail(SNNB_ERR_INVALID, "avgpool_linear_mean: unsupported dtype %d", dtype);
+  }
+}

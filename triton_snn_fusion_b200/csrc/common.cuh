@@ -63,25 +63,21 @@ template <typename T, int N>
 __device__ __forceinline__ void load_pack_stream(const T *p, float (&out)[N]) {
   // streaming (evict-first) load: the data is read exactly once
   constexpr int BYTES = sizeof(T) * N;
-  static_assert(BYTES % 16 == 0 || BYTES == 8 || BYTES == 4, "pack width");
+  Pack<T, N> pk;
   if constexpr (BYTES % 16 == 0) {
-    Pack<T, N> pk;
     int4 *dst = reinterpret_cast<int4 *>(&pk);
 #pragma unroll
     for (int i = 0; i < BYTES / 16; ++i) dst[i] = __ldcs(reinterpret_cast<const int4 *>(p) + i);
-#pragma unroll
-    for (int i = 0; i < N; ++i) out[i] = DT<T>::to_f(pk.v[i]);
   } else if constexpr (BYTES == 8) {
-    Pack<T, N> pk;
     *reinterpret_cast<int2 *>(&pk) = __ldcs(reinterpret_cast<const int2 *>(p));
-#pragma unroll
-    for (int i = 0; i < N; ++i) out[i] = DT<T>::to_f(pk.v[i]);
-  } else {
-    Pack<T, N> pk;
+  } else if constexpr (BYTES == 4) {
     *reinterpret_cast<int *>(&pk) = __ldcs(reinterpret_cast<const int *>(p));
+  } else {
 #pragma unroll
-    for (int i = 0; i < N; ++i) out[i] = DT<T>::to_f(pk.v[i]);
+    for (int i = 0; i < N; ++i) pk.v[i] = __ldcs(p + i);
   }
+#pragma unroll
+  for (int i = 0; i < N; ++i) out[i] = DT<T>::to_f(pk.v[i]);
 }
 
 template <typename T, int N>

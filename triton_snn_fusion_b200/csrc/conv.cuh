@@ -1,0 +1,29 @@
+// Argument block shared by the dense conv / linear + LIF implementations.
+#pragma once
+#include "common.cuh"
+
+namespace snnb {
+
+struct ConvArgs {
+  const void *x;        // [T][B][H][W][Cin], frames x_t_stride elements apart (0: one frame for all t)
+  int64_t x_t_stride;
+  const void *w;        // [Cout][KH][KW][Cin]
+  const void *b;        // [Cout] or null
+  const void *res;      // null or [T][B][Ho][Wo][Cout]
+  const void *v_init;   // null or [B][Ho][Wo][Cout]
+  void *spikes;         // [T][B][Ho][Wo][Cout]
+  void *v_out;          // [B][Ho][Wo][Cout]
+  int T, B, Cin, H, W, Cout, KH, KW, stride, pad, Ho, Wo;
+  int lif;              // 0: write conv + bias (+ residual) instead of spikes, no state
+  int dtype, spike_dtype, v_dtype;
+  LifParams p;
+};
+
+// CUDA-core implicit GEMM (any shape, fp32 accumulate).
+int conv_lif_simt(const ConvArgs &a, cudaStream_t stream);
+
+// tcgen05 / TMEM implicit GEMM fed by TMA. `why` receives the reason when unsupported.
+bool conv_lif_tc_supported(const ConvArgs &a, const char **why);
+int conv_lif_tc(const ConvArgs &a, cudaStream_t stream);
+
+}  // namespace snnb

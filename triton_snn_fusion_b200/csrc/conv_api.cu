@@ -1,0 +1,74 @@
+// extern "C" entry points of the dense conv / linear + LIF ops: argument validation and
+// the choice between the tensor-core and the CUDA-core implementation.
+#include "conv.cuh"
+
+namespace snnb {
+namespace {
+
+int run(const ConvArgs &a, int path, cudaStream_t stream, const char *what) {
+  const char *why = "";
+  const bool tc_ok = conv_lif_tc_supported(a, &why);
+  if (path == SNNB_PATH_TCGEN05) {
+    if (!tc_ok) return fail(SNNB_ERR_UNSUPPORTED, "%s: tcgen05 path not available for this call: %s", what, why);
+    return conv_lif_tc(a, stream);
+  }
+  if (path == SNNB_PATH_AUTO && tc_ok) return conv_lif_tc(a, stream);
+  return conv_lif_simt(a, stream);
+}
+
+}  // namespace
+}  // namespace snnb
+
+extern "C" int snnb_conv_lif(const void *x_seq, int64_t x_t_stride, const void *w, const void *b,
+                             const void *residual, const void *v_init, void *spikes, void *v_out,
+                             int T, int B, int Cin, int H, int W, int Cout, int KH, int KW,
+                             int stride, int pad, int lif, int dtype, int spike_dtype, int v_dtype,
+                             float v_th, float v_reset, float tau, int path, void *stream) {
+  using namespace snnb;
+  SNNB_CHECK_ARG(x_seq && w && spikes, "conv_lif: null pointer");
+  SNNB_CHECK_ARG(!lif || v_out, "conv_lif: v_out is required when lif != 0");
+  SNNB_CHECK_ARG(T >= 1 && B >= 1 && Cin >= 1 && Cout >= 1 && H >= 1 && W >= 1, "conv_lif: sizes must be positive");
+  SNNB_CHECK_ARG(KH >= 1 && KW >= 1 && stride >= 1 && pad >= 0, "conv_lif: bad kernel/stride/padding");
+  SNNB_CHECK_ARG(is_act_dtype(dtype), "conv_lif: unsupported dtype %d", dtype);
+  SNNB_CHECK_ARG(!lif || spike_dtype == dtype || spike_dtype == SNNB_U8, "conv_lif: spike dtype must be the x dtype or u8");
+  SNNB_CHECK_ARG(!lif || v_dtype == dtype || v_dtype == SNNB_F32, "conv_lif: v dtype must be the x dtype or f32");
+  SNNB_CHECK_ARG(path >= SNNB_PATH_AUTO && path <= SNNB_PATH_TCGEN05, "conv_lif: bad path %d", path);
+  SNNB_CHECK_ARG(x_t_stride >= 0, "conv_lif: negative frame stride");
+  SNNB_CHECK_ARG(!lif || tau != 0.0f, "conv_lif: unsupported_tau: tau must be nonzero");
+  const int Ho = (H + 2 * pad - KH) / stride + 1;
+  const int Wo = (W + 2 * pad - KW) / stride + 1;
+  SNNB_CHECK_ARG(H + 2 * pad >= KH && W + 2 * pad >= KW && Ho >= 1 && Wo >= 1, "conv_lif: empty output");
+  SNNB_CHECK_ARG((int64_t)B * Ho * Wo < (1LL << 31) && (int64_t)KH * KW * Cin < (1LL << 31), "conv_lif: problem too large");
+  ConvArgs a;
+  a.x = x_seq; a.x_t_stride = x_t_stride; a.w = w; a.b = b; a.res = residual;
+  a.v_init = lif ? v_init : nullptr; a.spikes = spikes; a.v_out = v_out;
+  a.T = T; a.B = B; a.Cin = Cin; a.H = H; a.W = W; a.Cout = Cout; a.KH = KH; a.KW = KW;
+  a.stride = stride; a.pad = pad; a.Ho = Ho; a.Wo = Wo; a.lif = lif ? 1 : 0;
+  a.dtype = dtype; a.spike_dtype = lif ? spike_dtype : dtype; a.v_dtype = lif ? v_dtype : dtype;
+  a.p = make_lif_params(v_th, v_reset, lif ? tau : 2.0f);
+  return run(a, path, static_cast<cudaStream_t>(stream), "conv_lif");
+}
+
+extern "C" int snnb_linear_lif(const void *x_seq, int64_t x_t_stride, const void *w, const void *b,
+                               const void *v_init, void *spikes, void *v_out,
+                               int T, int M, int K, int N, int dtype, int spike_dtype, int v_dtype,
+                               float v_th, float v_reset, float tau, int path, void *stream) {
+  using namespace snnb;
+  SNNB_CHECK_ARG(x_seq && w && spikes && v_out, "linear_lif: null pointer");
+  SNNB_CHECK_ARG(T >= 1 && M >= 1 && K >= 1 && N >= 1, "linear_lif: sizes must be positive");
+  SNNB_CHECK_ARG(is_act_dtype(dtype), "linear_lif: unsupported dtype %d", dtype);
+  SNNB_CHECK_ARG(spike_dtype == dtype || spike_dtype == SNNB_U8, "linear_lif: spike dtype must be the x dtype or u8");
+  SNNB_CHECK_ARG(v_dtype == dtype || v_dtype == SNNB_F32, "linear_lif: v dtype must be the x dtype or f32");
+  SNNB_CHECK_ARG(path >= SNNB_PATH_AUTO && path <= SNNB_PATH_TCGEN05, "linear_lif: bad path %d", path);
+  SNNB_CHECK_ARG(x_t_stride >= 0, "linear_lif: negative frame stride");
+  SNNB_CHECK_ARG(tau != 0.0f, "linear_lif: unsupported_tau: tau must be nonzero");
+  // A linear layer over [M][K] rows is a 1x1 convolution over one [1][M] frame with K channels.
+  ConvArgs a;
+  a.x = x_seq; a.x_t_stride = x_t_stride; a.w = w; a.b = b; a.res = nullptr;
+  a.v_init = v_init; a.spikes = spikes; a.v_out = v_out;
+  a.T = T; a.B = 1; a.Cin = K; a.H = 1; a.W = M; a.Cout = N; a.KH = 1; a.KW = 1;
+  a.stride = 1; a.pad = 0; a.Ho = 1; a.Wo = M; a.lif = 1;
+  a.dtype = dtype; a.spike_dtype = spike_dtype; a.v_dtype = v_dtype;
+  a.p = make_lif_params(v_th, v_reset, tau);
+  return run(a, path, static_cast<cudaStream_t>(stream), "linear_lif");
+}

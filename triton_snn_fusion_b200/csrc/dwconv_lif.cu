@@ -1,0 +1,205 @@
+// 3x3 depthwise conv (+ bias, + residual) + LIF over T, channels-last.
+//
+// HBM-bound: per output element it needs 1 (stride 1) or 4 (stride 2) input elements,
+// one spike per step and the membrane once. A thread owns VEC consecutive channels of
+// a strip of S consecutive output pixels of one output row; lanes run over channels
+// first, so every load/store instruction of a warp covers contiguous memory. Along the
+// strip the 3x3 window slides in registers: only the new input column(s) are fetched
+// for each output, the rest is reused, which keeps the load-unit traffic at ~4.5
+// (stride 1) accesses per output instead of 9. The T steps are the outer loop; the S
+// membrane vectors of the strip stay in registers for the whole call.
+#include "common.cuh"
+
+namespace snnb {
+namespace {
+
+constexpr int NT = 128;
+constexpr int S = 4;  // output pixels per thread
+
+template <typename XT, typename ST, typename VT, int VEC, int STRIDE>
+__global__ void __launch_bounds__(NT, 3)
+dwconv3x3_lif_kernel(const XT *__restrict__ x, int64_t x_t_stride, const XT *__restrict__ w,
+                     const XT *__restrict__ bias, const XT *__restrict__ res,
+                     const VT *__restrict__ v_init, ST *__restrict__ spikes, VT *__restrict__ v_out,
+                     int T, int B, int C, int H, int W, int Ho, int Wo, LifParams p) {
+  const int CV = C / VEC;
+  const int nstrips = (Wo + S - 1) / S;
+  const int64_t total = (int64_t)B * Ho * nstrips * CV;
+  int64_t idx = (int64_t)blockIdx.x * NT + threadIdx.x;
+  if (idx >= total) return;
+  const int cv = (int)(idx % CV);
+  idx /= CV;
+  const int strip = (int)(idx % nstrips);
+  idx /= nstrips;
+  const int ho = (int)(idx % Ho);
+  const int b = (int)(idx / Ho);
+  const int c0 = cv * VEC;
+  const int wo0 = strip * S;
+
+  float wr[9][VEC];
+#pragma unroll
+  for (int i = 0; i < VEC; ++i)
+#pragma unroll
+    for (int k = 0; k < 9; ++k) wr[k][i] = DT<XT>::to_f(w[(int64_t)(c0 + i) * 9 + k]);
+  float bs[VEC];
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) bs[i] = bias != nullptr ? DT<XT>::to_f(bias[c0 + i]) : 0.f;
+
+  const int64_t orow = ((int64_t)b * Ho + ho) * Wo;  // first output pixel of this row
+  const int64_t frame_out = (int64_t)B * Ho * Wo * C;
+
+  float v[S][VEC];
+#pragma unroll
+  for (int s = 0; s < S; ++s) {
+    if (v_init != nullptr && wo0 + s < Wo) {
+      load_pack<VT, VEC>(v_init + (orow + wo0 + s) * C + c0, v[s]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) v[s][i] = 0.f;
+    }
+  }
+
+  const int hi0 = ho * STRIDE - 1;
+  for (int t = 0; t < T; ++t) {
+    const XT *xt = x + (int64_t)t * x_t_stride + (int64_t)b * H * W * C + c0;
+    auto load_col = [&](int wi, float (&col)[3][VEC]) {
+#pragma unroll
+      for (int r = 0; r < 3; ++r) {
+        const int hi = hi0 + r;
+        if (hi >= 0 && hi < H && wi >= 0 && wi < W) {
+          load_pack<XT, VEC>(xt + ((int64_t)hi * W + wi) * C, col[r]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < VEC; ++i) col[r][i] = 0.f;
+        }
+      }
+    };
+    float c0v[3][VEC], c1v[3][VEC], c2v[3][VEC];
+    if constexpr (STRIDE == 1) {
+      load_col(wo0 - 1, c0v);
+      load_col(wo0, c1v);
+    } else {
+      load_col(2 * wo0 - 1, c0v);
+    }
+#pragma unroll
+    for (int s = 0; s < S; ++s) {
+      const int wo = wo0 + s;
+      if (wo >= Wo) break;
+      if constexpr (STRIDE == 1) {
+        load_col(wo + 1, c2v);
+      } else {
+        load_col(2 * wo, c1v);
+        load_col(2 * wo + 1, c2v);
+      }
+      float y[VEC];
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) {
+        float a = 0.f;
+#pragma unroll
+        for (int r = 0; r < 3; ++r) {
+          a = fmaf(c0v[r][i], wr[r * 3 + 0][i], a);
+          a = fmaf(c1v[r][i], wr[r * 3 + 1][i], a);
+          a = fmaf(c2v[r][i], wr[r * 3 + 2][i], a);
+        }
+        y[i] = a + bs[i];
+      }
+      const int64_t o = (int64_t)t * frame_out + (orow + wo) * C + c0;
+      if (res != nullptr) {
+        float rr[VEC];
+        load_pack<XT, VEC>(res + o, rr);
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) y[i] += rr[i];
+      }
+      float sp[VEC];
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) sp[i] = lif_step(y[i], v[s][i], p);
+      store_pack<ST, VEC>(spikes + o, sp);
+      // slide the window
+#pragma unroll
+      for (int r = 0; r < 3; ++r)
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) {
+          if constexpr (STRIDE == 1) {
+            c0v[r][i] = c1v[r][i];
+            c1v[r][i] = c2v[r][i];
+          } else {
+            c0v[r][i] = c2v[r][i];
+          }
+        }
+    }
+  }
+#pragma unroll
+  for (int s = 0; s < S; ++s)
+    if (wo0 + s < Wo) store_pack<VT, VEC>(v_out + (orow + wo0 + s) * C + c0, v[s]);
+}
+
+template <typename XT, typename ST, typename VT>
+int launch(const void *x, int64_t xts, const void *w, const void *b, const void *res, const void *v_init,
+           void *spikes, void *v_out, int T, int B, int C, int H, int W, int stride, const LifParams &p,
+           cudaStream_t stream) {
+  const int Ho = (H + 2 - 3) / stride + 1;
+  const int Wo = (W + 2 - 3) / stride + 1;
+  const int nstrips = (Wo + S - 1) / S;
+  const bool vec = (C % 4 == 0) && aligned16(x) && aligned16(spikes) && aligned16(v_out) &&
+                   (v_init == nullptr || aligned16(v_init)) && (res == nullptr || aligned16(res)) &&
+                   (xts % 4 == 0);
+  const int VEC = vec ? 4 : 1;
+  const int64_t total = (int64_t)B * Ho * nstrips * (C / VEC);
+  const int64_t blocks = (total + NT - 1) / NT;
+  if (blocks > 0x7fffffffLL) return fail(SNNB_ERR_INVALID, "dwconv3x3_lif: problem too large");
+#define SNNB_DW(VECN, STR)                                                                             \
+  dwconv3x3_lif_kernel<XT, ST, VT, VECN, STR><<<(unsigned)blocks, NT, 0, stream>>>(                    \
+      static_cast<const XT *>(x), xts, static_cast<const XT *>(w), static_cast<const XT *>(b),         \
+      static_cast<const XT *>(res), static_cast<const VT *>(v_init), static_cast<ST *>(spikes),        \
+      static_cast<VT *>(v_out), T, B, C, H, W, Ho, Wo, p)
+  if (vec) {
+    if (stride == 1) SNNB_DW(4, 1); else SNNB_DW(4, 2);
+  } else {
+    if (stride == 1) SNNB_DW(1, 1); else SNNB_DW(1, 2);
+  }
+#undef SNNB_DW
+  SNNB_CHECK_LAUNCH("dwconv3x3_lif");
+  return SNNB_OK;
+}
+
+template <typename XT>
+int dispatch(const void *x, int64_t xts, const void *w, const void *b, const void *res, const void *v_init,
+             void *spikes, void *v_out, int T, int B, int C, int H, int W, int stride, int spike_dtype,
+             int v_dtype, const LifParams &p, cudaStream_t stream) {
+  const bool s_u8 = spike_dtype == SNNB_U8;
+  const bool v_f32 = v_dtype == SNNB_F32;
+#define SNNB_ARGS x, xts, w, b, res, v_init, spikes, v_out, T, B, C, H, W, stride, p, stream
+  if (s_u8 && v_f32) return launch<XT, uint8_t, float>(SNNB_ARGS);
+  if (s_u8) return launch<XT, uint8_t, XT>(SNNB_ARGS);
+  if (v_f32) return launch<XT, XT, float>(SNNB_ARGS);
+  return launch<XT, XT, XT>(SNNB_ARGS);
+#undef SNNB_ARGS
+}
+
+}  // namespace
+}  // namespace snnb
+
+extern "C" int snnb_dwconv3x3_lif(const void *x_seq, int64_t x_t_stride, const void *w, const void *b,
+                                  const void *residual, const void *v_init, void *spikes, void *v_out,
+                                  int T, int B, int C, int H, int W, int stride,
+                                  int dtype, int spike_dtype, int v_dtype,
+                                  float v_th, float v_reset, float tau, void *stream) {
+  using namespace snnb;
+  SNNB_CHECK_ARG(x_seq && w && spikes && v_out, "dwconv3x3_lif: null pointer");
+  SNNB_CHECK_ARG(T >= 1 && B >= 1 && C >= 1 && H >= 1 && W >= 1, "dwconv3x3_lif: sizes must be positive");
+  SNNB_CHECK_ARG(stride == 1 || stride == 2, "dwconv3x3_lif: unsupported_stride: stride must be 1 or 2, got %d", stride);
+  SNNB_CHECK_ARG(is_act_dtype(dtype), "dwconv3x3_lif: unsupported dtype %d", dtype);
+  SNNB_CHECK_ARG(spike_dtype == dtype || spike_dtype == SNNB_U8, "dwconv3x3_lif: spike dtype must be the x dtype or u8");
+  SNNB_CHECK_ARG(v_dtype == dtype || v_dtype == SNNB_F32, "dwconv3x3_lif: v dtype must be the x dtype or f32");
+  SNNB_CHECK_ARG(x_t_stride >= 0, "dwconv3x3_lif: negative frame stride");
+  SNNB_CHECK_ARG(tau != 0.0f, "dwconv3x3_lif: unsupported_tau: tau must be nonzero");
+  const LifParams p = make_lif_params(v_th, v_reset, tau);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+#define SNNB_ARGS x_seq, x_t_stride, w, b, residual, v_init, spikes, v_out, T, B, C, H, W, stride, spike_dtype, v_dtype, p, s
+  switch (dtype) {
+    case SNNB_F32: return dispatch<float>(SNNB_ARGS);
+    case SNNB_BF16: return dispatch<__nv_bfloat16>(SNNB_ARGS);
+    default: return dispatch<__half>(SNNB_ARGS);
+  }
+#undef SNNB_ARGS
+}

@@ -30,14 +30,17 @@ lif_scan_kernel(const XT *__restrict__ x, const VT *__restrict__ v_init, ST *__r
   }
 
   if constexpr (TS > 0) {
-    float xr[TS][VEC];
+    // All T loads are issued before the first use; they stay packed (16 bytes per step)
+    // until their step is evaluated so that 16-bit inputs do not double the live registers.
+    Pack<XT, VEC> raw[TS];
 #pragma unroll
-    for (int t = 0; t < TS; ++t) load_pack_stream<XT, VEC>(x + (int64_t)t * n + i0, xr[t]);
+    for (int t = 0; t < TS; ++t)
+      *reinterpret_cast<int4 *>(&raw[t]) = __ldcs(reinterpret_cast<const int4 *>(x + (int64_t)t * n + i0));
 #pragma unroll
     for (int t = 0; t < TS; ++t) {
       float s[VEC];
 #pragma unroll
-      for (int i = 0; i < VEC; ++i) s[i] = lif_step(xr[t][i], v[i], p);
+      for (int i = 0; i < VEC; ++i) s[i] = lif_step(DT<XT>::to_f(raw[t].v[i]), v[i], p);
       store_pack<ST, VEC>(spikes + (int64_t)t * n + i0, s);
     }
   } else {

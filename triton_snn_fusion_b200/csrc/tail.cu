@@ -1,0 +1,207 @@
+// LIF -> global average pool -> linear, summed over T, in ONE kernel.
+//
+// A thread-block cluster of 8 CTAs serves a group of S samples. Phase 1 (HBM-bound):
+// each CTA scans its slice of the channels of every sample of the group over the T
+// steps with the membrane in registers, writes the last membrane, and counts spikes
+// per channel in shared memory. The counts are integers, so the shared-memory atomics
+// that collect them are order-independent and the result is deterministic (the
+// reference accumulates floats with global atomics). Phase 2: the CTAs exchange their
+// count slices through distributed shared memory, then each CTA computes its slice of
+// the classes for all S samples, one warp per class with a shuffle reduction:
+//   out[n][k] = (sum_c w[k][c] * count[n][c]) / HW + T * b[k]
+// which equals sum_t (W . mean_hw(spike_t) + b).
+#include <cooperative_groups.h>
+
+#include "common.cuh"
+
+namespace cg = cooperative_groups;
+
+namespace snnb {
+namespace {
+
+constexpr int CL = 8;     // CTAs per cluster
+constexpr int NT = 256;
+constexpr int SMAX = 8;   // samples per cluster (upper bound)
+
+template <typename XT, typename VT, bool NHWC, int VEC>
+__global__ void __launch_bounds__(NT)
+lif_avgpool_linear_kernel(const XT *__restrict__ x, const VT *__restrict__ v_init,
+                          const XT *__restrict__ fc_w, const XT *__restrict__ fc_b,
+                          XT *__restrict__ out, VT *__restrict__ v_out,
+                          int T, int N, int C, int HW, int K, int S, LifParams p) {
+  extern __shared__ int cnt[];  // [S][C] spike counts summed over t and pixels
+  cg::cluster_group cluster = cg::this_cluster();
+  const int r = (int)cluster.block_rank();
+  const int g = blockIdx.x / CL;
+  const int n0 = g * S;
+  const int ns = min(S, N - n0);
+  const int tid = threadIdx.x;
+
+  for (int i = tid; i < S * C; i += NT) cnt[i] = 0;
+  __syncthreads();
+
+  const int Cs = (C + CL - 1) / CL;
+  int cs = r * Cs, ce = min(C, cs + Cs);
+  if (VEC > 1) {  // keep slices vector-aligned
+    const int Cv = ((C / VEC + CL - 1) / CL) * VEC;
+    cs = min(C, r * Cv);
+    ce = min(C, cs + Cv);
+  }
+  const int64_t frame = (int64_t)N * C * HW;
+
+  for (int s = 0; s < ns; ++s) {
+    const int n = n0 + s;
+    if constexpr (NHWC) {
+      const int cvn = (ce - cs) / VEC;
+      const int items = HW * cvn;
+      for (int it = tid; it < items; it += NT) {
+        const int pix = it / cvn;
+        const int c = cs + (it % cvn) * VEC;
+        const int64_t e = ((int64_t)n * HW + pix) * C + c;
+        float v[VEC];
+        if (v_init != nullptr) load_pack_stream<VT, VEC>(v_init + e, v);
+        else {
+#pragma unroll
+          for (int i = 0; i < VEC; ++i) v[i] = 0.f;
+        }
+        int k[VEC];
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) k[i] = 0;
+        for (int t = 0; t < T; ++t) {
+          float xv[VEC];
+          load_pack_stream<XT, VEC>(x + (int64_t)t * frame + e, xv);
+#pragma unroll
+          for (int i = 0; i < VEC; ++i) k[i] += (int)lif_step(xv[i], v[i], p);
+        }
+        store_pack<VT, VEC>(v_out + e, v);
+#pragma unroll
+        for (int i = 0; i < VEC; ++i)
+          if (k[i]) atomicAdd(&cnt[s * C + c + i], k[i]);
+      }
+    } else {
+      const int items = (ce - cs) * HW;
+      const int64_t e0 = ((int64_t)n * C + cs) * HW;
+      for (int it = tid; it < items; it += NT) {
+        const int c = cs + it / HW;
+        const int64_t e = e0 + it;
+        float v = v_init != nullptr ? DT<VT>::to_f(v_init[e]) : 0.f;
+        int k = 0;
+        for (int t = 0; t < T; ++t) k += (int)lif_step(DT<XT>::to_f(x[(int64_t)t * frame + e]), v, p);
+        v_out[e] = DT<VT>::from_f(v);
+        if (k) atomicAdd(&cnt[s * C + c], k);
+      }
+    }
+  }
+
+  // ---- exchange the count slices through distributed shared memory
+  cluster.sync();
+  for (int q = 0; q < CL; ++q) {
+    if (q == r) continue;
+    int qs = q * Cs, qe = min(C, qs + Cs);
+    if (VEC > 1) {
+      const int Cv = ((C / VEC + CL - 1) / CL) * VEC;
+      qs = min(C, q * Cv);
+      qe = min(C, qs + Cv);
+    }
+    const int *peer = cluster.map_shared_rank(cnt, q);
+    const int len = qe - qs;
+    for (int i = tid; i < ns * len; i += NT) {
+      const int s = i / len, c = qs + i % len;
+      cnt[s * C + c] = peer[s * C + c];
+    }
+  }
+  cluster.sync();  // nobody leaves (or overwrites) before every peer has read its slice
+
+  // ---- linear: this CTA's classes for all samples of the group
+  const int Ks = (K + CL - 1) / CL;
+  const int ks = r * Ks, ke = min(K, ks + Ks);
+  const int warp = tid / 32, lane = tid % 32;
+  const float inv_hw = 1.0f / (float)HW;
+  for (int k = ks + warp; k < ke; k += NT / 32) {
+    float acc[SMAX];
+#pragma unroll
+    for (int s = 0; s < SMAX; ++s) acc[s] = 0.f;
+    const XT *wk = fc_w + (int64_t)k * C;
+    for (int c = lane; c < C; c += 32) {
+      const float wv = DT<XT>::to_f(wk[c]);
+#pragma unroll
+      for (int s = 0; s < SMAX; ++s)
+        if (s < ns) acc[s] = fmaf(wv, (float)cnt[s * C + c], acc[s]);
+    }
+    const float bk = fc_b != nullptr ? DT<XT>::to_f(fc_b[k]) * (float)T : 0.f;
+#pragma unroll
+    for (int s = 0; s < SMAX; ++s) {
+      float a = acc[s];
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) a += __shfl_xor_sync(0xffffffffu, a, off);
+      if (lane == 0 && s < ns) out[(int64_t)(n0 + s) * K + k] = DT<XT>::from_f(a * inv_hw + bk);
+    }
+  }
+}
+
+template <typename XT, typename VT, bool NHWC, int VEC>
+int launch(const void *x, const void *v_init, const void *w, const void *b, void *out, void *v_out,
+           int T, int N, int C, int HW, int K, const LifParams &p, cudaStream_t stream) {
+  int S = (N * CL + 147) / 148;
+  S = S < 1 ? 1 : (S > SMAX ? SMAX : S);
+  while (S > 1 && (size_t)S * C * sizeof(int) > 48 * 1024) --S;
+  const size_t smem = (size_t)S * C * sizeof(int);
+  if (smem > 48 * 1024) return fail(SNNB_ERR_UNSUPPORTED, "lif_avgpool_linear: C=%d too large", C);
+  const int groups = (N + S - 1) / S;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(groups * CL));
+  cfg.blockDim = dim3(NT);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = CL;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, lif_avgpool_linear_kernel<XT, VT, NHWC, VEC>,
+                                     static_cast<const XT *>(x), static_cast<const VT *>(v_init),
+                                     static_cast<const XT *>(w), static_cast<const XT *>(b),
+                                     static_cast<XT *>(out), static_cast<VT *>(v_out), T, N, C, HW, K, S, p);
+  if (e != cudaSuccess) return fail(SNNB_ERR_CUDA, "lif_avgpool_linear: launch failed: %s", cudaGetErrorString(e));
+  return SNNB_OK;
+}
+
+template <typename XT, typename VT>
+int pick(const void *x, const void *v_init, const void *w, const void *b, void *out, void *v_out,
+         int T, int N, int C, int HW, int K, int layout, const LifParams &p, cudaStream_t stream) {
+  if (layout == SNNB_NHWC) {
+    const bool vec = (C % 4 == 0) && aligned16(x) && aligned16(v_out) && (v_init == nullptr || aligned16(v_init));
+    if (vec) return launch<XT, VT, true, 4>(x, v_init, w, b, out, v_out, T, N, C, HW, K, p, stream);
+    return launch<XT, VT, true, 1>(x, v_init, w, b, out, v_out, T, N, C, HW, K, p, stream);
+  }
+  return launch<XT, VT, false, 1>(x, v_init, w, b, out, v_out, T, N, C, HW, K, p, stream);
+}
+
+}  // namespace
+}  // namespace snnb
+
+extern "C" int snnb_lif_avgpool_linear(const void *x_seq, const void *v_init, const void *fc_w,
+                                       const void *fc_b, void *out_sum, void *v_out,
+                                       int T, int N, int C, int HW, int K, int layout,
+                                       int dtype, int v_dtype,
+                                       float v_th, float v_reset, float tau, void *stream) {
+  using namespace snnb;
+  SNNB_CHECK_ARG(x_seq && fc_w && out_sum && v_out, "lif_avgpool_linear: null pointer");
+  SNNB_CHECK_ARG(T >= 1 && N >= 1 && C >= 1 && HW >= 1 && K >= 1, "lif_avgpool_linear: sizes must be positive");
+  SNNB_CHECK_ARG(layout == SNNB_NCHW || layout == SNNB_NHWC, "lif_avgpool_linear: bad layout %d", layout);
+  SNNB_CHECK_ARG(is_act_dtype(dtype), "lif_avgpool_linear: unsupported dtype %d", dtype);
+  SNNB_CHECK_ARG(v_dtype == dtype || v_dtype == SNNB_F32, "lif_avgpool_linear: v dtype must be the x dtype or f32");
+  SNNB_CHECK_ARG(tau != 0.0f, "lif_avgpool_linear: unsupported_tau: tau must be nonzero");
+  const LifParams p = make_lif_params(v_th, v_reset, tau);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const bool v_f32 = v_dtype == SNNB_F32;
+#define SNNB_ARGS x_seq, v_init, fc_w, fc_b, out_sum, v_out, T, N, C, HW, K, layout, p, s
+  switch (dtype) {
+    case SNNB_F32: return pick<float, float>(SNNB_ARGS);
+    case SNNB_BF16: return v_f32 ? pick<__nv_bfloat16, float>(SNNB_ARGS) : pick<__nv_bfloat16, __nv_bfloat16>(SNNB_ARGS);
+    default: return v_f32 ? pick<__half, float>(SNNB_ARGS) : pick<__half, __half>(SNNB_ARGS);
+  }
+#undef SNNB_ARGS
+}

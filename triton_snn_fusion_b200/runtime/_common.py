@@ -88,7 +88,7 @@ def stack_frames(xs: Sequence[torch.Tensor]) -> Tuple[torch.Tensor, int, bool]:
     out = empty_nhwc([T] + list(first.shape), first.dtype, first.device)
     for t, x in enumerate(xs):
         out[t].copy_(x)
-    return out, out.stride(0), True
+    return out[0], out.stride(0), True
 
 
 def lif_scalars(v_threshold, v_reset, tau):
