@@ -1,0 +1,265 @@
+"""Whole spiking networks on the fused kernels: layer specs, seeded parameters, and a
+static executor that issues one C-ABI call per fused layer.
+
+The reference reaches its kernels through FX rewrites of a torch.compile'd model
+(compiler/fx_lif_temporal_rewrite.py:2037-2889 in pengjh0111/triton-snn-fusion) and, for
+a rewritten graph, through a stream/graph executor (runtime/fx_standalone_executor.py:301-1260).
+This module is the equivalent of that executor for the three network families of the
+benchmark configurations: it owns a static buffer plan in channels-last layout, folds
+BatchNorm into the conv weights the way the rewrite does
+(compiler/fx_lif_rewrite.py:340-353), and replays the layer list — optionally as one CUDA
+graph. Every layer is a kernel of libsnnb200; the only torch op is the 1/T scaling of the
+logit sum that the LIF -> avgpool -> linear tail returns.
+
+A network is a list of dict specs (see ``spiking_resnet18`` etc.). Activations are named
+buffers holding all T steps: ``[T, B, H, W, C]`` memory.
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, List, Optional
+
+import torch
+
+from . import _lib
+
+LIF = dict(v_th=1.0, v_reset=0.0, tau=2.0)
+
+
+# ------------------------------------------------------------------ specs ----
+def _conv(name, src, dst, cin, cout, k, s, p, groups=1, residual=None, lif=True):
+    return dict(op="conv", name=name, src=src, dst=dst, cin=cin, cout=cout, k=k, s=s, p=p, groups=groups,
+                residual=residual, lif=lif)
+
+
+def spiking_cnn_small(num_classes: int = 10) -> List[dict]:
+    """conv3x3 3->64 s1, 64->128 s2, 128->256 s2 (each + BN + LIF), then LIF -> avgpool -> linear."""
+    return [
+        _conv("conv1", "input", "a1", 3, 64, 3, 1, 1),
+        _conv("conv2", "a1", "a2", 64, 128, 3, 2, 1),
+        _conv("conv3", "a2", "a3", 128, 256, 3, 2, 1),
+        dict(op="tail", name="tail", src="a3", cin=256, classes=num_classes),
+    ]
+
+
+def spiking_mobilenet_v1(num_classes: int = 1000) -> List[dict]:
+    """Width-1.0 MobileNetV1: stem conv3x3 s2 32, 13 depthwise/pointwise blocks, LIF -> avgpool -> linear."""
+    spec = [_conv("stem", "input", "s0", 3, 32, 3, 2, 1)]
+    plan = [(64, 1), (128, 2), (128, 1), (256, 2), (256, 1), (512, 2)] + [(512, 1)] * 5 + [(1024, 2), (1024, 1)]
+    cin, src = 32, "s0"
+    for i, (cout, s) in enumerate(plan):
+        spec.append(_conv(f"dw{i}", src, f"d{i}", cin, cin, 3, s, 1, groups=cin))
+        spec.append(_conv(f"pw{i}", f"d{i}", f"p{i}", cin, cout, 1, 1, 0))
+        cin, src = cout, f"p{i}"
+    spec.append(dict(op="tail", name="tail", src=src, cin=cin, classes=num_classes))
+    return spec
+
+
+def spiking_resnet18(num_classes: int = 1000) -> List[dict]:
+    """7x7 s2 stem + BN + LIF, maxpool, 8 basic blocks (conv-BN-LIF, conv-BN-add-LIF) with identity or
+    1x1-s2 conv+BN shortcuts, avgpool + linear averaged over T."""
+    spec = [_conv("stem", "input", "s0", 3, 64, 7, 2, 3), dict(op="maxpool", name="pool", src="s0", dst="x0", c=64)]
+    cin, src = 64, "x0"
+    for stage, cout in enumerate((64, 128, 256, 512)):
+        for blk in range(2):
+            s = 2 if (stage > 0 and blk == 0) else 1
+            tag = f"l{stage + 1}b{blk}"
+            spec.append(_conv(f"{tag}.conv1", src, f"{tag}.y", cin, cout, 3, s, 1))
+            if s != 1 or cin != cout:
+                spec.append(_conv(f"{tag}.down", src, f"{tag}.sc", cin, cout, 1, s, 0, lif=False))
+                res = f"{tag}.sc"
+            else:
+                res = src
+            spec.append(_conv(f"{tag}.conv2", f"{tag}.y", f"{tag}.out", cout, cout, 3, 1, 1, residual=res))
+            cin, src = cout, f"{tag}.out"
+    spec.append(dict(op="head", name="fc", src=src, cin=cin, classes=num_classes))
+    return spec
+
+
+NETS = {"cnn_small": spiking_cnn_small, "mobilenet_v1": spiking_mobilenet_v1, "resnet18": spiking_resnet18}
+
+
+# ------------------------------------------------------------- parameters ----
+def make_params(spec: List[dict], seed: int = 2026) -> Dict[str, Dict[str, torch.Tensor]]:
+    """Seeded fp32 CPU parameters: Kaiming-normal conv / linear weights, BN gamma U(0.5,1.5),
+    beta N(0,0.1), running mean N(0,0.1), running var U(0.5,1.5)."""
+    g = torch.Generator().manual_seed(seed)
+    params: Dict[str, Dict[str, torch.Tensor]] = {}
+    for L in spec:
+        if L["op"] == "conv":
+            fan_in = (L["cin"] // L["groups"]) * L["k"] * L["k"]
+            c = L["cout"]
+            params[L["name"]] = dict(
+                w=torch.randn(c, L["cin"] // L["groups"], L["k"], L["k"], generator=g) * math.sqrt(2.0 / fan_in),
+                gamma=torch.rand(c, generator=g) + 0.5,
+                beta=torch.randn(c, generator=g) * 0.1,
+                mean=torch.randn(c, generator=g) * 0.1,
+                var=torch.rand(c, generator=g) + 0.5,
+            )
+        elif L["op"] in ("tail", "head"):
+            params[L["name"]] = dict(
+                w=torch.randn(L["classes"], L["cin"], generator=g) * math.sqrt(2.0 / L["cin"]),
+                b=torch.randn(L["classes"], generator=g) * 0.01,
+            )
+    return params
+
+
+def fold_bn(w, gamma, beta, mean, var, eps: float = 1e-5):
+    """BatchNorm (inference) folded into a bias-free conv, as the reference's rewrite does
+    (compiler/fx_lif_rewrite.py:340-353): scale = gamma / sqrt(var + eps); W' = W * scale;
+    b' = (0 - mean) * scale + beta."""
+    scale = gamma / torch.sqrt(var + float(eps))
+    return w * scale.reshape(-1, 1, 1, 1), (torch.zeros_like(mean) - mean) * scale + beta
+
+
+def folded_params(spec, params, dtype) -> Dict[str, Dict[str, torch.Tensor]]:
+    """BN-folded parameters rounded to the compute dtype (CPU tensors, torch layouts)."""
+    out = {}
+    for L in spec:
+        p = params.get(L["name"])
+        if p is None:
+            continue
+        if L["op"] == "conv":
+            w, b = fold_bn(p["w"], p["gamma"], p["beta"], p["mean"], p["var"])
+            out[L["name"]] = dict(w=w.to(dtype), b=b.to(dtype))
+        else:
+            out[L["name"]] = dict(w=p["w"].to(dtype), b=p["b"].to(dtype))
+    return out
+
+
+# --------------------------------------------------------------- executor ----
+def _out_hw(h, w, k, s, p):
+    return (h + 2 * p - k) // s + 1, (w + 2 * p - k) // s + 1
+
+
+class CompiledNet:
+    """Static plan for one (spec, batch, T, dtype, input size) on one GPU.
+
+    ``forward(x)`` takes a device tensor [B, H, W, 3] (channels-last frame, compute dtype;
+    direct encoding: the same frame at every step) and returns fp32 logits [B, classes]
+    averaged over T. ``forward_nchw`` accepts the usual [B, 3, H, W] tensor.
+    """
+
+    def __init__(self, spec: List[dict], params, batch: int, T: int, in_hw=(224, 224),
+                 dtype=torch.bfloat16, device="cuda", conv_path: str = "auto", keep_membranes: bool = False):
+        self.spec, self.B, self.T, self.dtype = spec, int(batch), int(T), dtype
+        self.device = torch.device(device)
+        self.path = {"auto": _lib.PATH_AUTO, "simt": _lib.PATH_SIMT, "tcgen05": _lib.PATH_TCGEN05}[conv_path]
+        self.dt = _lib.dtype_code(dtype)
+        fp = folded_params(spec, params, dtype)
+        self.weights: Dict[str, Dict[str, torch.Tensor]] = {}
+        for L in spec:
+            if L["name"] not in fp:
+                continue
+            w, b = fp[L["name"]]["w"], fp[L["name"]]["b"]
+            if L["op"] == "conv" and L["groups"] == 1:
+                w = w.permute(0, 2, 3, 1).contiguous()  # [Cout][KH][KW][Cin]
+            self.weights[L["name"]] = dict(w=w.contiguous().to(self.device), b=b.contiguous().to(self.device))
+        # ---- buffer plan
+        H, W = in_hw
+        self.shapes = {"input": (H, W, 3)}
+        self.bufs: Dict[str, torch.Tensor] = {}
+        self.membranes: Dict[str, torch.Tensor] = {}
+        self.x_in = torch.empty((self.B, H, W, 3), dtype=dtype, device=self.device)
+        self.bufs["input"] = self.x_in
+        self.logits = None
+        for L in spec:
+            h, w_, c = self.shapes[L["src"]]
+            if L["op"] == "conv":
+                ho, wo = _out_hw(h, w_, L["k"], L["s"], L["p"])
+                self.shapes[L["dst"]] = (ho, wo, L["cout"])
+                self.bufs[L["dst"]] = torch.empty((self.T, self.B, ho, wo, L["cout"]), dtype=dtype, device=self.device)
+                if L["lif"]:
+                    self.membranes[L["name"]] = torch.empty((self.B, ho, wo, L["cout"]), dtype=dtype, device=self.device)
+            elif L["op"] == "maxpool":
+                ho, wo = _out_hw(h, w_, 3, 2, 1)
+                self.shapes[L["dst"]] = (ho, wo, c)
+                self.bufs[L["dst"]] = torch.empty((self.T, self.B, ho, wo, c), dtype=dtype, device=self.device)
+            elif L["op"] == "tail":
+                self.membranes[L["name"]] = torch.empty((self.B, h, w_, c), dtype=dtype, device=self.device)
+                self.tail_sum = torch.empty((self.B, L["classes"]), dtype=dtype, device=self.device)
+                self.logits = torch.empty((self.B, L["classes"]), dtype=torch.float32, device=self.device)
+            elif L["op"] == "head":
+                self.logits = torch.empty((self.B, L["classes"]), dtype=torch.float32, device=self.device)
+        self._calls = self._plan()
+        self.launches_per_forward = len(self._calls) + (1 if any(L["op"] == "tail" for L in spec) else 0)
+        self._graph: Optional[torch.cuda.CUDAGraph] = None
+
+    # one closure per kernel launch, all arguments resolved ahead of time
+    def _plan(self):
+        lib, calls = _lib.lib, []
+        T, B, dt = self.T, self.B, self.dt
+        for L in self.spec:
+            src = self.bufs[L["src"]]
+            h, w_, c = self.shapes[L["src"]]
+            x_stride = 0 if L["src"] == "input" else src.stride(0)
+            if L["op"] == "conv":
+                wt = self.weights[L["name"]]
+                dst = self.bufs[L["dst"]]
+                res = self.bufs[L["residual"]].data_ptr() if L.get("residual") else None
+                v = self.membranes[L["name"]].data_ptr() if L["lif"] else None
+                if L["groups"] == 1:
+                    args = (src.data_ptr(), x_stride, wt["w"].data_ptr(), wt["b"].data_ptr(), res, None, dst.data_ptr(), v,
+                            T, B, L["cin"], h, w_, L["cout"], L["k"], L["k"], L["s"], L["p"], 1 if L["lif"] else 0,
+                            dt, dt, dt, LIF["v_th"], LIF["v_reset"], LIF["tau"], self.path)
+                    calls.append((lib.snnb_conv_lif, args, L["name"]))
+                else:
+                    args = (src.data_ptr(), x_stride, wt["w"].data_ptr(), wt["b"].data_ptr(), res, None, dst.data_ptr(), v,
+                            T, B, L["cin"], h, w_, L["s"], dt, dt, dt, LIF["v_th"], LIF["v_reset"], LIF["tau"])
+                    calls.append((lib.snnb_dwconv3x3_lif, args, L["name"]))
+            elif L["op"] == "maxpool":
+                args = (src.data_ptr(), self.bufs[L["dst"]].data_ptr(), T * B, h, w_, c, dt)
+                calls.append((lib.snnb_maxpool3x3s2, args, L["name"]))
+            elif L["op"] == "tail":
+                wt = self.weights[L["name"]]
+                args = (src.data_ptr(), None, wt["w"].data_ptr(), wt["b"].data_ptr(), self.tail_sum.data_ptr(),
+                        self.membranes[L["name"]].data_ptr(), T, B, c, h * w_, L["classes"], _lib.NHWC, dt, dt,
+                        LIF["v_th"], LIF["v_reset"], LIF["tau"])
+                calls.append((lib.snnb_lif_avgpool_linear, args, L["name"]))
+            elif L["op"] == "head":
+                wt = self.weights[L["name"]]
+                args = (src.data_ptr(), wt["w"].data_ptr(), wt["b"].data_ptr(), self.logits.data_ptr(),
+                        T, B, c, h * w_, L["classes"], dt)
+                calls.append((lib.snnb_avgpool_linear_mean, args, L["name"]))
+        return calls
+
+    def _issue(self):
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        for fn, args, name in self._calls:
+            st = fn(*args, stream)
+            if st != 0:
+                _lib.check(st, f"layer {name}")
+        if hasattr(self, "tail_sum"):
+            # the tail returns sum_t logits in the compute dtype; the network output is their mean
+            torch.mul(self.tail_sum, 1.0 / float(self.T), out=self.logits)
+
+    def capture(self):
+        """Record the layer sequence into one CUDA graph (call after a warm-up forward)."""
+        self._issue()
+        torch.cuda.synchronize(self.device)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            self._issue()
+        self._graph = g
+        return self
+
+    def run(self):
+        """Run on whatever ``self.x_in`` holds; returns ``self.logits`` (valid after the stream catches up)."""
+        if self._graph is not None:
+            self._graph.replay()
+        else:
+            self._issue()
+        return self.logits
+
+    def forward(self, x_nhwc: torch.Tensor) -> torch.Tensor:
+        self.x_in.copy_(x_nhwc, non_blocking=True)
+        return self.run()
+
+    def forward_nchw(self, x: torch.Tensor) -> torch.Tensor:
+        """[B,3,H,W] input (any memory format, compute dtype or fp32)."""
+        self.x_in.copy_(x.permute(0, 2, 3, 1), non_blocking=True)
+        return self.run()
+
+    def activation(self, name: str) -> torch.Tensor:
+        """Named activation as a logical [T,B,C,H,W] tensor (channels-last memory)."""
+        return self.bufs[name].permute(0, 1, 4, 2, 3)
