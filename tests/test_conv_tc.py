@@ -1,0 +1,178 @@
+"""The tcgen05 / TMEM implicit-GEMM path of snnb_conv_lif and snnb_linear_lif against the oracle.
+
+Bounds: membrane within rtol 1e-2 for 16-bit inputs (fp32 accumulate, so usually far tighter) and a
+spike-flip rate of at most 1e-4, on seeded inputs the oracle finishes in seconds.
+"""
+import pytest
+import torch
+
+from oracle import snn_oracle as orc
+from util import check_parity
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+@pytest.fixture(autouse=True)
+def _force_tc_path():
+    from triton_snn_fusion_b200 import _lib
+    from triton_snn_fusion_b200.runtime import triton_convlif_backend as be
+    prev = be.set_conv_path("tcgen05")
+    yield
+    be.set_conv_path(prev)
+    assert _lib.device_status() == 0, "a bounded wait inside the tcgen05 kernel gave up"
+
+
+def _conv_be():
+    from triton_snn_fusion_b200.runtime import triton_convlif_backend as be
+    return be
+
+
+def _lin_be():
+    from triton_snn_fusion_b200.runtime import triton_temporal_linear_lif_backend as be
+    return be
+
+
+@pytest.mark.parametrize("shape", [(4, 128, 64, 64), (4, 256, 128, 128), (4, 300, 192, 80), (1, 128, 64, 16),
+                                   (8, 200, 128, 128), (16, 130, 64, 64), (4, 4096, 768, 3072)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_linear(shape, dtype):
+    T, M, K, N = shape
+    if dtype == torch.float16 and M > 1000:
+        pytest.skip("large case once")
+    torch.manual_seed(2026 + T + M + K + N)
+    x = (torch.rand(T, M, K) < 0.15).to(dtype)
+    w = (torch.randn(N, K) * (1.0 / K) ** 0.5 * 3.0).to(dtype)
+    b = (torch.randn(N) * 0.1).to(dtype)
+    v0 = (torch.randn(M, N) * 0.3).to(dtype)
+    rs, rv = orc.temporal_linear_lif(orc.widen(x), orc.widen(w), orc.widen(b), orc.widen(v0), 1.0, 0.0, 2.0)
+    r = _lin_be().run_triton_fused_temporal_linear_lif_state_packed(
+        x.to(DEV), w.to(DEV), b.to(DEV), v0.to(DEV), 1.0, 0.0, 2.0, False, strict=True)
+    check_parity(r.spikes, r.v_next, rs, rv, dtype, what=str(shape))
+    assert 0.02 < float(rs.mean()) < 0.6
+
+
+def test_linear_dense_inputs_no_bias_zero_state():
+    torch.manual_seed(3)
+    T, M, K, N = 4, 257, 256, 144
+    x = torch.randn(T, M, K).to(torch.bfloat16)
+    w = (torch.randn(N, K) * (1.0 / K) ** 0.5).to(torch.bfloat16)
+    rs, rv = orc.temporal_linear_lif(orc.widen(x), orc.widen(w), None, None, 1.0, 0.0, 2.0)
+    r = _lin_be().run_triton_fused_temporal_linear_lif_state_packed(
+        x.to(DEV), w.to(DEV), None, torch.tensor(0.0, device=DEV, dtype=torch.bfloat16), 1.0, 0.0, 2.0, False)
+    check_parity(r.spikes, r.v_next, rs, rv, torch.bfloat16)
+
+
+CONV = [
+    # B, cin, cout, k, s, p, H, W      (ResNet-18 / MobileNet layer shapes at small batch)
+    (2, 64, 64, 3, 1, 1, 56, 56),
+    (2, 64, 128, 3, 2, 1, 56, 56),
+    (2, 128, 128, 3, 1, 1, 28, 28),
+    (2, 128, 256, 3, 2, 1, 28, 28),
+    (3, 256, 256, 3, 1, 1, 14, 14),
+    (3, 256, 512, 3, 2, 1, 14, 14),
+    (5, 512, 512, 3, 1, 1, 7, 7),
+    (2, 64, 128, 1, 1, 0, 28, 28),
+    (2, 128, 64, 1, 1, 0, 13, 17),
+    (1, 64, 48, 3, 1, 1, 9, 11),
+    (2, 64, 64, 3, 2, 1, 15, 13),
+    (1, 64, 32, 5, 1, 2, 12, 12),
+]
+
+
+@pytest.mark.parametrize("case", CONV)
+@pytest.mark.parametrize("residual", [False, True])
+def test_conv(case, residual):
+    B, cin, cout, k, s, p, H, W = case
+    T, dtype = 4, torch.bfloat16
+    torch.manual_seed(2026 + cin + cout + k + H)
+    xs = [(torch.rand(B, cin, H, W) < 0.15).to(dtype) for _ in range(T)]
+    w = (torch.randn(cout, cin, k, k) * (2.0 / (cin * k * k)) ** 0.5 * 2.5).to(dtype)
+    b = (torch.randn(cout) * 0.1).to(dtype)
+    ho, wo = (H + 2 * p - k) // s + 1, (W + 2 * p - k) // s + 1
+    v0 = (torch.randn(B, cout, ho, wo) * 0.3).to(dtype)
+    res = [(torch.rand(B, cout, ho, wo) < 0.2).to(dtype) for _ in range(T)] if residual else None
+    rs, rv = orc.temporal_conv_lif([orc.widen(x) for x in xs], orc.widen(w), orc.widen(b), orc.widen(v0),
+                                   [s, s], [p, p], [1, 1], 1, 1.0, 0.0, 2.0,
+                                   residuals=[orc.widen(r) for r in res] if res else None)
+    be = _conv_be()
+    args = (w.to(DEV), b.to(DEV), v0.to(DEV), [s, s], [p, p], [1, 1], 1, 1.0, 0.0, 2.0, False)
+    xd = [x.to(DEV) for x in xs]
+    if residual:
+        r = be.run_triton_fused_temporal_conv_add_lif_state(xd, [q.to(DEV) for q in res], *args, strict=True)
+    elif k == 1:
+        r = be.run_triton_fused_temporal_pointwise_conv_lif_state(xd, *args, strict=True)
+    else:
+        r = be.run_triton_fused_temporal_conv_lif_state(xd, *args, strict=True)
+    check_parity(r.spikes, r.v_next, rs, rv, dtype, what=str(case))
+    assert 0.01 < float(rs.mean()) < 0.7
+
+
+@pytest.mark.parametrize("T", [1, 2, 8, 16])
+def test_conv_other_window_lengths(T):
+    B, cin, cout, H, W = 2, 64, 128, 14, 14
+    dtype = torch.bfloat16
+    torch.manual_seed(T)
+    xs = [(torch.rand(B, cin, H, W) < 0.2).to(dtype) for _ in range(T)]
+    w = (torch.randn(cout, cin, 3, 3) * 0.15).to(dtype)
+    b = (torch.randn(cout) * 0.1).to(dtype)
+    rs, rv = orc.temporal_conv_lif([orc.widen(x) for x in xs], orc.widen(w), orc.widen(b), None,
+                                   [1, 1], [1, 1], [1, 1], 1, 1.0, 0.0, 2.0)
+    r = _conv_be().run_triton_fused_temporal_conv_lif_state(
+        [x.to(DEV) for x in xs], w.to(DEV), b.to(DEV), torch.tensor(0.0, device=DEV, dtype=dtype),
+        [1, 1], [1, 1], [1, 1], 1, 1.0, 0.0, 2.0, False, strict=True)
+    check_parity(r.spikes, r.v_next, rs, rv, dtype)
+
+
+def test_conv_same_frame_every_step_and_soft_reset():
+    dtype = torch.bfloat16
+    torch.manual_seed(8)
+    x = torch.randn(2, 64, 12, 12).to(dtype)
+    w = (torch.randn(64, 64, 3, 3) * 0.05).to(dtype)
+    b = (torch.randn(64) * 0.1).to(dtype)
+    rs, rv = orc.temporal_conv_lif([orc.widen(x)] * 4, orc.widen(w), orc.widen(b), None,
+                                   [1, 1], [1, 1], [1, 1], 1, 0.8, -1.0, 2.0)
+    xd = x.to(DEV)
+    r = _conv_be().run_triton_fused_temporal_conv_lif_state(
+        [xd] * 4, w.to(DEV), b.to(DEV), torch.tensor(0.0, device=DEV, dtype=dtype),
+        [1, 1], [1, 1], [1, 1], 1, 0.8, -1.0, 2.0, False, strict=True)
+    check_parity(r.spikes, r.v_next, rs, rv, dtype)
+
+
+def test_shortcut_conv_without_lif():
+    dtype = torch.bfloat16
+    torch.manual_seed(4)
+    xs = [(torch.rand(2, 64, 28, 28) < 0.3).to(dtype) for _ in range(4)]
+    w = (torch.randn(128, 64, 1, 1) * 0.2).to(dtype)
+    b = (torch.randn(128) * 0.1).to(dtype)
+    ref = orc.temporal_conv_only([orc.widen(x) for x in xs], orc.widen(w), orc.widen(b), [2, 2], [0, 0])
+    out = _conv_be().conv_bias_only([x.to(DEV) for x in xs], w.to(DEV), b.to(DEV), [2, 2], [0, 0])
+    torch.testing.assert_close(out.cpu().float(), ref, rtol=1e-2, atol=1e-2)
+
+
+def test_config2_layer_properties_full_size():
+    """BASELINE config 2 at full size (T=4, batch 64, 128->128, 56x56, Bernoulli(0.15) spikes): too big for the
+    CPU oracle in seconds, so checked through size-independent properties: (a) batch independence - the
+    first two images of the batch-64 run equal a batch-2 run (which the oracle checks); (b) window
+    chaining - T=4 equals two chained T=2 calls with the membrane handed over."""
+    dtype = torch.bfloat16
+    be = _conv_be()
+    g = torch.Generator(device=DEV).manual_seed(2026)
+    B, C, H = 64, 128, 56
+    xs = [(torch.rand(B, H, H, C, device=DEV, generator=g) < 0.15).to(dtype).permute(0, 3, 1, 2) for _ in range(4)]
+    w = (torch.randn(C, C, 3, 3, device=DEV, generator=g) * (2.0 / (C * 9)) ** 0.5 * 2.5).to(dtype)
+    b = (torch.randn(C, device=DEV, generator=g) * 0.1).to(dtype)
+    z = torch.tensor(0.0, device=DEV, dtype=dtype)
+    a = ([1, 1], [1, 1], [1, 1], 1, 1.0, 0.0, 2.0, False)
+    full = be.run_triton_fused_temporal_conv_lif_state(xs, w, b, z, *a, strict=True)
+    small = be.run_triton_fused_temporal_conv_lif_state([x[:2] for x in xs], w, b, z, *a, strict=True)
+    assert torch.equal(full.spikes[:, :2], small.spikes) and torch.equal(full.v_next[:2], small.v_next)
+    rs, rv = orc.temporal_conv_lif([orc.widen(x[:2]) for x in xs], orc.widen(w), orc.widen(b), None,
+                                   [1, 1], [1, 1], [1, 1], 1, 1.0, 0.0, 2.0)
+    check_parity(small.spikes, small.v_next, rs, rv, dtype)
+    h1 = be.run_triton_fused_temporal_conv_lif_state(xs[:2], w, b, z, *a, strict=True)
+    h2 = be.run_triton_fused_temporal_conv_lif_state(xs[2:], w, b, h1.v_next, *a, strict=True)
+    # the hand-over rounds the membrane to bf16 once, so compare through flip rate, not bit equality
+    flips = float((torch.cat([h1.spikes, h2.spikes]) != full.spikes).float().mean())
+    assert flips < 2e-3
+    assert 0.01 < float(full.spikes.float().mean()) < 0.7

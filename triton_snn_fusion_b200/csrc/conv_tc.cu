@@ -1,7 +1,448 @@
-// placeholder until the tcgen05 kernel lands
+// Dense conv / linear (+ bias, + residual) + LIF over T as a tcgen05 implicit GEMM.
+//
+//   D[pixel][cout] (one fp32 accumulator per timestep, all T resident in tensor memory)
+//     = sum over (tap, 64-channel slab) of  A_t[pixel][slab] * W[cout][tap, slab]^T
+//
+// One CTA owns a tile of up to 128 output pixels x BN output channels for ALL timesteps:
+//   warp 4  TMA producer. Per K step it loads the weight tile once and then the activation
+//           tile of each timestep, so a weight tile fetched from L2 is reused T times.
+//           The activation tile of a (tap, slab) is the output-pixel tile shifted by the
+//           tap offset, fetched as a few boxes of a 5-D (C, W, H, B, T) tensor map; TMA's
+//           out-of-bounds zero fill is the conv padding. Stride-2 convs read four
+//           "phase" views of the input (even/odd rows x even/odd columns), each an
+//           ordinary dense tensor map with doubled strides.
+//   warp 5  MMA issuer: one elected thread issues tcgen05.mma (128 x BN x 16, bf16/f16 in,
+//           fp32 accumulate) into accumulator t at TMEM columns [t*BN, (t+1)*BN).
+//   warps 0-3  epilogue: thread r owns output pixel r of the tile (TMEM lane r). For each
+//           16-channel group it walks t = 0..T-1 in order: tcgen05.ld the accumulator
+//           slice, add bias (+ residual[t]), run the LIF update with the membrane
+//           potential held in registers across t, and store the spikes; the membrane is
+//           written once at the end.
+// Shared-memory operands use the 128-byte swizzle (64 16-bit channels per row), which is
+// what both TMA writes and the MMA descriptors describe. Every mbarrier wait is bounded:
+// on a timeout the CTA raises a device status word, skips the rest of its work, releases
+// its tensor memory and exits.
+#include <type_traits>
+
 #include "conv.cuh"
+#include "umma.cuh"
+
 namespace snnb {
-bool conv_lif_tc_supported(const ConvArgs &, const char **why) { *why = "not built"; return false; }
-int conv_lif_tc(const ConvArgs &, cudaStream_t) { return fail(SNNB_ERR_UNSUPPORTED, "tcgen05 path not built"); }
+
+static __device__ int g_tc_status = 0;
+
+namespace {
+
+constexpr int kSlotBytes = 16384;  // one 128-row x 128-byte operand tile
+constexpr int kMaxSlots = 13;
+constexpr int kMaxBoxes = 32;
+constexpr int kThreads = 192;
+
+struct TcGeom {
+  int T, Tacc, B, Cin, Cout, Ho, Wo, KH, KW, stride, pad;
+  int BN, BW, BH, nbox, WB, HB;
+  long long total_boxes;
+  int n_tiles_n, kchunks, slots, lif, tmem_cols, has_res, w_slot_bytes;
+};
+
+template <typename XT, typename ST, typename VT>
+__global__ void __launch_bounds__(kThreads)
+conv_lif_tc_kernel(const __grid_constant__ CUtensorMap xmap0, const __grid_constant__ CUtensorMap xmap1,
+                   const __grid_constant__ CUtensorMap xmap2, const __grid_constant__ CUtensorMap xmap3,
+                   const __grid_constant__ CUtensorMap wmap, const XT *__restrict__ bias,
+                   const XT *__restrict__ res, const VT *__restrict__ v_init, ST *__restrict__ spikes,
+                   VT *__restrict__ v_out, const TcGeom g, const LifParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bars[2 * kMaxSlots + 5];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int abort_s;
+  __shared__ int box_w0[kMaxBoxes], box_h0[kMaxBoxes], box_b[kMaxBoxes];
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_tile = blockIdx.x % g.n_tiles_n;
+  const long long m_tile = blockIdx.x / g.n_tiles_n;
+  const int n0 = n_tile * g.BN;
+  const uint32_t smem_base = (umma::smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t bar_base = umma::smem_u32(bars);
+  auto full_bar = [&](int s) { return bar_base + 8u * (uint32_t)s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (uint32_t)(kMaxSlots + s); };
+  const uint32_t acc_bar = bar_base + 8u * (uint32_t)(2 * kMaxSlots);
+  auto wfull_bar = [&](int s) { return bar_base + 8u * (uint32_t)(2 * kMaxSlots + 1 + s); };
+  auto wempty_bar = [&](int s) { return bar_base + 8u * (uint32_t)(2 * kMaxSlots + 3 + s); };
+  // shared memory: two weight buffers (double-buffered over K steps), then the ring of activation tiles
+  const uint32_t w_base = smem_base;
+  const uint32_t a_base = smem_base + 2u * (uint32_t)g.w_slot_bytes;
+  volatile int *abort_flag = &abort_s;
+
+  if (threadIdx.x == 0) {
+    abort_s = 0;
+    for (int s = 0; s < g.slots; ++s) {
+      umma::mbar_init(full_bar(s), 1);
+      umma::mbar_init(empty_bar(s), 1);
+    }
+    umma::mbar_init(acc_bar, 1);
+    for (int s = 0; s < 2; ++s) {
+      umma::mbar_init(wfull_bar(s), 1);
+      umma::mbar_init(wempty_bar(s), 1);
+    }
+    umma::fence_mbar_init();
+  }
+  if (warp == 5) {
+    umma::tmem_alloc(umma::smem_u32(&tmem_base_s), (uint32_t)g.tmem_cols);
+    umma::tmem_relinquish();
+  }
+  if (warp == 4) {
+    if (lane == 0) {
+      umma::prefetch_tensormap(&xmap0);
+      umma::prefetch_tensormap(&wmap);
+    }
+    for (int j = lane; j < g.nbox; j += 32) {
+      const long long gi = m_tile * g.nbox + j;
+      if (gi < g.total_boxes) {
+        box_w0[j] = (int)(gi % g.WB) * g.BW;
+        box_h0[j] = (int)((gi / g.WB) % g.HB) * g.BH;
+        box_b[j] = (int)(gi / ((long long)g.WB * g.HB));
+      } else {
+        box_b[j] = -1;
+      }
+    }
+  }
+  umma::tc_fence_before_sync();
+  __syncthreads();
+  umma::tc_fence_after_sync();
+  const uint32_t tmem_base = tmem_base_s;
+
+  const int ksteps = g.KH * g.KW * g.kchunks;
+  const uint32_t box_bytes = (uint32_t)(g.BW * g.BH) * 128u;
+
+  if (warp == 4) {
+    // ------------------------------------------------------------ TMA producer
+    int nvalid = 0;
+    for (int j = 0; j < g.nbox; ++j) nvalid += (box_b[j] >= 0);
+    const uint32_t a_bytes = (uint32_t)nvalid * box_bytes;
+    const uint32_t w_bytes = (uint32_t)g.BN * 128u;
+    const CUtensorMap *xmaps[4] = {&xmap0, &xmap1, &xmap2, &xmap3};
+    uint32_t n = 0;
+    bool ok = true;
+    for (int ks = 0; ks < ksteps && ok; ++ks) {
+      const int tap = ks / g.kchunks;
+      const int c0 = (ks - tap * g.kchunks) * 64;
+      const int kh = tap / g.KW, kw = tap - kh * g.KW;
+      int dh = kh - g.pad, dw = kw - g.pad, which = 0;
+      if (g.stride == 2) {
+        const int ph = dh & 1, pw = dw & 1;
+        which = ph * 2 + pw;
+        dh = (dh - ph) / 2;
+        dw = (dw - pw) / 2;
+      }
+      const CUtensorMap *xm = xmaps[which];
+      {  // weights of this K step
+        const int ws = ks & 1;
+        ok = umma::mbar_wait(wempty_bar(ws), (((uint32_t)ks >> 1) & 1u) ^ 1u, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        if (lane == 0) {
+          umma::mbar_expect_tx(wfull_bar(ws), w_bytes);
+          umma::tma_load_2d(w_base + (uint32_t)ws * (uint32_t)g.w_slot_bytes, &wmap, wfull_bar(ws), ks * 64, n0);
+        }
+      }
+      for (int t = 0; t < g.Tacc; ++t) {
+        const int slot = (int)(n % (uint32_t)g.slots);
+        ok = umma::mbar_wait(empty_bar(slot), ((n / (uint32_t)g.slots) & 1u) ^ 1u, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        if (lane == 0) umma::mbar_expect_tx(full_bar(slot), a_bytes);
+        __syncwarp();
+        for (int j = lane; j < g.nbox; j += 32) {
+          if (box_b[j] >= 0)
+            umma::tma_load_5d(a_base + (uint32_t)slot * kSlotBytes + (uint32_t)j * box_bytes, xm, full_bar(slot),
+                              c0, box_w0[j] + dw, box_h0[j] + dh, box_b[j], t);
+        }
+        ++n;
+      }
+    }
+  } else if (warp == 5) {
+    // -------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = umma::make_idesc_f16(128, g.BN, sizeof(XT) == 2 && std::is_same<XT, __nv_bfloat16>::value);
+      uint32_t n = 0;
+      bool ok = true;
+      for (int ks = 0; ks < ksteps && ok; ++ks) {
+        const int ws = ks & 1;
+        ok = umma::mbar_wait(wfull_bar(ws), ((uint32_t)ks >> 1) & 1u, abort_flag);
+        if (!ok) break;
+        const uint64_t bdesc = umma::make_sw128_kmajor_desc(w_base + (uint32_t)ws * (uint32_t)g.w_slot_bytes);
+        for (int t = 0; t < g.Tacc; ++t) {
+          const int aslot = (int)(n % (uint32_t)g.slots);
+          ok = umma::mbar_wait(full_bar(aslot), (n / (uint32_t)g.slots) & 1u, abort_flag);
+          if (!ok) break;
+          umma::tc_fence_after_sync();
+          const uint64_t adesc = umma::make_sw128_kmajor_desc(a_base + (uint32_t)aslot * kSlotBytes);
+          const uint32_t d = tmem_base + (uint32_t)(t * g.BN);
+#pragma unroll
+          for (int k = 0; k < 4; ++k)  // 4 x K=16 per 64-channel slab: +32 bytes along the swizzled row
+            umma::mma_f16_ss(d, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc, (ks > 0 || k > 0) ? 1u : 0u);
+          umma::mma_commit(empty_bar(aslot));
+          ++n;
+        }
+        if (ok) umma::mma_commit(wempty_bar(ws));
+      }
+      if (ok) umma::mma_commit(acc_bar);
+    }
+    __syncwarp();
+  } else {
+    // ---------------------------------------------------------------- epilogue
+    const int r = warp * 32 + lane;
+    const int per_box = g.BW * g.BH;
+    const int j = r / per_box, pp = r - j * per_box;
+    const int ph = pp / g.BW, pw = pp - ph * g.BW;
+    const long long gi = m_tile * g.nbox + j;
+    bool valid = (j < g.nbox) && (gi < g.total_boxes);
+    long long pix = 0;
+    if (valid) {
+      const int wo = (int)(gi % g.WB) * g.BW + pw;
+      const int ho = (int)((gi / g.WB) % g.HB) * g.BH + ph;
+      const long long b = gi / ((long long)g.WB * g.HB);
+      valid = (ho < g.Ho) && (wo < g.Wo);
+      pix = (b * g.Ho + ho) * g.Wo + wo;
+    }
+    const long long frame_out = (long long)g.B * g.Ho * g.Wo * g.Cout;
+    bool ok = umma::mbar_wait(acc_bar, 0u, abort_flag);
+    ok = __all_sync(0xffffffffu, ok);
+    umma::tc_fence_after_sync();
+    if (ok) {
+      const uint32_t lane_base = tmem_base + ((uint32_t)(warp * 32) << 16);
+      const bool alias = (g.Tacc != g.T);
+      for (int c = 0; c < g.BN / 16; ++c) {
+        const int n = n0 + c * 16;
+        if (n >= g.Cout) break;
+        float bj[16];
+        if (bias != nullptr) {
+          load_pack<XT, 16>(bias + n, bj);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) bj[i] = 0.f;
+        }
+        float v[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) v[i] = 0.f;
+        const long long o0 = pix * g.Cout + n;
+        if (g.lif && v_init != nullptr && valid) load_pack<VT, 16>(v_init + o0, v);
+        for (int t = 0; t < g.T; ++t) {
+          uint32_t acc[16];
+          umma::tmem_ld_x16(lane_base + (uint32_t)((alias ? 0 : t) * g.BN + c * 16), acc);
+          umma::tmem_ld_wait();
+          if (valid) {
+            float y[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) y[i] = __uint_as_float(acc[i]) + bj[i];
+            const long long o = (long long)t * frame_out + o0;
+            if (g.has_res) {
+              float rr[16];
+              load_pack<XT, 16>(res + o, rr);
+#pragma unroll
+              for (int i = 0; i < 16; ++i) y[i] += rr[i];
+            }
+            if (g.lif) {
+              float s[16];
+#pragma unroll
+              for (int i = 0; i < 16; ++i) s[i] = lif_step(y[i], v[i], p);
+              store_pack<ST, 16, false>(spikes + o, s);
+            } else {
+              store_pack<XT, 16, false>(reinterpret_cast<XT *>(spikes) + o, y);
+            }
+          }
+        }
+        if (g.lif && valid) store_pack<VT, 16, false>(v_out + o0, v);
+      }
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  umma::tc_fence_before_sync();
+  __syncthreads();
+  if (abort_s && threadIdx.x == 0) atomicExch(&g_tc_status, 1);
+  if (warp == 5) {
+    umma::tc_fence_after_sync();
+    umma::tmem_dealloc(tmem_base, (uint32_t)g.tmem_cols);
+  }
 }
-extern "C" int snnb_device_status(int *out) { if (out) *out = 0; return SNNB_OK; }
+
+// ------------------------------------------------------------------- host ----
+using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = [] {
+    void *p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+int encode(CUtensorMap *m, int dtype, int rank, const void *base, const cuuint64_t *dims, const cuuint64_t *strides,
+           const cuuint32_t *box) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fail(SNNB_ERR_CUDA, "conv_lif: cuTensorMapEncodeTiled is not available from the driver");
+  cuuint32_t ones[5] = {1, 1, 1, 1, 1};
+  const CUresult r = fn(m, dtype == SNNB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                        (cuuint32_t)rank, const_cast<void *>(base), dims, strides, box, ones,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(SNNB_ERR_CUDA, "conv_lif: cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  return SNNB_OK;
+}
+
+// Output-pixel tile = nbox boxes of BW x BH pixels (<= 128 pixels). Picks the geometry that wastes the
+// fewest MMA rows (partial boxes at image edges + unfilled tile rows), mildly preferring fewer boxes.
+void choose_boxes(int Ho, int Wo, int &BW, int &BH, int &nbox) {
+  double best = -1.0;
+  BW = 1; BH = 1; nbox = 1;
+  for (int bw = 1; bw <= Wo && bw <= 128; ++bw) {
+    for (int bh = 1; bh <= Ho && bw * bh <= 128; ++bh) {
+      const int per = bw * bh;
+      int nb = 128 / per;
+      if (nb > kMaxBoxes) nb = kMaxBoxes;
+      const double cover = (double)Wo * Ho / ((double)((Wo + bw - 1) / bw * bw) * ((Ho + bh - 1) / bh * bh));
+      const double score = cover * (per * nb / 128.0) - 0.004 * nb;
+      if (score > best + 1e-9) {
+        best = score;
+        BW = bw; BH = bh; nbox = nb;
+      }
+    }
+  }
+}
+
+int pick_bn(int Cout, int Tacc) {
+  int bn = Cout >= 128 ? 128 : ((Cout + 15) / 16) * 16;
+  while (bn > 16 && Tacc * bn > 512) bn /= 2;
+  return bn;
+}
+
+template <typename XT, typename ST, typename VT>
+int launch(const ConvArgs &a, cudaStream_t stream) {
+  TcGeom g;
+  g.T = a.T;
+  g.Tacc = (a.x_t_stride == 0) ? 1 : a.T;
+  g.B = a.B; g.Cin = a.Cin; g.Cout = a.Cout; g.Ho = a.Ho; g.Wo = a.Wo; g.KH = a.KH; g.KW = a.KW;
+  g.stride = a.stride; g.pad = a.pad;
+  g.BN = pick_bn(a.Cout, g.Tacc);
+  choose_boxes(a.Ho, a.Wo, g.BW, g.BH, g.nbox);
+  g.WB = (a.Wo + g.BW - 1) / g.BW;
+  g.HB = (a.Ho + g.BH - 1) / g.BH;
+  g.total_boxes = (long long)a.B * g.WB * g.HB;
+  g.n_tiles_n = (a.Cout + g.BN - 1) / g.BN;
+  g.kchunks = a.Cin / 64;
+  g.lif = a.lif;
+  g.has_res = a.res != nullptr;
+  int cols = 32;
+  while (cols < g.Tacc * g.BN) cols *= 2;
+  g.tmem_cols = cols;
+  // Shared memory: two weight buffers + a ring of 16 KB activation tiles. With <= 256 TMEM columns two
+  // CTAs can share an SM (one's epilogue overlaps the other's MMAs), so each takes half the budget.
+  g.w_slot_bytes = ((g.BN * 128 + 1023) / 1024) * 1024;
+  const int budget = (cols <= 256 ? 112 : 208) * 1024;
+  g.slots = (budget - 2 * g.w_slot_bytes) / kSlotBytes;
+  if (g.slots > kMaxSlots) g.slots = kMaxSlots;
+  const long long m_tiles = (g.total_boxes + g.nbox - 1) / g.nbox;
+  const long long grid = m_tiles * g.n_tiles_n;
+  if (grid > 0x7fffffffLL) return fail(SNNB_ERR_INVALID, "conv_lif: problem too large for the grid");
+
+  // ---- tensor maps
+  const int es = 2;
+  CUtensorMap xm[4], wm;
+  const int nphase = a.stride == 2 ? 4 : 1;
+  const cuuint64_t frame_bytes = (cuuint64_t)a.B * a.H * a.W * a.Cin * es;
+  for (int q = 0; q < 4; ++q) {
+    const int ph = nphase == 4 ? q / 2 : 0, pw = nphase == 4 ? q % 2 : 0;
+    const int s = a.stride;
+    if (q >= nphase) { xm[q] = xm[0]; continue; }
+    cuuint64_t dims[5] = {(cuuint64_t)a.Cin, (cuuint64_t)((a.W - pw + s - 1) / s), (cuuint64_t)((a.H - ph + s - 1) / s),
+                          (cuuint64_t)a.B, (cuuint64_t)g.Tacc};
+    cuuint64_t strides[4] = {(cuuint64_t)s * a.Cin * es, (cuuint64_t)s * a.W * a.Cin * es,
+                             (cuuint64_t)a.H * a.W * a.Cin * es,
+                             g.Tacc > 1 ? (cuuint64_t)a.x_t_stride * es : frame_bytes};
+    cuuint32_t box[5] = {64, (cuuint32_t)g.BW, (cuuint32_t)g.BH, 1, 1};
+    const char *base = static_cast<const char *>(a.x) + ((size_t)ph * a.W + pw) * a.Cin * es;
+    const int rc = encode(&xm[q], a.dtype, 5, base, dims, strides, box);
+    if (rc != SNNB_OK) return rc;
+  }
+  {
+    const cuuint64_t K = (cuuint64_t)a.KH * a.KW * a.Cin;
+    cuuint64_t dims[2] = {K, (cuuint64_t)a.Cout};
+    cuuint64_t strides[1] = {K * es};
+    cuuint32_t box[2] = {64, (cuuint32_t)g.BN};
+    const int rc = encode(&wm, a.dtype, 2, a.w, dims, strides, box);
+    if (rc != SNNB_OK) return rc;
+  }
+  const size_t smem = (size_t)g.slots * kSlotBytes + 2 * (size_t)g.w_slot_bytes + 1024;
+  auto kern = conv_lif_tc_kernel<XT, ST, VT>;
+  {  // per device and per kernel; cheap enough to repeat on every launch
+    const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return fail(SNNB_ERR_CUDA, "conv_lif: cannot raise the shared-memory limit: %s", cudaGetErrorString(e));
+  }
+  kern<<<(unsigned)grid, kThreads, smem, stream>>>(
+      xm[0], xm[1], xm[2], xm[3], wm, static_cast<const XT *>(a.b), static_cast<const XT *>(a.res),
+      static_cast<const VT *>(a.v_init), static_cast<ST *>(a.spikes), static_cast<VT *>(a.v_out), g, a.p);
+  SNNB_CHECK_LAUNCH("conv_lif_tc");
+  return SNNB_OK;
+}
+
+template <typename XT>
+int dispatch(const ConvArgs &a, cudaStream_t stream) {
+  const bool s_u8 = a.lif && a.spike_dtype == SNNB_U8;
+  const bool v_f32 = a.lif && a.v_dtype == SNNB_F32;
+  if (s_u8 && v_f32) return launch<XT, uint8_t, float>(a, stream);
+  if (s_u8) return launch<XT, uint8_t, XT>(a, stream);
+  if (v_f32) return launch<XT, XT, float>(a, stream);
+  return launch<XT, XT, XT>(a, stream);
+}
+
+}  // namespace
+
+bool conv_lif_tc_supported(const ConvArgs &a, const char **why) {
+  *why = "";
+  if (a.dtype != SNNB_BF16 && a.dtype != SNNB_F16) { *why = "activations must be bf16 or f16"; return false; }
+  if (a.Cin % 64 != 0) { *why = "Cin must be a multiple of 64"; return false; }
+  if (a.Cout % 16 != 0) { *why = "Cout must be a multiple of 16"; return false; }
+  if (a.KH != a.KW || a.KH > 11) { *why = "kernel must be square and at most 11x11"; return false; }
+  if (a.stride != 1 && a.stride != 2) { *why = "stride must be 1 or 2"; return false; }
+  if (a.stride == 2 && (a.H < 2 || a.W < 2)) { *why = "stride 2 needs H, W >= 2"; return false; }
+  if (a.T > 32) { *why = "T must be at most 32"; return false; }
+  if (a.x_t_stride % 8 != 0) { *why = "frame stride must be a multiple of 8 elements"; return false; }
+  if (!aligned16(a.x) || !aligned16(a.w) || !aligned16(a.spikes) || (a.b && !aligned16(a.b)) ||
+      (a.res && !aligned16(a.res)) || (a.v_init && !aligned16(a.v_init)) || (a.v_out && !aligned16(a.v_out))) {
+    *why = "pointers must be 16-byte aligned";
+    return false;
+  }
+  const int tacc = (a.x_t_stride == 0) ? 1 : a.T;
+  if (tacc * pick_bn(a.Cout, tacc) > 512) { *why = "T accumulators do not fit tensor memory"; return false; }
+  return true;
+}
+
+int conv_lif_tc(const ConvArgs &a, cudaStream_t stream) {
+  if (a.dtype == SNNB_BF16) return dispatch<__nv_bfloat16>(a, stream);
+  return dispatch<__half>(a, stream);
+}
+
+}  // namespace snnb
+
+extern "C" int snnb_device_status(int *status_out) {
+  using namespace snnb;
+  SNNB_CHECK_ARG(status_out != nullptr, "device_status: null pointer");
+  int h = 0;
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e == cudaSuccess) e = cudaMemcpyFromSymbol(&h, g_tc_status, sizeof(int));
+  if (e != cudaSuccess) return fail(SNNB_ERR_CUDA, "device_status: %s", cudaGetErrorString(e));
+  if (h != 0) {
+    const int zero = 0;
+    cudaMemcpyToSymbol(g_tc_status, &zero, sizeof(int));
+  }
+  *status_out = h;
+  return SNNB_OK;
+}

@@ -22,6 +22,7 @@ Deliberate differences from the reference backend:
 """
 from __future__ import annotations
 
+import weakref
 from collections import OrderedDict
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence, Tuple
@@ -161,7 +162,9 @@ def check_triton_support(x, weight, bias, v_prev, stride, padding, dilation, gro
 
 
 # ------------------------------------------------------------------ weights ----
-_PACKED: "OrderedDict[tuple, torch.Tensor]" = OrderedDict()
+# id(weight) -> (weak reference to the weight, its version counter, channels-last copy). The weak
+# reference is what makes the entry safe: a dead tensor's id or address may be handed to a new one.
+_PACKED: "OrderedDict[int, tuple]" = OrderedDict()
 _PACKED_MAX = 512
 
 
@@ -169,15 +172,16 @@ def _packed_weight(weight: torch.Tensor) -> torch.Tensor:
     """Dense-conv weight as [Cout][KH][KW][Cin] memory (channels_last); converted once per tensor version."""
     if is_nhwc_dense(weight):
         return weight
-    key = (weight.data_ptr(), weight._version, tuple(weight.shape), weight.dtype, weight.device)
-    hit = _PACKED.get(key)
-    if hit is not None:
-        _PACKED.move_to_end(key)
-        return hit
+    hit = _PACKED.get(id(weight))
+    if hit is not None and hit[0]() is weight and hit[1] == weight._version:
+        _PACKED.move_to_end(id(weight))
+        return hit[2]
     packed = weight.permute(0, 2, 3, 1).contiguous().permute(0, 3, 1, 2)
-    _PACKED[key] = packed
-    if len(_PACKED) > _PACKED_MAX:
+    _PACKED[id(weight)] = (weakref.ref(weight), weight._version, packed)
+    while len(_PACKED) > _PACKED_MAX:
         _PACKED.popitem(last=False)
+    for k in [k for k, v in list(_PACKED.items())[:8] if v[0]() is None]:
+        del _PACKED[k]
     return packed
 
 
