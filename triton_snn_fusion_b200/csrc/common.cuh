@@ -158,4 +158,18 @@ __device__ __forceinline__ float lif_step(float x, float &v, const LifParams &p)
   return s ? 1.0f : 0.0f;
 }
 
+// The same update with the charge mode and the reset kind fixed at compile time, for loops
+// that cannot afford the per-element branches (bit-identical to lif_step).
+template <int MODE, bool HARD>
+__device__ __forceinline__ float lif_step_t(float x, float &v, const LifParams &p) {
+  float h;
+  if constexpr (MODE == 0) h = __fadd_rn(v, x);
+  else if constexpr (MODE == 1) h = __fadd_rn(v, __fmul_rn(__fsub_rn(x, v), p.inv_tau));
+  else h = __fadd_rn(v, __fdiv_rn(__fsub_rn(x, v), p.tau));
+  const bool s = h >= p.v_th;
+  if constexpr (HARD) v = s ? p.v_reset : h;
+  else v = s ? __fsub_rn(h, p.v_th) : h;
+  return s ? 1.0f : 0.0f;
+}
+
 }  // namespace snnb

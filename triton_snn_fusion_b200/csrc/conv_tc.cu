@@ -36,7 +36,10 @@ namespace {
 constexpr int kSlotBytes = 16384;  // one 128-row x 128-byte operand tile
 constexpr int kMaxSlots = 13;
 constexpr int kMaxBoxes = 32;
-constexpr int kThreads = 192;
+constexpr int kEpiWarps = 8;               // two per TMEM lane quarter, splitting the columns
+constexpr int kProducerWarp = kEpiWarps;   // warp 8
+constexpr int kMmaWarp = kEpiWarps + 1;    // warp 9
+constexpr int kThreads = 32 * (kEpiWarps + 2);
 
 struct TcGeom {
   int T, Tacc, B, Cin, Cout, Ho, Wo, KH, KW, stride, pad;
@@ -44,6 +47,71 @@ struct TcGeom {
   long long total_boxes;
   int n_tiles_n, kchunks, slots, lif, tmem_cols, has_res, w_slot_bytes;
 };
+
+template <typename XT, typename ST, typename VT>
+struct EpiArgs {
+  const XT *bias;
+  const XT *res;
+  const VT *v_init;
+  ST *spikes;
+  VT *v_out;
+  uint32_t lane_base;   // TMEM address of this thread's lane, column 0 of accumulator 0
+  long long pix;        // flat output pixel index of this thread
+  long long frame_out;  // elements per output frame
+  int n0, c_begin, c_end;
+  bool valid;
+};
+
+// Epilogue of one thread: for each of its 16-channel groups, walk the T accumulators in order with
+// the membrane in registers. The TMEM load of step t+1 is in flight while step t is evaluated.
+template <typename XT, typename ST, typename VT, int MODE, bool HARD, bool LIFON>
+__device__ __forceinline__ void epilogue_cols(const EpiArgs<XT, ST, VT> &e, const TcGeom &g, const LifParams &p) {
+  const bool alias = (g.Tacc != g.T);
+  for (int c = e.c_begin; c < e.c_end; ++c) {
+    const int n = e.n0 + c * 16;
+    if (n >= g.Cout) break;
+    uint32_t nxt[16];
+    umma::tmem_ld_x16(e.lane_base + (uint32_t)(c * 16), nxt);
+    float bj[16];
+    if (e.bias != nullptr) {
+      load_pack<XT, 16>(e.bias + n, bj);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) bj[i] = 0.f;
+    }
+    float v[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = 0.f;
+    const long long o0 = e.pix * g.Cout + n;
+    if (LIFON && e.v_init != nullptr && e.valid) load_pack<VT, 16>(e.v_init + o0, v);
+    for (int t = 0; t < g.T; ++t) {
+      float y[16];
+      umma::tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 16; ++i) y[i] = __uint_as_float(nxt[i]) + bj[i];
+      if (t + 1 < g.T && !alias) umma::tmem_ld_x16(e.lane_base + (uint32_t)((t + 1) * g.BN + c * 16), nxt);
+      if (e.valid) {
+        const long long o = (long long)t * e.frame_out + o0;
+        if (g.has_res) {
+          float rr[16];
+          load_pack<XT, 16>(e.res + o, rr);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) y[i] += rr[i];
+        }
+        if constexpr (LIFON) {
+          float s[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) s[i] = lif_step_t<MODE, HARD>(y[i], v[i], p);
+          store_pack<ST, 16, false>(e.spikes + o, s);
+        } else {
+          store_pack<XT, 16, false>(reinterpret_cast<XT *>(e.spikes) + o, y);
+        }
+      }
+    }
+    if (LIFON && e.valid) store_pack<VT, 16, false>(e.v_out + o0, v);
+  }
+  umma::tmem_ld_wait();
+}
 
 template <typename XT, typename ST, typename VT>
 __global__ void __launch_bounds__(kThreads)
@@ -87,11 +155,11 @@ conv_lif_tc_kernel(const __grid_constant__ CUtensorMap xmap0, const __grid_const
     }
     umma::fence_mbar_init();
   }
-  if (warp == 5) {
+  if (warp == kMmaWarp) {
     umma::tmem_alloc(umma::smem_u32(&tmem_base_s), (uint32_t)g.tmem_cols);
     umma::tmem_relinquish();
   }
-  if (warp == 4) {
+  if (warp == kProducerWarp) {
     if (lane == 0) {
       umma::prefetch_tensormap(&xmap0);
       umma::prefetch_tensormap(&wmap);
@@ -115,7 +183,7 @@ conv_lif_tc_kernel(const __grid_constant__ CUtensorMap xmap0, const __grid_const
   const int ksteps = g.KH * g.KW * g.kchunks;
   const uint32_t box_bytes = (uint32_t)(g.BW * g.BH) * 128u;
 
-  if (warp == 4) {
+  if (warp == kProducerWarp) {
     // ------------------------------------------------------------ TMA producer
     int nvalid = 0;
     for (int j = 0; j < g.nbox; ++j) nvalid += (box_b[j] >= 0);
@@ -161,7 +229,7 @@ conv_lif_tc_kernel(const __grid_constant__ CUtensorMap xmap0, const __grid_const
         ++n;
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == kMmaWarp) {
     // -------------------------------------------------------------- MMA issuer
     if (lane == 0) {
       const uint32_t idesc = umma::make_idesc_f16(128, g.BN, sizeof(XT) == 2 && std::is_same<XT, __nv_bfloat16>::value);
@@ -192,7 +260,8 @@ conv_lif_tc_kernel(const __grid_constant__ CUtensorMap xmap0, const __grid_const
     __syncwarp();
   } else {
     // ---------------------------------------------------------------- epilogue
-    const int r = warp * 32 + lane;
+    const int quarter = warp & 3;          // TMEM lanes 32*quarter .. +31 are the ones this warp may read
+    const int r = quarter * 32 + lane;     // row of the tile = output pixel owned by this thread
     const int per_box = g.BW * g.BH;
     const int j = r / per_box, pp = r - j * per_box;
     const int ph = pp / g.BW, pw = pp - ph * g.BW;
@@ -206,54 +275,27 @@ conv_lif_tc_kernel(const __grid_constant__ CUtensorMap xmap0, const __grid_const
       valid = (ho < g.Ho) && (wo < g.Wo);
       pix = (b * g.Ho + ho) * g.Wo + wo;
     }
-    const long long frame_out = (long long)g.B * g.Ho * g.Wo * g.Cout;
     bool ok = umma::mbar_wait(acc_bar, 0u, abort_flag);
     ok = __all_sync(0xffffffffu, ok);
     umma::tc_fence_after_sync();
     if (ok) {
-      const uint32_t lane_base = tmem_base + ((uint32_t)(warp * 32) << 16);
-      const bool alias = (g.Tacc != g.T);
-      for (int c = 0; c < g.BN / 16; ++c) {
-        const int n = n0 + c * 16;
-        if (n >= g.Cout) break;
-        float bj[16];
-        if (bias != nullptr) {
-          load_pack<XT, 16>(bias + n, bj);
-        } else {
-#pragma unroll
-          for (int i = 0; i < 16; ++i) bj[i] = 0.f;
+      // the two warps of a lane quarter split the 16-column groups of the tile
+      const int nch = g.BN / 16, half = (nch + 1) / 2;
+      const int c_begin = (warp < 4) ? 0 : half;
+      const int c_end = (warp < 4) ? half : nch;
+      EpiArgs<XT, ST, VT> ea{bias, res, v_init, spikes, v_out, tmem_base + ((uint32_t)(quarter * 32) << 16),
+                             pix, (long long)g.B * g.Ho * g.Wo * g.Cout, n0, c_begin, c_end, valid};
+      if (!g.lif) {
+        epilogue_cols<XT, ST, VT, 0, true, false>(ea, g, p);
+      } else {
+        switch (p.mode * 2 + p.hard) {
+          case 0: epilogue_cols<XT, ST, VT, 0, false, true>(ea, g, p); break;
+          case 1: epilogue_cols<XT, ST, VT, 0, true, true>(ea, g, p); break;
+          case 2: epilogue_cols<XT, ST, VT, 1, false, true>(ea, g, p); break;
+          case 3: epilogue_cols<XT, ST, VT, 1, true, true>(ea, g, p); break;
+          case 4: epilogue_cols<XT, ST, VT, 2, false, true>(ea, g, p); break;
+          default: epilogue_cols<XT, ST, VT, 2, true, true>(ea, g, p); break;
         }
-        float v[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) v[i] = 0.f;
-        const long long o0 = pix * g.Cout + n;
-        if (g.lif && v_init != nullptr && valid) load_pack<VT, 16>(v_init + o0, v);
-        for (int t = 0; t < g.T; ++t) {
-          uint32_t acc[16];
-          umma::tmem_ld_x16(lane_base + (uint32_t)((alias ? 0 : t) * g.BN + c * 16), acc);
-          umma::tmem_ld_wait();
-          if (valid) {
-            float y[16];
-#pragma unroll
-            for (int i = 0; i < 16; ++i) y[i] = __uint_as_float(acc[i]) + bj[i];
-            const long long o = (long long)t * frame_out + o0;
-            if (g.has_res) {
-              float rr[16];
-              load_pack<XT, 16>(res + o, rr);
-#pragma unroll
-              for (int i = 0; i < 16; ++i) y[i] += rr[i];
-            }
-            if (g.lif) {
-              float s[16];
-#pragma unroll
-              for (int i = 0; i < 16; ++i) s[i] = lif_step(y[i], v[i], p);
-              store_pack<ST, 16, false>(spikes + o, s);
-            } else {
-              store_pack<XT, 16, false>(reinterpret_cast<XT *>(spikes) + o, y);
-            }
-          }
-        }
-        if (g.lif && valid) store_pack<VT, 16, false>(v_out + o0, v);
       }
     }
   }
@@ -262,7 +304,7 @@ conv_lif_tc_kernel(const __grid_constant__ CUtensorMap xmap0, const __grid_const
   umma::tc_fence_before_sync();
   __syncthreads();
   if (abort_s && threadIdx.x == 0) atomicExch(&g_tc_status, 1);
-  if (warp == 5) {
+  if (warp == kMmaWarp) {
     umma::tc_fence_after_sync();
     umma::tmem_dealloc(tmem_base, (uint32_t)g.tmem_cols);
   }

@@ -56,19 +56,21 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Bounded wait: polls the barrier; gives up after `limit_ns` of wall time and reports false.
-// `abort_flag` (shared memory) short-circuits every later wait of the CTA once one gave up.
+// Bounded wait: polls the barrier; gives up after `limit_cycles` SM clock cycles (about two seconds)
+// and reports false. `abort_flag` (shared memory) short-circuits every later wait of the CTA once
+// one gave up. The SM cycle counter is used because reading it costs a few cycles; the global
+// nanosecond timer is far slower to read and would sit on the critical path of every wait.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag,
-                                          uint64_t limit_ns = 2000000000ull) {
-  if (*abort_flag) return false;
+                                          long long limit_cycles = 4000000000ll) {
   if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = globaltimer_ns();
+  if (*abort_flag) return false;
+  const long long t0 = clock64();
   uint32_t spins = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((++spins & 1023u) == 0) {
+    if ((++spins & 255u) == 0) {
       if (*abort_flag) return false;
-      if (globaltimer_ns() - t0 > limit_ns) {
+      if (clock64() - t0 > limit_cycles) {
         *abort_flag = 1;
         return false;
       }
