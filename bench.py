@@ -267,6 +267,8 @@ def run_ours(args):
         "share_of_step": tc_ms / total_ms if total_ms else None,
         "top_layers_ms": {k: round(v, 4) for k, v in top},
     }
+    if args.layers:
+        print(json.dumps({"layers_ms": {k: round(v, 4) for k, v in layer_ms.items()}}), file=sys.stderr)
     cpu_batch = 8
     ips_cpu, cores, sec = cpu_eager_images_per_s(cpu_batch, 3) if world == 1 and not args.no_cpu else (None, None, None)
     line = {
@@ -303,6 +305,7 @@ def main():
     ap.add_argument("--path", default="auto", choices=["auto", "simt", "tcgen05"])
     ap.add_argument("--no-graph", dest="graph", action="store_false")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--layers", action="store_true", help="also print every layer's device time to stderr")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

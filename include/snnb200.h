@@ -137,6 +137,25 @@ int snnb_conv_lif(const void *x_seq, int64_t x_t_stride, const void *w, const vo
                   float v_th, float v_reset, float tau, int path, void *stream);
 
 /*
+ * 7x7 / stride 2 / padding 3 stem conv with 3 input channels (+ folded BN) + LIF over T on the
+ * tensor cores. Same reference items as snnb_conv_lif (kernel key k7_s2_p3,
+ * kernels/benchmark_conv_lif_temporal_general.py:561-710, runtime/triton_convlif_backend.py:393-430);
+ * snnb_conv_lif runs this shape on CUDA cores, this entry is the fast path for 16-bit data.
+ *   x_seq [T][B][H][W][3] (x_t_stride elements apart; 0 = one frame for every step, convolved once),
+ *   H and W even; w_packed [Cout][4][4][16] produced once by snnb_stem7x7_pack_weight from the
+ *   [Cout][7][7][3] channels-last weight; spikes [T][B][H/2][W/2][Cout]; v_init/v_out [B][H/2][W/2][Cout].
+ *   scratch: snnb_stem7x7_scratch_bytes(frames, H, W) bytes of device memory, 16-byte aligned, where
+ *   frames = B if x_t_stride == 0 else T*B. It holds the input re-laid as 2x2-pixel blocks with a
+ *   zero border; its contents are overwritten by every call.
+ */
+int64_t snnb_stem7x7_scratch_bytes(int frames, int H, int W);
+int snnb_stem7x7_pack_weight(const void *w, void *w_packed, int Cout, int dtype, void *stream);
+int snnb_stem7x7_lif(const void *x_seq, int64_t x_t_stride, const void *w_packed, const void *b,
+                     const void *v_init, void *spikes, void *v_out, void *scratch, int64_t scratch_bytes,
+                     int T, int B, int H, int W, int Cout, int dtype, int spike_dtype, int v_dtype,
+                     float v_th, float v_reset, float tau, void *stream);
+
+/*
  * Temporal linear + LIF.
  * Replaces run_triton_fused_temporal_linear_lif_state{,_packed,_packed_out}
  * (runtime/triton_temporal_linear_lif_backend.py:74-274) and

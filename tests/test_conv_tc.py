@@ -176,3 +176,24 @@ def test_config2_layer_properties_full_size():
     flips = float((torch.cat([h1.spikes, h2.spikes]) != full.spikes).float().mean())
     assert flips < 2e-3
     assert 0.01 < float(full.spikes.float().mean()) < 0.7
+
+
+@pytest.mark.parametrize("hw", [(64, 64), (32, 48), (224, 224)])
+@pytest.mark.parametrize("alias", [True, False])
+def test_stem_7x7_s2_three_channels(hw, alias):
+    """ResNet stem (7x7, stride 2, padding 3, 3 -> 64) through the tensor-core stem path."""
+    H, W = hw
+    dtype, T, B = torch.bfloat16, 4, (2 if H < 200 else 1)
+    torch.manual_seed(H + W + alias)
+    xs = [torch.randn(B, 3, H, W).to(dtype)] * T if alias else [torch.randn(B, 3, H, W).to(dtype) for _ in range(T)]
+    w = (torch.randn(64, 3, 7, 7) * (2.0 / 147) ** 0.5).to(dtype)
+    b = (torch.randn(64) * 0.1).to(dtype)
+    rs, rv = orc.temporal_conv_lif([orc.widen(x) for x in xs], orc.widen(w), orc.widen(b), None,
+                                   [2, 2], [3, 3], [1, 1], 1, 1.0, 0.0, 2.0)
+    xd = [xs[0].to(DEV)] * T if alias else [x.to(DEV) for x in xs]
+    r = _conv_be().run_triton_fused_temporal_conv_lif_state(
+        xd, w.to(DEV), b.to(DEV), torch.tensor(0.0, device=DEV, dtype=dtype), [2, 2], [3, 3], [1, 1], 1,
+        1.0, 0.0, 2.0, False, strict=True)
+    assert r.kernel_key == "k7_s2_p3"
+    check_parity(r.spikes, r.v_next, rs, rv, dtype, what=f"stem {hw} alias={alias}")
+    assert 0.02 < float(rs.mean()) < 0.6

@@ -17,6 +17,11 @@ struct ConvArgs {
   int lif;              // 0: write conv + bias (+ residual) instead of spikes, no state
   int dtype, spike_dtype, v_dtype;
   LifParams p;
+  // Optional strided view of x for the tensor-core path (all 0 = the dense [B][H][W][Cin] frame):
+  // element strides between neighbouring pixels / rows / images and the number of valid
+  // coordinates along W and H. Used to read overlapping windows as if they were pixels.
+  long long xs_w = 0, xs_h = 0, xs_b = 0;
+  int xd_w = 0, xd_h = 0;
 };
 
 // CUDA-core implicit GEMM (any shape, fp32 accumulate).

@@ -399,18 +399,21 @@ int launch(const ConvArgs &a, cudaStream_t stream) {
   const int es = 2;
   CUtensorMap xm[4], wm;
   const int nphase = a.stride == 2 ? 4 : 1;
-  const cuuint64_t frame_bytes = (cuuint64_t)a.B * a.H * a.W * a.Cin * es;
+  const long long xs_w = a.xs_w ? a.xs_w : a.Cin;
+  const long long xs_h = a.xs_h ? a.xs_h : (long long)a.W * a.Cin;
+  const long long xs_b = a.xs_b ? a.xs_b : (long long)a.H * a.W * a.Cin;
+  const int xd_w = a.xd_w ? a.xd_w : a.W, xd_h = a.xd_h ? a.xd_h : a.H;
+  const cuuint64_t frame_bytes = (cuuint64_t)a.B * xs_b * es;
   for (int q = 0; q < 4; ++q) {
     const int ph = nphase == 4 ? q / 2 : 0, pw = nphase == 4 ? q % 2 : 0;
     const int s = a.stride;
     if (q >= nphase) { xm[q] = xm[0]; continue; }
-    cuuint64_t dims[5] = {(cuuint64_t)a.Cin, (cuuint64_t)((a.W - pw + s - 1) / s), (cuuint64_t)((a.H - ph + s - 1) / s),
+    cuuint64_t dims[5] = {(cuuint64_t)a.Cin, (cuuint64_t)((xd_w - pw + s - 1) / s), (cuuint64_t)((xd_h - ph + s - 1) / s),
                           (cuuint64_t)a.B, (cuuint64_t)g.Tacc};
-    cuuint64_t strides[4] = {(cuuint64_t)s * a.Cin * es, (cuuint64_t)s * a.W * a.Cin * es,
-                             (cuuint64_t)a.H * a.W * a.Cin * es,
+    cuuint64_t strides[4] = {(cuuint64_t)(s * xs_w * es), (cuuint64_t)(s * xs_h * es), (cuuint64_t)(xs_b * es),
                              g.Tacc > 1 ? (cuuint64_t)a.x_t_stride * es : frame_bytes};
     cuuint32_t box[5] = {64, (cuuint32_t)g.BW, (cuuint32_t)g.BH, 1, 1};
-    const char *base = static_cast<const char *>(a.x) + ((size_t)ph * a.W + pw) * a.Cin * es;
+    const char *base = static_cast<const char *>(a.x) + ((size_t)ph * xs_h + (size_t)pw * xs_w) * es;
     const int rc = encode(&xm[q], a.dtype, 5, base, dims, strides, box);
     if (rc != SNNB_OK) return rc;
   }
@@ -452,7 +455,7 @@ bool conv_lif_tc_supported(const ConvArgs &a, const char **why) {
   if (a.dtype != SNNB_BF16 && a.dtype != SNNB_F16) { *why = "activations must be bf16 or f16"; return false; }
   if (a.Cin % 64 != 0) { *why = "Cin must be a multiple of 64"; return false; }
   if (a.Cout % 16 != 0) { *why = "Cout must be a multiple of 16"; return false; }
-  if (a.KH != a.KW || a.KH > 11) { *why = "kernel must be square and at most 11x11"; return false; }
+  if (a.KH > 11 || a.KW > 11) { *why = "kernel must be at most 11x11"; return false; }
   if (a.stride != 1 && a.stride != 2) { *why = "stride must be 1 or 2"; return false; }
   if (a.stride == 2 && (a.H < 2 || a.W < 2)) { *why = "stride 2 needs H, W >= 2"; return false; }
   if (a.T > 32) { *why = "T must be at most 32"; return false; }

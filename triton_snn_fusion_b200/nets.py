@@ -182,12 +182,19 @@ class CompiledNet:
             elif L["op"] == "head":
                 self.logits = torch.empty((self.B, L["classes"]), dtype=torch.float32, device=self.device)
         self._calls = self._plan()
-        self.launches_per_forward = len(self._calls) + (1 if any(L["op"] == "tail" for L in spec) else 0)
+        self.launches_per_forward = (len(self._calls) + self.extra_launches
+                                     + (1 if any(L["op"] == "tail" for L in spec) else 0))
         self._graph: Optional[torch.cuda.CUDAGraph] = None
+
+    def _is_tc_stem(self, L, h, w_) -> bool:
+        return (L["op"] == "conv" and L["groups"] == 1 and L["cin"] == 3 and L["k"] == 7 and L["s"] == 2 and L["p"] == 3
+                and L["lif"] and not L.get("residual") and self.dtype in (torch.bfloat16, torch.float16)
+                and h % 2 == 0 and w_ % 2 == 0 and L["cout"] % 16 == 0 and self.path != _lib.PATH_SIMT)
 
     # one closure per kernel launch, all arguments resolved ahead of time
     def _plan(self):
         lib, calls = _lib.lib, []
+        self.extra_launches = 0
         T, B, dt = self.T, self.B, self.dt
         for L in self.spec:
             src = self.bufs[L["src"]]
@@ -198,7 +205,22 @@ class CompiledNet:
                 dst = self.bufs[L["dst"]]
                 res = self.bufs[L["residual"]].data_ptr() if L.get("residual") else None
                 v = self.membranes[L["name"]].data_ptr() if L["lif"] else None
-                if L["groups"] == 1:
+                if self._is_tc_stem(L, h, w_):
+                    # 7x7/s2 stem on the tensor cores: weights re-packed once, input re-laid into scratch per call
+                    frames = B if x_stride == 0 else T * B
+                    nbytes = int(lib.snnb_stem7x7_scratch_bytes(frames, h, w_))
+                    self._scratch = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
+                    wp = torch.empty((L["cout"], 256), dtype=self.dtype, device=self.device)
+                    _lib.check(lib.snnb_stem7x7_pack_weight(wt["w"].data_ptr(), wp.data_ptr(), L["cout"], dt, None),
+                               "snnb_stem7x7_pack_weight")
+                    torch.cuda.synchronize(self.device)
+                    wt["w_stem"] = wp
+                    args = (src.data_ptr(), x_stride, wp.data_ptr(), wt["b"].data_ptr(), None, dst.data_ptr(), v,
+                            self._scratch.data_ptr(), nbytes, T, B, h, w_, L["cout"], dt, dt, dt,
+                            LIF["v_th"], LIF["v_reset"], LIF["tau"])
+                    calls.append((lib.snnb_stem7x7_lif, args, L["name"]))
+                    self.extra_launches += 1
+                elif L["groups"] == 1:
                     args = (src.data_ptr(), x_stride, wt["w"].data_ptr(), wt["b"].data_ptr(), res, None, dst.data_ptr(), v,
                             T, B, L["cin"], h, w_, L["cout"], L["k"], L["k"], L["s"], L["p"], 1 if L["lif"] else 0,
                             dt, dt, dt, LIF["v_th"], LIF["v_reset"], LIF["tau"], self.path)

@@ -185,6 +185,24 @@ def _packed_weight(weight: torch.Tensor) -> torch.Tensor:
     return packed
 
 
+_STEM: "OrderedDict[int, tuple]" = OrderedDict()
+
+
+def _stem_weight(weight: torch.Tensor, dt: int) -> torch.Tensor:
+    """[Cout,3,7,7] weight re-packed for snnb_stem7x7_lif ([Cout][4][4][16]); once per tensor version."""
+    hit = _STEM.get(id(weight))
+    if hit is not None and hit[0]() is weight and hit[1] == weight._version:
+        return hit[2]
+    w = _packed_weight(weight).permute(0, 2, 3, 1).contiguous()  # [Cout][7][7][3] memory
+    wp = torch.empty((int(weight.shape[0]), 256), dtype=weight.dtype, device=weight.device)
+    _lib.check(_lib.lib.snnb_stem7x7_pack_weight(_lib.ptr(w), _lib.ptr(wp), int(weight.shape[0]), dt,
+                                                 _lib.current_stream(weight.device)), "snnb_stem7x7_pack_weight")
+    _STEM[id(weight)] = (weakref.ref(weight), weight._version, wp)
+    while len(_STEM) > 64:
+        _STEM.popitem(last=False)
+    return wp
+
+
 def _validate_kind(kind: str, key: str) -> None:
     if kind == "regular" and key.startswith("depthwise_"):
         raise RuntimeError(f"regular conv op cannot dispatch depthwise kernel {key}")
@@ -208,6 +226,20 @@ def _launch(x_base, x_t_stride, T, weight, bias, residual, v_init, stride, paddi
     sdt = _lib.dtype_code(spike_dtype or x_base.dtype)
     vdt = _lib.dtype_code(v_dtype or x_base.dtype)
     stream = _lib.current_stream(x_base.device)
+    if (groups == 1 and lif and residual is None and Cin == 3 and KH == 7 and KW == 7 and s == 2 and p == 3
+            and x_base.dtype in (torch.bfloat16, torch.float16) and H % 2 == 0 and W % 2 == 0 and Cout % 16 == 0
+            and _conv_path != "simt"):
+        # 7x7/s2 three-channel stem: tensor-core path over a re-laid copy of the input held in scratch
+        wp = _stem_weight(weight, dt)
+        frames = B if x_t_stride == 0 else T * B
+        nbytes = int(_lib.lib.snnb_stem7x7_scratch_bytes(frames, H, W))
+        scratch = torch.empty(nbytes, dtype=torch.uint8, device=x_base.device)
+        _lib.check(
+            _lib.lib.snnb_stem7x7_lif(
+                _lib.ptr(x_base), x_t_stride, _lib.ptr(wp), _lib.ptr(bias), _lib.ptr(v_init), _lib.ptr(spikes),
+                _lib.ptr(v_next), _lib.ptr(scratch), nbytes, T, B, H, W, Cout, dt, sdt, vdt, th, vr, ta, stream),
+            "snnb_stem7x7_lif")
+        return
     if groups == 1:
         w = _packed_weight(weight)
         _lib.check(
