@@ -162,6 +162,7 @@ def run_ours(args):
     import torch.distributed as dist
 
     from triton_snn_fusion_b200 import _lib, nets
+    from triton_snn_fusion_b200.parallel import gather_logits, shard_range
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -172,9 +173,8 @@ def run_ours(args):
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-    if GLOBAL_BATCH % world:
-        raise SystemExit(f"global batch {GLOBAL_BATCH} is not divisible by {world} ranks")
-    B = GLOBAL_BATCH // world
+    start, stop = shard_range(GLOBAL_BATCH, rank, world)
+    B = stop - start
     K, Wm = args.steps, max(args.warmup, 3)
 
     spec = nets.spiking_resnet18(CLASSES)
@@ -193,15 +193,12 @@ def run_ours(args):
         net.capture()
 
     def step_resident():
-        logits = net.run()
-        if world > 1:
-            dist.all_gather_into_tensor(gathered, logits)
+        gather_logits(net.run(), out=gathered)
 
     def step_e2e():
         net.x_in.copy_(host_in, non_blocking=True)
         logits = net.run()
-        if world > 1:
-            dist.all_gather_into_tensor(gathered, logits)
+        gather_logits(logits, out=gathered)
         host_out.copy_(logits, non_blocking=True)
 
     def timed(step_fn):
