@@ -156,6 +156,34 @@ int snnb_stem7x7_lif(const void *x_seq, int64_t x_t_stride, const void *w_packed
                      float v_th, float v_reset, float tau, void *stream);
 
 /*
+ * snnb_stem7x7_lif without caller-provided scratch. No counterpart in the reference.
+ *
+ * For callers that cannot obtain device memory of their own at call time: a plugin slot of a
+ * host runtime that owns the whole device pool and passes a plugin nothing but its input and
+ * output buffers, or a serving loop that has frozen its memory plan and must not touch the
+ * driver allocator (cudaMalloc may block on the whole device). This entry neither allocates nor
+ * frees anything and calls no allocating library routine; the re-laid input goes into an array
+ * that is part of the library image (16 MiB, snnb_stem7x7_static_scratch_bytes()) and therefore
+ * occupies that much memory on every GPU the library is loaded on until the process exits.
+ *
+ *   - Limit: snnb_stem7x7_scratch_bytes(frames, H, W) must not exceed the array, where
+ *     frames = B if x_t_stride == 0 else T*B (e.g. up to 39 frames of 224x224). Larger calls are
+ *     rejected with SNNB_ERR_UNSUPPORTED and a message naming both sizes; nothing is launched.
+ *   - The first call on each device looks the array's device address up (one runtime query with
+ *     that device current); make that first call before starting any stream capture.
+ *   - All calls on a device share the one array and it keeps whatever the previous call left. No
+ *     part of it has to be cleared by the caller: each call rewrites every byte it later reads,
+ *     zero border included. Two calls that may overlap in time on the GPU (different streams
+ *     without an ordering between them) race on it; order them, or use snnb_stem7x7_lif.
+ * Arguments and results are those of snnb_stem7x7_lif.
+ */
+int64_t snnb_stem7x7_static_scratch_bytes(void);
+int snnb_stem7x7_lif_static(const void *x_seq, int64_t x_t_stride, const void *w_packed, const void *b,
+                            const void *v_init, void *spikes, void *v_out,
+                            int T, int B, int H, int W, int Cout, int dtype, int spike_dtype, int v_dtype,
+                            float v_th, float v_reset, float tau, void *stream);
+
+/*
  * Temporal linear + LIF.
  * Replaces run_triton_fused_temporal_linear_lif_state{,_packed,_packed_out}
  * (runtime/triton_temporal_linear_lif_backend.py:74-274) and

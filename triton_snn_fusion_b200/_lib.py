@@ -44,6 +44,10 @@ SIGNATURES = {
     "snnb_stem7x7_lif": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
                                  c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                  c_float, c_float, c_float, c_void_p]),
+    "snnb_stem7x7_static_scratch_bytes": (c_int64, []),
+    "snnb_stem7x7_lif_static": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                        c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                        c_float, c_float, c_float, c_void_p]),
     "snnb_nchw_to_nhwc": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_void_p]),
     "snnb_nhwc_to_nchw": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_void_p]),
     "snnb_maxpool3x3s2": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_void_p]),

@@ -8,7 +8,14 @@
 // becomes a GEMM with K = 4 x 64 (49*3 = 147 real taps, the rest multiply zero weights) read
 // through a tensor map whose "pixel" stride is one block (32 bytes): overlapping windows.
 // The re-laid image lives in caller-provided scratch memory.
+#include <mutex>
+
 #include "conv.cuh"
+
+// Built-in scratch for snnb_stem7x7_lif_static: lives in every GPU's memory from the moment the
+// library is loaded there until the process exits.
+#define SNNB_STEM_STATIC_SCRATCH_BYTES (16 * 1024 * 1024)
+static __device__ __align__(256) unsigned char g_stem_static_scratch[SNNB_STEM_STATIC_SCRATCH_BYTES];
 
 namespace snnb {
 namespace {
@@ -128,4 +135,57 @@ extern "C" int snnb_stem7x7_lif(const void *x_seq, int64_t x_t_stride, const voi
   const char *why = "";
   if (!conv_lif_tc_supported(a, &why)) return fail(SNNB_ERR_UNSUPPORTED, "stem7x7_lif: %s", why);
   return conv_lif_tc(a, st);
+}
+
+namespace snnb {
+namespace {
+
+constexpr int kMaxDevices = 64;
+std::mutex g_static_mu;
+void *g_static_ptr[kMaxDevices] = {};
+
+// Device address of the built-in scratch array on the current device. In host code the array's
+// name is only a handle, so the address is asked from the runtime once per device (with that
+// device current) and remembered.
+int static_scratch(void **out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail(SNNB_ERR_CUDA, "stem7x7_lif_static: cudaGetDevice: %s", cudaGetErrorString(e));
+  if (dev < 0 || dev >= kMaxDevices) return fail(SNNB_ERR_UNSUPPORTED, "stem7x7_lif_static: device index %d out of range", dev);
+  std::lock_guard<std::mutex> lock(g_static_mu);
+  if (g_static_ptr[dev] == nullptr) {
+    void *p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_stem_static_scratch);
+    if (e != cudaSuccess || p == nullptr)
+      return fail(SNNB_ERR_CUDA, "stem7x7_lif_static: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+    g_static_ptr[dev] = p;
+  }
+  *out = g_static_ptr[dev];
+  return SNNB_OK;
+}
+
+}  // namespace
+}  // namespace snnb
+
+extern "C" int64_t snnb_stem7x7_static_scratch_bytes(void) { return SNNB_STEM_STATIC_SCRATCH_BYTES; }
+
+extern "C" int snnb_stem7x7_lif_static(const void *x_seq, int64_t x_t_stride, const void *w_packed, const void *b,
+                                       const void *v_init, void *spikes, void *v_out,
+                                       int T, int B, int H, int W, int Cout, int dtype, int spike_dtype, int v_dtype,
+                                       float v_th, float v_reset, float tau, void *stream) {
+  using namespace snnb;
+  SNNB_CHECK_ARG(T >= 1 && B >= 1 && H >= 2 && W >= 2, "stem7x7_lif_static: bad sizes");
+  const int frames = (x_t_stride == 0) ? 1 : T;
+  const int64_t need = snnb_stem7x7_scratch_bytes(frames * B, H, W);
+  if (need > (int64_t)SNNB_STEM_STATIC_SCRATCH_BYTES)
+    return fail(SNNB_ERR_UNSUPPORTED,
+                "stem7x7_lif_static: this call needs %lld bytes of scratch but the built-in array holds %lld; "
+                "use a smaller batch or snnb_stem7x7_lif with caller-provided scratch",
+                (long long)need, (long long)SNNB_STEM_STATIC_SCRATCH_BYTES);
+  void *scratch = nullptr;
+  const int rc = static_scratch(&scratch);
+  if (rc != SNNB_OK) return rc;
+  return snnb_stem7x7_lif(x_seq, x_t_stride, w_packed, b, v_init, spikes, v_out, scratch,
+                          (int64_t)SNNB_STEM_STATIC_SCRATCH_BYTES, T, B, H, W, Cout, dtype, spike_dtype, v_dtype,
+                          v_th, v_reset, tau, stream);
 }
