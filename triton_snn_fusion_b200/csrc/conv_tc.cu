@@ -25,93 +25,41 @@
 #include <type_traits>
 
 #include "conv.cuh"
+#include "tc_epilogue.cuh"
+#include "tmap.cuh"
 #include "umma.cuh"
 
 namespace snnb {
 
 static __device__ int g_tc_status = 0;
 
+#ifdef SNNB_TC_TRACE
+// Development aid (not part of normal builds): per-event SM cycle stamps of one CTA.
+static __device__ long long g_trace[8][512];
+#define SNNB_TRACE(row, idx) do { const unsigned i_ = (idx); if (blockIdx.x == 300 && i_ < 512) g_trace[row][i_] = clock64(); } while (0)
+#else
+#define SNNB_TRACE(row, idx) do { } while (0)
+#endif
+
 namespace {
 
 constexpr int kSlotBytes = 16384;  // one 128-row x 128-byte operand tile
 constexpr int kMaxSlots = 13;
 constexpr int kMaxBoxes = 32;
-constexpr int kEpiWarps = 8;               // two per TMEM lane quarter, splitting the columns
-constexpr int kProducerWarp = kEpiWarps;   // warp 8
-constexpr int kMmaWarp = kEpiWarps + 1;    // warp 9
-constexpr int kThreads = 32 * (kEpiWarps + 2);
+constexpr int kWSlots = 4;  // weight tiles in flight: a weight load takes longer than one K step of MMAs
+constexpr int kEpiWarps = 8;                      // two per TMEM lane quarter, splitting the columns
+constexpr int kAProducers = 4;                    // warps that issue activation-tile loads, round robin
+constexpr int kProducerWarp = kEpiWarps;          // first activation producer (warps 8..11)
+constexpr int kWProducerWarp = kEpiWarps + kAProducers;      // weight-tile producer (warp 12)
+constexpr int kMmaWarp = kEpiWarps + kAProducers + 1;        // MMA issuer (warp 13)
+constexpr int kThreads = 32 * (kEpiWarps + kAProducers + 2);
 
 struct TcGeom {
   int T, Tacc, B, Cin, Cout, Ho, Wo, KH, KW, stride, pad;
   int BN, BW, BH, nbox, WB, HB;
   long long total_boxes;
-  int n_tiles_n, kchunks, slots, lif, tmem_cols, has_res, w_slot_bytes;
+  int n_tiles_n, kchunks, slots, lif, tmem_cols, has_res, w_slot_bytes, nprod;
 };
-
-template <typename XT, typename ST, typename VT>
-struct EpiArgs {
-  const XT *bias;
-  const XT *res;
-  const VT *v_init;
-  ST *spikes;
-  VT *v_out;
-  uint32_t lane_base;   // TMEM address of this thread's lane, column 0 of accumulator 0
-  long long pix;        // flat output pixel index of this thread
-  long long frame_out;  // elements per output frame
-  int n0, c_begin, c_end;
-  bool valid;
-};
-
-// Epilogue of one thread: for each of its 16-channel groups, walk the T accumulators in order with
-// the membrane in registers. The TMEM load of step t+1 is in flight while step t is evaluated.
-template <typename XT, typename ST, typename VT, int MODE, bool HARD, bool LIFON>
-__device__ __forceinline__ void epilogue_cols(const EpiArgs<XT, ST, VT> &e, const TcGeom &g, const LifParams &p) {
-  const bool alias = (g.Tacc != g.T);
-  for (int c = e.c_begin; c < e.c_end; ++c) {
-    const int n = e.n0 + c * 16;
-    if (n >= g.Cout) break;
-    uint32_t nxt[16];
-    umma::tmem_ld_x16(e.lane_base + (uint32_t)(c * 16), nxt);
-    float bj[16];
-    if (e.bias != nullptr) {
-      load_pack<XT, 16>(e.bias + n, bj);
-    } else {
-#pragma unroll
-      for (int i = 0; i < 16; ++i) bj[i] = 0.f;
-    }
-    float v[16];
-#pragma unroll
-    for (int i = 0; i < 16; ++i) v[i] = 0.f;
-    const long long o0 = e.pix * g.Cout + n;
-    if (LIFON && e.v_init != nullptr && e.valid) load_pack<VT, 16>(e.v_init + o0, v);
-    for (int t = 0; t < g.T; ++t) {
-      float y[16];
-      umma::tmem_ld_wait();
-#pragma unroll
-      for (int i = 0; i < 16; ++i) y[i] = __uint_as_float(nxt[i]) + bj[i];
-      if (t + 1 < g.T && !alias) umma::tmem_ld_x16(e.lane_base + (uint32_t)((t + 1) * g.BN + c * 16), nxt);
-      if (e.valid) {
-        const long long o = (long long)t * e.frame_out + o0;
-        if (g.has_res) {
-          float rr[16];
-          load_pack<XT, 16>(e.res + o, rr);
-#pragma unroll
-          for (int i = 0; i < 16; ++i) y[i] += rr[i];
-        }
-        if constexpr (LIFON) {
-          float s[16];
-#pragma unroll
-          for (int i = 0; i < 16; ++i) s[i] = lif_step_t<MODE, HARD>(y[i], v[i], p);
-          store_pack<ST, 16, false>(e.spikes + o, s);
-        } else {
-          store_pack<XT, 16, false>(reinterpret_cast<XT *>(e.spikes) + o, y);
-        }
-      }
-    }
-    if (LIFON && e.valid) store_pack<VT, 16, false>(e.v_out + o0, v);
-  }
-  umma::tmem_ld_wait();
-}
 
 template <typename XT, typename ST, typename VT>
 __global__ void __launch_bounds__(kThreads)
@@ -121,7 +69,7 @@ conv_lif_tc_kernel(const __grid_constant__ CUtensorMap xmap0, const __grid_const
                    const XT *__restrict__ res, const VT *__restrict__ v_init, ST *__restrict__ spikes,
                    VT *__restrict__ v_out, const TcGeom g, const LifParams p) {
   extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t bars[2 * kMaxSlots + 5];
+  __shared__ __align__(8) uint64_t bars[2 * kMaxSlots + 1 + 2 * kWSlots];
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_s;
   __shared__ int box_w0[kMaxBoxes], box_h0[kMaxBoxes], box_b[kMaxBoxes];
@@ -136,10 +84,10 @@ conv_lif_tc_kernel(const __grid_constant__ CUtensorMap xmap0, const __grid_const
   auto empty_bar = [&](int s) { return bar_base + 8u * (uint32_t)(kMaxSlots + s); };
   const uint32_t acc_bar = bar_base + 8u * (uint32_t)(2 * kMaxSlots);
   auto wfull_bar = [&](int s) { return bar_base + 8u * (uint32_t)(2 * kMaxSlots + 1 + s); };
-  auto wempty_bar = [&](int s) { return bar_base + 8u * (uint32_t)(2 * kMaxSlots + 3 + s); };
-  // shared memory: two weight buffers (double-buffered over K steps), then the ring of activation tiles
+  auto wempty_bar = [&](int s) { return bar_base + 8u * (uint32_t)(2 * kMaxSlots + 1 + kWSlots + s); };
+  // shared memory: a ring of kWSlots weight tiles, then the ring of activation tiles
   const uint32_t w_base = smem_base;
-  const uint32_t a_base = smem_base + 2u * (uint32_t)g.w_slot_bytes;
+  const uint32_t a_base = smem_base + (uint32_t)kWSlots * (uint32_t)g.w_slot_bytes;
   volatile int *abort_flag = &abort_s;
 
   if (threadIdx.x == 0) {
@@ -149,7 +97,7 @@ conv_lif_tc_kernel(const __grid_constant__ CUtensorMap xmap0, const __grid_const
       umma::mbar_init(empty_bar(s), 1);
     }
     umma::mbar_init(acc_bar, 1);
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < kWSlots; ++s) {
       umma::mbar_init(wfull_bar(s), 1);
       umma::mbar_init(wempty_bar(s), 1);
     }
@@ -180,22 +128,41 @@ conv_lif_tc_kernel(const __grid_constant__ CUtensorMap xmap0, const __grid_const
   umma::tc_fence_after_sync();
   const uint32_t tmem_base = tmem_base_s;
 
+  if (threadIdx.x == 0) SNNB_TRACE(2, 0);
   const int ksteps = g.KH * g.KW * g.kchunks;
   const uint32_t box_bytes = (uint32_t)(g.BW * g.BH) * 128u;
 
-  if (warp == kProducerWarp) {
-    // ------------------------------------------------------------ TMA producer
-    int nvalid = 0;
-    for (int j = 0; j < g.nbox; ++j) nvalid += (box_b[j] >= 0);
-    const uint32_t a_bytes = (uint32_t)nvalid * box_bytes;
-    const uint32_t w_bytes = (uint32_t)g.BN * 128u;
+  if (warp >= kProducerWarp && warp < kProducerWarp + kAProducers) {
+    // -------------------------------------------------- TMA producers, activations
+    // Activation tiles are numbered n = kstep * Tacc + t; producer p issues tiles p, p + nprod, ... One
+    // warp needs several hundred cycles per tile (barrier wait, expect_tx, TMA issue are dependent
+    // long-latency steps), more than the MMAs of a tile take, so the issue work is spread over four
+    // warps. The loop carries no divisions and no shared-memory reads: ring position, phase and the
+    // (tap, slab, t) of the next tile advance incrementally, lane j keeps box j in registers.
+    const int p = warp - kProducerWarp;
+    const bool mine = lane < g.nbox && box_b[lane] >= 0;
+    const int my_w0 = mine ? box_w0[lane] : 0, my_h0 = mine ? box_h0[lane] : 0, my_b = mine ? box_b[lane] : 0;
+    const uint32_t my_off = (uint32_t)lane * box_bytes;
+    const uint32_t a_bytes = (uint32_t)__popc(__ballot_sync(0xffffffffu, mine)) * box_bytes;
     const CUtensorMap *xmaps[4] = {&xmap0, &xmap1, &xmap2, &xmap3};
-    uint32_t n = 0;
+    const int ntiles = ksteps * g.Tacc;
+    int t = 0, c0 = 0, kh = 0, kw = 0;          // state of tile n
+    uint32_t slot = 0, phase = 1;               // waiting on parity 1 of a fresh barrier passes at once
+    auto advance = [&](int steps) {
+      for (int i = 0; i < steps; ++i) {
+        if (++t == g.Tacc) {
+          t = 0;
+          if ((c0 += 64) == g.Cin) {
+            c0 = 0;
+            if (++kw == g.KW) { kw = 0; ++kh; }
+          }
+        }
+        if (++slot == (uint32_t)g.slots) { slot = 0; phase ^= 1u; }
+      }
+    };
+    advance(p);
     bool ok = true;
-    for (int ks = 0; ks < ksteps && ok; ++ks) {
-      const int tap = ks / g.kchunks;
-      const int c0 = (ks - tap * g.kchunks) * 64;
-      const int kh = tap / g.KW, kw = tap - kh * g.KW;
+    for (int n = p; n < ntiles && p < g.nprod; n += g.nprod) {
       int dh = kh - g.pad, dw = kw - g.pad, which = 0;
       if (g.stride == 2) {
         const int ph = dh & 1, pw = dw & 1;
@@ -203,61 +170,67 @@ conv_lif_tc_kernel(const __grid_constant__ CUtensorMap xmap0, const __grid_const
         dh = (dh - ph) / 2;
         dw = (dw - pw) / 2;
       }
-      const CUtensorMap *xm = xmaps[which];
-      {  // weights of this K step
-        const int ws = ks & 1;
-        ok = umma::mbar_wait(wempty_bar(ws), (((uint32_t)ks >> 1) & 1u) ^ 1u, abort_flag);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        if (lane == 0) {
-          umma::mbar_expect_tx(wfull_bar(ws), w_bytes);
-          umma::tma_load_2d(w_base + (uint32_t)ws * (uint32_t)g.w_slot_bytes, &wmap, wfull_bar(ws), ks * 64, n0);
-        }
+      if (lane == 0) {
+        ok = umma::mbar_wait(empty_bar(slot), phase, abort_flag);
+        if (ok) umma::mbar_expect_tx(full_bar(slot), a_bytes);
       }
-      for (int t = 0; t < g.Tacc; ++t) {
-        const int slot = (int)(n % (uint32_t)g.slots);
-        ok = umma::mbar_wait(empty_bar(slot), ((n / (uint32_t)g.slots) & 1u) ^ 1u, abort_flag);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        if (lane == 0) umma::mbar_expect_tx(full_bar(slot), a_bytes);
-        __syncwarp();
-        for (int j = lane; j < g.nbox; j += 32) {
-          if (box_b[j] >= 0)
-            umma::tma_load_5d(a_base + (uint32_t)slot * kSlotBytes + (uint32_t)j * box_bytes, xm, full_bar(slot),
-                              c0, box_w0[j] + dw, box_h0[j] + dh, box_b[j], t);
-        }
-        ++n;
+      ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+      if (!ok) break;
+      if (mine)
+        umma::tma_load_5d(a_base + slot * kSlotBytes + my_off, xmaps[which], full_bar(slot), c0, my_w0 + dw, my_h0 + dh,
+                          my_b, t);
+      advance(g.nprod);
+    }
+  } else if (warp == kWProducerWarp) {
+    // ------------------------------------------------------ TMA producer, weights
+    if (lane == 0) {
+      const uint32_t w_bytes = (uint32_t)g.BN * 128u;
+      uint32_t ws = 0, wphase = 1;
+      for (int ks = 0; ks < ksteps; ++ks) {
+        if (!umma::mbar_wait(wempty_bar(ws), wphase, abort_flag)) break;
+        umma::mbar_expect_tx(wfull_bar(ws), w_bytes);
+        umma::tma_load_2d(w_base + ws * (uint32_t)g.w_slot_bytes, &wmap, wfull_bar(ws), ks * 64, n0);
+        if (++ws == (uint32_t)kWSlots) { ws = 0; wphase ^= 1u; }
       }
     }
+    __syncwarp();
   } else if (warp == kMmaWarp) {
     // -------------------------------------------------------------- MMA issuer
     if (lane == 0) {
-      const uint32_t idesc = umma::make_idesc_f16(128, g.BN, sizeof(XT) == 2 && std::is_same<XT, __nv_bfloat16>::value);
-      uint32_t n = 0;
+      const uint32_t idesc = umma::make_idesc_f16(128, g.BN, std::is_same<XT, __nv_bfloat16>::value);
+      const uint64_t adesc0 = umma::make_sw128_kmajor_desc(a_base);
+      const uint64_t bdesc0 = umma::make_sw128_kmajor_desc(w_base);
+      uint32_t slot = 0, phase = 0, ws = 0, wphase = 0;
       bool ok = true;
       for (int ks = 0; ks < ksteps && ok; ++ks) {
-        const int ws = ks & 1;
-        ok = umma::mbar_wait(wfull_bar(ws), ((uint32_t)ks >> 1) & 1u, abort_flag);
+        ok = umma::mbar_wait(wfull_bar(ws), wphase, abort_flag);
         if (!ok) break;
-        const uint64_t bdesc = umma::make_sw128_kmajor_desc(w_base + (uint32_t)ws * (uint32_t)g.w_slot_bytes);
+        const uint64_t bdesc = bdesc0 + (uint64_t)((ws * (uint32_t)g.w_slot_bytes) >> 4);
         for (int t = 0; t < g.Tacc; ++t) {
-          const int aslot = (int)(n % (uint32_t)g.slots);
-          ok = umma::mbar_wait(full_bar(aslot), (n / (uint32_t)g.slots) & 1u, abort_flag);
+          ok = umma::mbar_wait(full_bar(slot), phase, abort_flag);
           if (!ok) break;
           umma::tc_fence_after_sync();
-          const uint64_t adesc = umma::make_sw128_kmajor_desc(a_base + (uint32_t)aslot * kSlotBytes);
+          const uint64_t adesc = adesc0 + (uint64_t)((slot * kSlotBytes) >> 4);
           const uint32_t d = tmem_base + (uint32_t)(t * g.BN);
 #pragma unroll
           for (int k = 0; k < 4; ++k)  // 4 x K=16 per 64-channel slab: +32 bytes along the swizzled row
             umma::mma_f16_ss(d, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc, (ks > 0 || k > 0) ? 1u : 0u);
-          umma::mma_commit(empty_bar(aslot));
-          ++n;
+          umma::mma_commit(empty_bar(slot));
+          if (++slot == (uint32_t)g.slots) { slot = 0; phase ^= 1u; }
         }
         if (ok) umma::mma_commit(wempty_bar(ws));
+        if (++ws == (uint32_t)kWSlots) { ws = 0; wphase ^= 1u; }
       }
-      if (ok) umma::mma_commit(acc_bar);
+      if (ok) {
+        umma::mma_commit(acc_bar);
+        umma::mbar_wait(acc_bar, 0u, abort_flag);  // the accumulators are complete
+      }
     }
     __syncwarp();
+    // Wake the epilogue warps. They sleep on a hardware named barrier instead of polling the
+    // mbarrier: polling warps share issue slots with this warp and the producer and slow them down.
+    umma::tc_fence_before_sync();
+    asm volatile("bar.arrive 1, %0;" ::"r"(32 * (kEpiWarps + 1)) : "memory");
   } else {
     // ---------------------------------------------------------------- epilogue
     const int quarter = warp & 3;          // TMEM lanes 32*quarter .. +31 are the ones this warp may read
@@ -275,9 +248,10 @@ conv_lif_tc_kernel(const __grid_constant__ CUtensorMap xmap0, const __grid_const
       valid = (ho < g.Ho) && (wo < g.Wo);
       pix = (b * g.Ho + ho) * g.Wo + wo;
     }
-    bool ok = umma::mbar_wait(acc_bar, 0u, abort_flag);
-    ok = __all_sync(0xffffffffu, ok);
+    asm volatile("bar.sync 1, %0;" ::"r"(32 * (kEpiWarps + 1)) : "memory");  // released by the MMA warp
+    const bool ok = (*abort_flag == 0);
     umma::tc_fence_after_sync();
+    if (threadIdx.x == 0) SNNB_TRACE(2, 1);
     if (ok) {
       // the two warps of a lane quarter split the 16-column groups of the tile
       const int nch = g.BN / 16, half = (nch + 1) / 2;
@@ -285,24 +259,16 @@ conv_lif_tc_kernel(const __grid_constant__ CUtensorMap xmap0, const __grid_const
       const int c_end = (warp < 4) ? half : nch;
       EpiArgs<XT, ST, VT> ea{bias, res, v_init, spikes, v_out, tmem_base + ((uint32_t)(quarter * 32) << 16),
                              pix, (long long)g.B * g.Ho * g.Wo * g.Cout, n0, c_begin, c_end, valid};
-      if (!g.lif) {
-        epilogue_cols<XT, ST, VT, 0, true, false>(ea, g, p);
-      } else {
-        switch (p.mode * 2 + p.hard) {
-          case 0: epilogue_cols<XT, ST, VT, 0, false, true>(ea, g, p); break;
-          case 1: epilogue_cols<XT, ST, VT, 0, true, true>(ea, g, p); break;
-          case 2: epilogue_cols<XT, ST, VT, 1, false, true>(ea, g, p); break;
-          case 3: epilogue_cols<XT, ST, VT, 1, true, true>(ea, g, p); break;
-          case 4: epilogue_cols<XT, ST, VT, 2, false, true>(ea, g, p); break;
-          default: epilogue_cols<XT, ST, VT, 2, true, true>(ea, g, p); break;
-        }
-      }
+      const EpiGeom eg{g.T, g.Tacc, g.BN, g.Cout, g.has_res};
+      epilogue_dispatch<XT, ST, VT>(ea, eg, g.lif, p);
     }
   }
 
   // ------------------------------------------------------------------ teardown
+  if (threadIdx.x == 0) SNNB_TRACE(2, 2);
   umma::tc_fence_before_sync();
   __syncthreads();
+  if (threadIdx.x == 0) SNNB_TRACE(2, 3);
   if (abort_s && threadIdx.x == 0) atomicExch(&g_tc_status, 1);
   if (warp == kMmaWarp) {
     umma::tc_fence_after_sync();
@@ -311,35 +277,6 @@ conv_lif_tc_kernel(const __grid_constant__ CUtensorMap xmap0, const __grid_const
 }
 
 // ------------------------------------------------------------------- host ----
-using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
-                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
-                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = [] {
-    void *p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
-        q != cudaDriverEntryPointSuccess)
-      p = nullptr;
-    return reinterpret_cast<EncodeTiledFn>(p);
-  }();
-  return fn;
-}
-
-int encode(CUtensorMap *m, int dtype, int rank, const void *base, const cuuint64_t *dims, const cuuint64_t *strides,
-           const cuuint32_t *box) {
-  EncodeTiledFn fn = encode_fn();
-  if (!fn) return fail(SNNB_ERR_CUDA, "conv_lif: cuTensorMapEncodeTiled is not available from the driver");
-  cuuint32_t ones[5] = {1, 1, 1, 1, 1};
-  const CUresult r = fn(m, dtype == SNNB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
-                        (cuuint32_t)rank, const_cast<void *>(base), dims, strides, box, ones,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return fail(SNNB_ERR_CUDA, "conv_lif: cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
-  return SNNB_OK;
-}
-
 // Output-pixel tile = nbox boxes of BW x BH pixels (<= 128 pixels). Picks the geometry that wastes the
 // fewest MMA rows (partial boxes at image edges + unfilled tile rows), mildly preferring fewer boxes.
 void choose_boxes(int Ho, int Wo, int &BW, int &BH, int &nbox) {
@@ -360,8 +297,10 @@ void choose_boxes(int Ho, int Wo, int &BW, int &BH, int &nbox) {
   }
 }
 
+// Output-channel tile: as wide as the T accumulators allow in the 512 TMEM columns (a wider tile
+// re-reads the activations fewer times), at most 256.
 int pick_bn(int Cout, int Tacc) {
-  int bn = Cout >= 128 ? 128 : ((Cout + 15) / 16) * 16;
+  int bn = Cout >= 256 ? 256 : (Cout >= 128 ? 128 : ((Cout + 15) / 16) * 16);
   while (bn > 16 && Tacc * bn > 512) bn /= 2;
   return bn;
 }
@@ -385,12 +324,21 @@ int launch(const ConvArgs &a, cudaStream_t stream) {
   int cols = 32;
   while (cols < g.Tacc * g.BN) cols *= 2;
   g.tmem_cols = cols;
-  // Shared memory: two weight buffers + a ring of 16 KB activation tiles. With <= 256 TMEM columns two
+  // Shared memory: kWSlots weight tiles + a ring of 16 KB activation tiles. With <= 256 TMEM columns two
   // CTAs can share an SM (one's epilogue overlaps the other's MMAs), so each takes half the budget.
   g.w_slot_bytes = ((g.BN * 128 + 1023) / 1024) * 1024;
-  const int budget = (cols <= 256 ? 112 : 208) * 1024;
-  g.slots = (budget - 2 * g.w_slot_bytes) / kSlotBytes;
+  int budget = (cols <= 256 ? 112 : 208) * 1024;
+  g.slots = (budget - kWSlots * g.w_slot_bytes) / kSlotBytes;
+  if (g.slots < kAProducers + 2) {  // too shallow to share an SM: take the whole SM instead
+    budget = 208 * 1024;
+    g.slots = (budget - kWSlots * g.w_slot_bytes) / kSlotBytes;
+  }
   if (g.slots > kMaxSlots) g.slots = kMaxSlots;
+  // A producer only waits on the ring slots of its own tiles, and an mbarrier wait tells phases
+  // apart by parity alone. That is sound while no producer can run two laps ahead of the MMA
+  // warp, which holds when the ring has more slots than there are producers.
+  g.nprod = g.slots - 1 < kAProducers ? g.slots - 1 : kAProducers;
+  if (g.nprod < 1) return fail(SNNB_ERR_UNSUPPORTED, "conv_lif: not enough shared memory for the operand ring");
   const long long m_tiles = (g.total_boxes + g.nbox - 1) / g.nbox;
   const long long grid = m_tiles * g.n_tiles_n;
   if (grid > 0x7fffffffLL) return fail(SNNB_ERR_INVALID, "conv_lif: problem too large for the grid");
@@ -414,7 +362,7 @@ int launch(const ConvArgs &a, cudaStream_t stream) {
                              g.Tacc > 1 ? (cuuint64_t)a.x_t_stride * es : frame_bytes};
     cuuint32_t box[5] = {64, (cuuint32_t)g.BW, (cuuint32_t)g.BH, 1, 1};
     const char *base = static_cast<const char *>(a.x) + ((size_t)ph * xs_h + (size_t)pw * xs_w) * es;
-    const int rc = encode(&xm[q], a.dtype, 5, base, dims, strides, box);
+    const int rc = encode_tmap(&xm[q], a.dtype, 5, base, dims, strides, box);
     if (rc != SNNB_OK) return rc;
   }
   {
@@ -422,10 +370,10 @@ int launch(const ConvArgs &a, cudaStream_t stream) {
     cuuint64_t dims[2] = {K, (cuuint64_t)a.Cout};
     cuuint64_t strides[1] = {K * es};
     cuuint32_t box[2] = {64, (cuuint32_t)g.BN};
-    const int rc = encode(&wm, a.dtype, 2, a.w, dims, strides, box);
+    const int rc = encode_tmap(&wm, a.dtype, 2, a.w, dims, strides, box);
     if (rc != SNNB_OK) return rc;
   }
-  const size_t smem = (size_t)g.slots * kSlotBytes + 2 * (size_t)g.w_slot_bytes + 1024;
+  const size_t smem = (size_t)g.slots * kSlotBytes + kWSlots * (size_t)g.w_slot_bytes + 1024;
   auto kern = conv_lif_tc_kernel<XT, ST, VT>;
   {  // per device and per kernel; cheap enough to repeat on every launch
     const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -491,3 +439,10 @@ extern "C" int snnb_device_status(int *status_out) {
   *status_out = h;
   return SNNB_OK;
 }
+
+#ifdef SNNB_TC_TRACE
+extern "C" int snnb_debug_read_trace(long long *host_buf) {
+  cudaDeviceSynchronize();
+  return (int)cudaMemcpyFromSymbol(host_buf, snnb::g_trace, sizeof(long long) * 8 * 512);
+}
+#endif

@@ -39,9 +39,15 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 __device__ __forceinline__ void fence_mbar_init() {
   asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 }
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
+// One try; the hardware may suspend the thread for a short, implementation-defined time before it
+// reports "not yet". (An explicit long suspend-time hint was measured to be slower here: a thread
+// parked that way wakes up late after the phase completes.)
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
@@ -56,10 +62,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Bounded wait: polls the barrier; gives up after `limit_cycles` SM clock cycles (about two seconds)
-// and reports false. `abort_flag` (shared memory) short-circuits every later wait of the CTA once
-// one gave up. The SM cycle counter is used because reading it costs a few cycles; the global
-// nanosecond timer is far slower to read and would sit on the critical path of every wait.
+// Bounded wait: gives up after `limit_cycles` SM clock cycles (about two seconds) and reports
+// false. `abort_flag` (shared memory) short-circuits every later wait of the CTA once one gave up.
+// The SM cycle counter is used because reading it costs a few cycles.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag,
                                           long long limit_cycles = 4000000000ll) {
   if (mbar_try_wait(bar, parity)) return true;
@@ -68,7 +73,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   uint32_t spins = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((++spins & 255u) == 0) {
+    if ((++spins & 63u) == 0) {
       if (*abort_flag) return false;
       if (clock64() - t0 > limit_cycles) {
         *abort_flag = 1;
