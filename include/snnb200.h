@@ -45,10 +45,17 @@ extern "C" {
 typedef enum snnb_dtype { SNNB_F32 = 0, SNNB_BF16 = 1, SNNB_F16 = 2, SNNB_U8 = 3 } snnb_dtype;
 typedef enum snnb_layout { SNNB_NCHW = 0, SNNB_NHWC = 1 } snnb_layout;
 
-/* Which conv / linear implementation to use. AUTO picks the tcgen05 path when
+/* Which conv / linear implementation to use. AUTO picks a tcgen05 kernel when
  * the shape qualifies (16-bit activations, Cin a multiple of 64, see
- * snnb_conv_lif) and the CUDA-core path otherwise. */
-typedef enum snnb_path { SNNB_PATH_AUTO = 0, SNNB_PATH_SIMT = 1, SNNB_PATH_TCGEN05 = 2 } snnb_path;
+ * snnb_conv_lif) and the CUDA-core path otherwise. TCGEN05 insists on a tensor-core
+ * kernel (error if none applies). Among the tensor-core kernels, 3x3 / stride 1 /
+ * padding 1 convs prefer the timestep-pair kernel (T = 1, 2, 4; weights as the M
+ * operand, 256 pixels as N), then the shared-memory halo kernel; TCGEN05_HALO skips
+ * the first, TCGEN05_TAPS forces the general one-load-per-tap kernel (for comparison). */
+typedef enum snnb_path {
+  SNNB_PATH_AUTO = 0, SNNB_PATH_SIMT = 1, SNNB_PATH_TCGEN05 = 2, SNNB_PATH_TCGEN05_TAPS = 3,
+  SNNB_PATH_TCGEN05_HALO = 4
+} snnb_path;
 
 /* Library version (major*10000 + minor*100 + patch). */
 int snnb_version(void);
@@ -125,9 +132,9 @@ int snnb_dwconv3x3_lif(const void *x_seq, int64_t x_t_stride, const void *w, con
  * `lif` = 0 turns the LIF off: `spikes` then receives conv + bias (+ residual)
  * in the activation dtype for every t and v_init / v_out are ignored (used for
  * the BN-folded shortcut convs that feed a residual input).
- * path: SNNB_PATH_TCGEN05 needs dtype bf16/f16, Cin % 64 == 0, Cout % 16 == 0,
- * (KH,KW,stride,pad) in {(1,1,1|2,0), (3,3,1|2,1)} and T*min(Cout,128)-column
- * accumulators that fit TMEM (T <= 16); anything else runs on SNNB_PATH_SIMT.
+ * path: the tensor-core kernels need dtype bf16/f16, Cin % 64 == 0, Cout % 16 == 0,
+ * stride 1 or 2, kernel at most 11x11 and T accumulators that fit the 512 TMEM
+ * columns (T <= 32); anything else runs on SNNB_PATH_SIMT.
  */
 int snnb_conv_lif(const void *x_seq, int64_t x_t_stride, const void *w, const void *b,
                   const void *residual, const void *v_init, void *spikes, void *v_out,

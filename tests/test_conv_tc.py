@@ -13,11 +13,14 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda"
 
 
-@pytest.fixture(autouse=True)
-def _force_tc_path():
+@pytest.fixture(autouse=True, params=["tcgen05", "tcgen05_halo", "tcgen05_taps"])
+def _force_tc_path(request):
+    """Every case runs with the preferred tensor-core kernel for its shape (3x3/s1 convs with T in {1,2,4}
+    take the timestep-pair kernel), with the halo kernel forced where it applies, and with the general
+    one-load-per-tap kernel forced."""
     from triton_snn_fusion_b200 import _lib
     from triton_snn_fusion_b200.runtime import triton_convlif_backend as be
-    prev = be.set_conv_path("tcgen05")
+    prev = be.set_conv_path(request.param)
     yield
     be.set_conv_path(prev)
     assert _lib.device_status() == 0, "a bounded wait inside the tcgen05 kernel gave up"

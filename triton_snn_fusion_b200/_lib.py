@@ -16,7 +16,7 @@ LIB_PATH = Path(__file__).resolve().parent / "libsnnb200.so"
 SNNB_OK = 0
 F32, BF16, F16, U8 = 0, 1, 2, 3
 NCHW, NHWC = 0, 1
-PATH_AUTO, PATH_SIMT, PATH_TCGEN05 = 0, 1, 2
+PATH_AUTO, PATH_SIMT, PATH_TCGEN05, PATH_TCGEN05_TAPS, PATH_TCGEN05_HALO = 0, 1, 2, 3, 4
 
 _DTYPE_CODE = {torch.float32: F32, torch.bfloat16: BF16, torch.float16: F16, torch.uint8: U8}
 

@@ -31,4 +31,17 @@ int conv_lif_simt(const ConvArgs &a, cudaStream_t stream);
 bool conv_lif_tc_supported(const ConvArgs &a, const char **why);
 int conv_lif_tc(const ConvArgs &a, cudaStream_t stream);
 
+// tcgen05 implicit GEMM for 3x3 / stride 1 / padding 1 that reads all nine taps from one
+// shared-memory halo tile (far less L2 traffic than conv_lif_tc). Preferred when supported.
+bool conv3x3_halo_supported(const ConvArgs &a);
+int conv3x3_halo(const ConvArgs &a, cudaStream_t stream);
+int halo_device_status(int *out);
+
+// tcgen05 implicit GEMM for 3x3 / stride 1 / padding 1, T in {1, 2, 4}: weights as the M operand and
+// the pixels of two timesteps as a 256-wide N operand (the only shape that runs the tensor pipe at
+// its full rate), halo tiles in shared memory. Preferred over conv3x3_halo when supported.
+bool conv3x3_pair_supported(const ConvArgs &a);
+int conv3x3_pair(const ConvArgs &a, cudaStream_t stream);
+int pair_device_status(int *out);
+
 }  // namespace snnb

@@ -6,14 +6,16 @@ namespace snnb {
 namespace {
 
 int run(const ConvArgs &a, int path, cudaStream_t stream, const char *what) {
+  if (path == SNNB_PATH_SIMT) return conv_lif_simt(a, stream);
+  const bool taps_only = path == SNNB_PATH_TCGEN05_TAPS;
+  // The pair kernel always multiplies a 128-channel weight tile, so with Cout <= 64 half of its MMA
+  // rows are padding and the halo kernel is faster.
+  if (!taps_only && path != SNNB_PATH_TCGEN05_HALO && a.Cout > 64 && conv3x3_pair_supported(a)) return conv3x3_pair(a, stream);
+  if (!taps_only && conv3x3_halo_supported(a)) return conv3x3_halo(a, stream);
   const char *why = "";
-  const bool tc_ok = conv_lif_tc_supported(a, &why);
-  if (path == SNNB_PATH_TCGEN05) {
-    if (!tc_ok) return fail(SNNB_ERR_UNSUPPORTED, "%s: tcgen05 path not available for this call: %s", what, why);
-    return conv_lif_tc(a, stream);
-  }
-  if (path == SNNB_PATH_AUTO && tc_ok) return conv_lif_tc(a, stream);
-  return conv_lif_simt(a, stream);
+  if (conv_lif_tc_supported(a, &why)) return conv_lif_tc(a, stream);
+  if (path == SNNB_PATH_AUTO) return conv_lif_simt(a, stream);
+  return fail(SNNB_ERR_UNSUPPORTED, "%s: tcgen05 path not available for this call: %s", what, why);
 }
 
 }  // namespace
@@ -32,7 +34,7 @@ extern "C" int snnb_conv_lif(const void *x_seq, int64_t x_t_stride, const void *
   SNNB_CHECK_ARG(is_act_dtype(dtype), "conv_lif: unsupported dtype %d", dtype);
   SNNB_CHECK_ARG(!lif || spike_dtype == dtype || spike_dtype == SNNB_U8, "conv_lif: spike dtype must be the x dtype or u8");
   SNNB_CHECK_ARG(!lif || v_dtype == dtype || v_dtype == SNNB_F32, "conv_lif: v dtype must be the x dtype or f32");
-  SNNB_CHECK_ARG(path >= SNNB_PATH_AUTO && path <= SNNB_PATH_TCGEN05, "conv_lif: bad path %d", path);
+  SNNB_CHECK_ARG(path >= SNNB_PATH_AUTO && path <= SNNB_PATH_TCGEN05_HALO, "conv_lif: bad path %d", path);
   SNNB_CHECK_ARG(x_t_stride >= 0, "conv_lif: negative frame stride");
   SNNB_CHECK_ARG(!lif || tau != 0.0f, "conv_lif: unsupported_tau: tau must be nonzero");
   const int Ho = (H + 2 * pad - KH) / stride + 1;
@@ -59,7 +61,7 @@ extern "C" int snnb_linear_lif(const void *x_seq, int64_t x_t_stride, const void
   SNNB_CHECK_ARG(is_act_dtype(dtype), "linear_lif: unsupported dtype %d", dtype);
   SNNB_CHECK_ARG(spike_dtype == dtype || spike_dtype == SNNB_U8, "linear_lif: spike dtype must be the x dtype or u8");
   SNNB_CHECK_ARG(v_dtype == dtype || v_dtype == SNNB_F32, "linear_lif: v dtype must be the x dtype or f32");
-  SNNB_CHECK_ARG(path >= SNNB_PATH_AUTO && path <= SNNB_PATH_TCGEN05, "linear_lif: bad path %d", path);
+  SNNB_CHECK_ARG(path >= SNNB_PATH_AUTO && path <= SNNB_PATH_TCGEN05_HALO, "linear_lif: bad path %d", path);
   SNNB_CHECK_ARG(x_t_stride >= 0, "linear_lif: negative frame stride");
   SNNB_CHECK_ARG(tau != 0.0f, "linear_lif: unsupported_tau: tau must be nonzero");
   // A linear layer over [M][K] rows is a 1x1 convolution over one [1][M] frame with K channels.

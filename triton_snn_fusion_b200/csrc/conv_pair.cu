@@ -1,0 +1,390 @@
+// 3x3 / stride 1 / padding 1 conv (+ bias, + residual) + LIF over T <= 4 with the operand roles
+// swapped so that one tcgen05.mma covers 256 output pixels.
+//
+// Measured on B200: a tcgen05.mma (cta_group::1, K = 16) occupies the tensor pipe for ~128 cycles
+// whether its N is 64, 128 or 256, so only N = 256 instructions reach the pipe's rate. With output
+// pixels as the M dimension (conv_tc.cu, conv_halo.cu) N is the channel tile and T accumulators of
+// 256 columns do not fit the 512 TMEM columns. Here the weight tile is the M operand (128 output
+// channels, rows beyond Cout are zero) and the pixels of TWO consecutive timesteps are the N operand:
+//
+//   D_pair[cout][tq * 128 + pixel] = sum_(tap, slab)  W[cout][tap, slab] . X_(2*pair+tq)[pixel + tap][slab]^T
+//
+// A CTA owns 8 (wide) x 14 (high) output pixels. Per 64-channel slab and timestep it keeps the
+// 10 x 16 input pixels those need (a 20 KB halo tile; out-of-image pixels arrive as zeros = padding);
+// the halo tiles of a timestep pair are adjacent in shared memory, so a K-major operand descriptor
+// with its start shifted by (kh * 10 + kw) rows and 8-row groups one halo row (1280 bytes) apart
+// addresses 32 groups = 16 output rows x 8 pixels for each of the two timesteps (rows 14, 15 of each
+// are junk and never stored). All nine taps are read from that one copy.
+//
+// Timestep pairs are processed one after the other: pair 0 (t = 0, 1) is accumulated over all slabs
+// and taps into TMEM columns 0..255, then pair 1 into 256..511. The epilogue warps convert pair 0
+// (bias, residual, LIF steps 0 and 1, spikes out) while the MMA warp works on pair 1, keep the membrane
+// potentials in registers, and finish with pair 1. TMEM lane = output channel, so a thread owns one
+// channel of 64 pixels and a warp's stores cover 32 consecutive channels of one pixel.
+#include <type_traits>
+
+#include "conv.cuh"
+#include "tmap.cuh"
+#include "umma.cuh"
+
+namespace snnb {
+
+static __device__ int g_pair_status = 0;
+
+#ifdef SNNB_TC_TRACE
+static __device__ long long g_ptrace[64];
+#define PTRACE(idx) do { if (blockIdx.x == 300) g_ptrace[idx] = clock64(); } while (0)
+#else
+#define PTRACE(idx) do { } while (0)
+#endif
+
+namespace {
+
+constexpr int kPW = 10, kPH = 16;                      // halo tile: 10 x 16 pixels
+constexpr int kRowBytes = kPW * 128;                   // 1280
+constexpr int kHaloT = kPW * kPH * 128;                // 20480 bytes per timestep
+constexpr int kTileRows = 14;                          // valid output rows per tile
+constexpr int kPairRing = 4;                           // halo (pair) slots
+constexpr int kWRingP = 3;                             // weight-tile slots (16 KB each)
+constexpr int kWSlot = 128 * 128;
+constexpr int kEpiW = 8;
+constexpr int kHaloWarpP = kEpiW, kWWarpP = kEpiW + 1, kMmaWarpP = kEpiW + 2;
+constexpr int kThreadsP = 32 * (kEpiW + 3);
+
+struct PairGeom {
+  int T, Tacc, B, Cin, Cout, Ho, Wo;
+  int kslabs, npairs, tq;   // tq = timesteps per pair (1 or 2)
+  int n_tiles_n, row_tiles, w_strips;
+  int tmem_cols, lif, has_res;
+};
+
+// LIF flavours compiled into the epilogue: the common one (tau a power of two, hard reset) with its
+// branches resolved at compile time, every other kind through the run-time lif_step, or no LIF.
+enum : int { kLifFast = 0, kLifAny = 1, kLifOff = 2 };
+
+// Converts one timestep pair for the 64 pixels of this thread's channel: TMEM -> + bias (+ residual)
+// -> LIF (membrane in v[]) -> spikes.
+template <typename XT, typename ST, int KIND>
+__device__ __forceinline__ void pair_epilogue(const PairGeom &g, const LifParams &p, int pair, uint32_t tmem_lane_base,
+                                              int col_begin, int c, bool c_ok, float bias_c, const XT *__restrict__ res,
+                                              ST *__restrict__ spikes, long long frame_out, long long img_base, int h0,
+                                              int w0, float (&v)[64]) {
+  const int t0 = pair * g.tq;
+#pragma unroll
+  for (int chunk = 0; chunk < 4; ++chunk) {
+    const int px0 = col_begin + chunk * 16;
+    uint32_t a0[16], a1[16];
+    umma::tmem_ld_x16(tmem_lane_base + (uint32_t)(pair * 256 + px0), a0);
+    if (g.tq == 2) umma::tmem_ld_x16(tmem_lane_base + (uint32_t)(pair * 256 + 128 + px0), a1);
+    umma::tmem_ld_wait();
+    // the 16 pixels of a chunk are two full tile rows: rows (px0 >> 3) and (px0 >> 3) + 1
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const int row = (px0 >> 3) + (i >> 3);
+      const int ho = h0 + row, wo = w0 + (i & 7);
+      const bool ok = c_ok && row < kTileRows && ho < g.Ho && wo < g.Wo;
+      const long long o = (long long)t0 * frame_out + img_base + ((long long)ho * g.Wo + wo) * g.Cout + c;
+      float y0 = __uint_as_float(a0[i]) + bias_c;
+      float y1 = __uint_as_float(a1[i]) + bias_c;
+      if (ok) {
+        if (g.has_res) {
+          y0 += DT<XT>::to_f(res[o]);
+          if (g.tq == 2) y1 += DT<XT>::to_f(res[o + frame_out]);
+        }
+        if constexpr (KIND == kLifOff) {
+          reinterpret_cast<XT *>(spikes)[o] = DT<XT>::from_f(y0);
+          if (g.tq == 2) reinterpret_cast<XT *>(spikes)[o + frame_out] = DT<XT>::from_f(y1);
+        } else {
+          float &vv = v[chunk * 16 + i];
+          const float s0 = (KIND == kLifFast) ? lif_step_t<1, true>(y0, vv, p) : lif_step(y0, vv, p);
+          spikes[o] = DT<ST>::from_f(s0);
+          if (g.tq == 2) {
+            const float s1 = (KIND == kLifFast) ? lif_step_t<1, true>(y1, vv, p) : lif_step(y1, vv, p);
+            spikes[o + frame_out] = DT<ST>::from_f(s1);
+          }
+        }
+      }
+    }
+  }
+}
+
+template <typename XT, typename ST, typename VT>
+__global__ void __launch_bounds__(kThreadsP)
+conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap,
+                    const XT *__restrict__ bias, const XT *__restrict__ res, const VT *__restrict__ v_init,
+                    ST *__restrict__ spikes, VT *__restrict__ v_out, const PairGeom g, const LifParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bars[2 * kPairRing + 2 * kWRingP + 2];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int abort_s;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_tile = blockIdx.x % g.n_tiles_n;
+  int m = blockIdx.x / g.n_tiles_n;
+  const int strip = m % g.w_strips;
+  m /= g.w_strips;
+  const int rt = m % g.row_tiles;
+  const int b = m / g.row_tiles;
+  const int n0 = n_tile * 128, w0 = strip * 8, h0 = rt * kTileRows;
+
+  const uint32_t smem_base = (umma::smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t w_base = smem_base;
+  const uint32_t h_base = smem_base + (uint32_t)(kWRingP * kWSlot);
+  const uint32_t slot_bytes = (uint32_t)(g.tq * kHaloT);
+  const uint32_t bar_base = umma::smem_u32(bars);
+  auto hfull = [&](uint32_t s) { return bar_base + 8u * s; };
+  auto hempty = [&](uint32_t s) { return bar_base + 8u * ((uint32_t)kPairRing + s); };
+  auto wfull = [&](uint32_t s) { return bar_base + 8u * (2u * kPairRing + s); };
+  auto wempty = [&](uint32_t s) { return bar_base + 8u * (2u * kPairRing + kWRingP + s); };
+  auto accfull = [&](uint32_t s) { return bar_base + 8u * (2u * kPairRing + 2u * kWRingP + s); };
+  volatile int *abort_flag = &abort_s;
+
+  if (threadIdx.x == 0) {
+    abort_s = 0;
+    for (int s = 0; s < kPairRing; ++s) { umma::mbar_init(hfull(s), 1); umma::mbar_init(hempty(s), 1); }
+    for (int s = 0; s < kWRingP; ++s) { umma::mbar_init(wfull(s), 1); umma::mbar_init(wempty(s), 1); }
+    umma::mbar_init(accfull(0), 1);
+    umma::mbar_init(accfull(1), 1);
+    umma::fence_mbar_init();
+  }
+  if (warp == kMmaWarpP) {
+    umma::tmem_alloc(umma::smem_u32(&tmem_base_s), (uint32_t)g.tmem_cols);
+    umma::tmem_relinquish();
+  }
+  if (warp == kHaloWarpP && lane == 0) {
+    umma::prefetch_tensormap(&xmap);
+    umma::prefetch_tensormap(&wmap);
+  }
+  umma::tc_fence_before_sync();
+  __syncthreads();
+  umma::tc_fence_after_sync();
+  const uint32_t tmem_base = tmem_base_s;
+  if (threadIdx.x == 0) PTRACE(0);
+
+  if (warp == kHaloWarpP) {
+    // ------------------------------------------------- halo producer: lane q loads timestep q of the pair
+    uint32_t slot = 0, phase = 1;
+    bool ok = true;
+    for (int pair = 0; pair < g.npairs && ok; ++pair) {
+      for (int slab = 0; slab < g.kslabs; ++slab) {
+        if (lane == 0) {
+          ok = umma::mbar_wait(hempty(slot), phase, abort_flag);
+          if (ok) umma::mbar_expect_tx(hfull(slot), slot_bytes);
+        }
+        ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+        if (!ok) break;
+        if (lane < g.tq)
+          umma::tma_load_5d(h_base + slot * slot_bytes + (uint32_t)lane * kHaloT, &xmap, hfull(slot), slab * 64, w0 - 1,
+                            h0 - 1, b, pair * g.tq + lane);
+        if (++slot == (uint32_t)kPairRing) { slot = 0; phase ^= 1u; }
+      }
+    }
+  } else if (warp == kWWarpP) {
+    // ---------------------------------------------------------- weight producer
+    if (lane == 0) {
+      uint32_t ws = 0, wphase = 1;
+      bool ok = true;
+      for (int pair = 0; pair < g.npairs && ok; ++pair)
+        for (int slab = 0; slab < g.kslabs && ok; ++slab)
+          for (int tap = 0; tap < 9; ++tap) {
+            ok = umma::mbar_wait(wempty(ws), wphase, abort_flag);
+            if (!ok) break;
+            umma::mbar_expect_tx(wfull(ws), (uint32_t)kWSlot);
+            umma::tma_load_2d(w_base + ws * (uint32_t)kWSlot, &wmap, wfull(ws), tap * g.Cin + slab * 64, n0);
+            if (++ws == (uint32_t)kWRingP) { ws = 0; wphase ^= 1u; }
+          }
+    }
+    __syncwarp();
+  } else if (warp == kMmaWarpP) {
+    // -------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = umma::make_idesc_f16(128, 128 * g.tq, std::is_same<XT, __nv_bfloat16>::value);
+      uint64_t hdesc0 = umma::make_sw128_kmajor_desc(h_base);
+      hdesc0 = (hdesc0 & ~((uint64_t)0x3FFF << 32)) | ((uint64_t)(kRowBytes >> 4) << 32);
+      const uint64_t wdesc0 = umma::make_sw128_kmajor_desc(w_base);
+      uint32_t slot = 0, phase = 0, ws = 0, wphase = 0;
+      bool ok = true;
+      for (int pair = 0; pair < g.npairs && ok; ++pair) {
+        const uint32_t d = tmem_base + (uint32_t)(pair * 256);
+        for (int slab = 0; slab < g.kslabs && ok; ++slab) {
+          ok = umma::mbar_wait(hfull(slot), phase, abort_flag);
+          if (!ok) break;
+          for (int tap = 0; tap < 9; ++tap) {
+            ok = umma::mbar_wait(wfull(ws), wphase, abort_flag);
+            if (!ok) break;
+            umma::tc_fence_after_sync();
+            const int kh = tap / 3, kw = tap - kh * 3;
+            const uint64_t xdesc = hdesc0 + (uint64_t)((slot * slot_bytes + (uint32_t)(kh * kPW + kw) * 128u) >> 4);
+            const uint64_t wdesc = wdesc0 + (uint64_t)((ws * (uint32_t)kWSlot) >> 4);
+#pragma unroll
+            for (int k = 0; k < 4; ++k)   // A = weights (M = 128 channels), B = pixels (N = 128 per timestep)
+              umma::mma_f16_ss(d, wdesc + (uint64_t)(2 * k), xdesc + (uint64_t)(2 * k), idesc,
+                               (slab > 0 || tap > 0 || k > 0) ? 1u : 0u);
+            umma::mma_commit(wempty(ws));
+            if (++ws == (uint32_t)kWRingP) { ws = 0; wphase ^= 1u; }
+          }
+          if (ok) umma::mma_commit(hempty(slot));
+          if (++slot == (uint32_t)kPairRing) { slot = 0; phase ^= 1u; }
+        }
+        if (ok) umma::mma_commit(accfull(pair));
+        PTRACE(1 + pair);
+      }
+    }
+    __syncwarp();
+  } else {
+    // ---------------------------------------------------------------- epilogue
+    const int quarter = warp & 3;
+    const int c = n0 + quarter * 32 + lane;          // output channel of this thread (= TMEM lane)
+    const bool c_ok = c < g.Cout;
+    const int col_begin = (warp < 4) ? 0 : 64;       // the two warps of a lane quarter split the pixels
+    const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    const float bias_c = (bias != nullptr && c_ok) ? DT<XT>::to_f(bias[c]) : 0.f;
+    const long long frame_out = (long long)g.B * g.Ho * g.Wo * g.Cout;
+    const long long img_base = (long long)b * g.Ho * g.Wo * g.Cout;
+    float v[64];
+#pragma unroll
+    for (int i = 0; i < 64; ++i) v[i] = 0.f;
+    if (g.lif && v_init != nullptr && c_ok) {
+#pragma unroll
+      for (int i = 0; i < 64; ++i) {
+        const int px = col_begin + i;
+        const int ho = h0 + (px >> 3), wo = w0 + (px & 7);
+        if ((px >> 3) < kTileRows && ho < g.Ho && wo < g.Wo)
+          v[i] = DT<VT>::to_f(v_init[img_base + ((long long)ho * g.Wo + wo) * g.Cout + c]);
+      }
+    }
+    bool ok = true;
+    for (int pair = 0; pair < g.npairs && ok; ++pair) {
+      if (lane == 0) ok = umma::mbar_wait(accfull(pair), 0u, abort_flag);
+      ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+      if (!ok) break;
+      umma::tc_fence_after_sync();
+      if (threadIdx.x == 0) PTRACE(4 + 2 * pair);
+#define SNNB_PAIR_EPI(KIND) \
+  pair_epilogue<XT, ST, KIND>(g, p, pair, lane_base, col_begin, c, c_ok, bias_c, res, spikes, frame_out, img_base, h0, w0, v)
+      if (!g.lif) SNNB_PAIR_EPI(kLifOff);
+      else if (p.mode == 1 && p.hard) SNNB_PAIR_EPI(kLifFast);
+      else SNNB_PAIR_EPI(kLifAny);
+#undef SNNB_PAIR_EPI
+      if (threadIdx.x == 0) PTRACE(5 + 2 * pair);
+    }
+    if (ok && g.lif && c_ok) {
+#pragma unroll
+      for (int i = 0; i < 64; ++i) {
+        const int px = col_begin + i;
+        const int ho = h0 + (px >> 3), wo = w0 + (px & 7);
+        if ((px >> 3) < kTileRows && ho < g.Ho && wo < g.Wo)
+          v_out[img_base + ((long long)ho * g.Wo + wo) * g.Cout + c] = DT<VT>::from_f(v[i]);
+      }
+    }
+  }
+
+  if (threadIdx.x == 0) PTRACE(10);
+  umma::tc_fence_before_sync();
+  __syncthreads();
+  if (threadIdx.x == 0) PTRACE(11);
+  if (abort_s && threadIdx.x == 0) atomicExch(&g_pair_status, 1);
+  if (warp == kMmaWarpP) {
+    umma::tc_fence_after_sync();
+    umma::tmem_dealloc(tmem_base, (uint32_t)g.tmem_cols);
+  }
+}
+
+template <typename XT, typename ST, typename VT>
+int launch(const ConvArgs &a, cudaStream_t stream) {
+  PairGeom g;
+  g.T = a.T;
+  g.Tacc = (a.x_t_stride == 0) ? 1 : a.T;
+  g.B = a.B; g.Cin = a.Cin; g.Cout = a.Cout; g.Ho = a.Ho; g.Wo = a.Wo;
+  g.kslabs = a.Cin / 64;
+  g.tq = g.Tacc >= 2 ? 2 : 1;
+  g.npairs = g.Tacc / g.tq;
+  g.n_tiles_n = (a.Cout + 127) / 128;
+  g.row_tiles = (a.Ho + kTileRows - 1) / kTileRows;
+  g.w_strips = (a.Wo + 7) / 8;
+  g.tmem_cols = g.npairs * 256 > 256 ? 512 : (g.tq == 2 ? 256 : 128);
+  g.lif = a.lif;
+  g.has_res = a.res != nullptr;
+  const long long grid = (long long)a.B * g.row_tiles * g.w_strips * g.n_tiles_n;
+  if (grid > 0x7fffffffLL) return fail(SNNB_ERR_INVALID, "conv_lif: problem too large for the grid");
+  const int es = 2;
+  CUtensorMap xm, wm;
+  {
+    cuuint64_t dims[5] = {(cuuint64_t)a.Cin, (cuuint64_t)a.W, (cuuint64_t)a.H, (cuuint64_t)a.B, (cuuint64_t)g.Tacc};
+    const cuuint64_t frame_bytes = (cuuint64_t)a.B * a.H * a.W * a.Cin * es;
+    cuuint64_t strides[4] = {(cuuint64_t)a.Cin * es, (cuuint64_t)a.W * a.Cin * es, (cuuint64_t)a.H * a.W * a.Cin * es,
+                             g.Tacc > 1 ? (cuuint64_t)a.x_t_stride * es : frame_bytes};
+    cuuint32_t box[5] = {64, (cuuint32_t)kPW, (cuuint32_t)kPH, 1, 1};
+    const int rc = encode_tmap(&xm, a.dtype, 5, a.x, dims, strides, box);
+    if (rc != SNNB_OK) return rc;
+  }
+  {
+    const cuuint64_t K = (cuuint64_t)9 * a.Cin;
+    cuuint64_t dims[2] = {K, (cuuint64_t)a.Cout};
+    cuuint64_t strides[1] = {K * es};
+    cuuint32_t box[2] = {64, 128};
+    const int rc = encode_tmap(&wm, a.dtype, 2, a.w, dims, strides, box);
+    if (rc != SNNB_OK) return rc;
+  }
+  // weight ring + halo ring + room for the junk rows the last descriptor group reads past a slot
+  const size_t smem = (size_t)kWRingP * kWSlot + (size_t)kPairRing * g.tq * kHaloT + 4 * kRowBytes + 1024;
+  auto kern = conv3x3_pair_kernel<XT, ST, VT>;
+  const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return fail(SNNB_ERR_CUDA, "conv_lif: cannot raise the shared-memory limit: %s", cudaGetErrorString(e));
+  kern<<<(unsigned)grid, kThreadsP, smem, stream>>>(xm, wm, static_cast<const XT *>(a.b), static_cast<const XT *>(a.res),
+                                                    static_cast<const VT *>(a.v_init), static_cast<ST *>(a.spikes),
+                                                    static_cast<VT *>(a.v_out), g, a.p);
+  SNNB_CHECK_LAUNCH("conv3x3_pair");
+  return SNNB_OK;
+}
+
+template <typename XT>
+int dispatch(const ConvArgs &a, cudaStream_t stream) {
+  const bool s_u8 = a.lif && a.spike_dtype == SNNB_U8;
+  const bool v_f32 = a.lif && a.v_dtype == SNNB_F32;
+  if (s_u8 && v_f32) return launch<XT, uint8_t, float>(a, stream);
+  if (s_u8) return launch<XT, uint8_t, XT>(a, stream);
+  if (v_f32) return launch<XT, XT, float>(a, stream);
+  return launch<XT, XT, XT>(a, stream);
+}
+
+}  // namespace
+
+bool conv3x3_pair_supported(const ConvArgs &a) {
+  if (a.dtype != SNNB_BF16 && a.dtype != SNNB_F16) return false;
+  if (a.KH != 3 || a.KW != 3 || a.stride != 1 || a.pad != 1) return false;
+  if (a.Cin % 64 != 0) return false;
+  if (a.x_t_stride == 0 && a.T > 1) return false;   // one frame for all steps: left to the other kernels
+  if (a.T != 1 && a.T != 2 && a.T != 4) return false;
+  if (a.Ho < 8) return false;   // small maps: the stacked-image tiles of conv_halo.cu waste fewer rows
+  if (a.xs_w || a.xs_h || a.xs_b || a.xd_w || a.xd_h) return false;
+  if (a.x_t_stride % 8 != 0) return false;
+  if (!aligned16(a.x) || !aligned16(a.w)) return false;
+  return true;
+}
+
+int conv3x3_pair(const ConvArgs &a, cudaStream_t stream) {
+  if (a.dtype == SNNB_BF16) return dispatch<__nv_bfloat16>(a, stream);
+  return dispatch<__half>(a, stream);
+}
+
+int pair_device_status(int *out) {
+  int h = 0;
+  cudaError_t e = cudaMemcpyFromSymbol(&h, g_pair_status, sizeof(int));
+  if (e != cudaSuccess) return fail(SNNB_ERR_CUDA, "device_status: %s", cudaGetErrorString(e));
+  if (h != 0) {
+    const int zero = 0;
+    cudaMemcpyToSymbol(g_pair_status, &zero, sizeof(int));
+  }
+  *out = h;
+  return SNNB_OK;
+}
+
+}  // namespace snnb
+
+#ifdef SNNB_TC_TRACE
+extern "C" int snnb_debug_read_ptrace(long long *host_buf) {
+  cudaDeviceSynchronize();
+  return (int)cudaMemcpyFromSymbol(host_buf, snnb::g_ptrace, sizeof(long long) * 64);
+}
+#endif

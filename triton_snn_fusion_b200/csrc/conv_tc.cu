@@ -436,7 +436,13 @@ extern "C" int snnb_device_status(int *status_out) {
     const int zero = 0;
     cudaMemcpyToSymbol(g_tc_status, &zero, sizeof(int));
   }
-  *status_out = h;
+  int h2 = 0;
+  const int rc = halo_device_status(&h2);
+  if (rc != SNNB_OK) return rc;
+  int h3 = 0;
+  const int rc3 = pair_device_status(&h3);
+  if (rc3 != SNNB_OK) return rc3;
+  *status_out = h | h2 | h3;
   return SNNB_OK;
 }
 

@@ -144,7 +144,8 @@ class CompiledNet:
                  dtype=torch.bfloat16, device="cuda", conv_path: str = "auto", keep_membranes: bool = False):
         self.spec, self.B, self.T, self.dtype = spec, int(batch), int(T), dtype
         self.device = torch.device(device)
-        self.path = {"auto": _lib.PATH_AUTO, "simt": _lib.PATH_SIMT, "tcgen05": _lib.PATH_TCGEN05}[conv_path]
+        self.path = {"auto": _lib.PATH_AUTO, "simt": _lib.PATH_SIMT, "tcgen05": _lib.PATH_TCGEN05,
+                     "tcgen05_taps": _lib.PATH_TCGEN05_TAPS, "tcgen05_halo": _lib.PATH_TCGEN05_HALO}[conv_path]
         self.dt = _lib.dtype_code(dtype)
         fp = folded_params(spec, params, dtype)
         self.weights: Dict[str, Dict[str, torch.Tensor]] = {}

@@ -47,13 +47,14 @@ class TritonConvLIFResult:
 
 _as_pair = as_pair
 
-# Implementation choice forwarded to the C ABI: "auto", "simt" or "tcgen05".
-_PATH = {"auto": _lib.PATH_AUTO, "simt": _lib.PATH_SIMT, "tcgen05": _lib.PATH_TCGEN05}
+# Implementation choice forwarded to the C ABI: "auto", "simt", "tcgen05" or "tcgen05_taps".
+_PATH = {"auto": _lib.PATH_AUTO, "simt": _lib.PATH_SIMT, "tcgen05": _lib.PATH_TCGEN05,
+         "tcgen05_taps": _lib.PATH_TCGEN05_TAPS, "tcgen05_halo": _lib.PATH_TCGEN05_HALO}
 _conv_path = "auto"
 
 
 def set_conv_path(path: str) -> str:
-    """Select the dense-conv implementation ("auto" | "simt" | "tcgen05"); returns the previous one."""
+    """Select the dense-conv implementation ("auto" | "simt" | "tcgen05" | "tcgen05_taps"); returns the previous one."""
     global _conv_path
     if path not in _PATH:
         raise ValueError(f"path must be one of {sorted(_PATH)}, got {path!r}")
