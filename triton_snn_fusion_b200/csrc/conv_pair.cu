@@ -55,52 +55,57 @@ struct PairGeom {
   int T, Tacc, B, Cin, Cout, Ho, Wo;
   int kslabs, npairs, tq;   // tq = timesteps per pair (1 or 2)
   int n_tiles_n, row_tiles, w_strips;
-  int tmem_cols, lif, has_res;
+  int tmem_cols, lif, has_res, total_tiles;
 };
 
 // LIF flavours compiled into the epilogue: the common one (tau a power of two, hard reset) with its
 // branches resolved at compile time, every other kind through the run-time lif_step, or no LIF.
 enum : int { kLifFast = 0, kLifAny = 1, kLifOff = 2 };
 
+// Where this thread's 64 pixels of the current tile live in the output.
+struct PixMap {
+  long long row0_off;   // element offset of (tile row 0 of this thread, column w0, channel c) inside a frame
+  int row_stride;       // Wo * Cout
+  int Cout;
+  int rows_ok;          // bit r set: this thread's r-th tile row (0..7) exists in the image and in the tile
+  int cols_ok;          // bit j set: column w0 + j exists
+};
+
 // Converts one timestep pair for the 64 pixels of this thread's channel: TMEM -> + bias (+ residual)
-// -> LIF (membrane in v[]) -> spikes.
-template <typename XT, typename ST, int KIND>
-__device__ __forceinline__ void pair_epilogue(const PairGeom &g, const LifParams &p, int pair, uint32_t tmem_lane_base,
-                                              int col_begin, int c, bool c_ok, float bias_c, const XT *__restrict__ res,
-                                              ST *__restrict__ spikes, long long frame_out, long long img_base, int h0,
-                                              int w0, float (&v)[64]) {
-  const int t0 = pair * g.tq;
+// -> LIF (membrane in v[]) -> spikes. TQ2: the pair holds two timesteps; RES: a residual is added.
+template <typename XT, typename ST, int KIND, bool TQ2, bool RES>
+__device__ __forceinline__ void pair_epilogue(const LifParams &p, uint32_t tmem_addr, float bias_c,
+                                              const XT *__restrict__ res, ST *__restrict__ out, long long frame_out,
+                                              const PixMap &pm, float (&v)[64]) {
+  // out / res already point at (timestep t0 of the pair, this thread's first row, column w0, channel c)
 #pragma unroll
   for (int chunk = 0; chunk < 4; ++chunk) {
-    const int px0 = col_begin + chunk * 16;
     uint32_t a0[16], a1[16];
-    umma::tmem_ld_x16(tmem_lane_base + (uint32_t)(pair * 256 + px0), a0);
-    if (g.tq == 2) umma::tmem_ld_x16(tmem_lane_base + (uint32_t)(pair * 256 + 128 + px0), a1);
+    umma::tmem_ld_x16(tmem_addr + (uint32_t)(chunk * 16), a0);
+    if (TQ2) umma::tmem_ld_x16(tmem_addr + (uint32_t)(128 + chunk * 16), a1);
     umma::tmem_ld_wait();
-    // the 16 pixels of a chunk are two full tile rows: rows (px0 >> 3) and (px0 >> 3) + 1
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
-      const int row = (px0 >> 3) + (i >> 3);
-      const int ho = h0 + row, wo = w0 + (i & 7);
-      const bool ok = c_ok && row < kTileRows && ho < g.Ho && wo < g.Wo;
-      const long long o = (long long)t0 * frame_out + img_base + ((long long)ho * g.Wo + wo) * g.Cout + c;
+      const int r = chunk * 2 + (i >> 3), j = i & 7;   // a chunk of 16 pixels is two tile rows of 8
+      const bool ok = ((pm.rows_ok >> r) & 1) && ((pm.cols_ok >> j) & 1);
+      const long long o = pm.row0_off + (long long)r * pm.row_stride + j * pm.Cout;
       float y0 = __uint_as_float(a0[i]) + bias_c;
-      float y1 = __uint_as_float(a1[i]) + bias_c;
+      float y1 = TQ2 ? __uint_as_float(a1[i]) + bias_c : 0.f;
       if (ok) {
-        if (g.has_res) {
+        if (RES && res != nullptr) {
           y0 += DT<XT>::to_f(res[o]);
-          if (g.tq == 2) y1 += DT<XT>::to_f(res[o + frame_out]);
+          if (TQ2) y1 += DT<XT>::to_f(res[o + frame_out]);
         }
         if constexpr (KIND == kLifOff) {
-          reinterpret_cast<XT *>(spikes)[o] = DT<XT>::from_f(y0);
-          if (g.tq == 2) reinterpret_cast<XT *>(spikes)[o + frame_out] = DT<XT>::from_f(y1);
+          reinterpret_cast<XT *>(out)[o] = DT<XT>::from_f(y0);
+          if (TQ2) reinterpret_cast<XT *>(out)[o + frame_out] = DT<XT>::from_f(y1);
         } else {
           float &vv = v[chunk * 16 + i];
           const float s0 = (KIND == kLifFast) ? lif_step_t<1, true>(y0, vv, p) : lif_step(y0, vv, p);
-          spikes[o] = DT<ST>::from_f(s0);
-          if (g.tq == 2) {
+          out[o] = DT<ST>::from_f(s0);
+          if (TQ2) {
             const float s1 = (KIND == kLifFast) ? lif_step_t<1, true>(y1, vv, p) : lif_step(y1, vv, p);
-            spikes[o + frame_out] = DT<ST>::from_f(s1);
+            out[o + frame_out] = DT<ST>::from_f(s1);
           }
         }
       }
@@ -114,18 +119,11 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
                     const XT *__restrict__ bias, const XT *__restrict__ res, const VT *__restrict__ v_init,
                     ST *__restrict__ spikes, VT *__restrict__ v_out, const PairGeom g, const LifParams p) {
   extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t bars[2 * kPairRing + 2 * kWRingP + 2];
+  __shared__ __align__(8) uint64_t bars[2 * kPairRing + 2 * kWRingP + 4];
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_s;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n_tile = blockIdx.x % g.n_tiles_n;
-  int m = blockIdx.x / g.n_tiles_n;
-  const int strip = m % g.w_strips;
-  m /= g.w_strips;
-  const int rt = m % g.row_tiles;
-  const int b = m / g.row_tiles;
-  const int n0 = n_tile * 128, w0 = strip * 8, h0 = rt * kTileRows;
 
   const uint32_t smem_base = (umma::smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t w_base = smem_base;
@@ -137,14 +135,28 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
   auto wfull = [&](uint32_t s) { return bar_base + 8u * (2u * kPairRing + s); };
   auto wempty = [&](uint32_t s) { return bar_base + 8u * (2u * kPairRing + kWRingP + s); };
   auto accfull = [&](uint32_t s) { return bar_base + 8u * (2u * kPairRing + 2u * kWRingP + s); };
+  auto accempty = [&](uint32_t s) { return bar_base + 8u * (2u * kPairRing + 2u * kWRingP + 2u + s); };
   volatile int *abort_flag = &abort_s;
+
+  // A CTA walks tiles blockIdx.x, blockIdx.x + gridDim.x, ...; tile index -> (image, row tile, column
+  // strip, channel tile) with the channel tile fastest so neighbouring CTAs share their halo tiles in L2.
+  auto decode = [&](int tile, int &n0, int &w0, int &h0, int &b) {
+    const int n_tile = tile % g.n_tiles_n;
+    int m = tile / g.n_tiles_n;
+    const int strip = m % g.w_strips;
+    m /= g.w_strips;
+    const int rt = m % g.row_tiles;
+    b = m / g.row_tiles;
+    n0 = n_tile * 128;
+    w0 = strip * 8;
+    h0 = rt * kTileRows;
+  };
 
   if (threadIdx.x == 0) {
     abort_s = 0;
     for (int s = 0; s < kPairRing; ++s) { umma::mbar_init(hfull(s), 1); umma::mbar_init(hempty(s), 1); }
     for (int s = 0; s < kWRingP; ++s) { umma::mbar_init(wfull(s), 1); umma::mbar_init(wempty(s), 1); }
-    umma::mbar_init(accfull(0), 1);
-    umma::mbar_init(accfull(1), 1);
+    for (int s = 0; s < 2; ++s) { umma::mbar_init(accfull(s), 1); umma::mbar_init(accempty(s), kEpiW); }
     umma::fence_mbar_init();
   }
   if (warp == kMmaWarpP) {
@@ -159,24 +171,27 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
   __syncthreads();
   umma::tc_fence_after_sync();
   const uint32_t tmem_base = tmem_base_s;
-  if (threadIdx.x == 0) PTRACE(0);
 
   if (warp == kHaloWarpP) {
     // ------------------------------------------------- halo producer: lane q loads timestep q of the pair
     uint32_t slot = 0, phase = 1;
     bool ok = true;
-    for (int pair = 0; pair < g.npairs && ok; ++pair) {
-      for (int slab = 0; slab < g.kslabs; ++slab) {
-        if (lane == 0) {
-          ok = umma::mbar_wait(hempty(slot), phase, abort_flag);
-          if (ok) umma::mbar_expect_tx(hfull(slot), slot_bytes);
+    for (int tile = blockIdx.x; tile < g.total_tiles && ok; tile += gridDim.x) {
+      int n0, w0, h0, b;
+      decode(tile, n0, w0, h0, b);
+      for (int pair = 0; pair < g.npairs && ok; ++pair) {
+        for (int slab = 0; slab < g.kslabs; ++slab) {
+          if (lane == 0) {
+            ok = umma::mbar_wait(hempty(slot), phase, abort_flag);
+            if (ok) umma::mbar_expect_tx(hfull(slot), slot_bytes);
+          }
+          ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+          if (!ok) break;
+          if (lane < g.tq)
+            umma::tma_load_5d(h_base + slot * slot_bytes + (uint32_t)lane * kHaloT, &xmap, hfull(slot), slab * 64,
+                              w0 - 1, h0 - 1, b, pair * g.tq + lane);
+          if (++slot == (uint32_t)kPairRing) { slot = 0; phase ^= 1u; }
         }
-        ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
-        if (!ok) break;
-        if (lane < g.tq)
-          umma::tma_load_5d(h_base + slot * slot_bytes + (uint32_t)lane * kHaloT, &xmap, hfull(slot), slab * 64, w0 - 1,
-                            h0 - 1, b, pair * g.tq + lane);
-        if (++slot == (uint32_t)kPairRing) { slot = 0; phase ^= 1u; }
       }
     }
   } else if (warp == kWWarpP) {
@@ -184,15 +199,18 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
     if (lane == 0) {
       uint32_t ws = 0, wphase = 1;
       bool ok = true;
-      for (int pair = 0; pair < g.npairs && ok; ++pair)
-        for (int slab = 0; slab < g.kslabs && ok; ++slab)
-          for (int tap = 0; tap < 9; ++tap) {
-            ok = umma::mbar_wait(wempty(ws), wphase, abort_flag);
-            if (!ok) break;
-            umma::mbar_expect_tx(wfull(ws), (uint32_t)kWSlot);
-            umma::tma_load_2d(w_base + ws * (uint32_t)kWSlot, &wmap, wfull(ws), tap * g.Cin + slab * 64, n0);
-            if (++ws == (uint32_t)kWRingP) { ws = 0; wphase ^= 1u; }
-          }
+      for (int tile = blockIdx.x; tile < g.total_tiles && ok; tile += gridDim.x) {
+        const int n0 = (tile % g.n_tiles_n) * 128;
+        for (int pair = 0; pair < g.npairs && ok; ++pair)
+          for (int slab = 0; slab < g.kslabs && ok; ++slab)
+            for (int tap = 0; tap < 9; ++tap) {
+              ok = umma::mbar_wait(wempty(ws), wphase, abort_flag);
+              if (!ok) break;
+              umma::mbar_expect_tx(wfull(ws), (uint32_t)kWSlot);
+              umma::tma_load_2d(w_base + ws * (uint32_t)kWSlot, &wmap, wfull(ws), tap * g.Cin + slab * 64, n0);
+              if (++ws == (uint32_t)kWRingP) { ws = 0; wphase ^= 1u; }
+            }
+      }
     }
     __syncwarp();
   } else if (warp == kMmaWarpP) {
@@ -202,87 +220,110 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
       uint64_t hdesc0 = umma::make_sw128_kmajor_desc(h_base);
       hdesc0 = (hdesc0 & ~((uint64_t)0x3FFF << 32)) | ((uint64_t)(kRowBytes >> 4) << 32);
       const uint64_t wdesc0 = umma::make_sw128_kmajor_desc(w_base);
-      uint32_t slot = 0, phase = 0, ws = 0, wphase = 0;
+      uint32_t slot = 0, phase = 0, ws = 0, wphase = 0, it = 0;
       bool ok = true;
-      for (int pair = 0; pair < g.npairs && ok; ++pair) {
-        const uint32_t d = tmem_base + (uint32_t)(pair * 256);
-        for (int slab = 0; slab < g.kslabs && ok; ++slab) {
-          ok = umma::mbar_wait(hfull(slot), phase, abort_flag);
+      for (int tile = blockIdx.x; tile < g.total_tiles && ok; tile += gridDim.x, ++it) {
+        for (int pair = 0; pair < g.npairs && ok; ++pair) {
+          // the epilogue warps must have drained this accumulator (previous tile) before it is overwritten
+          ok = umma::mbar_wait(accempty(pair), (it & 1u) ^ 1u, abort_flag);
           if (!ok) break;
-          for (int tap = 0; tap < 9; ++tap) {
-            ok = umma::mbar_wait(wfull(ws), wphase, abort_flag);
+          umma::tc_fence_after_sync();
+          const uint32_t d = tmem_base + (uint32_t)(pair * 256);
+          for (int slab = 0; slab < g.kslabs && ok; ++slab) {
+            ok = umma::mbar_wait(hfull(slot), phase, abort_flag);
             if (!ok) break;
-            umma::tc_fence_after_sync();
-            const int kh = tap / 3, kw = tap - kh * 3;
-            const uint64_t xdesc = hdesc0 + (uint64_t)((slot * slot_bytes + (uint32_t)(kh * kPW + kw) * 128u) >> 4);
-            const uint64_t wdesc = wdesc0 + (uint64_t)((ws * (uint32_t)kWSlot) >> 4);
+            for (int tap = 0; tap < 9; ++tap) {
+              ok = umma::mbar_wait(wfull(ws), wphase, abort_flag);
+              if (!ok) break;
+              umma::tc_fence_after_sync();
+              const int kh = tap / 3, kw = tap - kh * 3;
+              const uint64_t xdesc = hdesc0 + (uint64_t)((slot * slot_bytes + (uint32_t)(kh * kPW + kw) * 128u) >> 4);
+              const uint64_t wdesc = wdesc0 + (uint64_t)((ws * (uint32_t)kWSlot) >> 4);
 #pragma unroll
-            for (int k = 0; k < 4; ++k)   // A = weights (M = 128 channels), B = pixels (N = 128 per timestep)
-              umma::mma_f16_ss(d, wdesc + (uint64_t)(2 * k), xdesc + (uint64_t)(2 * k), idesc,
-                               (slab > 0 || tap > 0 || k > 0) ? 1u : 0u);
-            umma::mma_commit(wempty(ws));
-            if (++ws == (uint32_t)kWRingP) { ws = 0; wphase ^= 1u; }
+              for (int k = 0; k < 4; ++k)   // A = weights (M = 128 channels), B = pixels (N = 128 per timestep)
+                umma::mma_f16_ss(d, wdesc + (uint64_t)(2 * k), xdesc + (uint64_t)(2 * k), idesc,
+                                 (slab > 0 || tap > 0 || k > 0) ? 1u : 0u);
+              umma::mma_commit(wempty(ws));
+              if (++ws == (uint32_t)kWRingP) { ws = 0; wphase ^= 1u; }
+            }
+            if (ok) umma::mma_commit(hempty(slot));
+            if (++slot == (uint32_t)kPairRing) { slot = 0; phase ^= 1u; }
           }
-          if (ok) umma::mma_commit(hempty(slot));
-          if (++slot == (uint32_t)kPairRing) { slot = 0; phase ^= 1u; }
+          if (ok) umma::mma_commit(accfull(pair));
         }
-        if (ok) umma::mma_commit(accfull(pair));
-        PTRACE(1 + pair);
       }
     }
     __syncwarp();
   } else {
     // ---------------------------------------------------------------- epilogue
     const int quarter = warp & 3;
-    const int c = n0 + quarter * 32 + lane;          // output channel of this thread (= TMEM lane)
-    const bool c_ok = c < g.Cout;
-    const int col_begin = (warp < 4) ? 0 : 64;       // the two warps of a lane quarter split the pixels
-    const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
-    const float bias_c = (bias != nullptr && c_ok) ? DT<XT>::to_f(bias[c]) : 0.f;
+    const int r_begin = (warp < 4) ? 0 : 8;          // the two warps of a lane quarter split the 16 tile rows
+    const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(r_begin * 8);
     const long long frame_out = (long long)g.B * g.Ho * g.Wo * g.Cout;
-    const long long img_base = (long long)b * g.Ho * g.Wo * g.Cout;
-    float v[64];
-#pragma unroll
-    for (int i = 0; i < 64; ++i) v[i] = 0.f;
-    if (g.lif && v_init != nullptr && c_ok) {
-#pragma unroll
-      for (int i = 0; i < 64; ++i) {
-        const int px = col_begin + i;
-        const int ho = h0 + (px >> 3), wo = w0 + (px & 7);
-        if ((px >> 3) < kTileRows && ho < g.Ho && wo < g.Wo)
-          v[i] = DT<VT>::to_f(v_init[img_base + ((long long)ho * g.Wo + wo) * g.Cout + c]);
-      }
-    }
     bool ok = true;
-    for (int pair = 0; pair < g.npairs && ok; ++pair) {
-      if (lane == 0) ok = umma::mbar_wait(accfull(pair), 0u, abort_flag);
-      ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
-      if (!ok) break;
-      umma::tc_fence_after_sync();
-      if (threadIdx.x == 0) PTRACE(4 + 2 * pair);
-#define SNNB_PAIR_EPI(KIND) \
-  pair_epilogue<XT, ST, KIND>(g, p, pair, lane_base, col_begin, c, c_ok, bias_c, res, spikes, frame_out, img_base, h0, w0, v)
-      if (!g.lif) SNNB_PAIR_EPI(kLifOff);
-      else if (p.mode == 1 && p.hard) SNNB_PAIR_EPI(kLifFast);
-      else SNNB_PAIR_EPI(kLifAny);
-#undef SNNB_PAIR_EPI
-      if (threadIdx.x == 0) PTRACE(5 + 2 * pair);
-    }
-    if (ok && g.lif && c_ok) {
+    uint32_t it = 0;
+    for (int tile = blockIdx.x; tile < g.total_tiles && ok; tile += gridDim.x, ++it) {
+      int n0, w0, h0, b;
+      decode(tile, n0, w0, h0, b);
+      const int c = n0 + quarter * 32 + lane;          // output channel of this thread (= TMEM lane)
+      const bool c_ok = c < g.Cout;
+      const float bias_c = (bias != nullptr && c_ok) ? DT<XT>::to_f(bias[c]) : 0.f;
+      PixMap pm;
+      pm.Cout = g.Cout;
+      pm.row_stride = g.Wo * g.Cout;
+      pm.row0_off = ((long long)b * g.Ho + (h0 + r_begin)) * pm.row_stride + (long long)w0 * g.Cout + c;
+      pm.rows_ok = 0;
+      pm.cols_ok = 0;
 #pragma unroll
-      for (int i = 0; i < 64; ++i) {
-        const int px = col_begin + i;
-        const int ho = h0 + (px >> 3), wo = w0 + (px & 7);
-        if ((px >> 3) < kTileRows && ho < g.Ho && wo < g.Wo)
-          v_out[img_base + ((long long)ho * g.Wo + wo) * g.Cout + c] = DT<VT>::from_f(v[i]);
+      for (int r = 0; r < 8; ++r)
+        if (c_ok && r_begin + r < kTileRows && h0 + r_begin + r < g.Ho) pm.rows_ok |= 1 << r;
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (w0 + j < g.Wo) pm.cols_ok |= 1 << j;
+      float v[64];
+#pragma unroll
+      for (int i = 0; i < 64; ++i) v[i] = 0.f;
+      if (g.lif && v_init != nullptr) {
+#pragma unroll
+        for (int i = 0; i < 64; ++i)
+          if (((pm.rows_ok >> (i >> 3)) & 1) && ((pm.cols_ok >> (i & 7)) & 1))
+            v[i] = DT<VT>::to_f(v_init[pm.row0_off + (long long)(i >> 3) * pm.row_stride + (i & 7) * pm.Cout]);
+      }
+      for (int pair = 0; pair < g.npairs && ok; ++pair) {
+        if (lane == 0) ok = umma::mbar_wait(accfull(pair), it & 1u, abort_flag);
+        ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+        if (!ok) break;
+        umma::tc_fence_after_sync();
+        const long long toff = (long long)(pair * g.tq) * frame_out;
+        const uint32_t taddr = lane_base + (uint32_t)(pair * 256);
+        ST *out = spikes + toff;
+        const XT *rs = g.has_res ? res + toff : nullptr;
+        if (g.lif && p.mode == 1 && p.hard && g.tq == 2) {
+          if (g.has_res) pair_epilogue<XT, ST, kLifFast, true, true>(p, taddr, bias_c, rs, out, frame_out, pm, v);
+          else pair_epilogue<XT, ST, kLifFast, true, false>(p, taddr, bias_c, rs, out, frame_out, pm, v);
+        } else if (g.lif) {
+          if (g.tq == 2) pair_epilogue<XT, ST, kLifAny, true, true>(p, taddr, bias_c, g.has_res ? rs : nullptr, out, frame_out, pm, v);
+          else pair_epilogue<XT, ST, kLifAny, false, true>(p, taddr, bias_c, rs, out, frame_out, pm, v);
+        } else {
+          if (g.tq == 2) pair_epilogue<XT, ST, kLifOff, true, true>(p, taddr, bias_c, rs, out, frame_out, pm, v);
+          else pair_epilogue<XT, ST, kLifOff, false, true>(p, taddr, bias_c, rs, out, frame_out, pm, v);
+        }
+        // this accumulator may now be overwritten by the next tile's MMAs
+        umma::tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) umma::mbar_arrive(accempty(pair));
+      }
+      if (ok && g.lif) {
+#pragma unroll
+        for (int i = 0; i < 64; ++i)
+          if (((pm.rows_ok >> (i >> 3)) & 1) && ((pm.cols_ok >> (i & 7)) & 1))
+            v_out[pm.row0_off + (long long)(i >> 3) * pm.row_stride + (i & 7) * pm.Cout] = DT<VT>::from_f(v[i]);
       }
     }
   }
 
-  if (threadIdx.x == 0) PTRACE(10);
   umma::tc_fence_before_sync();
   __syncthreads();
-  if (threadIdx.x == 0) PTRACE(11);
   if (abort_s && threadIdx.x == 0) atomicExch(&g_pair_status, 1);
   if (warp == kMmaWarpP) {
     umma::tc_fence_after_sync();
@@ -305,8 +346,13 @@ int launch(const ConvArgs &a, cudaStream_t stream) {
   g.tmem_cols = g.npairs * 256 > 256 ? 512 : (g.tq == 2 ? 256 : 128);
   g.lif = a.lif;
   g.has_res = a.res != nullptr;
-  const long long grid = (long long)a.B * g.row_tiles * g.w_strips * g.n_tiles_n;
-  if (grid > 0x7fffffffLL) return fail(SNNB_ERR_INVALID, "conv_lif: problem too large for the grid");
+  const long long tiles = (long long)a.B * g.row_tiles * g.w_strips * g.n_tiles_n;
+  if (tiles > 0x7fffffffLL) return fail(SNNB_ERR_INVALID, "conv_lif: problem too large for the grid");
+  g.total_tiles = (int)tiles;
+  int dev = 0, sms = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 1)
+    return fail(SNNB_ERR_CUDA, "conv_lif: cannot query the SM count");
+  const long long grid = tiles < sms ? tiles : sms;   // persistent: one CTA per SM walks the tiles
   const int es = 2;
   CUtensorMap xm, wm;
   {
