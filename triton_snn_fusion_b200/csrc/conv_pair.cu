@@ -44,7 +44,8 @@ constexpr int kPW = 10, kPH = 16;                      // halo tile: 10 x 16 pix
 constexpr int kRowBytes = kPW * 128;                   // 1280
 constexpr int kHaloT = kPW * kPH * 128;                // 20480 bytes per timestep
 constexpr int kTileRows = 14;                          // valid output rows per tile
-constexpr int kPairRing = 4;                           // halo (pair) slots
+constexpr int kPairRing = 4;                           // halo (pair) slots (3 when a residual is added)
+constexpr int kIdentBytes = 192 * 128;                 // zero rows / 64x64 identity / zero rows, see the residual path
 constexpr int kWRingP = 3;                             // weight-tile slots (16 KB each)
 constexpr int kWSlot = 128 * 128;
 constexpr int kEpiW = 8;
@@ -56,6 +57,7 @@ struct PairGeom {
   int kslabs, npairs, tq;   // tq = timesteps per pair (1 or 2)
   int n_tiles_n, row_tiles, w_strips;
   int tmem_cols, lif, has_res, total_tiles;
+  int ring;   // halo slots in use
 };
 
 // LIF flavours compiled into the epilogue: the common one (tau a power of two, hard reset) with its
@@ -116,7 +118,7 @@ __device__ __forceinline__ void pair_epilogue(const LifParams &p, uint32_t tmem_
 template <typename XT, typename ST, typename VT>
 __global__ void __launch_bounds__(kThreadsP)
 conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap,
-                    const XT *__restrict__ bias, const XT *__restrict__ res, const VT *__restrict__ v_init,
+                    const __grid_constant__ CUtensorMap rmap, const XT *__restrict__ bias, const VT *__restrict__ v_init,
                     ST *__restrict__ spikes, VT *__restrict__ v_out, const PairGeom g, const LifParams p) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bars[2 * kPairRing + 2 * kWRingP + 4];
@@ -126,8 +128,10 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   const uint32_t smem_base = (umma::smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t w_base = smem_base;
-  const uint32_t h_base = smem_base + (uint32_t)(kWRingP * kWSlot);
+  // [identity block (residual path only)] [weight ring] [halo ring]
+  const uint32_t ident_base = smem_base;
+  const uint32_t w_base = smem_base + (g.has_res ? (uint32_t)kIdentBytes : 0u);
+  const uint32_t h_base = w_base + (uint32_t)(kWRingP * kWSlot);
   const uint32_t slot_bytes = (uint32_t)(g.tq * kHaloT);
   const uint32_t bar_base = umma::smem_u32(bars);
   auto hfull = [&](uint32_t s) { return bar_base + 8u * s; };
@@ -154,7 +158,7 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
 
   if (threadIdx.x == 0) {
     abort_s = 0;
-    for (int s = 0; s < kPairRing; ++s) { umma::mbar_init(hfull(s), 1); umma::mbar_init(hempty(s), 1); }
+    for (int s = 0; s < g.ring; ++s) { umma::mbar_init(hfull(s), 1); umma::mbar_init(hempty(s), 1); }
     for (int s = 0; s < kWRingP; ++s) { umma::mbar_init(wfull(s), 1); umma::mbar_init(wempty(s), 1); }
     for (int s = 0; s < 2; ++s) { umma::mbar_init(accfull(s), 1); umma::mbar_init(accempty(s), kEpiW); }
     umma::fence_mbar_init();
@@ -166,6 +170,22 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
   if (warp == kHaloWarpP && lane == 0) {
     umma::prefetch_tensormap(&xmap);
     umma::prefetch_tensormap(&wmap);
+    if (g.has_res) umma::prefetch_tensormap(&rmap);
+  }
+  if (g.has_res && warp < kEpiW) {
+    // Residual add on the tensor cores: D += I . R with a 64x64 identity as the weight operand. The block
+    // is 192 rows of 128 bytes: 64 zero rows, the identity (row 64 + k has a one in column k, stored where
+    // the 128-byte swizzle puts it), 64 zero rows. Read from row 64 it is [I; 0] (channels n0..n0+63 of the
+    // tile), read from row 0 it is [0; I] (channels n0+64..n0+127).
+    uint4 *blk = reinterpret_cast<uint4 *>(smem_raw + (ident_base - umma::smem_u32(smem_raw)));
+    for (int i = threadIdx.x; i < kIdentBytes / 16; i += 32 * kEpiW) blk[i] = make_uint4(0u, 0u, 0u, 0u);
+    asm volatile("bar.sync 2, %0;" ::"r"(32 * kEpiW) : "memory");
+    if (threadIdx.x < 64) {
+      const int k = threadIdx.x, r = 64 + k;
+      uint8_t *row = smem_raw + (ident_base - umma::smem_u32(smem_raw)) + r * 128;
+      *reinterpret_cast<XT *>(row + (((k >> 3) ^ (r & 7)) << 4) + (k & 7) * 2) = DT<XT>::from_f(1.0f);
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // make the writes visible to the MMA unit
   }
   umma::tc_fence_before_sync();
   __syncthreads();
@@ -190,7 +210,21 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
           if (lane < g.tq)
             umma::tma_load_5d(h_base + slot * slot_bytes + (uint32_t)lane * kHaloT, &xmap, hfull(slot), slab * 64,
                               w0 - 1, h0 - 1, b, pair * g.tq + lane);
-          if (++slot == (uint32_t)kPairRing) { slot = 0; phase ^= 1u; }
+          if (++slot == (uint32_t)g.ring) { slot = 0; phase ^= 1u; }
+        }
+        // residual tiles of this pair: one per 64-channel half of the output-channel tile
+        for (int rs = 0; rs < 2 && g.has_res && ok; ++rs) {
+          if (n0 + rs * 64 >= g.Cout) break;
+          if (lane == 0) {
+            ok = umma::mbar_wait(hempty(slot), phase, abort_flag);
+            if (ok) umma::mbar_expect_tx(hfull(slot), slot_bytes);
+          }
+          ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+          if (!ok) break;
+          if (lane < g.tq)
+            umma::tma_load_5d(h_base + slot * slot_bytes + (uint32_t)lane * kHaloT, &rmap, hfull(slot), n0 + rs * 64,
+                              w0 - 1, h0 - 1, b, pair * g.tq + lane);
+          if (++slot == (uint32_t)g.ring) { slot = 0; phase ^= 1u; }
         }
       }
     }
@@ -247,7 +281,21 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
               if (++ws == (uint32_t)kWRingP) { ws = 0; wphase ^= 1u; }
             }
             if (ok) umma::mma_commit(hempty(slot));
-            if (++slot == (uint32_t)kPairRing) { slot = 0; phase ^= 1u; }
+            if (++slot == (uint32_t)g.ring) { slot = 0; phase ^= 1u; }
+          }
+          // residual: accumulate I . R (centre tap of the residual's halo tile)
+          const int n0 = (tile % g.n_tiles_n) * 128;
+          for (int rs = 0; rs < 2 && g.has_res && ok; ++rs) {
+            if (n0 + rs * 64 >= g.Cout) break;
+            ok = umma::mbar_wait(hfull(slot), phase, abort_flag);
+            if (!ok) break;
+            umma::tc_fence_after_sync();
+            const uint64_t idesc_a = umma::make_sw128_kmajor_desc(ident_base + (rs == 0 ? 64u * 128u : 0u));
+            const uint64_t xdesc = hdesc0 + (uint64_t)((slot * slot_bytes + (uint32_t)(kPW + 1) * 128u) >> 4);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) umma::mma_f16_ss(d, idesc_a + (uint64_t)(2 * k), xdesc + (uint64_t)(2 * k), idesc, 1u);
+            umma::mma_commit(hempty(slot));
+            if (++slot == (uint32_t)g.ring) { slot = 0; phase ^= 1u; }
           }
           if (ok) umma::mma_commit(accfull(pair));
         }
@@ -297,16 +345,15 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
         const long long toff = (long long)(pair * g.tq) * frame_out;
         const uint32_t taddr = lane_base + (uint32_t)(pair * 256);
         ST *out = spikes + toff;
-        const XT *rs = g.has_res ? res + toff : nullptr;
+        const XT *rs = nullptr;   // the residual was already added by the tensor cores
         if (g.lif && p.mode == 1 && p.hard && g.tq == 2) {
-          if (g.has_res) pair_epilogue<XT, ST, kLifFast, true, true>(p, taddr, bias_c, rs, out, frame_out, pm, v);
-          else pair_epilogue<XT, ST, kLifFast, true, false>(p, taddr, bias_c, rs, out, frame_out, pm, v);
+          pair_epilogue<XT, ST, kLifFast, true, false>(p, taddr, bias_c, rs, out, frame_out, pm, v);
         } else if (g.lif) {
-          if (g.tq == 2) pair_epilogue<XT, ST, kLifAny, true, true>(p, taddr, bias_c, g.has_res ? rs : nullptr, out, frame_out, pm, v);
-          else pair_epilogue<XT, ST, kLifAny, false, true>(p, taddr, bias_c, rs, out, frame_out, pm, v);
+          if (g.tq == 2) pair_epilogue<XT, ST, kLifAny, true, false>(p, taddr, bias_c, rs, out, frame_out, pm, v);
+          else pair_epilogue<XT, ST, kLifAny, false, false>(p, taddr, bias_c, rs, out, frame_out, pm, v);
         } else {
-          if (g.tq == 2) pair_epilogue<XT, ST, kLifOff, true, true>(p, taddr, bias_c, rs, out, frame_out, pm, v);
-          else pair_epilogue<XT, ST, kLifOff, false, true>(p, taddr, bias_c, rs, out, frame_out, pm, v);
+          if (g.tq == 2) pair_epilogue<XT, ST, kLifOff, true, false>(p, taddr, bias_c, rs, out, frame_out, pm, v);
+          else pair_epilogue<XT, ST, kLifOff, false, false>(p, taddr, bias_c, rs, out, frame_out, pm, v);
         }
         // this accumulator may now be overwritten by the next tile's MMAs
         umma::tc_fence_before_sync();
@@ -372,12 +419,23 @@ int launch(const ConvArgs &a, cudaStream_t stream) {
     const int rc = encode_tmap(&wm, a.dtype, 2, a.w, dims, strides, box);
     if (rc != SNNB_OK) return rc;
   }
-  // weight ring + halo ring + room for the junk rows the last descriptor group reads past a slot
-  const size_t smem = (size_t)kWRingP * kWSlot + (size_t)kPairRing * g.tq * kHaloT + 4 * kRowBytes + 1024;
+  CUtensorMap rm = xm;
+  if (g.has_res) {   // the residual has the output's shape: [T][B][Ho][Wo][Cout]
+    cuuint64_t dims[5] = {(cuuint64_t)a.Cout, (cuuint64_t)a.Wo, (cuuint64_t)a.Ho, (cuuint64_t)a.B, (cuuint64_t)a.T};
+    cuuint64_t strides[4] = {(cuuint64_t)a.Cout * es, (cuuint64_t)a.Wo * a.Cout * es, (cuuint64_t)a.Ho * a.Wo * a.Cout * es,
+                             (cuuint64_t)a.B * a.Ho * a.Wo * a.Cout * es};
+    cuuint32_t box[5] = {64, (cuuint32_t)kPW, (cuuint32_t)kPH, 1, 1};
+    const int rc = encode_tmap(&rm, a.dtype, 5, a.res, dims, strides, box);
+    if (rc != SNNB_OK) return rc;
+  }
+  // [identity block] + weight ring + halo ring + room for the junk rows the last descriptor group reads past a slot
+  g.ring = g.has_res ? kPairRing - 1 : kPairRing;
+  const size_t smem = (g.has_res ? (size_t)kIdentBytes : 0) + (size_t)kWRingP * kWSlot + (size_t)g.ring * g.tq * kHaloT +
+                      4 * kRowBytes + 1024;
   auto kern = conv3x3_pair_kernel<XT, ST, VT>;
   const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return fail(SNNB_ERR_CUDA, "conv_lif: cannot raise the shared-memory limit: %s", cudaGetErrorString(e));
-  kern<<<(unsigned)grid, kThreadsP, smem, stream>>>(xm, wm, static_cast<const XT *>(a.b), static_cast<const XT *>(a.res),
+  kern<<<(unsigned)grid, kThreadsP, smem, stream>>>(xm, wm, rm, static_cast<const XT *>(a.b),
                                                     static_cast<const VT *>(a.v_init), static_cast<ST *>(a.spikes),
                                                     static_cast<VT *>(a.v_out), g, a.p);
   SNNB_CHECK_LAUNCH("conv3x3_pair");
