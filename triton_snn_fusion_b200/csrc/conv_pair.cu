@@ -33,7 +33,7 @@ static __device__ int g_pair_status = 0;
 
 #ifdef SNNB_TC_TRACE
 static __device__ long long g_ptrace[64];
-#define PTRACE(idx) do { if (blockIdx.x == 300) g_ptrace[idx] = clock64(); } while (0)
+#define PTRACE(idx) do { if (blockIdx.x == 100 && (idx) < 64) g_ptrace[idx] = clock64(); } while (0)
 #else
 #define PTRACE(idx) do { } while (0)
 #endif
@@ -44,9 +44,9 @@ constexpr int kPW = 10, kPH = 16;                      // halo tile: 10 x 16 pix
 constexpr int kRowBytes = kPW * 128;                   // 1280
 constexpr int kHaloT = kPW * kPH * 128;                // 20480 bytes per timestep
 constexpr int kTileRows = 14;                          // valid output rows per tile
-constexpr int kPairRing = 4;                           // halo (pair) slots (3 when a residual is added)
+constexpr int kPairRing = 3;                           // halo (pair) slots
 constexpr int kIdentBytes = 192 * 128;                 // zero rows / 64x64 identity / zero rows, see the residual path
-constexpr int kWRingP = 3;                             // weight-tile slots (16 KB each)
+constexpr int kWRingP = 5;                             // weight-tile slots (16 KB each): a load must cover ~1 us of L2 latency
 constexpr int kWSlot = 128 * 128;
 constexpr int kEpiW = 8;
 constexpr int kHaloWarpP = kEpiW, kWWarpP = kEpiW + 1, kMmaWarpP = kEpiW + 2;
@@ -58,6 +58,7 @@ struct PairGeom {
   int n_tiles_n, row_tiles, w_strips;
   int tmem_cols, lif, has_res, total_tiles;
   int ring;   // halo slots in use
+  int wring;  // weight slots in use (<= kWRingP)
 };
 
 // LIF flavours compiled into the epilogue: the common one (tau a power of two, hard reset) with its
@@ -75,6 +76,7 @@ struct PixMap {
 
 // Converts one timestep pair for the 64 pixels of this thread's channel: TMEM -> + bias (+ residual)
 // -> LIF (membrane in v[]) -> spikes. TQ2: the pair holds two timesteps; RES: a residual is added.
+// General version: every pixel is predicated on the tile / image edges.
 template <typename XT, typename ST, int KIND, bool TQ2, bool RES>
 __device__ __forceinline__ void pair_epilogue(const LifParams &p, uint32_t tmem_addr, float bias_c,
                                               const XT *__restrict__ res, ST *__restrict__ out, long long frame_out,
@@ -115,6 +117,33 @@ __device__ __forceinline__ void pair_epilogue(const LifParams &p, uint32_t tmem_
   }
 }
 
+// Hot version: two timesteps, tau a power of two, hard reset, and a tile that lies completely inside
+// the image with a valid channel, so nothing is predicated. NROWS = tile rows of this thread (8 for
+// the warps that own rows 0..7, 6 for those that own rows 8..13).
+template <typename XT, typename ST, int NROWS>
+__device__ __forceinline__ void pair_epilogue_full(const LifParams &p, uint32_t tmem_addr, float bias_c,
+                                                   ST *__restrict__ out, long long frame_out, const PixMap &pm,
+                                                   float (&v)[64]) {
+  ST *const p0 = out + pm.row0_off;
+  ST *const p1 = p0 + frame_out;
+#pragma unroll
+  for (int chunk = 0; chunk < NROWS / 2; ++chunk) {
+    uint32_t a0[16], a1[16];
+    umma::tmem_ld_x16(tmem_addr + (uint32_t)(chunk * 16), a0);
+    umma::tmem_ld_x16(tmem_addr + (uint32_t)(128 + chunk * 16), a1);
+    umma::tmem_ld_wait();
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const int o = (chunk * 2 + (i >> 3)) * pm.row_stride + (i & 7) * pm.Cout;   // fits 32 bits: one tile
+      float &vv = v[chunk * 16 + i];
+      const float s0 = lif_step_t<1, true>(__uint_as_float(a0[i]) + bias_c, vv, p);
+      p0[o] = DT<ST>::from_f(s0);
+      const float s1 = lif_step_t<1, true>(__uint_as_float(a1[i]) + bias_c, vv, p);
+      p1[o] = DT<ST>::from_f(s1);
+    }
+  }
+}
+
 template <typename XT, typename ST, typename VT>
 __global__ void __launch_bounds__(kThreadsP)
 conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap,
@@ -131,7 +160,7 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
   // [identity block (residual path only)] [weight ring] [halo ring]
   const uint32_t ident_base = smem_base;
   const uint32_t w_base = smem_base + (g.has_res ? (uint32_t)kIdentBytes : 0u);
-  const uint32_t h_base = w_base + (uint32_t)(kWRingP * kWSlot);
+  const uint32_t h_base = w_base + (uint32_t)(g.wring * kWSlot);
   const uint32_t slot_bytes = (uint32_t)(g.tq * kHaloT);
   const uint32_t bar_base = umma::smem_u32(bars);
   auto hfull = [&](uint32_t s) { return bar_base + 8u * s; };
@@ -159,7 +188,7 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
   if (threadIdx.x == 0) {
     abort_s = 0;
     for (int s = 0; s < g.ring; ++s) { umma::mbar_init(hfull(s), 1); umma::mbar_init(hempty(s), 1); }
-    for (int s = 0; s < kWRingP; ++s) { umma::mbar_init(wfull(s), 1); umma::mbar_init(wempty(s), 1); }
+    for (int s = 0; s < g.wring; ++s) { umma::mbar_init(wfull(s), 1); umma::mbar_init(wempty(s), 1); }
     for (int s = 0; s < 2; ++s) { umma::mbar_init(accfull(s), 1); umma::mbar_init(accempty(s), kEpiW); }
     umma::fence_mbar_init();
   }
@@ -191,6 +220,7 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
   __syncthreads();
   umma::tc_fence_after_sync();
   const uint32_t tmem_base = tmem_base_s;
+  if (threadIdx.x == 0) PTRACE(0);
 
   if (warp == kHaloWarpP) {
     // ------------------------------------------------- halo producer: lane q loads timestep q of the pair
@@ -242,7 +272,7 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
               if (!ok) break;
               umma::mbar_expect_tx(wfull(ws), (uint32_t)kWSlot);
               umma::tma_load_2d(w_base + ws * (uint32_t)kWSlot, &wmap, wfull(ws), tap * g.Cin + slab * 64, n0);
-              if (++ws == (uint32_t)kWRingP) { ws = 0; wphase ^= 1u; }
+              if (++ws == (uint32_t)g.wring) { ws = 0; wphase ^= 1u; }
             }
       }
     }
@@ -278,7 +308,7 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
                 umma::mma_f16_ss(d, wdesc + (uint64_t)(2 * k), xdesc + (uint64_t)(2 * k), idesc,
                                  (slab > 0 || tap > 0 || k > 0) ? 1u : 0u);
               umma::mma_commit(wempty(ws));
-              if (++ws == (uint32_t)kWRingP) { ws = 0; wphase ^= 1u; }
+              if (++ws == (uint32_t)g.wring) { ws = 0; wphase ^= 1u; }
             }
             if (ok) umma::mma_commit(hempty(slot));
             if (++slot == (uint32_t)g.ring) { slot = 0; phase ^= 1u; }
@@ -298,6 +328,7 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
             if (++slot == (uint32_t)g.ring) { slot = 0; phase ^= 1u; }
           }
           if (ok) umma::mma_commit(accfull(pair));
+          PTRACE(12 + it * 8 + pair);
         }
       }
     }
@@ -342,11 +373,18 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
         ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
         if (!ok) break;
         umma::tc_fence_after_sync();
+        if (threadIdx.x == 0) PTRACE(8 + it * 8 + pair * 2);
         const long long toff = (long long)(pair * g.tq) * frame_out;
         const uint32_t taddr = lane_base + (uint32_t)(pair * 256);
         ST *out = spikes + toff;
         const XT *rs = nullptr;   // the residual was already added by the tensor cores
-        if (g.lif && p.mode == 1 && p.hard && g.tq == 2) {
+        const int rows_want = (warp < 4) ? 0xFF : 0x3F;   // rows 14, 15 of a tile never exist
+        // warp-uniform choice: the TMEM loads inside are warp-collective
+        const bool full = __all_sync(0xffffffffu, pm.rows_ok == rows_want && pm.cols_ok == 0xFF);
+        if (g.lif && p.mode == 1 && p.hard && g.tq == 2 && full) {
+          if (warp < 4) pair_epilogue_full<XT, ST, 8>(p, taddr, bias_c, out, frame_out, pm, v);
+          else pair_epilogue_full<XT, ST, 6>(p, taddr, bias_c, out, frame_out, pm, v);
+        } else if (g.lif && p.mode == 1 && p.hard && g.tq == 2) {
           pair_epilogue<XT, ST, kLifFast, true, false>(p, taddr, bias_c, rs, out, frame_out, pm, v);
         } else if (g.lif) {
           if (g.tq == 2) pair_epilogue<XT, ST, kLifAny, true, false>(p, taddr, bias_c, rs, out, frame_out, pm, v);
@@ -355,6 +393,7 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
           if (g.tq == 2) pair_epilogue<XT, ST, kLifOff, true, false>(p, taddr, bias_c, rs, out, frame_out, pm, v);
           else pair_epilogue<XT, ST, kLifOff, false, false>(p, taddr, bias_c, rs, out, frame_out, pm, v);
         }
+        if (threadIdx.x == 0) PTRACE(9 + it * 8 + pair * 2);
         // this accumulator may now be overwritten by the next tile's MMAs
         umma::tc_fence_before_sync();
         __syncwarp();
@@ -429,8 +468,9 @@ int launch(const ConvArgs &a, cudaStream_t stream) {
     if (rc != SNNB_OK) return rc;
   }
   // [identity block] + weight ring + halo ring + room for the junk rows the last descriptor group reads past a slot
-  g.ring = g.has_res ? kPairRing - 1 : kPairRing;
-  const size_t smem = (g.has_res ? (size_t)kIdentBytes : 0) + (size_t)kWRingP * kWSlot + (size_t)g.ring * g.tq * kHaloT +
+  g.ring = kPairRing;
+  g.wring = g.has_res ? kWRingP - 1 : kWRingP;
+  const size_t smem = (g.has_res ? (size_t)kIdentBytes : 0) + (size_t)g.wring * kWSlot + (size_t)g.ring * g.tq * kHaloT +
                       4 * kRowBytes + 1024;
   auto kern = conv3x3_pair_kernel<XT, ST, VT>;
   const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
