@@ -12,7 +12,7 @@ int run(const ConvArgs &a, int path, cudaStream_t stream, const char *what) {
   const bool taps_only = path == SNNB_PATH_TCGEN05_TAPS;
   // The pair kernel always multiplies a 128-channel weight tile, so with Cout <= 64 half of its MMA
   // rows are padding and the halo kernel is faster.
-  static const int min_cout = [] { const char *e = getenv("SNNB_PAIR_MIN_COUT"); return e ? atoi(e) : 65; }();
+  static const int min_cout = [] { const char *e = getenv("SNNB_PAIR_MIN_COUT"); return e ? atoi(e) : 1; }();
   if (!taps_only && path != SNNB_PATH_TCGEN05_HALO && a.Cout >= min_cout && conv3x3_pair_supported(a)) return conv3x3_pair(a, stream);
   if (!taps_only && conv3x3_halo_supported(a)) return conv3x3_halo(a, stream);
   const char *why = "";

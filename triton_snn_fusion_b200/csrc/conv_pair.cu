@@ -59,6 +59,8 @@ struct PairGeom {
   int tmem_cols, lif, has_res, total_tiles;
   int ring;   // halo slots in use
   int wring;  // weight slots in use (<= kWRingP)
+  int dup;    // Cout <= 64: the 64 weight rows are loaded twice (M rows 64..127 repeat 0..63) so that all
+              // eight epilogue warps can read the accumulator and split the pixels four ways
 };
 
 // LIF flavours compiled into the epilogue: the common one (tau a power of two, hard reset) with its
@@ -80,10 +82,11 @@ struct PixMap {
 template <typename XT, typename ST, int KIND, bool TQ2, bool RES>
 __device__ __forceinline__ void pair_epilogue(const LifParams &p, uint32_t tmem_addr, float bias_c,
                                               const XT *__restrict__ res, ST *__restrict__ out, long long frame_out,
-                                              const PixMap &pm, float (&v)[64]) {
+                                              const PixMap &pm, float (&v)[64], int nchunks) {
   // out / res already point at (timestep t0 of the pair, this thread's first row, column w0, channel c)
 #pragma unroll
   for (int chunk = 0; chunk < 4; ++chunk) {
+    if (chunk < nchunks) {   // warp-uniform; written as a guard so that the loop stays fully unrolled
     uint32_t a0[16], a1[16];
     umma::tmem_ld_x16(tmem_addr + (uint32_t)(chunk * 16), a0);
     if (TQ2) umma::tmem_ld_x16(tmem_addr + (uint32_t)(128 + chunk * 16), a1);
@@ -114,12 +117,15 @@ __device__ __forceinline__ void pair_epilogue(const LifParams &p, uint32_t tmem_
         }
       }
     }
+    }
   }
 }
 
-// Hot version: two timesteps, tau a power of two, hard reset, and a tile that lies completely inside
-// the image with a valid channel, so nothing is predicated. NROWS = tile rows of this thread (8 for
-// the warps that own rows 0..7, 6 for those that own rows 8..13).
+// Hot version: two timesteps, tau a power of two, hard reset, a valid channel and a tile that lies
+// completely inside the image, so nothing is predicated. NROWS = tile rows of this thread. The tile
+// grid is laid out so that (for maps of at least 14 x 8) every tile is such a tile: keeping a whole
+// layer on this one code path matters, because alternating between two large unrolled bodies thrashes
+// the instruction cache.
 template <typename XT, typename ST, int NROWS>
 __device__ __forceinline__ void pair_epilogue_full(const LifParams &p, uint32_t tmem_addr, float bias_c,
                                                    ST *__restrict__ out, long long frame_out, const PixMap &pm,
@@ -137,8 +143,8 @@ __device__ __forceinline__ void pair_epilogue_full(const LifParams &p, uint32_t 
       const int o = (chunk * 2 + (i >> 3)) * pm.row_stride + (i & 7) * pm.Cout;   // fits 32 bits: one tile
       float &vv = v[chunk * 16 + i];
       const float s0 = lif_step_t<1, true>(__uint_as_float(a0[i]) + bias_c, vv, p);
-      p0[o] = DT<ST>::from_f(s0);
       const float s1 = lif_step_t<1, true>(__uint_as_float(a1[i]) + bias_c, vv, p);
+      p0[o] = DT<ST>::from_f(s0);
       p1[o] = DT<ST>::from_f(s1);
     }
   }
@@ -147,7 +153,8 @@ __device__ __forceinline__ void pair_epilogue_full(const LifParams &p, uint32_t 
 template <typename XT, typename ST, typename VT>
 __global__ void __launch_bounds__(kThreadsP)
 conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap,
-                    const __grid_constant__ CUtensorMap rmap, const XT *__restrict__ bias, const VT *__restrict__ v_init,
+                    const __grid_constant__ CUtensorMap rmap, const __grid_constant__ CUtensorMap wmap64,
+                    const XT *__restrict__ bias, const VT *__restrict__ v_init,
                     ST *__restrict__ spikes, VT *__restrict__ v_out, const PairGeom g, const LifParams p) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bars[2 * kPairRing + 2 * kWRingP + 4];
@@ -181,8 +188,10 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
     const int rt = m % g.row_tiles;
     b = m / g.row_tiles;
     n0 = n_tile * 128;
-    w0 = strip * 8;
-    h0 = rt * kTileRows;
+    // The last strip / row tile is shifted back inside the image instead of sticking out of it: it then
+    // recomputes a few pixels of its neighbour (both write the same values) and every tile is complete.
+    w0 = min(strip * 8, max(g.Wo - 8, 0));
+    h0 = min(rt * kTileRows, max(g.Ho - kTileRows, 0));
   };
 
   if (threadIdx.x == 0) {
@@ -209,8 +218,9 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
     uint4 *blk = reinterpret_cast<uint4 *>(smem_raw + (ident_base - umma::smem_u32(smem_raw)));
     for (int i = threadIdx.x; i < kIdentBytes / 16; i += 32 * kEpiW) blk[i] = make_uint4(0u, 0u, 0u, 0u);
     asm volatile("bar.sync 2, %0;" ::"r"(32 * kEpiW) : "memory");
-    if (threadIdx.x < 64) {
-      const int k = threadIdx.x, r = 64 + k;
+    if (g.dup ? threadIdx.x < 128 : threadIdx.x < 64) {
+      // dup mode: rows 0..127 carry the identity twice (row r has its one in column r % 64)
+      const int k = threadIdx.x & 63, r = g.dup ? (int)threadIdx.x : 64 + k;
       uint8_t *row = smem_raw + (ident_base - umma::smem_u32(smem_raw)) + r * 128;
       *reinterpret_cast<XT *>(row + (((k >> 3) ^ (r & 7)) << 4) + (k & 7) * 2) = DT<XT>::from_f(1.0f);
     }
@@ -271,7 +281,12 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
               ok = umma::mbar_wait(wempty(ws), wphase, abort_flag);
               if (!ok) break;
               umma::mbar_expect_tx(wfull(ws), (uint32_t)kWSlot);
-              umma::tma_load_2d(w_base + ws * (uint32_t)kWSlot, &wmap, wfull(ws), tap * g.Cin + slab * 64, n0);
+              if (g.dup) {   // the same 64 rows into both halves of the tile
+                umma::tma_load_2d(w_base + ws * (uint32_t)kWSlot, &wmap64, wfull(ws), tap * g.Cin + slab * 64, 0);
+                umma::tma_load_2d(w_base + ws * (uint32_t)kWSlot + 64u * 128u, &wmap64, wfull(ws), tap * g.Cin + slab * 64, 0);
+              } else {
+                umma::tma_load_2d(w_base + ws * (uint32_t)kWSlot, &wmap, wfull(ws), tap * g.Cin + slab * 64, n0);
+              }
               if (++ws == (uint32_t)g.wring) { ws = 0; wphase ^= 1u; }
             }
       }
@@ -320,7 +335,7 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
             ok = umma::mbar_wait(hfull(slot), phase, abort_flag);
             if (!ok) break;
             umma::tc_fence_after_sync();
-            const uint64_t idesc_a = umma::make_sw128_kmajor_desc(ident_base + (rs == 0 ? 64u * 128u : 0u));
+            const uint64_t idesc_a = umma::make_sw128_kmajor_desc(ident_base + ((rs == 0 && !g.dup) ? 64u * 128u : 0u));
             const uint64_t xdesc = hdesc0 + (uint64_t)((slot * slot_bytes + (uint32_t)(kPW + 1) * 128u) >> 4);
 #pragma unroll
             for (int k = 0; k < 4; ++k) umma::mma_f16_ss(d, idesc_a + (uint64_t)(2 * k), xdesc + (uint64_t)(2 * k), idesc, 1u);
@@ -336,7 +351,11 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
   } else {
     // ---------------------------------------------------------------- epilogue
     const int quarter = warp & 3;
-    const int r_begin = (warp < 4) ? 0 : 8;          // the two warps of a lane quarter split the 16 tile rows
+    // Pixel split: normally the two warps of a lane quarter take tile rows 0..7 / 8..15. In dup mode lanes
+    // 64..127 repeat lanes 0..63, so the four warps that see the same 32 channels take 4 rows each.
+    const int r_begin = g.dup ? ((quarter >> 1) * 2 + (warp >> 2)) * 4 : ((warp < 4) ? 0 : 8);
+    const int my_rows = g.dup ? 4 : 8;
+    const int ch_in_tile = g.dup ? (quarter & 1) * 32 + lane : quarter * 32 + lane;
     const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(r_begin * 8);
     const long long frame_out = (long long)g.B * g.Ho * g.Wo * g.Cout;
     bool ok = true;
@@ -344,7 +363,7 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
     for (int tile = blockIdx.x; tile < g.total_tiles && ok; tile += gridDim.x, ++it) {
       int n0, w0, h0, b;
       decode(tile, n0, w0, h0, b);
-      const int c = n0 + quarter * 32 + lane;          // output channel of this thread (= TMEM lane)
+      const int c = n0 + ch_in_tile;                   // output channel of this thread
       const bool c_ok = c < g.Cout;
       const float bias_c = (bias != nullptr && c_ok) ? DT<XT>::to_f(bias[c]) : 0.f;
       PixMap pm;
@@ -355,7 +374,7 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
       pm.cols_ok = 0;
 #pragma unroll
       for (int r = 0; r < 8; ++r)
-        if (c_ok && r_begin + r < kTileRows && h0 + r_begin + r < g.Ho) pm.rows_ok |= 1 << r;
+        if (c_ok && r < my_rows && r_begin + r < kTileRows && h0 + r_begin + r < g.Ho) pm.rows_ok |= 1 << r;
 #pragma unroll
       for (int j = 0; j < 8; ++j)
         if (w0 + j < g.Wo) pm.cols_ok |= 1 << j;
@@ -378,20 +397,24 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
         const uint32_t taddr = lane_base + (uint32_t)(pair * 256);
         ST *out = spikes + toff;
         const XT *rs = nullptr;   // the residual was already added by the tensor cores
-        const int rows_want = (warp < 4) ? 0xFF : 0x3F;   // rows 14, 15 of a tile never exist
+        const int rows_valid = min(my_rows, kTileRows - r_begin);   // rows 14, 15 of a tile never exist
+        const int rows_want = (1 << rows_valid) - 1;
+        const int nchunks = (rows_valid + 1) / 2;
         // warp-uniform choice: the TMEM loads inside are warp-collective
         const bool full = __all_sync(0xffffffffu, pm.rows_ok == rows_want && pm.cols_ok == 0xFF);
         if (g.lif && p.mode == 1 && p.hard && g.tq == 2 && full) {
-          if (warp < 4) pair_epilogue_full<XT, ST, 8>(p, taddr, bias_c, out, frame_out, pm, v);
-          else pair_epilogue_full<XT, ST, 6>(p, taddr, bias_c, out, frame_out, pm, v);
+if (rows_valid == 8) pair_epilogue_full<XT, ST, 8>(p, taddr, bias_c, out, frame_out, pm, v);
+          else if (rows_valid == 6) pair_epilogue_full<XT, ST, 6>(p, taddr, bias_c, out, frame_out, pm, v);
+          else if (rows_valid == 4) pair_epilogue_full<XT, ST, 4>(p, taddr, bias_c, out, frame_out, pm, v);
+          else pair_epilogue_full<XT, ST, 2>(p, taddr, bias_c, out, frame_out, pm, v);
         } else if (g.lif && p.mode == 1 && p.hard && g.tq == 2) {
-          pair_epilogue<XT, ST, kLifFast, true, false>(p, taddr, bias_c, rs, out, frame_out, pm, v);
+          pair_epilogue<XT, ST, kLifFast, true, false>(p, taddr, bias_c, rs, out, frame_out, pm, v, nchunks);
         } else if (g.lif) {
-          if (g.tq == 2) pair_epilogue<XT, ST, kLifAny, true, false>(p, taddr, bias_c, rs, out, frame_out, pm, v);
-          else pair_epilogue<XT, ST, kLifAny, false, false>(p, taddr, bias_c, rs, out, frame_out, pm, v);
+          if (g.tq == 2) pair_epilogue<XT, ST, kLifAny, true, false>(p, taddr, bias_c, rs, out, frame_out, pm, v, nchunks);
+          else pair_epilogue<XT, ST, kLifAny, false, false>(p, taddr, bias_c, rs, out, frame_out, pm, v, nchunks);
         } else {
-          if (g.tq == 2) pair_epilogue<XT, ST, kLifOff, true, false>(p, taddr, bias_c, rs, out, frame_out, pm, v);
-          else pair_epilogue<XT, ST, kLifOff, false, false>(p, taddr, bias_c, rs, out, frame_out, pm, v);
+          if (g.tq == 2) pair_epilogue<XT, ST, kLifOff, true, false>(p, taddr, bias_c, rs, out, frame_out, pm, v, nchunks);
+          else pair_epilogue<XT, ST, kLifOff, false, false>(p, taddr, bias_c, rs, out, frame_out, pm, v, nchunks);
         }
         if (threadIdx.x == 0) PTRACE(9 + it * 8 + pair * 2);
         // this accumulator may now be overwritten by the next tile's MMAs
@@ -458,6 +481,16 @@ int launch(const ConvArgs &a, cudaStream_t stream) {
     const int rc = encode_tmap(&wm, a.dtype, 2, a.w, dims, strides, box);
     if (rc != SNNB_OK) return rc;
   }
+  g.dup = a.Cout <= 64 ? 1 : 0;
+  CUtensorMap wm64 = wm;
+  if (g.dup) {
+    const cuuint64_t K = (cuuint64_t)9 * a.Cin;
+    cuuint64_t dims[2] = {K, (cuuint64_t)a.Cout};
+    cuuint64_t strides[1] = {K * es};
+    cuuint32_t box[2] = {64, 64};
+    const int rc = encode_tmap(&wm64, a.dtype, 2, a.w, dims, strides, box);
+    if (rc != SNNB_OK) return rc;
+  }
   CUtensorMap rm = xm;
   if (g.has_res) {   // the residual has the output's shape: [T][B][Ho][Wo][Cout]
     cuuint64_t dims[5] = {(cuuint64_t)a.Cout, (cuuint64_t)a.Wo, (cuuint64_t)a.Ho, (cuuint64_t)a.B, (cuuint64_t)a.T};
@@ -475,7 +508,7 @@ int launch(const ConvArgs &a, cudaStream_t stream) {
   auto kern = conv3x3_pair_kernel<XT, ST, VT>;
   const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return fail(SNNB_ERR_CUDA, "conv_lif: cannot raise the shared-memory limit: %s", cudaGetErrorString(e));
-  kern<<<(unsigned)grid, kThreadsP, smem, stream>>>(xm, wm, rm, static_cast<const XT *>(a.b),
+  kern<<<(unsigned)grid, kThreadsP, smem, stream>>>(xm, wm, rm, wm64, static_cast<const XT *>(a.b),
                                                     static_cast<const VT *>(a.v_init), static_cast<ST *>(a.spikes),
                                                     static_cast<VT *>(a.v_out), g, a.p);
   SNNB_CHECK_LAUNCH("conv3x3_pair");
@@ -500,7 +533,7 @@ bool conv3x3_pair_supported(const ConvArgs &a) {
   if (a.Cin % 64 != 0) return false;
   if (a.x_t_stride == 0 && a.T > 1) return false;   // one frame for all steps: left to the other kernels
   if (a.T != 1 && a.T != 2 && a.T != 4) return false;
-  if (a.Ho < 8) return false;   // small maps: the stacked-image tiles of conv_halo.cu waste fewer rows
+  if (a.Ho < 8 || a.Wo < 8) return false;   // small maps: the stacked-image tiles of conv_halo.cu waste fewer rows
   if (a.xs_w || a.xs_h || a.xs_b || a.xd_w || a.xd_h) return false;
   if (a.x_t_stride % 8 != 0) return false;
   if (!aligned16(a.x) || !aligned16(a.w)) return false;
