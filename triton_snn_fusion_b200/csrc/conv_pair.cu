@@ -1,531 +1,13 @@
-// 3x3 / stride 1 / padding 1 conv (+ bias, + residual) + LIF over T <= 4 with the operand roles
-// swapped so that one tcgen05.mma covers 256 output pixels.
-//
-// Measured on B200: a tcgen05.mma (cta_group::1, K = 16) occupies the tensor pipe for ~128 cycles
-// whether its N is 64, 128 or 256, so only N = 256 instructions reach the pipe's rate. With output
-// pixels as the M dimension (conv_tc.cu, conv_halo.cu) N is the channel tile and T accumulators of
-// 256 columns do not fit the 512 TMEM columns. Here the weight tile is the M operand (128 output
-// channels, rows beyond Cout are zero) and the pixels of TWO consecutive timesteps are the N operand:
-//
-//   D_pair[cout][tq * 128 + pixel] = sum_(tap, slab)  W[cout][tap, slab] . X_(2*pair+tq)[pixel + tap][slab]^T
-//
-// A CTA owns 8 (wide) x 14 (high) output pixels. Per 64-channel slab and timestep it keeps the
-// 10 x 16 input pixels those need (a 20 KB halo tile; out-of-image pixels arrive as zeros = padding);
-// the halo tiles of a timestep pair are adjacent in shared memory, so a K-major operand descriptor
-// with its start shifted by (kh * 10 + kw) rows and 8-row groups one halo row (1280 bytes) apart
-// addresses 32 groups = 16 output rows x 8 pixels for each of the two timesteps (rows 14, 15 of each
-// are junk and never stored). All nine taps are read from that one copy.
-//
-// Timestep pairs are processed one after the other: pair 0 (t = 0, 1) is accumulated over all slabs
-// and taps into TMEM columns 0..255, then pair 1 into 256..511. The epilogue warps convert pair 0
-// (bias, residual, LIF steps 0 and 1, spikes out) while the MMA warp works on pair 1, keep the membrane
-// potentials in registers, and finish with pair 1. TMEM lane = output channel, so a thread owns one
-// channel of 64 pixels and a warp's stores cover 32 consecutive channels of one pixel.
-#include <type_traits>
-
+// Host-side gate of the timestep-pair conv kernel (conv_pair_impl.cuh): which calls it takes, and the
+// routing to the per-dtype translation units.
 #include "conv.cuh"
-#include "tmap.cuh"
-#include "umma.cuh"
 
 namespace snnb {
 
-static __device__ int g_pair_status = 0;
-
-#ifdef SNNB_TC_TRACE
-static __device__ long long g_ptrace[64];
-#define PTRACE(idx) do { if (blockIdx.x == 100 && (idx) < 64) g_ptrace[idx] = clock64(); } while (0)
-#else
-#define PTRACE(idx) do { } while (0)
-#endif
-
-namespace {
-
-constexpr int kPW = 10, kPH = 16;                      // halo tile: 10 x 16 pixels
-constexpr int kRowBytes = kPW * 128;                   // 1280
-constexpr int kHaloT = kPW * kPH * 128;                // 20480 bytes per timestep
-constexpr int kTileRows = 14;                          // valid output rows per tile
-constexpr int kPairRing = 3;                           // halo (pair) slots
-constexpr int kIdentBytes = 192 * 128;                 // zero rows / 64x64 identity / zero rows, see the residual path
-constexpr int kWRingP = 5;                             // weight-tile slots (16 KB each): a load must cover ~1 us of L2 latency
-constexpr int kWSlot = 128 * 128;
-constexpr int kEpiW = 8;
-constexpr int kHaloWarpP = kEpiW, kWWarpP = kEpiW + 1, kMmaWarpP = kEpiW + 2;
-constexpr int kThreadsP = 32 * (kEpiW + 3);
-
-struct PairGeom {
-  int T, Tacc, B, Cin, Cout, Ho, Wo;
-  int kslabs, npairs, tq;   // tq = timesteps per pair (1 or 2)
-  int n_tiles_n, row_tiles, w_strips;
-  int tmem_cols, lif, has_res, total_tiles;
-  int ring;   // halo slots in use
-  int wring;  // weight slots in use (<= kWRingP)
-  int dup;    // Cout <= 64: the 64 weight rows are loaded twice (M rows 64..127 repeat 0..63) so that all
-              // eight epilogue warps can read the accumulator and split the pixels four ways
-};
-
-// LIF flavours compiled into the epilogue: the common one (tau a power of two, hard reset) with its
-// branches resolved at compile time, every other kind through the run-time lif_step, or no LIF.
-enum : int { kLifFast = 0, kLifAny = 1, kLifOff = 2 };
-
-// Where this thread's 64 pixels of the current tile live in the output.
-struct PixMap {
-  long long row0_off;   // element offset of (tile row 0 of this thread, column w0, channel c) inside a frame
-  int row_stride;       // Wo * Cout
-  int Cout;
-  int rows_ok;          // bit r set: this thread's r-th tile row (0..7) exists in the image and in the tile
-  int cols_ok;          // bit j set: column w0 + j exists
-};
-
-// Converts one timestep pair for the 64 pixels of this thread's channel: TMEM -> + bias (+ residual)
-// -> LIF (membrane in v[]) -> spikes. TQ2: the pair holds two timesteps; RES: a residual is added.
-// General version: every pixel is predicated on the tile / image edges.
-template <typename XT, typename ST, int KIND, bool TQ2, bool RES>
-__device__ __forceinline__ void pair_epilogue(const LifParams &p, uint32_t tmem_addr, float bias_c,
-                                              const XT *__restrict__ res, ST *__restrict__ out, long long frame_out,
-                                              const PixMap &pm, float (&v)[64], int nchunks) {
-  // out / res already point at (timestep t0 of the pair, this thread's first row, column w0, channel c)
-#pragma unroll
-  for (int chunk = 0; chunk < 4; ++chunk) {
-    if (chunk < nchunks) {   // warp-uniform; written as a guard so that the loop stays fully unrolled
-    uint32_t a0[16], a1[16];
-    umma::tmem_ld_x16(tmem_addr + (uint32_t)(chunk * 16), a0);
-    if (TQ2) umma::tmem_ld_x16(tmem_addr + (uint32_t)(128 + chunk * 16), a1);
-    umma::tmem_ld_wait();
-#pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      const int r = chunk * 2 + (i >> 3), j = i & 7;   // a chunk of 16 pixels is two tile rows of 8
-      const bool ok = ((pm.rows_ok >> r) & 1) && ((pm.cols_ok >> j) & 1);
-      const long long o = pm.row0_off + (long long)r * pm.row_stride + j * pm.Cout;
-      float y0 = __uint_as_float(a0[i]) + bias_c;
-      float y1 = TQ2 ? __uint_as_float(a1[i]) + bias_c : 0.f;
-      if (ok) {
-        if (RES && res != nullptr) {
-          y0 += DT<XT>::to_f(res[o]);
-          if (TQ2) y1 += DT<XT>::to_f(res[o + frame_out]);
-        }
-        if constexpr (KIND == kLifOff) {
-          reinterpret_cast<XT *>(out)[o] = DT<XT>::from_f(y0);
-          if (TQ2) reinterpret_cast<XT *>(out)[o + frame_out] = DT<XT>::from_f(y1);
-        } else {
-          float &vv = v[chunk * 16 + i];
-          const float s0 = (KIND == kLifFast) ? lif_step_t<1, true>(y0, vv, p) : lif_step(y0, vv, p);
-          out[o] = DT<ST>::from_f(s0);
-          if (TQ2) {
-            const float s1 = (KIND == kLifFast) ? lif_step_t<1, true>(y1, vv, p) : lif_step(y1, vv, p);
-            out[o + frame_out] = DT<ST>::from_f(s1);
-          }
-        }
-      }
-    }
-    }
-  }
-}
-
-// Hot version: two timesteps, tau a power of two, hard reset, a valid channel and a tile that lies
-// completely inside the image, so nothing is predicated. NROWS = tile rows of this thread. The tile
-// grid is laid out so that (for maps of at least 14 x 8) every tile is such a tile: keeping a whole
-// layer on this one code path matters, because alternating between two large unrolled bodies thrashes
-// the instruction cache.
-template <typename XT, typename ST, int NROWS>
-__device__ __forceinline__ void pair_epilogue_full(const LifParams &p, uint32_t tmem_addr, float bias_c,
-                                                   ST *__restrict__ out, long long frame_out, const PixMap &pm,
-                                                   float (&v)[64]) {
-  ST *const p0 = out + pm.row0_off;
-  ST *const p1 = p0 + frame_out;
-#pragma unroll
-  for (int chunk = 0; chunk < NROWS / 2; ++chunk) {
-    uint32_t a0[16], a1[16];
-    umma::tmem_ld_x16(tmem_addr + (uint32_t)(chunk * 16), a0);
-    umma::tmem_ld_x16(tmem_addr + (uint32_t)(128 + chunk * 16), a1);
-    umma::tmem_ld_wait();
-#pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      const int o = (chunk * 2 + (i >> 3)) * pm.row_stride + (i & 7) * pm.Cout;   // fits 32 bits: one tile
-      float &vv = v[chunk * 16 + i];
-      const float s0 = lif_step_t<1, true>(__uint_as_float(a0[i]) + bias_c, vv, p);
-      const float s1 = lif_step_t<1, true>(__uint_as_float(a1[i]) + bias_c, vv, p);
-      p0[o] = DT<ST>::from_f(s0);
-      p1[o] = DT<ST>::from_f(s1);
-    }
-  }
-}
-
-template <typename XT, typename ST, typename VT>
-__global__ void __launch_bounds__(kThreadsP)
-conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap,
-                    const __grid_constant__ CUtensorMap rmap, const __grid_constant__ CUtensorMap wmap64,
-                    const XT *__restrict__ bias, const VT *__restrict__ v_init,
-                    ST *__restrict__ spikes, VT *__restrict__ v_out, const PairGeom g, const LifParams p) {
-  extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t bars[2 * kPairRing + 2 * kWRingP + 4];
-  __shared__ uint32_t tmem_base_s;
-  __shared__ int abort_s;
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-
-  const uint32_t smem_base = (umma::smem_u32(smem_raw) + 1023u) & ~1023u;
-  // [identity block (residual path only)] [weight ring] [halo ring]
-  const uint32_t ident_base = smem_base;
-  const uint32_t w_base = smem_base + (g.has_res ? (uint32_t)kIdentBytes : 0u);
-  const uint32_t h_base = w_base + (uint32_t)(g.wring * kWSlot);
-  const uint32_t slot_bytes = (uint32_t)(g.tq * kHaloT);
-  const uint32_t bar_base = umma::smem_u32(bars);
-  auto hfull = [&](uint32_t s) { return bar_base + 8u * s; };
-  auto hempty = [&](uint32_t s) { return bar_base + 8u * ((uint32_t)kPairRing + s); };
-  auto wfull = [&](uint32_t s) { return bar_base + 8u * (2u * kPairRing + s); };
-  auto wempty = [&](uint32_t s) { return bar_base + 8u * (2u * kPairRing + kWRingP + s); };
-  auto accfull = [&](uint32_t s) { return bar_base + 8u * (2u * kPairRing + 2u * kWRingP + s); };
-  auto accempty = [&](uint32_t s) { return bar_base + 8u * (2u * kPairRing + 2u * kWRingP + 2u + s); };
-  volatile int *abort_flag = &abort_s;
-
-  // A CTA walks tiles blockIdx.x, blockIdx.x + gridDim.x, ...; tile index -> (image, row tile, column
-  // strip, channel tile) with the channel tile fastest so neighbouring CTAs share their halo tiles in L2.
-  auto decode = [&](int tile, int &n0, int &w0, int &h0, int &b) {
-    const int n_tile = tile % g.n_tiles_n;
-    int m = tile / g.n_tiles_n;
-    const int strip = m % g.w_strips;
-    m /= g.w_strips;
-    const int rt = m % g.row_tiles;
-    b = m / g.row_tiles;
-    n0 = n_tile * 128;
-    // The last strip / row tile is shifted back inside the image instead of sticking out of it: it then
-    // recomputes a few pixels of its neighbour (both write the same values) and every tile is complete.
-    w0 = min(strip * 8, max(g.Wo - 8, 0));
-    h0 = min(rt * kTileRows, max(g.Ho - kTileRows, 0));
-  };
-
-  if (threadIdx.x == 0) {
-    abort_s = 0;
-    for (int s = 0; s < g.ring; ++s) { umma::mbar_init(hfull(s), 1); umma::mbar_init(hempty(s), 1); }
-    for (int s = 0; s < g.wring; ++s) { umma::mbar_init(wfull(s), 1); umma::mbar_init(wempty(s), 1); }
-    for (int s = 0; s < 2; ++s) { umma::mbar_init(accfull(s), 1); umma::mbar_init(accempty(s), kEpiW); }
-    umma::fence_mbar_init();
-  }
-  if (warp == kMmaWarpP) {
-    umma::tmem_alloc(umma::smem_u32(&tmem_base_s), (uint32_t)g.tmem_cols);
-    umma::tmem_relinquish();
-  }
-  if (warp == kHaloWarpP && lane == 0) {
-    umma::prefetch_tensormap(&xmap);
-    umma::prefetch_tensormap(&wmap);
-    if (g.has_res) umma::prefetch_tensormap(&rmap);
-  }
-  if (g.has_res && warp < kEpiW) {
-    // Residual add on the tensor cores: D += I . R with a 64x64 identity as the weight operand. The block
-    // is 192 rows of 128 bytes: 64 zero rows, the identity (row 64 + k has a one in column k, stored where
-    // the 128-byte swizzle puts it), 64 zero rows. Read from row 64 it is [I; 0] (channels n0..n0+63 of the
-    // tile), read from row 0 it is [0; I] (channels n0+64..n0+127).
-    uint4 *blk = reinterpret_cast<uint4 *>(smem_raw + (ident_base - umma::smem_u32(smem_raw)));
-    for (int i = threadIdx.x; i < kIdentBytes / 16; i += 32 * kEpiW) blk[i] = make_uint4(0u, 0u, 0u, 0u);
-    asm volatile("bar.sync 2, %0;" ::"r"(32 * kEpiW) : "memory");
-    if (g.dup ? threadIdx.x < 128 : threadIdx.x < 64) {
-      // dup mode: rows 0..127 carry the identity twice (row r has its one in column r % 64)
-      const int k = threadIdx.x & 63, r = g.dup ? (int)threadIdx.x : 64 + k;
-      uint8_t *row = smem_raw + (ident_base - umma::smem_u32(smem_raw)) + r * 128;
-      *reinterpret_cast<XT *>(row + (((k >> 3) ^ (r & 7)) << 4) + (k & 7) * 2) = DT<XT>::from_f(1.0f);
-    }
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // make the writes visible to the MMA unit
-  }
-  umma::tc_fence_before_sync();
-  __syncthreads();
-  umma::tc_fence_after_sync();
-  const uint32_t tmem_base = tmem_base_s;
-  if (threadIdx.x == 0) PTRACE(0);
-
-  if (warp == kHaloWarpP) {
-    // ------------------------------------------------- halo producer: lane q loads timestep q of the pair
-    uint32_t slot = 0, phase = 1;
-    bool ok = true;
-    for (int tile = blockIdx.x; tile < g.total_tiles && ok; tile += gridDim.x) {
-      int n0, w0, h0, b;
-      decode(tile, n0, w0, h0, b);
-      for (int pair = 0; pair < g.npairs && ok; ++pair) {
-        for (int slab = 0; slab < g.kslabs; ++slab) {
-          if (lane == 0) {
-            ok = umma::mbar_wait(hempty(slot), phase, abort_flag);
-            if (ok) umma::mbar_expect_tx(hfull(slot), slot_bytes);
-          }
-          ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
-          if (!ok) break;
-          if (lane < g.tq)
-            umma::tma_load_5d(h_base + slot * slot_bytes + (uint32_t)lane * kHaloT, &xmap, hfull(slot), slab * 64,
-                              w0 - 1, h0 - 1, b, pair * g.tq + lane);
-          if (++slot == (uint32_t)g.ring) { slot = 0; phase ^= 1u; }
-        }
-        // residual tiles of this pair: one per 64-channel half of the output-channel tile
-        for (int rs = 0; rs < 2 && g.has_res && ok; ++rs) {
-          if (n0 + rs * 64 >= g.Cout) break;
-          if (lane == 0) {
-            ok = umma::mbar_wait(hempty(slot), phase, abort_flag);
-            if (ok) umma::mbar_expect_tx(hfull(slot), slot_bytes);
-          }
-          ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
-          if (!ok) break;
-          if (lane < g.tq)
-            umma::tma_load_5d(h_base + slot * slot_bytes + (uint32_t)lane * kHaloT, &rmap, hfull(slot), n0 + rs * 64,
-                              w0 - 1, h0 - 1, b, pair * g.tq + lane);
-          if (++slot == (uint32_t)g.ring) { slot = 0; phase ^= 1u; }
-        }
-      }
-    }
-  } else if (warp == kWWarpP) {
-    // ---------------------------------------------------------- weight producer
-    if (lane == 0) {
-      uint32_t ws = 0, wphase = 1;
-      bool ok = true;
-      for (int tile = blockIdx.x; tile < g.total_tiles && ok; tile += gridDim.x) {
-        const int n0 = (tile % g.n_tiles_n) * 128;
-        for (int pair = 0; pair < g.npairs && ok; ++pair)
-          for (int slab = 0; slab < g.kslabs && ok; ++slab)
-            for (int tap = 0; tap < 9; ++tap) {
-              ok = umma::mbar_wait(wempty(ws), wphase, abort_flag);
-              if (!ok) break;
-              umma::mbar_expect_tx(wfull(ws), (uint32_t)kWSlot);
-              if (g.dup) {   // the same 64 rows into both halves of the tile
-                umma::tma_load_2d(w_base + ws * (uint32_t)kWSlot, &wmap64, wfull(ws), tap * g.Cin + slab * 64, 0);
-                umma::tma_load_2d(w_base + ws * (uint32_t)kWSlot + 64u * 128u, &wmap64, wfull(ws), tap * g.Cin + slab * 64, 0);
-              } else {
-                umma::tma_load_2d(w_base + ws * (uint32_t)kWSlot, &wmap, wfull(ws), tap * g.Cin + slab * 64, n0);
-              }
-              if (++ws == (uint32_t)g.wring) { ws = 0; wphase ^= 1u; }
-            }
-      }
-    }
-    __syncwarp();
-  } else if (warp == kMmaWarpP) {
-    // -------------------------------------------------------------- MMA issuer
-    if (lane == 0) {
-      const uint32_t idesc = umma::make_idesc_f16(128, 128 * g.tq, std::is_same<XT, __nv_bfloat16>::value);
-      uint64_t hdesc0 = umma::make_sw128_kmajor_desc(h_base);
-      hdesc0 = (hdesc0 & ~((uint64_t)0x3FFF << 32)) | ((uint64_t)(kRowBytes >> 4) << 32);
-      const uint64_t wdesc0 = umma::make_sw128_kmajor_desc(w_base);
-      uint32_t slot = 0, phase = 0, ws = 0, wphase = 0, it = 0;
-      bool ok = true;
-      for (int tile = blockIdx.x; tile < g.total_tiles && ok; tile += gridDim.x, ++it) {
-        for (int pair = 0; pair < g.npairs && ok; ++pair) {
-          // the epilogue warps must have drained this accumulator (previous tile) before it is overwritten
-          ok = umma::mbar_wait(accempty(pair), (it & 1u) ^ 1u, abort_flag);
-          if (!ok) break;
-          umma::tc_fence_after_sync();
-          const uint32_t d = tmem_base + (uint32_t)(pair * 256);
-          for (int slab = 0; slab < g.kslabs && ok; ++slab) {
-            ok = umma::mbar_wait(hfull(slot), phase, abort_flag);
-            if (!ok) break;
-            for (int tap = 0; tap < 9; ++tap) {
-              ok = umma::mbar_wait(wfull(ws), wphase, abort_flag);
-              if (!ok) break;
-              umma::tc_fence_after_sync();
-              const int kh = tap / 3, kw = tap - kh * 3;
-              const uint64_t xdesc = hdesc0 + (uint64_t)((slot * slot_bytes + (uint32_t)(kh * kPW + kw) * 128u) >> 4);
-              const uint64_t wdesc = wdesc0 + (uint64_t)((ws * (uint32_t)kWSlot) >> 4);
-#pragma unroll
-              for (int k = 0; k < 4; ++k)   // A = weights (M = 128 channels), B = pixels (N = 128 per timestep)
-                umma::mma_f16_ss(d, wdesc + (uint64_t)(2 * k), xdesc + (uint64_t)(2 * k), idesc,
-                                 (slab > 0 || tap > 0 || k > 0) ? 1u : 0u);
-              umma::mma_commit(wempty(ws));
-              if (++ws == (uint32_t)g.wring) { ws = 0; wphase ^= 1u; }
-            }
-            if (ok) umma::mma_commit(hempty(slot));
-            if (++slot == (uint32_t)g.ring) { slot = 0; phase ^= 1u; }
-          }
-          // residual: accumulate I . R (centre tap of the residual's halo tile)
-          const int n0 = (tile % g.n_tiles_n) * 128;
-          for (int rs = 0; rs < 2 && g.has_res && ok; ++rs) {
-            if (n0 + rs * 64 >= g.Cout) break;
-            ok = umma::mbar_wait(hfull(slot), phase, abort_flag);
-            if (!ok) break;
-            umma::tc_fence_after_sync();
-            const uint64_t idesc_a = umma::make_sw128_kmajor_desc(ident_base + ((rs == 0 && !g.dup) ? 64u * 128u : 0u));
-            const uint64_t xdesc = hdesc0 + (uint64_t)((slot * slot_bytes + (uint32_t)(kPW + 1) * 128u) >> 4);
-#pragma unroll
-            for (int k = 0; k < 4; ++k) umma::mma_f16_ss(d, idesc_a + (uint64_t)(2 * k), xdesc + (uint64_t)(2 * k), idesc, 1u);
-            umma::mma_commit(hempty(slot));
-            if (++slot == (uint32_t)g.ring) { slot = 0; phase ^= 1u; }
-          }
-          if (ok) umma::mma_commit(accfull(pair));
-          PTRACE(12 + it * 8 + pair);
-        }
-      }
-    }
-    __syncwarp();
-  } else {
-    // ---------------------------------------------------------------- epilogue
-    const int quarter = warp & 3;
-    // Pixel split: normally the two warps of a lane quarter take tile rows 0..7 / 8..15. In dup mode lanes
-    // 64..127 repeat lanes 0..63, so the four warps that see the same 32 channels take 4 rows each.
-    const int r_begin = g.dup ? ((quarter >> 1) * 2 + (warp >> 2)) * 4 : ((warp < 4) ? 0 : 8);
-    const int my_rows = g.dup ? 4 : 8;
-    const int ch_in_tile = g.dup ? (quarter & 1) * 32 + lane : quarter * 32 + lane;
-    const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(r_begin * 8);
-    const long long frame_out = (long long)g.B * g.Ho * g.Wo * g.Cout;
-    bool ok = true;
-    uint32_t it = 0;
-    for (int tile = blockIdx.x; tile < g.total_tiles && ok; tile += gridDim.x, ++it) {
-      int n0, w0, h0, b;
-      decode(tile, n0, w0, h0, b);
-      const int c = n0 + ch_in_tile;                   // output channel of this thread
-      const bool c_ok = c < g.Cout;
-      const float bias_c = (bias != nullptr && c_ok) ? DT<XT>::to_f(bias[c]) : 0.f;
-      PixMap pm;
-      pm.Cout = g.Cout;
-      pm.row_stride = g.Wo * g.Cout;
-      pm.row0_off = ((long long)b * g.Ho + (h0 + r_begin)) * pm.row_stride + (long long)w0 * g.Cout + c;
-      pm.rows_ok = 0;
-      pm.cols_ok = 0;
-#pragma unroll
-      for (int r = 0; r < 8; ++r)
-        if (c_ok && r < my_rows && r_begin + r < kTileRows && h0 + r_begin + r < g.Ho) pm.rows_ok |= 1 << r;
-#pragma unroll
-      for (int j = 0; j < 8; ++j)
-        if (w0 + j < g.Wo) pm.cols_ok |= 1 << j;
-      float v[64];
-#pragma unroll
-      for (int i = 0; i < 64; ++i) v[i] = 0.f;
-      if (g.lif && v_init != nullptr) {
-#pragma unroll
-        for (int i = 0; i < 64; ++i)
-          if (((pm.rows_ok >> (i >> 3)) & 1) && ((pm.cols_ok >> (i & 7)) & 1))
-            v[i] = DT<VT>::to_f(v_init[pm.row0_off + (long long)(i >> 3) * pm.row_stride + (i & 7) * pm.Cout]);
-      }
-      for (int pair = 0; pair < g.npairs && ok; ++pair) {
-        if (lane == 0) ok = umma::mbar_wait(accfull(pair), it & 1u, abort_flag);
-        ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
-        if (!ok) break;
-        umma::tc_fence_after_sync();
-        if (threadIdx.x == 0) PTRACE(8 + it * 8 + pair * 2);
-        const long long toff = (long long)(pair * g.tq) * frame_out;
-        const uint32_t taddr = lane_base + (uint32_t)(pair * 256);
-        ST *out = spikes + toff;
-        const XT *rs = nullptr;   // the residual was already added by the tensor cores
-        const int rows_valid = min(my_rows, kTileRows - r_begin);   // rows 14, 15 of a tile never exist
-        const int rows_want = (1 << rows_valid) - 1;
-        const int nchunks = (rows_valid + 1) / 2;
-        // warp-uniform choice: the TMEM loads inside are warp-collective
-        const bool full = __all_sync(0xffffffffu, pm.rows_ok == rows_want && pm.cols_ok == 0xFF);
-        if (g.lif && p.mode == 1 && p.hard && g.tq == 2 && full) {
-if (rows_valid == 8) pair_epilogue_full<XT, ST, 8>(p, taddr, bias_c, out, frame_out, pm, v);
-          else if (rows_valid == 6) pair_epilogue_full<XT, ST, 6>(p, taddr, bias_c, out, frame_out, pm, v);
-          else if (rows_valid == 4) pair_epilogue_full<XT, ST, 4>(p, taddr, bias_c, out, frame_out, pm, v);
-          else pair_epilogue_full<XT, ST, 2>(p, taddr, bias_c, out, frame_out, pm, v);
-        } else if (g.lif && p.mode == 1 && p.hard && g.tq == 2) {
-          pair_epilogue<XT, ST, kLifFast, true, false>(p, taddr, bias_c, rs, out, frame_out, pm, v, nchunks);
-        } else if (g.lif) {
-          if (g.tq == 2) pair_epilogue<XT, ST, kLifAny, true, false>(p, taddr, bias_c, rs, out, frame_out, pm, v, nchunks);
-          else pair_epilogue<XT, ST, kLifAny, false, false>(p, taddr, bias_c, rs, out, frame_out, pm, v, nchunks);
-        } else {
-          if (g.tq == 2) pair_epilogue<XT, ST, kLifOff, true, false>(p, taddr, bias_c, rs, out, frame_out, pm, v, nchunks);
-          else pair_epilogue<XT, ST, kLifOff, false, false>(p, taddr, bias_c, rs, out, frame_out, pm, v, nchunks);
-        }
-        if (threadIdx.x == 0) PTRACE(9 + it * 8 + pair * 2);
-        // this accumulator may now be overwritten by the next tile's MMAs
-        umma::tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) umma::mbar_arrive(accempty(pair));
-      }
-      if (ok && g.lif) {
-#pragma unroll
-        for (int i = 0; i < 64; ++i)
-          if (((pm.rows_ok >> (i >> 3)) & 1) && ((pm.cols_ok >> (i & 7)) & 1))
-            v_out[pm.row0_off + (long long)(i >> 3) * pm.row_stride + (i & 7) * pm.Cout] = DT<VT>::from_f(v[i]);
-      }
-    }
-  }
-
-  umma::tc_fence_before_sync();
-  __syncthreads();
-  if (abort_s && threadIdx.x == 0) atomicExch(&g_pair_status, 1);
-  if (warp == kMmaWarpP) {
-    umma::tc_fence_after_sync();
-    umma::tmem_dealloc(tmem_base, (uint32_t)g.tmem_cols);
-  }
-}
-
-template <typename XT, typename ST, typename VT>
-int launch(const ConvArgs &a, cudaStream_t stream) {
-  PairGeom g;
-  g.T = a.T;
-  g.Tacc = (a.x_t_stride == 0) ? 1 : a.T;
-  g.B = a.B; g.Cin = a.Cin; g.Cout = a.Cout; g.Ho = a.Ho; g.Wo = a.Wo;
-  g.kslabs = a.Cin / 64;
-  g.tq = g.Tacc >= 2 ? 2 : 1;
-  g.npairs = g.Tacc / g.tq;
-  g.n_tiles_n = (a.Cout + 127) / 128;
-  g.row_tiles = (a.Ho + kTileRows - 1) / kTileRows;
-  g.w_strips = (a.Wo + 7) / 8;
-  g.tmem_cols = g.npairs * 256 > 256 ? 512 : (g.tq == 2 ? 256 : 128);
-  g.lif = a.lif;
-  g.has_res = a.res != nullptr;
-  const long long tiles = (long long)a.B * g.row_tiles * g.w_strips * g.n_tiles_n;
-  if (tiles > 0x7fffffffLL) return fail(SNNB_ERR_INVALID, "conv_lif: problem too large for the grid");
-  g.total_tiles = (int)tiles;
-  int dev = 0, sms = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 1)
-    return fail(SNNB_ERR_CUDA, "conv_lif: cannot query the SM count");
-  const long long grid = tiles < sms ? tiles : sms;   // persistent: one CTA per SM walks the tiles
-  const int es = 2;
-  CUtensorMap xm, wm;
-  {
-    cuuint64_t dims[5] = {(cuuint64_t)a.Cin, (cuuint64_t)a.W, (cuuint64_t)a.H, (cuuint64_t)a.B, (cuuint64_t)g.Tacc};
-    const cuuint64_t frame_bytes = (cuuint64_t)a.B * a.H * a.W * a.Cin * es;
-    cuuint64_t strides[4] = {(cuuint64_t)a.Cin * es, (cuuint64_t)a.W * a.Cin * es, (cuuint64_t)a.H * a.W * a.Cin * es,
-                             g.Tacc > 1 ? (cuuint64_t)a.x_t_stride * es : frame_bytes};
-    cuuint32_t box[5] = {64, (cuuint32_t)kPW, (cuuint32_t)kPH, 1, 1};
-    const int rc = encode_tmap(&xm, a.dtype, 5, a.x, dims, strides, box);
-    if (rc != SNNB_OK) return rc;
-  }
-  {
-    const cuuint64_t K = (cuuint64_t)9 * a.Cin;
-    cuuint64_t dims[2] = {K, (cuuint64_t)a.Cout};
-    cuuint64_t strides[1] = {K * es};
-    cuuint32_t box[2] = {64, 128};
-    const int rc = encode_tmap(&wm, a.dtype, 2, a.w, dims, strides, box);
-    if (rc != SNNB_OK) return rc;
-  }
-  g.dup = a.Cout <= 64 ? 1 : 0;
-  CUtensorMap wm64 = wm;
-  if (g.dup) {
-    const cuuint64_t K = (cuuint64_t)9 * a.Cin;
-    cuuint64_t dims[2] = {K, (cuuint64_t)a.Cout};
-    cuuint64_t strides[1] = {K * es};
-    cuuint32_t box[2] = {64, 64};
-    const int rc = encode_tmap(&wm64, a.dtype, 2, a.w, dims, strides, box);
-    if (rc != SNNB_OK) return rc;
-  }
-  CUtensorMap rm = xm;
-  if (g.has_res) {   // the residual has the output's shape: [T][B][Ho][Wo][Cout]
-    cuuint64_t dims[5] = {(cuuint64_t)a.Cout, (cuuint64_t)a.Wo, (cuuint64_t)a.Ho, (cuuint64_t)a.B, (cuuint64_t)a.T};
-    cuuint64_t strides[4] = {(cuuint64_t)a.Cout * es, (cuuint64_t)a.Wo * a.Cout * es, (cuuint64_t)a.Ho * a.Wo * a.Cout * es,
-                             (cuuint64_t)a.B * a.Ho * a.Wo * a.Cout * es};
-    cuuint32_t box[5] = {64, (cuuint32_t)kPW, (cuuint32_t)kPH, 1, 1};
-    const int rc = encode_tmap(&rm, a.dtype, 5, a.res, dims, strides, box);
-    if (rc != SNNB_OK) return rc;
-  }
-  // [identity block] + weight ring + halo ring + room for the junk rows the last descriptor group reads past a slot
-  g.ring = kPairRing;
-  g.wring = g.has_res ? kWRingP - 1 : kWRingP;
-  const size_t smem = (g.has_res ? (size_t)kIdentBytes : 0) + (size_t)g.wring * kWSlot + (size_t)g.ring * g.tq * kHaloT +
-                      4 * kRowBytes + 1024;
-  auto kern = conv3x3_pair_kernel<XT, ST, VT>;
-  const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  if (e != cudaSuccess) return fail(SNNB_ERR_CUDA, "conv_lif: cannot raise the shared-memory limit: %s", cudaGetErrorString(e));
-  kern<<<(unsigned)grid, kThreadsP, smem, stream>>>(xm, wm, rm, wm64, static_cast<const XT *>(a.b),
-                                                    static_cast<const VT *>(a.v_init), static_cast<ST *>(a.spikes),
-                                                    static_cast<VT *>(a.v_out), g, a.p);
-  SNNB_CHECK_LAUNCH("conv3x3_pair");
-  return SNNB_OK;
-}
-
-template <typename XT>
-int dispatch(const ConvArgs &a, cudaStream_t stream) {
-  const bool s_u8 = a.lif && a.spike_dtype == SNNB_U8;
-  const bool v_f32 = a.lif && a.v_dtype == SNNB_F32;
-  if (s_u8 && v_f32) return launch<XT, uint8_t, float>(a, stream);
-  if (s_u8) return launch<XT, uint8_t, XT>(a, stream);
-  if (v_f32) return launch<XT, XT, float>(a, stream);
-  return launch<XT, XT, XT>(a, stream);
-}
-
-}  // namespace
+int conv3x3_pair_bf16(const ConvArgs &a, cudaStream_t stream);
+int conv3x3_pair_f16(const ConvArgs &a, cudaStream_t stream);
+int pair_status_bf16(int *out);
+int pair_status_f16(int *out);
 
 bool conv3x3_pair_supported(const ConvArgs &a) {
   if (a.dtype != SNNB_BF16 && a.dtype != SNNB_F16) return false;
@@ -541,27 +23,17 @@ bool conv3x3_pair_supported(const ConvArgs &a) {
 }
 
 int conv3x3_pair(const ConvArgs &a, cudaStream_t stream) {
-  if (a.dtype == SNNB_BF16) return dispatch<__nv_bfloat16>(a, stream);
-  return dispatch<__half>(a, stream);
+  return a.dtype == SNNB_BF16 ? conv3x3_pair_bf16(a, stream) : conv3x3_pair_f16(a, stream);
 }
 
 int pair_device_status(int *out) {
-  int h = 0;
-  cudaError_t e = cudaMemcpyFromSymbol(&h, g_pair_status, sizeof(int));
-  if (e != cudaSuccess) return fail(SNNB_ERR_CUDA, "device_status: %s", cudaGetErrorString(e));
-  if (h != 0) {
-    const int zero = 0;
-    cudaMemcpyToSymbol(g_pair_status, &zero, sizeof(int));
-  }
-  *out = h;
+  int h1 = 0, h2 = 0;
+  int rc = pair_status_bf16(&h1);
+  if (rc != SNNB_OK) return rc;
+  rc = pair_status_f16(&h2);
+  if (rc != SNNB_OK) return rc;
+  *out = h1 | h2;
   return SNNB_OK;
 }
 
 }  // namespace snnb
-
-#ifdef SNNB_TC_TRACE
-extern "C" int snnb_debug_read_ptrace(long long *host_buf) {
-  cudaDeviceSynchronize();
-  return (int)cudaMemcpyFromSymbol(host_buf, snnb::g_ptrace, sizeof(long long) * 64);
-}
-#endif
