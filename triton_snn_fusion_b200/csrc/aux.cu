@@ -93,7 +93,7 @@ int maxpool(const void *x, void *y, int64_t frames, int H, int W, int C, cudaStr
 
 // One CTA per group of SB samples: channel sums over (t, pixel) into shared memory, then a
 // warp-per-class mat-vec for the SB samples with the fc row read once.
-constexpr int SB = 4;
+constexpr int SB = 2;
 template <typename XT>
 __global__ void __launch_bounds__(256)
 avgpool_linear_mean_kernel(const XT *__restrict__ x, const XT *__restrict__ w, const XT *__restrict__ b,
@@ -105,11 +105,20 @@ avgpool_linear_mean_kernel(const XT *__restrict__ x, const XT *__restrict__ w, c
   const int64_t frame = (int64_t)N * HW * C;
   for (int i = tid; i < ns * C; i += 256) {
     const int s = i / C, c = i % C;
-    float a = 0.f;
+    // T*HW strided loads per channel: four independent partial sums keep several loads in flight
+    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
     for (int t = 0; t < T; ++t) {
       const XT *px = x + (int64_t)t * frame + (int64_t)(n0 + s) * HW * C + c;
-      for (int p = 0; p < HW; ++p) a += DT<XT>::to_f(px[(int64_t)p * C]);
+      int p = 0;
+      for (; p + 4 <= HW; p += 4) {
+        a0 += DT<XT>::to_f(px[(int64_t)p * C]);
+        a1 += DT<XT>::to_f(px[(int64_t)(p + 1) * C]);
+        a2 += DT<XT>::to_f(px[(int64_t)(p + 2) * C]);
+        a3 += DT<XT>::to_f(px[(int64_t)(p + 3) * C]);
+      }
+      for (; p < HW; ++p) a0 += DT<XT>::to_f(px[(int64_t)p * C]);
     }
+    const float a = (a0 + a1) + (a2 + a3);
     sums[s * C + c] = a;
   }
   __syncthreads();
