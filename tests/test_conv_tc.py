@@ -181,16 +181,31 @@ def test_config2_layer_properties_full_size():
     assert 0.01 < float(full.spikes.float().mean()) < 0.7
 
 
-@pytest.mark.parametrize("hw", [(64, 64), (32, 48), (224, 224)])
+@pytest.mark.parametrize("hw", [(64, 64), (32, 48), (36, 52), (224, 224)])
 @pytest.mark.parametrize("alias", [True, False])
 def test_stem_7x7_s2_three_channels(hw, alias):
     """ResNet stem (7x7, stride 2, padding 3, 3 -> 64) through the tensor-core stem path."""
+    _check_stem(hw, alias, cout=64, T=4)
+
+
+@pytest.mark.parametrize("cout,T,alias", [
+    (32, 4, True),      # persistent stem kernel, one 16-channel group per epilogue warp
+    (128, 2, False),    # persistent kernel, two real frames, two accumulator stages
+    (96, 2, True),      # persistent kernel, odd split of the channel groups
+    (48, 4, True),      # not a multiple of 32 channels: general implicit-GEMM kernel on the re-laid view
+    (64, 8, False),     # eight real frames do not fit two accumulator stages: general kernel
+])
+def test_stem_other_widths_and_frame_counts(cout, T, alias):
+    _check_stem((40, 56), alias, cout=cout, T=T)
+
+
+def _check_stem(hw, alias, cout, T):
     H, W = hw
-    dtype, T, B = torch.bfloat16, 4, (2 if H < 200 else 1)
-    torch.manual_seed(H + W + alias)
+    dtype, B = torch.bfloat16, (2 if H < 200 else 1)
+    torch.manual_seed(H + W + alias + cout + T)
     xs = [torch.randn(B, 3, H, W).to(dtype)] * T if alias else [torch.randn(B, 3, H, W).to(dtype) for _ in range(T)]
-    w = (torch.randn(64, 3, 7, 7) * (2.0 / 147) ** 0.5).to(dtype)
-    b = (torch.randn(64) * 0.1).to(dtype)
+    w = (torch.randn(cout, 3, 7, 7) * (2.0 / 147) ** 0.5).to(dtype)
+    b = (torch.randn(cout) * 0.1).to(dtype)
     rs, rv = orc.temporal_conv_lif([orc.widen(x) for x in xs], orc.widen(w), orc.widen(b), None,
                                    [2, 2], [3, 3], [1, 1], 1, 1.0, 0.0, 2.0)
     xd = [xs[0].to(DEV)] * T if alias else [x.to(DEV) for x in xs]
@@ -198,5 +213,5 @@ def test_stem_7x7_s2_three_channels(hw, alias):
         xd, w.to(DEV), b.to(DEV), torch.tensor(0.0, device=DEV, dtype=dtype), [2, 2], [3, 3], [1, 1], 1,
         1.0, 0.0, 2.0, False, strict=True)
     assert r.kernel_key == "k7_s2_p3"
-    check_parity(r.spikes, r.v_next, rs, rv, dtype, what=f"stem {hw} alias={alias}")
+    check_parity(r.spikes, r.v_next, rs, rv, dtype, what=f"stem {hw} alias={alias} cout={cout} T={T}")
     assert 0.02 < float(rs.mean()) < 0.6

@@ -77,10 +77,13 @@ def build(force: bool = False, verbose: bool = False, ptxas_v: bool = False) -> 
                 f.result()
     need_link = bool(jobs) or not LIB_PATH.exists() or any(o.stat().st_mtime > LIB_PATH.stat().st_mtime for o in objs)
     if need_link:
-        cmd = [nvcc, "-shared", "-o", str(LIB_PATH), *map(str, objs), "-lcudart", "-ldl"]
+        # link beside the target and rename: a reader never sees a half-written library
+        tmp = LIB_PATH.with_suffix(".so.tmp")
+        cmd = [nvcc, "-shared", "-o", str(tmp), *map(str, objs), "-lcudart", "-ldl"]
         proc = subprocess.run(cmd, capture_output=True, text=True)
         if proc.returncode != 0:
             raise RuntimeError(f"link failed:\n{proc.stdout}\n{proc.stderr}")
+        tmp.replace(LIB_PATH)
     return LIB_PATH
 
 

@@ -44,4 +44,19 @@ bool conv3x3_pair_supported(const ConvArgs &a);
 int conv3x3_pair(const ConvArgs &a, cudaStream_t stream);
 int pair_device_status(int *out);
 
+// GEMM + LIF stage of the 7x7 / stride 2 stem on the re-laid image (stem.cu): persistent tcgen05 kernel
+// with the packed weight resident in shared memory.
+struct StemGemmArgs {
+  const void *s2d;        // re-laid input [frames * B][Hb][Wb][16]
+  const void *w_packed;   // [Cout][4][4][16]
+  const void *b, *v_init;
+  void *spikes, *v_out;
+  int T, frames, B, Ho, Wo, Hb, Wb, Cout;   // frames = 1 (one frame for every step) or T
+  int dtype, spike_dtype, v_dtype;
+  LifParams p;
+};
+bool stem_gemm_supported(const StemGemmArgs &a);
+int stem_gemm_lif(const StemGemmArgs &a, cudaStream_t stream);
+int stem_device_status(int *out);
+
 }  // namespace snnb

@@ -1,6 +1,5 @@
 // extern "C" entry points of the dense conv / linear + LIF ops: argument validation and
 // the choice between the tensor-core and the CUDA-core implementation.
-#include <cstdlib>
 
 #include "conv.cuh"
 
@@ -10,10 +9,7 @@ namespace {
 int run(const ConvArgs &a, int path, cudaStream_t stream, const char *what) {
   if (path == SNNB_PATH_SIMT) return conv_lif_simt(a, stream);
   const bool taps_only = path == SNNB_PATH_TCGEN05_TAPS;
-  // The pair kernel always multiplies a 128-channel weight tile, so with Cout <= 64 half of its MMA
-  // rows are padding and the halo kernel is faster.
-  static const int min_cout = [] { const char *e = getenv("SNNB_PAIR_MIN_COUT"); return e ? atoi(e) : 1; }();
-  if (!taps_only && path != SNNB_PATH_TCGEN05_HALO && a.Cout >= min_cout && conv3x3_pair_supported(a)) return conv3x3_pair(a, stream);
+  if (!taps_only && path != SNNB_PATH_TCGEN05_HALO && conv3x3_pair_supported(a)) return conv3x3_pair(a, stream);
   if (!taps_only && conv3x3_halo_supported(a)) return conv3x3_halo(a, stream);
   const char *why = "";
   if (conv_lif_tc_supported(a, &why)) return conv_lif_tc(a, stream);

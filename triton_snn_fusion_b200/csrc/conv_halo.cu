@@ -33,13 +33,6 @@ namespace snnb {
 
 static __device__ int g_halo_status = 0;
 
-#ifdef SNNB_TC_TRACE
-static __device__ long long g_htrace[4][512];
-#define HTRACE(row, idx) do { const unsigned i_ = (idx); if (blockIdx.x == 300 && i_ < 512) g_htrace[row][i_] = clock64(); } while (0)
-#else
-#define HTRACE(row, idx) do { } while (0)
-#endif
-
 namespace {
 
 constexpr int kHaloW = 10, kHaloH = 18;
@@ -121,7 +114,6 @@ conv3x3_halo_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
   __syncthreads();
   umma::tc_fence_after_sync();
   const uint32_t tmem_base = tmem_base_s;
-  if (threadIdx.x == 0) HTRACE(2, 0);
 
   if (warp == kHaloWarp) {
     // ------------------------------------------------------------ halo producer
@@ -143,7 +135,6 @@ conv3x3_halo_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
         }
         ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
         if (!ok) break;
-        if (lane == 0) HTRACE(1, 1 + slab * g.Tacc + t);
         if (mine)
           umma::tma_load_5d(h_base + slot * (uint32_t)kHaloBytes + my_off, &xmap, hfull(slot), slab * 64, w0 - 1, ch,
                             my_b, t);
@@ -198,7 +189,6 @@ conv3x3_halo_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
                 if (!ok) break;
                 umma::tc_fence_after_sync();
               }
-              HTRACE(0, 1 + (slab * 9 + tap) * g.Tacc + t);
               const uint64_t adesc = hdesc0 + (uint64_t)((slot * (uint32_t)kHaloBytes + tap_off) >> 4);
               const uint32_t d = tmem_base + (uint32_t)(t * g.BN);
 #pragma unroll
@@ -247,7 +237,6 @@ conv3x3_halo_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
     asm volatile("bar.sync 1, %0;" ::"r"(32 * (kEpiWarpsH + 1)) : "memory");  // released by the MMA warp
     const bool ok = (*abort_flag == 0);
     umma::tc_fence_after_sync();
-    if (threadIdx.x == 0) HTRACE(2, 1);
     if (ok) {
       const int nch = g.BN / 16, half = (nch + 1) / 2;
       const int c_begin = (warp < 4) ? 0 : half;
@@ -259,10 +248,8 @@ conv3x3_halo_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
     }
   }
 
-  if (threadIdx.x == 0) HTRACE(2, 2);
   umma::tc_fence_before_sync();
   __syncthreads();
-  if (threadIdx.x == 0) HTRACE(2, 3);
   if (abort_s && threadIdx.x == 0) atomicExch(&g_halo_status, 1);
   if (warp == kMmaWarpH) {
     umma::tc_fence_after_sync();
@@ -385,9 +372,3 @@ int halo_device_status(int *out) {
 
 }  // namespace snnb
 
-#ifdef SNNB_TC_TRACE
-extern "C" int snnb_debug_read_htrace(long long *host_buf) {
-  cudaDeviceSynchronize();
-  return (int)cudaMemcpyFromSymbol(host_buf, snnb::g_htrace, sizeof(long long) * 4 * 512);
-}
-#endif

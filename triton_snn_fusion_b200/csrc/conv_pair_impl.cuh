@@ -32,13 +32,6 @@ namespace snnb {
 
 static __device__ int g_pair_status = 0;
 
-#ifdef SNNB_TC_TRACE
-static __device__ long long g_ptrace[64];
-#define PTRACE(idx) do { if (blockIdx.x == 100 && (idx) < 64) g_ptrace[idx] = clock64(); } while (0)
-#else
-#define PTRACE(idx) do { } while (0)
-#endif
-
 namespace {
 
 constexpr int kPW = 10, kPH = 16;                      // halo tile: 10 x 16 pixels
@@ -124,30 +117,46 @@ __device__ __forceinline__ void pair_epilogue(const LifParams &p, uint32_t tmem_
 
 // Hot version: two timesteps, tau a power of two, hard reset, a valid channel and a tile that lies
 // completely inside the image, so nothing is predicated. NROWS = tile rows of this thread. The tile
-// grid is laid out so that (for maps of at least 14 x 8) every tile is such a tile: keeping a whole
-// layer on this one code path matters, because alternating between two large unrolled bodies thrashes
-// the instruction cache.
+// grid is laid out so that (for maps of at least 14 x 8) every tile is such a tile.
+// Code size matters here: eight warps stream through this body once per pair, and when all of a
+// thread's pixels are unrolled (several thousand instructions) the warps mostly wait for instruction
+// fetch. So the loop over 16-pixel chunks stays a real loop. The membrane potentials must be
+// registers, which cannot be indexed by the loop counter: each trip works on v[0..15] and then
+// rotates the thread's NROWS * 8 potentials by 16, so they are back in place after the last trip.
 template <typename XT, typename ST, int NROWS>
 __device__ __forceinline__ void pair_epilogue_full(const LifParams &p, uint32_t tmem_addr, float bias_c,
                                                    ST *__restrict__ out, long long frame_out, const PixMap &pm,
                                                    float (&v)[64]) {
-  ST *const p0 = out + pm.row0_off;
-  ST *const p1 = p0 + frame_out;
-#pragma unroll
+  constexpr int NPIX = NROWS * 8;
+  ST *p0 = out + pm.row0_off;
+  ST *p1 = p0 + frame_out;
+  const int two_rows = 2 * pm.row_stride;
+#pragma unroll 1
   for (int chunk = 0; chunk < NROWS / 2; ++chunk) {
     uint32_t a0[16], a1[16];
-    umma::tmem_ld_x16(tmem_addr + (uint32_t)(chunk * 16), a0);
-    umma::tmem_ld_x16(tmem_addr + (uint32_t)(128 + chunk * 16), a1);
+    umma::tmem_ld_x16(tmem_addr, a0);
+    umma::tmem_ld_x16(tmem_addr + 128u, a1);
     umma::tmem_ld_wait();
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
-      const int o = (chunk * 2 + (i >> 3)) * pm.row_stride + (i & 7) * pm.Cout;   // fits 32 bits: one tile
-      float &vv = v[chunk * 16 + i];
-      const float s0 = lif_step_t<1, true>(__uint_as_float(a0[i]) + bias_c, vv, p);
-      const float s1 = lif_step_t<1, true>(__uint_as_float(a1[i]) + bias_c, vv, p);
+      const int o = (i >> 3) * pm.row_stride + (i & 7) * pm.Cout;   // fits 32 bits: one tile
+      const float s0 = lif_step_t<1, true>(__uint_as_float(a0[i]) + bias_c, v[i], p);
+      const float s1 = lif_step_t<1, true>(__uint_as_float(a1[i]) + bias_c, v[i], p);
       p0[o] = DT<ST>::from_f(s0);
       p1[o] = DT<ST>::from_f(s1);
     }
+    if (NPIX > 16) {
+      float head[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) head[i] = v[i];
+#pragma unroll
+      for (int i = 0; i < NPIX - 16; ++i) v[i] = v[i + 16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) v[NPIX - 16 + i] = head[i];
+    }
+    p0 += two_rows;
+    p1 += two_rows;
+    tmem_addr += 16u;
   }
 }
 
@@ -231,7 +240,6 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
   __syncthreads();
   umma::tc_fence_after_sync();
   const uint32_t tmem_base = tmem_base_s;
-  if (threadIdx.x == 0) PTRACE(0);
 
   if (warp == kHaloWarpP) {
     // ------------------------------------------------- halo producer: lane q loads timestep q of the pair
@@ -344,7 +352,6 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
             if (++slot == (uint32_t)g.ring) { slot = 0; phase ^= 1u; }
           }
           if (ok) umma::mma_commit(accfull(pair));
-          PTRACE(12 + it * 8 + pair);
         }
       }
     }
@@ -393,7 +400,6 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
         ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
         if (!ok) break;
         umma::tc_fence_after_sync();
-        if (threadIdx.x == 0) PTRACE(8 + it * 8 + pair * 2);
         const long long toff = (long long)(pair * g.tq) * frame_out;
         const uint32_t taddr = lane_base + (uint32_t)(pair * 256);
         ST *out = spikes + toff;
@@ -404,7 +410,7 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
         // warp-uniform choice: the TMEM loads inside are warp-collective
         const bool full = __all_sync(0xffffffffu, pm.rows_ok == rows_want && pm.cols_ok == 0xFF);
         if (g.lif && p.mode == 1 && p.hard && g.tq == 2 && full) {
-if (rows_valid == 8) pair_epilogue_full<XT, ST, 8>(p, taddr, bias_c, out, frame_out, pm, v);
+          if (rows_valid == 8) pair_epilogue_full<XT, ST, 8>(p, taddr, bias_c, out, frame_out, pm, v);
           else if (rows_valid == 6) pair_epilogue_full<XT, ST, 6>(p, taddr, bias_c, out, frame_out, pm, v);
           else if (rows_valid == 4) pair_epilogue_full<XT, ST, 4>(p, taddr, bias_c, out, frame_out, pm, v);
           else pair_epilogue_full<XT, ST, 2>(p, taddr, bias_c, out, frame_out, pm, v);
@@ -417,7 +423,6 @@ if (rows_valid == 8) pair_epilogue_full<XT, ST, 8>(p, taddr, bias_c, out, frame_
           if (g.tq == 2) pair_epilogue<XT, ST, kLifOff, true, false>(p, taddr, bias_c, rs, out, frame_out, pm, v, nchunks);
           else pair_epilogue<XT, ST, kLifOff, false, false>(p, taddr, bias_c, rs, out, frame_out, pm, v, nchunks);
         }
-        if (threadIdx.x == 0) PTRACE(9 + it * 8 + pair * 2);
         // this accumulator may now be overwritten by the next tile's MMAs
         umma::tc_fence_before_sync();
         __syncwarp();

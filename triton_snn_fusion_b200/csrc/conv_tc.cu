@@ -33,14 +33,6 @@ namespace snnb {
 
 static __device__ int g_tc_status = 0;
 
-#ifdef SNNB_TC_TRACE
-// Development aid (not part of normal builds): per-event SM cycle stamps of one CTA.
-static __device__ long long g_trace[8][512];
-#define SNNB_TRACE(row, idx) do { const unsigned i_ = (idx); if (blockIdx.x == 300 && i_ < 512) g_trace[row][i_] = clock64(); } while (0)
-#else
-#define SNNB_TRACE(row, idx) do { } while (0)
-#endif
-
 namespace {
 
 constexpr int kSlotBytes = 16384;  // one 128-row x 128-byte operand tile
@@ -128,7 +120,6 @@ conv_lif_tc_kernel(const __grid_constant__ CUtensorMap xmap0, const __grid_const
   umma::tc_fence_after_sync();
   const uint32_t tmem_base = tmem_base_s;
 
-  if (threadIdx.x == 0) SNNB_TRACE(2, 0);
   const int ksteps = g.KH * g.KW * g.kchunks;
   const uint32_t box_bytes = (uint32_t)(g.BW * g.BH) * 128u;
 
@@ -251,7 +242,6 @@ conv_lif_tc_kernel(const __grid_constant__ CUtensorMap xmap0, const __grid_const
     asm volatile("bar.sync 1, %0;" ::"r"(32 * (kEpiWarps + 1)) : "memory");  // released by the MMA warp
     const bool ok = (*abort_flag == 0);
     umma::tc_fence_after_sync();
-    if (threadIdx.x == 0) SNNB_TRACE(2, 1);
     if (ok) {
       // the two warps of a lane quarter split the 16-column groups of the tile
       const int nch = g.BN / 16, half = (nch + 1) / 2;
@@ -265,10 +255,8 @@ conv_lif_tc_kernel(const __grid_constant__ CUtensorMap xmap0, const __grid_const
   }
 
   // ------------------------------------------------------------------ teardown
-  if (threadIdx.x == 0) SNNB_TRACE(2, 2);
   umma::tc_fence_before_sync();
   __syncthreads();
-  if (threadIdx.x == 0) SNNB_TRACE(2, 3);
   if (abort_s && threadIdx.x == 0) atomicExch(&g_tc_status, 1);
   if (warp == kMmaWarp) {
     umma::tc_fence_after_sync();
@@ -442,13 +430,10 @@ extern "C" int snnb_device_status(int *status_out) {
   int h3 = 0;
   const int rc3 = pair_device_status(&h3);
   if (rc3 != SNNB_OK) return rc3;
-  *status_out = h | h2 | h3;
+  int h4 = 0;
+  const int rc4 = stem_device_status(&h4);
+  if (rc4 != SNNB_OK) return rc4;
+  *status_out = h | h2 | h3 | h4;
   return SNNB_OK;
 }
 
-#ifdef SNNB_TC_TRACE
-extern "C" int snnb_debug_read_trace(long long *host_buf) {
-  cudaDeviceSynchronize();
-  return (int)cudaMemcpyFromSymbol(host_buf, snnb::g_trace, sizeof(long long) * 8 * 512);
-}
-#endif

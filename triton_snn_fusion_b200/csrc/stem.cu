@@ -122,6 +122,15 @@ extern "C" int snnb_stem7x7_lif(const void *x_seq, int64_t x_t_stride, const voi
           static_cast<__half *>(scratch) + (int64_t)f * B * Hb * Wb * 16, B, H, W);
     SNNB_CHECK_LAUNCH("stem7x7_s2d");
   }
+  {
+    StemGemmArgs sa;
+    sa.s2d = scratch; sa.w_packed = w_packed; sa.b = b; sa.v_init = v_init; sa.spikes = spikes; sa.v_out = v_out;
+    sa.T = T; sa.frames = frames; sa.B = B; sa.Ho = H / 2; sa.Wo = W / 2; sa.Hb = Hb; sa.Wb = Wb; sa.Cout = Cout;
+    sa.dtype = dtype; sa.spike_dtype = spike_dtype; sa.v_dtype = v_dtype;
+    sa.p = make_lif_params(v_th, v_reset, tau);
+    if (stem_gemm_supported(sa)) return stem_gemm_lif(sa, st);
+  }
+  // other channel counts / many real frames: the general implicit-GEMM kernel on a strided view
   ConvArgs a;
   a.x = scratch;
   a.x_t_stride = frames > 1 ? (int64_t)B * Hb * Wb * 16 : 0;

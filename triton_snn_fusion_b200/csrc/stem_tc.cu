@@ -1,0 +1,294 @@
+// GEMM + LIF stage of the 7x7 / stride 2 stem conv (stem.cu re-lays the image first): a persistent
+// tcgen05 kernel.
+//
+// In the re-laid image the window of output pixel (oh, ow) is 4 runs (block rows oh .. oh+3) of 64
+// contiguous values, so the conv is a GEMM with K = 4 x 64 whose A rows are read through a tensor map
+// with a 32-byte pixel stride. K is tiny and the layer writes T spike frames per convolved frame: the
+// kernel is bound by its output stream, not by the tensor pipe. What matters is that stores never
+// wait for anything else, hence:
+//   * one CTA per SM walks the output tiles (128 pixels = a BW x BH box, all Cout channels);
+//   * the whole packed weight (Cout x 512 bytes) is loaded once per CTA and stays in shared memory;
+//   * the activation chunks of the coming tiles stream through a ring of 16 KB slots;
+//   * accumulators rotate through several TMEM stages, so the MMAs of tile i+1, i+2 run while the
+//     epilogue warps convert and store tile i.
+// Warps 0-7: epilogue (two per TMEM lane quarter, splitting the channels); warp 8: TMA producer;
+// warp 9: MMA issuer. Every mbarrier wait is bounded; on a timeout the CTA raises a status word,
+// skips its remaining work, frees its tensor memory and exits.
+#include <type_traits>
+
+#include "conv.cuh"
+#include "tc_epilogue.cuh"
+#include "tmap.cuh"
+#include "umma.cuh"
+
+namespace snnb {
+
+static __device__ int g_stem_status = 0;
+
+namespace {
+
+constexpr int kChunkBytes = 16384;   // 128 pixels x 128 bytes: one K chunk of a tile
+constexpr int kMaxRing = 12;
+constexpr int kMaxAcc = 4;
+constexpr int kEpiWarpsS = 8;
+constexpr int kProdWarpS = kEpiWarpsS, kMmaWarpS = kEpiWarpsS + 1;
+constexpr int kThreadsS = 32 * (kEpiWarpsS + 2);
+
+struct StemGeom {
+  int T, Tacc, B, Ho, Wo, Cout;
+  int BW, BH, WB, HB;   // tile = BW x BH output pixels; WB x HB tiles per image
+  int total_tiles;
+  int ring;             // activation slots
+  int nacc;             // accumulator stages in TMEM
+  int stage_cols;       // TMEM columns per stage = Tacc * Cout
+  int tmem_cols;
+  int w_chunk_bytes;    // Cout * 128
+};
+
+template <typename XT, typename ST, typename VT>
+__global__ void __launch_bounds__(kThreadsS)
+stem_gemm_lif_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap,
+                     const XT *__restrict__ bias, const VT *__restrict__ v_init, ST *__restrict__ spikes,
+                     VT *__restrict__ v_out, const StemGeom g, const LifParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bars[2 * kMaxRing + 1 + 2 * kMaxAcc];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int abort_s;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t smem_base = (umma::smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t w_base = smem_base;                                   // 4 weight chunks, resident
+  const uint32_t a_base = smem_base + 4u * (uint32_t)g.w_chunk_bytes;  // activation ring
+  const uint32_t bar_base = umma::smem_u32(bars);
+  auto afull = [&](uint32_t s) { return bar_base + 8u * s; };
+  auto aempty = [&](uint32_t s) { return bar_base + 8u * ((uint32_t)kMaxRing + s); };
+  const uint32_t wfull = bar_base + 8u * (2u * kMaxRing);
+  auto accfull = [&](uint32_t s) { return bar_base + 8u * (2u * kMaxRing + 1u + s); };
+  auto accempty = [&](uint32_t s) { return bar_base + 8u * (2u * kMaxRing + 1u + kMaxAcc + s); };
+  volatile int *abort_flag = &abort_s;
+
+  auto decode = [&](int tile, int &w0, int &h0, int &b) {
+    const int wb = tile % g.WB;
+    const int m = tile / g.WB;
+    w0 = wb * g.BW;
+    h0 = (m % g.HB) * g.BH;
+    b = m / g.HB;
+  };
+
+  if (threadIdx.x == 0) {
+    abort_s = 0;
+    for (int s = 0; s < g.ring; ++s) { umma::mbar_init(afull(s), 1); umma::mbar_init(aempty(s), 1); }
+    umma::mbar_init(wfull, 1);
+    for (int s = 0; s < g.nacc; ++s) { umma::mbar_init(accfull(s), 1); umma::mbar_init(accempty(s), kEpiWarpsS); }
+    umma::fence_mbar_init();
+  }
+  if (warp == kMmaWarpS) {
+    umma::tmem_alloc(umma::smem_u32(&tmem_base_s), (uint32_t)g.tmem_cols);
+    umma::tmem_relinquish();
+  }
+  if (warp == kProdWarpS && lane == 0) {
+    umma::prefetch_tensormap(&xmap);
+    umma::prefetch_tensormap(&wmap);
+  }
+  umma::tc_fence_before_sync();
+  __syncthreads();
+  umma::tc_fence_after_sync();
+  const uint32_t tmem_base = tmem_base_s;
+
+  if (warp == kProdWarpS) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      umma::mbar_expect_tx(wfull, 4u * (uint32_t)g.w_chunk_bytes);
+      for (int i = 0; i < 4; ++i) umma::tma_load_2d(w_base + (uint32_t)(i * g.w_chunk_bytes), &wmap, wfull, i * 64, 0);
+      uint32_t slot = 0, phase = 1;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < g.total_tiles && ok; tile += gridDim.x) {
+        int w0, h0, b;
+        decode(tile, w0, h0, b);
+        for (int t = 0; t < g.Tacc && ok; ++t)
+          for (int i = 0; i < 4; ++i) {   // block row h0 + i of the window = K chunk i
+            ok = umma::mbar_wait(aempty(slot), phase, abort_flag);
+            if (!ok) break;
+            umma::mbar_expect_tx(afull(slot), (uint32_t)kChunkBytes);
+            umma::tma_load_4d(a_base + slot * (uint32_t)kChunkBytes, &xmap, afull(slot), 0, w0, h0 + i, t * g.B + b);
+            if (++slot == (uint32_t)g.ring) { slot = 0; phase ^= 1u; }
+          }
+      }
+    }
+    __syncwarp();
+  } else if (warp == kMmaWarpS) {
+    // -------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = umma::make_idesc_f16(128, g.Cout, std::is_same<XT, __nv_bfloat16>::value);
+      const uint64_t adesc0 = umma::make_sw128_kmajor_desc(a_base);
+      const uint64_t wdesc0 = umma::make_sw128_kmajor_desc(w_base);
+      uint32_t slot = 0, phase = 0, acc = 0, accphase = 0;
+      bool ok = umma::mbar_wait(wfull, 0u, abort_flag);
+      for (int tile = blockIdx.x; tile < g.total_tiles && ok; tile += gridDim.x) {
+        // the epilogue warps must have read this stage (tile - nacc * gridDim.x) out of tensor memory
+        ok = umma::mbar_wait(accempty(acc), accphase ^ 1u, abort_flag);
+        if (!ok) break;
+        umma::tc_fence_after_sync();
+        for (int t = 0; t < g.Tacc && ok; ++t) {
+          const uint32_t d = tmem_base + acc * (uint32_t)g.stage_cols + (uint32_t)(t * g.Cout);
+          for (int i = 0; i < 4; ++i) {
+            ok = umma::mbar_wait(afull(slot), phase, abort_flag);
+            if (!ok) break;
+            umma::tc_fence_after_sync();
+            const uint64_t adesc = adesc0 + (uint64_t)((slot * (uint32_t)kChunkBytes) >> 4);
+            const uint64_t wdesc = wdesc0 + (uint64_t)((uint32_t)(i * g.w_chunk_bytes) >> 4);
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+              umma::mma_f16_ss(d, adesc + (uint64_t)(2 * k), wdesc + (uint64_t)(2 * k), idesc, (i > 0 || k > 0) ? 1u : 0u);
+            umma::mma_commit(aempty(slot));
+            if (++slot == (uint32_t)g.ring) { slot = 0; phase ^= 1u; }
+          }
+        }
+        if (ok) umma::mma_commit(accfull(acc));
+        if (++acc == (uint32_t)g.nacc) { acc = 0; accphase ^= 1u; }
+      }
+    }
+    __syncwarp();
+  } else {
+    // ---------------------------------------------------------------- epilogue
+    const int quarter = warp & 3;          // TMEM lanes 32*quarter .. +31 are the ones this warp may read
+    const int r = quarter * 32 + lane;     // row of the tile = output pixel owned by this thread
+    const int ph = r / g.BW, pw = r - ph * g.BW;
+    const int nch = g.Cout / 16, half = (nch + 1) / 2;
+    const int c_begin = (warp < 4) ? 0 : half;
+    const int c_end = (warp < 4) ? half : nch;
+    const EpiGeom eg{g.T, g.Tacc, g.Cout, g.Cout, 0};
+    const long long frame_out = (long long)g.B * g.Ho * g.Wo * g.Cout;
+    uint32_t acc = 0, accphase = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < g.total_tiles && ok; tile += gridDim.x) {
+      int w0, h0, b;
+      decode(tile, w0, h0, b);
+      const int wo = w0 + pw, ho = h0 + ph;
+      const bool valid = wo < g.Wo && ho < g.Ho;
+      const long long pix = ((long long)b * g.Ho + ho) * g.Wo + wo;
+      if (lane == 0) ok = umma::mbar_wait(accfull(acc), accphase, abort_flag);
+      ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+      if (!ok) break;
+      umma::tc_fence_after_sync();
+      const EpiArgs<XT, ST, VT> ea{bias, nullptr, v_init, spikes, v_out,
+                                   tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * (uint32_t)g.stage_cols,
+                                   pix, frame_out, 0, c_begin, c_end, valid};
+      epilogue_dispatch<XT, ST, VT>(ea, eg, 1, p);
+      // this stage may now be overwritten
+      umma::tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) umma::mbar_arrive(accempty(acc));
+      if (++acc == (uint32_t)g.nacc) { acc = 0; accphase ^= 1u; }
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  umma::tc_fence_before_sync();
+  __syncthreads();
+  if (abort_s && threadIdx.x == 0) atomicExch(&g_stem_status, 1);
+  if (warp == kMmaWarpS) {
+    umma::tc_fence_after_sync();
+    umma::tmem_dealloc(tmem_base, (uint32_t)g.tmem_cols);
+  }
+}
+
+// Tile box with BW * BH = 128 that covers the Ho x Wo map with the fewest wasted pixels (ties: the wider).
+void choose_tile(int Ho, int Wo, int &BW, int &BH) {
+  long long best = -1;
+  BW = 128; BH = 1;
+  for (int bw = 128; bw >= 1; bw /= 2) {
+    const int bh = 128 / bw;
+    const long long covered = (long long)((Wo + bw - 1) / bw) * bw * ((Ho + bh - 1) / bh) * bh;
+    if (best < 0 || covered < best) { best = covered; BW = bw; BH = bh; }
+  }
+}
+
+template <typename XT, typename ST, typename VT>
+int launch(const StemGemmArgs &a, cudaStream_t stream) {
+  StemGeom g;
+  g.T = a.T; g.Tacc = a.frames; g.B = a.B; g.Ho = a.Ho; g.Wo = a.Wo; g.Cout = a.Cout;
+  choose_tile(a.Ho, a.Wo, g.BW, g.BH);
+  g.WB = (a.Wo + g.BW - 1) / g.BW;
+  g.HB = (a.Ho + g.BH - 1) / g.BH;
+  const long long tiles = (long long)a.B * g.WB * g.HB;
+  if (tiles > 0x7fffffffLL) return fail(SNNB_ERR_INVALID, "stem7x7_lif: problem too large for the grid");
+  g.total_tiles = (int)tiles;
+  g.stage_cols = g.Tacc * a.Cout;
+  g.nacc = 512 / g.stage_cols < kMaxAcc ? 512 / g.stage_cols : kMaxAcc;
+  int cols = 32;
+  while (cols < g.nacc * g.stage_cols) cols *= 2;
+  g.tmem_cols = cols;
+  g.w_chunk_bytes = a.Cout * 128;
+  const int budget = 224 * 1024 - 1024 - 4 * g.w_chunk_bytes;
+  g.ring = budget / kChunkBytes < kMaxRing ? budget / kChunkBytes : kMaxRing;
+  int dev = 0, sms = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 1)
+    return fail(SNNB_ERR_CUDA, "stem7x7_lif: cannot query the SM count");
+  const long long grid = tiles < sms ? tiles : sms;
+
+  const int es = 2;
+  CUtensorMap xm, wm;
+  {  // windows of 64 values, one per output column, overlapping: the pixel stride is one 16-value block
+    cuuint64_t dims[4] = {64, (cuuint64_t)a.Wo, (cuuint64_t)a.Hb, (cuuint64_t)a.frames * a.B};
+    cuuint64_t strides[3] = {(cuuint64_t)16 * es, (cuuint64_t)a.Wb * 16 * es, (cuuint64_t)a.Hb * a.Wb * 16 * es};
+    cuuint32_t box[4] = {64, (cuuint32_t)g.BW, (cuuint32_t)g.BH, 1};
+    const int rc = encode_tmap(&xm, a.dtype, 4, a.s2d, dims, strides, box);
+    if (rc != SNNB_OK) return rc;
+  }
+  {
+    cuuint64_t dims[2] = {256, (cuuint64_t)a.Cout};
+    cuuint64_t strides[1] = {(cuuint64_t)256 * es};
+    cuuint32_t box[2] = {64, (cuuint32_t)a.Cout};
+    const int rc = encode_tmap(&wm, a.dtype, 2, a.w_packed, dims, strides, box);
+    if (rc != SNNB_OK) return rc;
+  }
+  const size_t smem = (size_t)4 * g.w_chunk_bytes + (size_t)g.ring * kChunkBytes + 1024;
+  auto kern = stem_gemm_lif_kernel<XT, ST, VT>;
+  const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return fail(SNNB_ERR_CUDA, "stem7x7_lif: cannot raise the shared-memory limit: %s", cudaGetErrorString(e));
+  kern<<<(unsigned)grid, kThreadsS, smem, stream>>>(xm, wm, static_cast<const XT *>(a.b), static_cast<const VT *>(a.v_init),
+                                                    static_cast<ST *>(a.spikes), static_cast<VT *>(a.v_out), g, a.p);
+  SNNB_CHECK_LAUNCH("stem_gemm_lif");
+  return SNNB_OK;
+}
+
+template <typename XT>
+int dispatch(const StemGemmArgs &a, cudaStream_t stream) {
+  const bool s_u8 = a.spike_dtype == SNNB_U8;
+  const bool v_f32 = a.v_dtype == SNNB_F32;
+  if (s_u8 && v_f32) return launch<XT, uint8_t, float>(a, stream);
+  if (s_u8) return launch<XT, uint8_t, XT>(a, stream);
+  if (v_f32) return launch<XT, XT, float>(a, stream);
+  return launch<XT, XT, XT>(a, stream);
+}
+
+}  // namespace
+
+bool stem_gemm_supported(const StemGemmArgs &a) {
+  if (a.dtype != SNNB_BF16 && a.dtype != SNNB_F16) return false;
+  if (a.Cout % 32 != 0 || a.Cout > 128) return false;        // the two warps of a lane quarter split 16-channel groups evenly
+  if (a.frames * a.Cout > 256) return false;                  // at least two accumulator stages
+  if (!aligned16(a.s2d) || !aligned16(a.w_packed) || !aligned16(a.spikes) || !aligned16(a.v_out) ||
+      (a.b && !aligned16(a.b)) || (a.v_init && !aligned16(a.v_init)))
+    return false;
+  return true;
+}
+
+int stem_gemm_lif(const StemGemmArgs &a, cudaStream_t stream) {
+  return a.dtype == SNNB_BF16 ? dispatch<__nv_bfloat16>(a, stream) : dispatch<__half>(a, stream);
+}
+
+int stem_device_status(int *out) {
+  int h = 0;
+  cudaError_t e = cudaMemcpyFromSymbol(&h, g_stem_status, sizeof(int));
+  if (e != cudaSuccess) return fail(SNNB_ERR_CUDA, "device_status: %s", cudaGetErrorString(e));
+  if (h != 0) {
+    const int zero = 0;
+    cudaMemcpyToSymbol(g_stem_status, &zero, sizeof(int));
+  }
+  *out = h;
+  return SNNB_OK;
+}
+
+}  // namespace snnb

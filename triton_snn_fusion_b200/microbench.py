@@ -1,0 +1,201 @@
+"""Single-kernel timing of the library's fused ops through the C ABI.
+
+    python -m triton_snn_fusion_b200.microbench conv --B 64 --cin 128 --cout 128 --hw 56
+    python -m triton_snn_fusion_b200.microbench lif  --n 16777216
+    python -m triton_snn_fusion_b200.microbench dw   --B 32 --c 128 --hw 56
+    python -m triton_snn_fusion_b200.microbench tail --B 256 --c 1024 --hw 7 --classes 1000
+    python -m triton_snn_fusion_b200.microbench stem --B 128 --hw 224
+
+Each case builds seeded synthetic spikes/currents on the GPU (larger than L2 at the default sizes),
+warms the op up three times, times `--reps` launches with CUDA events and prints the algorithmic
+GB/s and TFLOP/s. With `--reps 1` it is the small case a profiler is pointed at.
+
+The conv case follows the workload of the reference's operator benchmark
+(benchmarks/bench_kernel_fusion.py: conv + folded BN + LIF over T steps, binary spike inputs).
+"""
+from __future__ import annotations
+
+import argparse
+
+import torch
+
+from . import _lib
+
+DEV = "cuda"
+LIF = (1.0, 0.0, 2.0)   # v_th, v_reset, tau: the reference's defaults
+
+
+def _time(call, reps):
+    for _ in range(3):
+        call()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        call()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / reps
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def case_conv(a):
+    dt = torch.bfloat16 if a.dtype == "bf16" else torch.float16
+    p = (a.k - 1) // 2
+    ho = (a.hw + 2 * p - a.k) // a.s + 1
+    g = torch.Generator(device=DEV).manual_seed(0)
+    x = (torch.rand(a.T, a.B, a.hw, a.hw, a.cin, device=DEV, generator=g) < 0.15).to(dt)
+    w = (torch.randn(a.cout, a.k, a.k, a.cin, device=DEV, generator=g)
+         * (2.0 / (a.cin * a.k * a.k)) ** 0.5 * 2.5).to(dt)
+    b = (torch.randn(a.cout, device=DEV, generator=g) * 0.1).to(dt)
+    res = (torch.rand(a.T, a.B, ho, ho, a.cout, device=DEV, generator=g) < 0.2).to(dt) if a.res else None
+    sp = torch.empty(a.T, a.B, ho, ho, a.cout, device=DEV, dtype=dt)
+    v = torch.empty(a.B, ho, ho, a.cout, device=DEV, dtype=dt)
+    dc = _lib.dtype_code(dt)
+
+    def call():
+        st = _lib.lib.snnb_conv_lif(
+            x.data_ptr(), x.stride(0), w.data_ptr(), b.data_ptr(),
+            res.data_ptr() if res is not None else None, None, sp.data_ptr(), v.data_ptr(),
+            a.T, a.B, a.cin, a.hw, a.hw, a.cout, a.k, a.k, a.s, p,
+            1, dc, dc, dc, *LIF, a.path, _stream())
+        _lib.check(st, "snnb_conv_lif")
+
+    ms = _time(call, a.reps)
+    flops = 2.0 * a.T * a.B * ho * ho * a.cout * a.cin * a.k * a.k
+    nbytes = 2 * (x.numel() + sp.numel() + v.numel() + w.numel() + (res.numel() if res is not None else 0))
+    print(f"conv_lif B{a.B} {a.cin}->{a.cout} k{a.k}s{a.s} {a.hw}^2 T{a.T} res={a.res} path={a.path}: "
+          f"{ms:.4f} ms  {flops / ms / 1e9:.1f} TFLOP/s  {nbytes / ms / 1e6:.0f} GB/s  "
+          f"spike rate {float(sp.float().mean()):.3f}  device status {_lib.device_status()}")
+
+
+def case_lif(a):
+    g = torch.Generator(device=DEV).manual_seed(0)
+    x = torch.randn(a.T, a.n, device=DEV, generator=g) * 0.8 + 0.6
+    sp = torch.empty_like(x)
+    v = torch.empty(a.n, device=DEV)
+
+    def call():
+        _lib.check(_lib.lib.snnb_lif_scan(x.data_ptr(), None, sp.data_ptr(), v.data_ptr(), a.T, a.n,
+                                          0, 0, 0, *LIF, _stream()), "snnb_lif_scan")
+
+    ms = _time(call, a.reps)
+    nbytes = 4 * (2 * a.T + 1) * a.n
+    print(f"lif_scan T{a.T} n={a.n} f32: {ms:.4f} ms  {nbytes / ms / 1e6:.0f} GB/s  "
+          f"spike rate {float(sp.mean()):.3f}")
+
+
+def case_dw(a):
+    dt = torch.bfloat16
+    g = torch.Generator(device=DEV).manual_seed(0)
+    x = (torch.rand(a.T, a.B, a.hw, a.hw, a.c, device=DEV, generator=g) < 0.2).to(dt)
+    w = (torch.randn(a.c, 3, 3, device=DEV, generator=g) * 0.3).to(dt)
+    b = torch.zeros(a.c, device=DEV, dtype=dt)
+    sp = torch.empty_like(x)
+    v = torch.empty(a.B, a.hw, a.hw, a.c, device=DEV, dtype=dt)
+
+    def call():
+        _lib.check(_lib.lib.snnb_dwconv3x3_lif(x.data_ptr(), x.stride(0), w.data_ptr(), b.data_ptr(), None, None,
+                                               sp.data_ptr(), v.data_ptr(), a.T, a.B, a.c, a.hw, a.hw, 1,
+                                               1, 1, 1, *LIF, _stream()), "snnb_dwconv3x3_lif")
+
+    ms = _time(call, a.reps)
+    nbytes = 2 * (x.numel() + sp.numel() + v.numel())
+    print(f"dwconv3x3_lif B{a.B} C{a.c} {a.hw}^2 T{a.T} bf16: {ms:.4f} ms  {nbytes / ms / 1e6:.0f} GB/s  "
+          f"spike rate {float(sp.float().mean()):.3f}")
+
+
+def case_tail(a):
+    dt = torch.bfloat16
+    hw = a.hw * a.hw
+    g = torch.Generator(device=DEV).manual_seed(0)
+    x = (torch.randn(a.T, a.B, hw, a.c, device=DEV, generator=g) * 0.75 + 0.15).to(dt)
+    w = (torch.randn(a.classes, a.c, device=DEV, generator=g) * 0.05).to(dt)
+    b = torch.zeros(a.classes, device=DEV, dtype=dt)
+    out = torch.empty(a.B, a.classes, device=DEV, dtype=dt)
+    v = torch.empty(a.B, hw, a.c, device=DEV, dtype=dt)
+
+    def call():
+        _lib.check(_lib.lib.snnb_lif_avgpool_linear(x.data_ptr(), None, w.data_ptr(), b.data_ptr(), out.data_ptr(),
+                                                    v.data_ptr(), a.T, a.B, a.c, hw, a.classes, 1, 1, 1,
+                                                    *LIF, _stream()), "snnb_lif_avgpool_linear")
+
+    ms = _time(call, a.reps)
+    nbytes = 2 * (x.numel() + v.numel() + w.numel() + out.numel())
+    print(f"lif_avgpool_linear B{a.B} C{a.c} {a.hw}^2 -> {a.classes} T{a.T} bf16: {ms:.4f} ms  "
+          f"{nbytes / ms / 1e6:.0f} GB/s")
+
+
+def case_stem(a):
+    dt = torch.bfloat16
+    ho = a.hw // 2
+    g = torch.Generator(device=DEV).manual_seed(0)
+    x = torch.randn(a.B, a.hw, a.hw, 3, device=DEV, generator=g).to(dt)
+    w = (torch.randn(a.cout, 7, 7, 3, device=DEV, generator=g) * (2.0 / 147) ** 0.5).to(dt)
+    b = (torch.randn(a.cout, device=DEV, generator=g) * 0.1).to(dt)
+    wp = torch.empty(a.cout, 256, device=DEV, dtype=dt)
+    _lib.check(_lib.lib.snnb_stem7x7_pack_weight(w.data_ptr(), wp.data_ptr(), a.cout, 1, _stream()), "pack")
+    nscratch = int(_lib.lib.snnb_stem7x7_scratch_bytes(a.B, a.hw, a.hw))
+    scratch = torch.empty(nscratch, device=DEV, dtype=torch.uint8)
+    sp = torch.empty(a.T, a.B, ho, ho, a.cout, device=DEV, dtype=dt)
+    v = torch.empty(a.B, ho, ho, a.cout, device=DEV, dtype=dt)
+
+    def call():   # one frame for all T steps (direct encoding)
+        _lib.check(_lib.lib.snnb_stem7x7_lif(x.data_ptr(), 0, wp.data_ptr(), b.data_ptr(), None, sp.data_ptr(),
+                                             v.data_ptr(), scratch.data_ptr(), nscratch, a.T, a.B, a.hw, a.hw,
+                                             a.cout, 1, 1, 1, *LIF, _stream()), "snnb_stem7x7_lif")
+
+    ms = _time(call, a.reps)
+    nbytes = 2 * (x.numel() + sp.numel() + v.numel()) + 2 * nscratch
+    print(f"stem7x7_lif B{a.B} 3->{a.cout} {a.hw}^2 T{a.T} bf16 (s2d + GEMM): {ms:.4f} ms  {nbytes / ms / 1e6:.0f} GB/s  "
+          f"spike rate {float(sp.float().mean()):.3f}  device status {_lib.device_status()}")
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    sub = ap.add_subparsers(dest="case", required=True)
+    c = sub.add_parser("conv")
+    c.add_argument("--B", type=int, default=64)
+    c.add_argument("--cin", type=int, default=128)
+    c.add_argument("--cout", type=int, default=128)
+    c.add_argument("--hw", type=int, default=56)
+    c.add_argument("--k", type=int, default=3)
+    c.add_argument("--s", type=int, default=1)
+    c.add_argument("--res", type=int, default=0)
+    c.add_argument("--dtype", choices=["bf16", "f16"], default="bf16")
+    c.add_argument("--path", type=int, default=_lib.PATH_TCGEN05,
+                   help="snnb_path: 0 auto, 1 simt, 2 tcgen05, 3 per-tap kernel, 4 halo kernel")
+    c.set_defaults(fn=case_conv)
+    l = sub.add_parser("lif")
+    l.add_argument("--n", type=int, default=1 << 24)
+    l.set_defaults(fn=case_lif)
+    d = sub.add_parser("dw")
+    d.add_argument("--B", type=int, default=32)
+    d.add_argument("--c", type=int, default=128)
+    d.add_argument("--hw", type=int, default=56)
+    d.set_defaults(fn=case_dw)
+    t = sub.add_parser("tail")
+    t.add_argument("--B", type=int, default=256)
+    t.add_argument("--c", type=int, default=1024)
+    t.add_argument("--hw", type=int, default=7)
+    t.add_argument("--classes", type=int, default=1000)
+    t.set_defaults(fn=case_tail)
+    m = sub.add_parser("stem")
+    m.add_argument("--B", type=int, default=128)
+    m.add_argument("--hw", type=int, default=224)
+    m.add_argument("--cout", type=int, default=64)
+    m.set_defaults(fn=case_stem)
+    for p in (c, l, d, t, m):
+        p.add_argument("--T", type=int, default=4)
+        p.add_argument("--reps", type=int, default=10)
+    a = ap.parse_args(argv)
+    if not torch.cuda.is_available():
+        raise SystemExit("microbench needs a CUDA device")
+    a.fn(a)
+
+
+if __name__ == "__main__":
+    main()
