@@ -133,6 +133,138 @@ dwconv3x3_lif_kernel(const XT *__restrict__ x, int64_t x_t_stride, const XT *__r
     if (wo0 + s < Wo) store_pack<VT, VEC>(v_out + (orow + wo0 + s) * C + c0, v[s]);
 }
 
+// Fast path: 4 channels per thread (a warp's load covers 32 x 4 consecutive channels), a strip of SS
+// output pixels, and per timestep ALL window loads of the strip issued before the first use, with the
+// loads of step t+1 in flight while step t is evaluated. Bounds, offsets and the LIF flavour are
+// resolved once per thread / at compile time; the window stays packed (16-bit) until it is used.
+template <typename XT> struct Raw4 { using type = uint2; };        // four 16-bit values
+template <> struct Raw4<float> { using type = uint4; };            // four fp32 values
+
+template <typename XT>
+__device__ __forceinline__ void unpack4(const typename Raw4<XT>::type &r, float (&f)[4]) {
+  if constexpr (sizeof(XT) == 4) {
+    f[0] = __uint_as_float(r.x); f[1] = __uint_as_float(r.y); f[2] = __uint_as_float(r.z); f[3] = __uint_as_float(r.w);
+  } else {
+    const XT *h = reinterpret_cast<const XT *>(&r);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) f[i] = DT<XT>::to_f(h[i]);
+  }
+}
+
+template <typename XT, typename ST, typename VT, int STRIDE, bool FAST>
+__global__ void __launch_bounds__(NT)
+dwconv3x3_lif_fast_kernel(const XT *__restrict__ x, int64_t x_t_stride, const XT *__restrict__ w,
+                          const XT *__restrict__ bias, const XT *__restrict__ res,
+                          const VT *__restrict__ v_init, ST *__restrict__ spikes, VT *__restrict__ v_out,
+                          int T, int B, int C, int H, int W, int Ho, int Wo, LifParams p) {
+  using Raw = typename Raw4<XT>::type;
+  constexpr int SS = STRIDE == 1 ? 4 : 2;                  // output pixels per thread
+  constexpr int NCOL = STRIDE == 1 ? SS + 2 : 2 * SS + 1;  // input columns the strip touches
+  const int CV = C / 4;
+  const int nstrips = (Wo + SS - 1) / SS;
+  const int64_t total = (int64_t)B * Ho * nstrips * CV;
+  int64_t idx = (int64_t)blockIdx.x * NT + threadIdx.x;
+  if (idx >= total) return;
+  const int cv = (int)(idx % CV);
+  idx /= CV;
+  const int strip = (int)(idx % nstrips);
+  idx /= nstrips;
+  const int ho = (int)(idx % Ho);
+  const int b = (int)(idx / Ho);
+  const int c0 = cv * 4;
+  const int wo0 = strip * SS;
+
+  float wr[9][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int k = 0; k < 9; ++k) wr[k][i] = DT<XT>::to_f(w[(int64_t)(c0 + i) * 9 + k]);
+  float bs[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) bs[i] = bias != nullptr ? DT<XT>::to_f(bias[c0 + i]) : 0.f;
+
+  // window geometry, fixed for the whole call: element offsets inside a frame and validity bits
+  const int hi0 = ho * STRIDE - 1, wi0 = wo0 * STRIDE - 1;
+  int off[3][NCOL];
+  unsigned ok_bits = 0;
+#pragma unroll
+  for (int r = 0; r < 3; ++r)
+#pragma unroll
+    for (int j = 0; j < NCOL; ++j) {
+      const int hi = hi0 + r, wi = wi0 + j;
+      const bool ok = hi >= 0 && hi < H && wi >= 0 && wi < W;
+      if (ok) ok_bits |= 1u << (r * NCOL + j);
+      off[r][j] = ok ? (hi * W + wi) * C : 0;
+    }
+  const XT *xb = x + (int64_t)b * H * W * C + c0;
+  auto load_window = [&](int t, Raw (&win)[3][NCOL]) {
+    const XT *xt = xb + (int64_t)t * x_t_stride;
+#pragma unroll
+    for (int r = 0; r < 3; ++r)
+#pragma unroll
+      for (int j = 0; j < NCOL; ++j) {
+        if ((ok_bits >> (r * NCOL + j)) & 1u) win[r][j] = __ldg(reinterpret_cast<const Raw *>(xt + off[r][j]));
+        else win[r][j] = Raw{};
+      }
+  };
+
+  const int64_t orow = ((int64_t)b * Ho + ho) * Wo;
+  const int64_t frame_out = (int64_t)B * Ho * Wo * C;
+  float v[SS][4];
+#pragma unroll
+  for (int s = 0; s < SS; ++s) {
+    if (v_init != nullptr && wo0 + s < Wo) {
+      load_pack<VT, 4>(v_init + (orow + wo0 + s) * C + c0, v[s]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) v[s][i] = 0.f;
+    }
+  }
+
+  Raw cur[3][NCOL], nxt[3][NCOL];
+  load_window(0, cur);
+  for (int t = 0; t < T; ++t) {
+    if (t + 1 < T) load_window(t + 1, nxt);
+#pragma unroll
+    for (int s = 0; s < SS; ++s) {
+      float y[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) y[i] = 0.f;
+#pragma unroll
+      for (int r = 0; r < 3; ++r)
+#pragma unroll
+        for (int k = 0; k < 3; ++k) {
+          float f[4];
+          unpack4<XT>(cur[r][s * STRIDE + k], f);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) y[i] = fmaf(f[i], wr[r * 3 + k][i], y[i]);
+        }
+      if (wo0 + s < Wo) {
+        const int64_t o = (int64_t)t * frame_out + (orow + wo0 + s) * C + c0;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) y[i] += bs[i];
+        if (res != nullptr) {
+          float rr[4];
+          load_pack<XT, 4>(res + o, rr);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) y[i] += rr[i];
+        }
+        float sp[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) sp[i] = FAST ? lif_step_t<1, true>(y[i], v[s][i], p) : lif_step(y[i], v[s][i], p);
+        store_pack<ST, 4>(spikes + o, sp);
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < 3; ++r)
+#pragma unroll
+      for (int j = 0; j < NCOL; ++j) cur[r][j] = nxt[r][j];
+  }
+#pragma unroll
+  for (int s = 0; s < SS; ++s)
+    if (wo0 + s < Wo) store_pack<VT, 4>(v_out + (orow + wo0 + s) * C + c0, v[s]);
+}
+
 template <typename XT, typename ST, typename VT>
 int launch(const void *x, int64_t xts, const void *w, const void *b, const void *res, const void *v_init,
            void *spikes, void *v_out, int T, int B, int C, int H, int W, int stride, const LifParams &p,
@@ -144,6 +276,24 @@ int launch(const void *x, int64_t xts, const void *w, const void *b, const void 
                    (v_init == nullptr || aligned16(v_init)) && (res == nullptr || aligned16(res)) &&
                    (xts % 4 == 0);
   const int VEC = vec ? 4 : 1;
+  // the fast kernel keeps 32-bit element offsets inside one image
+  if (vec && (int64_t)H * W * C < 0x7fffffffLL) {
+    const int SS = stride == 1 ? 4 : 2;
+    const int64_t tot = (int64_t)B * Ho * ((Wo + SS - 1) / SS) * (C / 4);
+    const int64_t nb = (tot + NT - 1) / NT;
+    if (nb > 0x7fffffffLL) return fail(SNNB_ERR_INVALID, "dwconv3x3_lif: problem too large");
+    const bool fast = p.mode == 1 && p.hard;
+#define SNNB_DWF(STR, FAST)                                                                            \
+  dwconv3x3_lif_fast_kernel<XT, ST, VT, STR, FAST><<<(unsigned)nb, NT, 0, stream>>>(                  \
+      static_cast<const XT *>(x), xts, static_cast<const XT *>(w), static_cast<const XT *>(b),         \
+      static_cast<const XT *>(res), static_cast<const VT *>(v_init), static_cast<ST *>(spikes),        \
+      static_cast<VT *>(v_out), T, B, C, H, W, Ho, Wo, p)
+    if (stride == 1) { if (fast) SNNB_DWF(1, true); else SNNB_DWF(1, false); }
+    else { if (fast) SNNB_DWF(2, true); else SNNB_DWF(2, false); }
+#undef SNNB_DWF
+    SNNB_CHECK_LAUNCH("dwconv3x3_lif");
+    return SNNB_OK;
+  }
   const int64_t total = (int64_t)B * Ho * nstrips * (C / VEC);
   const int64_t blocks = (total + NT - 1) / NT;
   if (blocks > 0x7fffffffLL) return fail(SNNB_ERR_INVALID, "dwconv3x3_lif: problem too large");

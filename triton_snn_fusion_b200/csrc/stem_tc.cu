@@ -10,7 +10,12 @@
 //   * the whole packed weight (Cout x 512 bytes) is loaded once per CTA and stays in shared memory;
 //   * the activation chunks of the coming tiles stream through a ring of 16 KB slots;
 //   * accumulators rotate through several TMEM stages, so the MMAs of tile i+1, i+2 run while the
-//     epilogue warps convert and store tile i.
+//     epilogue warps convert and store tile i;
+//   * with 64 output channels and 16-bit spikes a pixel's channels are one 128-byte row: each epilogue
+//     warp writes the rows of its 32 pixels for one timestep into a swizzled shared-memory slot of its
+//     own and a TMA store moves them out, with no synchronisation between warps. (A thread owns a
+//     pixel, so direct stores put every lane of a store instruction on a different 128-byte line,
+//     32 memory transactions per instruction.) Warps 0-3 and 4-7 work on alternate tiles.
 // Warps 0-7: epilogue (two per TMEM lane quarter, splitting the channels); warp 8: TMA producer;
 // warp 9: MMA issuer. Every mbarrier wait is bounded; on a timeout the CTA raises a status word,
 // skips its remaining work, frees its tensor memory and exits.
@@ -30,6 +35,7 @@ namespace {
 constexpr int kChunkBytes = 16384;   // 128 pixels x 128 bytes: one K chunk of a tile
 constexpr int kMaxRing = 12;
 constexpr int kMaxAcc = 4;
+constexpr int kStage = 4;            // staged epilogue: 4 x 16 KB = two 4 KB slots of outgoing rows per epilogue warp
 constexpr int kEpiWarpsS = 8;
 constexpr int kProdWarpS = kEpiWarpsS, kMmaWarpS = kEpiWarpsS + 1;
 constexpr int kThreadsS = 32 * (kEpiWarpsS + 2);
@@ -43,22 +49,103 @@ struct StemGeom {
   int stage_cols;       // TMEM columns per stage = Tacc * Cout
   int tmem_cols;
   int w_chunk_bytes;    // Cout * 128
+  int staged;           // spikes leave through shared memory + TMA stores (Cout = 64, 16-bit spikes)
 };
+
+// Staged epilogue of one tile for one warp, which owns 32 pixel rows of the tile (its TMEM lane quarter)
+// with all 64 channels: LIF over T with the 64 membrane potentials of a thread in registers, the
+// accumulator re-read from tensor memory at every step (that is cheap; keeping 64 more values in
+// registers is not). The spikes of a step go to a 4 KB slot owned by the warp (128-byte swizzle:
+// 16-byte chunk j of row r sits at chunk j ^ (r & 7)), which lane 0 hands to TMA as one box. The warp
+// synchronises with nobody else. FAST: tau a power of two and hard reset, resolved at compile time.
+template <typename XT, typename VT, bool FAST>
+__device__ __forceinline__ void staged_tile(const StemGeom &g, const LifParams &p, const CUtensorMap *smap,
+                                            uint32_t acc_addr, uint32_t accempty_bar, uint32_t slots, uint32_t &sslot,
+                                            const float *bias_s, const VT *__restrict__ v_init, VT *__restrict__ v_out,
+                                            int bx, int by, int b, long long pix, bool valid) {
+  const int lane = threadIdx.x & 31;
+  float v[64];
+  const bool alias = g.Tacc != g.T;
+  const long long o0 = pix * 64;
+  if (v_init != nullptr && valid) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      float tmp[16];
+      load_pack<VT, 16>(v_init + o0 + q * 16, tmp);
+#pragma unroll
+      for (int i = 0; i < 16; ++i) v[q * 16 + i] = tmp[i];
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 64; ++i) v[i] = 0.f;
+  }
+  for (int t = 0; t < g.T; ++t) {
+    // the slot written now was handed to TMA two steps ago: that store must have read it out
+    if (lane == 0) umma::bulk_wait_group_read<1>();
+    __syncwarp();
+    const uint32_t row = slots + sslot * 4096u + (uint32_t)lane * 128u;
+    const uint32_t src = acc_addr + (uint32_t)((alias ? 0 : t) * 64);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      uint32_t a[16];
+      umma::tmem_ld_x16(src + (uint32_t)(q * 16), a);
+      umma::tmem_ld_wait();
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        Pack<XT, 8> pk;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int c = q * 16 + h * 8 + i;
+          const float y = __uint_as_float(a[h * 8 + i]) + bias_s[c];
+          pk.v[i] = DT<XT>::from_f(FAST ? lif_step_t<1, true>(y, v[c], p) : lif_step(y, v[c], p));
+        }
+        const uint4 u = *reinterpret_cast<const uint4 *>(&pk);
+        const uint32_t dst = row + ((uint32_t)((q * 2 + h) ^ (lane & 7)) << 4);
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(u.x), "r"(u.y), "r"(u.z), "r"(u.w) : "memory");
+      }
+    }
+    if (t == g.T - 1) {   // last read of this accumulator stage: the MMA warp may overwrite it
+      umma::tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) umma::mbar_arrive(accempty_bar);
+    }
+    umma::fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) {
+      umma::tma_store_4d(smap, slots + sslot * 4096u, 0, bx, by, t * g.B + b);
+      umma::bulk_commit_group();
+    }
+    sslot ^= 1u;
+  }
+  if (valid) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      float tmp[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) tmp[i] = v[q * 16 + i];
+      store_pack<VT, 16, false>(v_out + o0 + q * 16, tmp);
+    }
+  }
+}
 
 template <typename XT, typename ST, typename VT>
 __global__ void __launch_bounds__(kThreadsS)
 stem_gemm_lif_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap,
-                     const XT *__restrict__ bias, const VT *__restrict__ v_init, ST *__restrict__ spikes,
-                     VT *__restrict__ v_out, const StemGeom g, const LifParams p) {
+                     const __grid_constant__ CUtensorMap smap, const XT *__restrict__ bias,
+                     const VT *__restrict__ v_init, ST *__restrict__ spikes, VT *__restrict__ v_out,
+                     const StemGeom g, const LifParams p) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bars[2 * kMaxRing + 1 + 2 * kMaxAcc];
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_s;
+  __shared__ float bias_s[128];
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x < 128) bias_s[threadIdx.x] = (bias != nullptr && (int)threadIdx.x < g.Cout) ? DT<XT>::to_f(bias[threadIdx.x]) : 0.f;
   const uint32_t smem_base = (umma::smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t w_base = smem_base;                                   // 4 weight chunks, resident
   const uint32_t a_base = smem_base + 4u * (uint32_t)g.w_chunk_bytes;  // activation ring
+  const uint32_t stage_base = a_base + (uint32_t)g.ring * (uint32_t)kChunkBytes;   // outgoing spike tiles (staged epilogue)
   const uint32_t bar_base = umma::smem_u32(bars);
   auto afull = [&](uint32_t s) { return bar_base + 8u * s; };
   auto aempty = [&](uint32_t s) { return bar_base + 8u * ((uint32_t)kMaxRing + s); };
@@ -79,7 +166,7 @@ stem_gemm_lif_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_cons
     abort_s = 0;
     for (int s = 0; s < g.ring; ++s) { umma::mbar_init(afull(s), 1); umma::mbar_init(aempty(s), 1); }
     umma::mbar_init(wfull, 1);
-    for (int s = 0; s < g.nacc; ++s) { umma::mbar_init(accfull(s), 1); umma::mbar_init(accempty(s), kEpiWarpsS); }
+    for (int s = 0; s < g.nacc; ++s) { umma::mbar_init(accfull(s), 1); umma::mbar_init(accempty(s), g.staged ? kEpiWarpsS / 2 : kEpiWarpsS); }
     umma::fence_mbar_init();
   }
   if (warp == kMmaWarpS) {
@@ -89,6 +176,7 @@ stem_gemm_lif_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_cons
   if (warp == kProdWarpS && lane == 0) {
     umma::prefetch_tensormap(&xmap);
     umma::prefetch_tensormap(&wmap);
+    if (g.staged) umma::prefetch_tensormap(&smap);
   }
   umma::tc_fence_before_sync();
   __syncthreads();
@@ -159,8 +247,43 @@ stem_gemm_lif_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_cons
     const int c_end = (warp < 4) ? half : nch;
     const EpiGeom eg{g.T, g.Tacc, g.Cout, g.Cout, 0};
     const long long frame_out = (long long)g.B * g.Ho * g.Wo * g.Cout;
-    uint32_t acc = 0, accphase = 0;
     bool ok = true;
+    if constexpr (std::is_same<ST, XT>::value) {
+      if (g.staged) {
+        // Warps 0-3 take this CTA's even tiles, warps 4-7 the odd ones; a warp converts all 64 channels of
+        // its 32 pixels and sends them out by itself, so the epilogue has no block-wide synchronisation.
+        const int group = warp >> 2;
+        const uint32_t slots = stage_base + (uint32_t)warp * 8192u;   // two 4 KB slots per warp
+        uint32_t sslot = 0;
+        // box of this warp inside the tile: 32 consecutive tile rows
+        const int bx_off = (g.BW >= 32) ? (quarter * 32) % g.BW : 0;
+        const int by_off = (g.BW >= 32) ? (quarter * 32) / g.BW : quarter * (32 / g.BW);
+        int it = group;
+        for (int tile = blockIdx.x + group * gridDim.x; tile < g.total_tiles && ok; tile += 2 * gridDim.x, it += 2) {
+          int w0, h0, b;
+          decode(tile, w0, h0, b);
+          const int wo = w0 + pw, ho = h0 + ph;
+          const bool valid = wo < g.Wo && ho < g.Ho;
+          const long long pix = ((long long)b * g.Ho + ho) * g.Wo + wo;
+          const uint32_t acc = (uint32_t)(it % g.nacc), accphase = (uint32_t)((it / g.nacc) & 1);
+          if (lane == 0) ok = umma::mbar_wait(accfull(acc), accphase, abort_flag);
+          ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+          if (!ok) break;
+          umma::tc_fence_after_sync();
+          const uint32_t acc_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * (uint32_t)g.stage_cols;
+          if (p.mode == 1 && p.hard)
+            staged_tile<XT, VT, true>(g, p, &smap, acc_addr, accempty(acc), slots, sslot, bias_s, v_init, v_out,
+                                      w0 + bx_off, h0 + by_off, b, pix, valid);
+          else
+            staged_tile<XT, VT, false>(g, p, &smap, acc_addr, accempty(acc), slots, sslot, bias_s, v_init, v_out,
+                                       w0 + bx_off, h0 + by_off, b, pix, valid);
+        }
+        // the shared-memory slots must outlive the TMA stores that read them
+        if (lane == 0) umma::bulk_wait_group_read<0>();
+        ok = false;   // done: skip the direct-store loop below
+      }
+    }
+    uint32_t acc = 0, accphase = 0;
     for (int tile = blockIdx.x; tile < g.total_tiles && ok; tile += gridDim.x) {
       int w0, h0, b;
       decode(tile, w0, h0, b);
@@ -171,8 +294,8 @@ stem_gemm_lif_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_cons
       ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
       if (!ok) break;
       umma::tc_fence_after_sync();
-      const EpiArgs<XT, ST, VT> ea{bias, nullptr, v_init, spikes, v_out,
-                                   tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * (uint32_t)g.stage_cols,
+      const uint32_t acc_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * (uint32_t)g.stage_cols;
+      const EpiArgs<XT, ST, VT> ea{bias, nullptr, v_init, spikes, v_out, acc_addr,
                                    pix, frame_out, 0, c_begin, c_end, valid};
       epilogue_dispatch<XT, ST, VT>(ea, eg, 1, p);
       // this stage may now be overwritten
@@ -220,7 +343,8 @@ int launch(const StemGemmArgs &a, cudaStream_t stream) {
   while (cols < g.nacc * g.stage_cols) cols *= 2;
   g.tmem_cols = cols;
   g.w_chunk_bytes = a.Cout * 128;
-  const int budget = 224 * 1024 - 1024 - 4 * g.w_chunk_bytes;
+  g.staged = (a.Cout == 64 && std::is_same<ST, XT>::value) ? 1 : 0;
+  const int budget = 224 * 1024 - 1024 - 4 * g.w_chunk_bytes - (g.staged ? kStage * kChunkBytes : 0);
   g.ring = budget / kChunkBytes < kMaxRing ? budget / kChunkBytes : kMaxRing;
   int dev = 0, sms = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 1)
@@ -243,11 +367,20 @@ int launch(const StemGemmArgs &a, cudaStream_t stream) {
     const int rc = encode_tmap(&wm, a.dtype, 2, a.w_packed, dims, strides, box);
     if (rc != SNNB_OK) return rc;
   }
-  const size_t smem = (size_t)4 * g.w_chunk_bytes + (size_t)g.ring * kChunkBytes + 1024;
+  CUtensorMap sm = xm;
+  if (g.staged) {  // spikes [T * B][Ho][Wo][64]: a tile of one step leaves as one box
+    cuuint64_t dims[4] = {64, (cuuint64_t)a.Wo, (cuuint64_t)a.Ho, (cuuint64_t)a.T * a.B};
+    cuuint64_t strides[3] = {(cuuint64_t)64 * es, (cuuint64_t)a.Wo * 64 * es, (cuuint64_t)a.Ho * a.Wo * 64 * es};
+    // a warp stores its 32 tile rows: part of one image row, or 32 / BW whole rows of the tile
+    cuuint32_t box[4] = {64, (cuuint32_t)(g.BW >= 32 ? 32 : g.BW), (cuuint32_t)(g.BW >= 32 ? 1 : 32 / g.BW), 1};
+    const int rc = encode_tmap(&sm, a.dtype, 4, a.spikes, dims, strides, box);
+    if (rc != SNNB_OK) return rc;
+  }
+  const size_t smem = (size_t)4 * g.w_chunk_bytes + (size_t)g.ring * kChunkBytes + (g.staged ? (size_t)kStage * kChunkBytes : 0) + 1024;
   auto kern = stem_gemm_lif_kernel<XT, ST, VT>;
   const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return fail(SNNB_ERR_CUDA, "stem7x7_lif: cannot raise the shared-memory limit: %s", cudaGetErrorString(e));
-  kern<<<(unsigned)grid, kThreadsS, smem, stream>>>(xm, wm, static_cast<const XT *>(a.b), static_cast<const VT *>(a.v_init),
+  kern<<<(unsigned)grid, kThreadsS, smem, stream>>>(xm, wm, sm, static_cast<const XT *>(a.b), static_cast<const VT *>(a.v_init),
                                                     static_cast<ST *>(a.spikes), static_cast<VT *>(a.v_out), g, a.p);
   SNNB_CHECK_LAUNCH("stem_gemm_lif");
   return SNNB_OK;
