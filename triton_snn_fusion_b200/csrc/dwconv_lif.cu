@@ -152,7 +152,7 @@ __device__ __forceinline__ void unpack4(const typename Raw4<XT>::type &r, float 
 }
 
 template <typename XT, typename ST, typename VT, int STRIDE, bool FAST>
-__global__ void __launch_bounds__(NT)
+__global__ void __launch_bounds__(NT, 3)
 dwconv3x3_lif_fast_kernel(const XT *__restrict__ x, int64_t x_t_stride, const XT *__restrict__ w,
                           const XT *__restrict__ bias, const XT *__restrict__ res,
                           const VT *__restrict__ v_init, ST *__restrict__ spikes, VT *__restrict__ v_out,
@@ -185,7 +185,6 @@ dwconv3x3_lif_fast_kernel(const XT *__restrict__ x, int64_t x_t_stride, const XT
 
   // window geometry, fixed for the whole call: element offsets inside a frame and validity bits
   const int hi0 = ho * STRIDE - 1, wi0 = wo0 * STRIDE - 1;
-  int off[3][NCOL];
   unsigned ok_bits = 0;
 #pragma unroll
   for (int r = 0; r < 3; ++r)
@@ -194,8 +193,8 @@ dwconv3x3_lif_fast_kernel(const XT *__restrict__ x, int64_t x_t_stride, const XT
       const int hi = hi0 + r, wi = wi0 + j;
       const bool ok = hi >= 0 && hi < H && wi >= 0 && wi < W;
       if (ok) ok_bits |= 1u << (r * NCOL + j);
-      off[r][j] = ok ? (hi * W + wi) * C : 0;
     }
+  const int off0 = (hi0 * W + wi0) * C, row_step = W * C;   // offset of window element (r, j): off0 + r * row_step + j * C
   const XT *xb = x + (int64_t)b * H * W * C + c0;
   auto load_window = [&](int t, Raw (&win)[3][NCOL]) {
     const XT *xt = xb + (int64_t)t * x_t_stride;
@@ -203,7 +202,7 @@ dwconv3x3_lif_fast_kernel(const XT *__restrict__ x, int64_t x_t_stride, const XT
     for (int r = 0; r < 3; ++r)
 #pragma unroll
       for (int j = 0; j < NCOL; ++j) {
-        if ((ok_bits >> (r * NCOL + j)) & 1u) win[r][j] = __ldg(reinterpret_cast<const Raw *>(xt + off[r][j]));
+        if ((ok_bits >> (r * NCOL + j)) & 1u) win[r][j] = __ldg(reinterpret_cast<const Raw *>(xt + (off0 + r * row_step + j * C)));
         else win[r][j] = Raw{};
       }
   };
@@ -221,44 +220,63 @@ dwconv3x3_lif_fast_kernel(const XT *__restrict__ x, int64_t x_t_stride, const XT
     }
   }
 
-  Raw cur[3][NCOL], nxt[3][NCOL];
+  // 16-bit data: the window of step t+1 is fetched while step t is evaluated (fp32 windows are too
+  // large to hold twice)
+  constexpr bool PF = sizeof(XT) == 2;
+  Raw cur[3][NCOL], nxt[PF ? 3 : 1][PF ? NCOL : 1];
   load_window(0, cur);
+#pragma unroll 1
   for (int t = 0; t < T; ++t) {
-    if (t + 1 < T) load_window(t + 1, nxt);
+    if constexpr (PF) {
+      if (t + 1 < T) load_window(t + 1, nxt);
+    }
+    // column by column: a window column is unpacked once and feeds every output of the strip that
+    // touches it, so only one column of fp32 values is live besides the accumulators
+    float y[SS][4];
+#pragma unroll
+    for (int s = 0; s < SS; ++s)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) y[s][i] = bs[i];
+#pragma unroll
+    for (int j = 0; j < NCOL; ++j) {
+      float f[3][4];
+#pragma unroll
+      for (int r = 0; r < 3; ++r) unpack4<XT>(cur[r][j], f[r]);
+#pragma unroll
+      for (int s = 0; s < SS; ++s) {
+        const int k = j - s * STRIDE;
+        if (k >= 0 && k < 3) {
+#pragma unroll
+          for (int r = 0; r < 3; ++r)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) y[s][i] = fmaf(f[r][i], wr[r * 3 + k][i], y[s][i]);
+        }
+      }
+    }
 #pragma unroll
     for (int s = 0; s < SS; ++s) {
-      float y[4];
-#pragma unroll
-      for (int i = 0; i < 4; ++i) y[i] = 0.f;
-#pragma unroll
-      for (int r = 0; r < 3; ++r)
-#pragma unroll
-        for (int k = 0; k < 3; ++k) {
-          float f[4];
-          unpack4<XT>(cur[r][s * STRIDE + k], f);
-#pragma unroll
-          for (int i = 0; i < 4; ++i) y[i] = fmaf(f[i], wr[r * 3 + k][i], y[i]);
-        }
       if (wo0 + s < Wo) {
         const int64_t o = (int64_t)t * frame_out + (orow + wo0 + s) * C + c0;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) y[i] += bs[i];
         if (res != nullptr) {
           float rr[4];
           load_pack<XT, 4>(res + o, rr);
 #pragma unroll
-          for (int i = 0; i < 4; ++i) y[i] += rr[i];
+          for (int i = 0; i < 4; ++i) y[s][i] += rr[i];
         }
         float sp[4];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) sp[i] = FAST ? lif_step_t<1, true>(y[i], v[s][i], p) : lif_step(y[i], v[s][i], p);
+        for (int i = 0; i < 4; ++i) sp[i] = FAST ? lif_step_t<1, true>(y[s][i], v[s][i], p) : lif_step(y[s][i], v[s][i], p);
         store_pack<ST, 4>(spikes + o, sp);
       }
     }
+    if constexpr (PF) {
 #pragma unroll
-    for (int r = 0; r < 3; ++r)
+      for (int r = 0; r < 3; ++r)
 #pragma unroll
-      for (int j = 0; j < NCOL; ++j) cur[r][j] = nxt[r][j];
+        for (int j = 0; j < NCOL; ++j) cur[r][j] = nxt[r][j];
+    } else {
+      if (t + 1 < T) load_window(t + 1, cur);
+    }
   }
 #pragma unroll
   for (int s = 0; s < SS; ++s)
