@@ -128,7 +128,9 @@ int snnb_dwconv3x3_lif(const void *x_seq, int64_t x_t_stride, const void *w, con
  *   frame at every step: the conv is evaluated once and only the LIF runs T
  *   times), w [Cout][KH][KW][Cin] (the torch weight in channels_last memory
  *   format), b [Cout], residual NULL or [T][B][Ho][Wo][Cout],
- *   spikes [T][B][Ho][Wo][Cout], v_init/v_out [B][Ho][Wo][Cout].
+ *   spikes [T][B][Ho][Wo][Cout], v_init/v_out [B][Ho][Wo][Cout]. v_out may be NULL: the
+ *   membrane after step T is then not written (a forward pass through a whole network needs
+ *   only the spikes; the reference's op always returns it).
  * `lif` = 0 turns the LIF off: `spikes` then receives conv + bias (+ residual)
  * in the activation dtype for every t and v_init / v_out are ignored (used for
  * the BN-folded shortcut convs that feed a residual input).
@@ -150,7 +152,8 @@ int snnb_conv_lif(const void *x_seq, int64_t x_t_stride, const void *w, const vo
  * snnb_conv_lif runs this shape on CUDA cores, this entry is the fast path for 16-bit data.
  *   x_seq [T][B][H][W][3] (x_t_stride elements apart; 0 = one frame for every step, convolved once),
  *   H and W even; w_packed [Cout][4][4][16] produced once by snnb_stem7x7_pack_weight from the
- *   [Cout][7][7][3] channels-last weight; spikes [T][B][H/2][W/2][Cout]; v_init/v_out [B][H/2][W/2][Cout].
+ *   [Cout][7][7][3] channels-last weight; spikes [T][B][H/2][W/2][Cout]; v_init/v_out [B][H/2][W/2][Cout]
+ *   (v_out may be NULL, as for snnb_conv_lif).
  *   scratch: snnb_stem7x7_scratch_bytes(frames, H, W) bytes of device memory, 16-byte aligned, where
  *   frames = B if x_t_stride == 0 else T*B. It holds the input re-laid as 2x2-pixel blocks with a
  *   zero border; its contents are overwritten by every call.
@@ -217,6 +220,15 @@ int snnb_nchw_to_nhwc(const void *src, void *dst, int64_t frames, int C, int HW,
 int snnb_nhwc_to_nchw(const void *src, void *dst, int64_t frames, int C, int HW, int dtype, void *stream);
 /* max_pool2d(kernel 3, stride 2, padding 1) over `frames` NHWC frames. */
 int snnb_maxpool3x3s2(const void *x, void *y, int64_t frames, int H, int W, int C, int dtype, void *stream);
+
+/*
+ * The same pooling for spikes stored as one byte each (spike_dtype = SNNB_U8 of the fused entry
+ * points): x [frames][H][W][C] uint8 (0 / 1) -> y [frames][Ho][Wo][C] in out_dtype. C % 16 == 0.
+ * Reading one byte per spike halves the traffic of the widest activation of a ResNet (the stem
+ * output). No counterpart in the reference, whose spikes always have the activation dtype.
+ */
+int snnb_maxpool3x3s2_u8(const void *x, void *y, int64_t frames, int H, int W, int C, int out_dtype,
+                         void *stream);
 /* out[n][k] = (1/T) sum_t ( fc_w . mean_hw x[t][n] + fc_b ), x NHWC [T][N][HW][C], out fp32. */
 int snnb_avgpool_linear_mean(const void *x_seq, const void *fc_w, const void *fc_b, float *out,
                              int T, int N, int C, int HW, int K, int dtype, void *stream);

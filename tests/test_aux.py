@@ -41,6 +41,21 @@ def test_maxpool(dtype, shape):
     assert torch.equal(y.cpu().float().permute(0, 3, 1, 2), ref)
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("shape", [(3, 64, 16, 16), (2, 16, 9, 7), (1, 32, 112, 112)])
+def test_maxpool_of_byte_spikes(dtype, shape):
+    """snnb_maxpool3x3s2_u8: one-byte spikes in, pooled spikes in the activation dtype out."""
+    L = _lib()
+    F_, C, H, W = shape
+    x = (torch.rand(shape) < 0.3)
+    ref = F.max_pool2d(x.float(), 3, 2, 1)
+    xd = x.to(torch.uint8).permute(0, 2, 3, 1).contiguous().to(DEV)
+    Ho, Wo = ref.shape[2], ref.shape[3]
+    y = torch.empty(F_, Ho, Wo, C, dtype=dtype, device=DEV)
+    L.check(L.lib.snnb_maxpool3x3s2_u8(xd.data_ptr(), y.data_ptr(), F_, H, W, C, L.dtype_code(dtype), None), "maxpool_u8")
+    assert torch.equal(y.cpu().float().permute(0, 3, 1, 2), ref)
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_avgpool_linear_mean(dtype):
     L = _lib()

@@ -215,3 +215,32 @@ def _check_stem(hw, alias, cout, T):
     assert r.kernel_key == "k7_s2_p3"
     check_parity(r.spikes, r.v_next, rs, rv, dtype, what=f"stem {hw} alias={alias} cout={cout} T={T}")
     assert 0.02 < float(rs.mean()) < 0.6
+
+
+@pytest.mark.parametrize("hw,alias", [((64, 64), True), ((36, 52), True), ((40, 56), False)])
+def test_stem_byte_spikes_and_no_membrane_output(hw, alias):
+    """snnb_stem7x7_lif with spike_dtype = U8 (64-byte rows through the TMA-store epilogue) and v_out = NULL:
+    the same spikes as with 16-bit spikes and a membrane output."""
+    from triton_snn_fusion_b200 import _lib as L
+    H, W = hw
+    dtype, T, B, cout = torch.bfloat16, 4, 2, 64
+    torch.manual_seed(H * W + alias)
+    frames = 1 if alias else T
+    x = torch.randn(frames, B, H, W, 3).to(dtype).to(DEV)
+    w = (torch.randn(cout, 7, 7, 3) * (2.0 / 147) ** 0.5).to(dtype).to(DEV)
+    b = (torch.randn(cout) * 0.1).to(dtype).to(DEV)
+    wp = torch.empty(cout, 256, dtype=dtype, device=DEV)
+    L.check(L.lib.snnb_stem7x7_pack_weight(w.data_ptr(), wp.data_ptr(), cout, L.dtype_code(dtype), None), "pack")
+    nbytes = int(L.lib.snnb_stem7x7_scratch_bytes(frames * B, H, W))
+    scratch = torch.empty(nbytes, dtype=torch.uint8, device=DEV)
+    xts = 0 if alias else x.stride(0)
+    outs = {}
+    for name, sdt, with_v in (("wide", dtype, True), ("bytes", torch.uint8, False)):
+        sp = torch.empty(T, B, H // 2, W // 2, cout, dtype=sdt, device=DEV)
+        v = torch.empty(B, H // 2, W // 2, cout, dtype=dtype, device=DEV) if with_v else None
+        L.check(L.lib.snnb_stem7x7_lif(x.data_ptr(), xts, wp.data_ptr(), b.data_ptr(), None, sp.data_ptr(),
+                                       v.data_ptr() if with_v else None, scratch.data_ptr(), nbytes, T, B, H, W, cout,
+                                       L.dtype_code(dtype), L.dtype_code(sdt), L.dtype_code(dtype), 1.0, 0.0, 2.0, None), name)
+        outs[name] = sp.float().cpu()
+    assert torch.equal(outs["wide"], outs["bytes"])
+    assert 0.02 < float(outs["wide"].mean()) < 0.6

@@ -17,7 +17,8 @@ def _run_net(name, B, T, hw, dtype, classes, path="auto"):
     from triton_snn_fusion_b200 import nets
     spec = nets.NETS[name](classes)
     params = nets.make_params(spec, seed=2026)
-    net = nets.CompiledNet(spec, params, batch=B, T=T, in_hw=(hw, hw), dtype=dtype, device="cuda", conv_path=path)
+    net = nets.CompiledNet(spec, params, batch=B, T=T, in_hw=(hw, hw), dtype=dtype, device="cuda", conv_path=path,
+                           keep_membranes=True)
     x = torch.randn(B, 3, hw, hw, generator=torch.Generator().manual_seed(2026)).to(dtype)
     logits = net.forward_nchw(x.cuda()).cpu()
     torch.cuda.synchronize()
@@ -82,3 +83,40 @@ def test_cuda_graph_replay_matches_eager_issue():
     b = net.forward(x).clone()
     torch.cuda.synchronize()
     assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("name,dtype", [("resnet18", torch.bfloat16), ("resnet18", torch.float32),
+                                        ("mobilenet_v1", torch.bfloat16)])
+def test_forward_without_membrane_outputs(name, dtype):
+    """v_out = NULL (the executor's default): same spikes, hence bit-identical logits."""
+    from triton_snn_fusion_b200 import nets
+    spec = nets.NETS[name](100)
+    params = nets.make_params(spec, seed=7)
+    x = torch.randn(2, 64, 64, 3, generator=torch.Generator().manual_seed(3)).to(dtype).cuda()
+    outs = []
+    for keep in (True, False):
+        net = nets.CompiledNet(spec, params, batch=2, T=4, in_hw=(64, 64), dtype=dtype, device="cuda",
+                               keep_membranes=keep)
+        outs.append(net.forward(x).clone())
+    torch.cuda.synchronize()
+    assert torch.equal(outs[0], outs[1])
+
+
+def test_pipelined_submit_matches_forward():
+    """submit(): staged host->device copies on a side stream; same logits as forward() for every batch."""
+    from triton_snn_fusion_b200 import nets
+    spec = nets.spiking_resnet18(100)
+    params = nets.make_params(spec, seed=5)
+    net = nets.CompiledNet(spec, params, batch=2, T=4, in_hw=(64, 64), dtype=torch.bfloat16, device="cuda")
+    g = torch.Generator().manual_seed(11)
+    batches = [torch.randn(2, 64, 64, 3, generator=g).to(torch.bfloat16).pin_memory() for _ in range(5)]
+    want = []
+    for b in batches:
+        want.append(net.forward(b.cuda()).clone())
+    net.capture()
+    outs = [torch.empty(2, 100, dtype=torch.float32).pin_memory() for _ in batches]
+    for b, o in zip(batches, outs):
+        net.submit(b, o)
+    torch.cuda.synchronize()
+    for w, o in zip(want, outs):
+        assert torch.equal(w.cpu(), o)

@@ -91,6 +91,41 @@ int maxpool(const void *x, void *y, int64_t frames, int H, int W, int C, cudaStr
   return SNNB_OK;
 }
 
+// The same pooling over one-byte spikes (0 / 1), written out in the activation dtype: a thread owns
+// 16 channels of one output pixel (16 bytes in, 32 bytes out for 16-bit activations). Bytes are
+// combined with a per-byte unsigned max, four at a time.
+template <typename XT>
+__global__ void __launch_bounds__(256)
+maxpool3x3s2_u8_kernel(const uint8_t *__restrict__ x, XT *__restrict__ y, int64_t frames, int H, int W, int C, int Ho, int Wo) {
+  const int CV = C / 16;
+  const int64_t total = frames * Ho * Wo * CV;
+  int64_t idx = (int64_t)blockIdx.x * 256 + threadIdx.x;
+  if (idx >= total) return;
+  const int cv = (int)(idx % CV); idx /= CV;
+  const int wo = (int)(idx % Wo); idx /= Wo;
+  const int ho = (int)(idx % Ho);
+  const int64_t f = idx / Ho;
+  uint4 m = make_uint4(0u, 0u, 0u, 0u);
+  const uint8_t *xf = x + f * (int64_t)H * W * C + cv * 16;
+#pragma unroll
+  for (int r = 0; r < 3; ++r) {
+    const int hi = ho * 2 - 1 + r;
+    if (hi < 0 || hi >= H) continue;
+#pragma unroll
+    for (int c = 0; c < 3; ++c) {
+      const int wi = wo * 2 - 1 + c;
+      if (wi < 0 || wi >= W) continue;
+      const uint4 v = __ldg(reinterpret_cast<const uint4 *>(xf + ((int64_t)hi * W + wi) * C));
+      m.x = __vmaxu4(m.x, v.x); m.y = __vmaxu4(m.y, v.y); m.z = __vmaxu4(m.z, v.z); m.w = __vmaxu4(m.w, v.w);
+    }
+  }
+  const uint32_t words[4] = {m.x, m.y, m.z, m.w};
+  float out[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) out[i] = (float)((words[i >> 2] >> ((i & 3) * 8)) & 0xffu);
+  store_pack<XT, 16, false>(y + ((f * Ho + ho) * (int64_t)Wo + wo) * C + cv * 16, out);
+}
+
 // One CTA per group of SB samples: channel sums over (t, pixel) into shared memory, then a
 // warp-per-class mat-vec for the SB samples with the fc row read once.
 constexpr int SB = 2;
@@ -178,6 +213,26 @@ extern "C" int snnb_maxpool3x3s2(const void *x, void *y, int64_t frames, int H, 
     case SNNB_F16: return maxpool<__half>(x, y, frames, H, W, C, st);
     default: return fail(SNNB_ERR_INVALID, "maxpool3x3s2: unsupported dtype %d", dtype);
   }
+}
+
+extern "C" int snnb_maxpool3x3s2_u8(const void *x, void *y, int64_t frames, int H, int W, int C, int out_dtype, void *stream) {
+  using namespace snnb;
+  SNNB_CHECK_ARG(x && y, "maxpool3x3s2_u8: null pointer");
+  SNNB_CHECK_ARG(frames >= 0 && H >= 1 && W >= 1 && C >= 16 && C % 16 == 0, "maxpool3x3s2_u8: bad sizes (C must be a multiple of 16)");
+  SNNB_CHECK_ARG(is_act_dtype(out_dtype), "maxpool3x3s2_u8: unsupported output dtype %d", out_dtype);
+  SNNB_CHECK_ARG(aligned16(x) && aligned16(y), "maxpool3x3s2_u8: buffers must be 16-byte aligned");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int Ho = (H + 2 - 3) / 2 + 1, Wo = (W + 2 - 3) / 2 + 1;
+  const int64_t total = frames * Ho * Wo * (C / 16);
+  const int64_t blocks = (total + 255) / 256;
+  if (blocks > 0x7fffffffLL) return fail(SNNB_ERR_INVALID, "maxpool3x3s2_u8: problem too large");
+  if (blocks == 0) return SNNB_OK;
+  const uint8_t *xs = static_cast<const uint8_t *>(x);
+  if (out_dtype == SNNB_F32) maxpool3x3s2_u8_kernel<float><<<(unsigned)blocks, 256, 0, st>>>(xs, static_cast<float *>(y), frames, H, W, C, Ho, Wo);
+  else if (out_dtype == SNNB_BF16) maxpool3x3s2_u8_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, st>>>(xs, static_cast<__nv_bfloat16 *>(y), frames, H, W, C, Ho, Wo);
+  else maxpool3x3s2_u8_kernel<__half><<<(unsigned)blocks, 256, 0, st>>>(xs, static_cast<__half *>(y), frames, H, W, C, Ho, Wo);
+  SNNB_CHECK_LAUNCH("maxpool3x3s2_u8");
+  return SNNB_OK;
 }
 
 extern "C" int snnb_avgpool_linear_mean(const void *x_seq, const void *fc_w, const void *fc_b, float *out,

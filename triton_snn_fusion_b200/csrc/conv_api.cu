@@ -27,7 +27,6 @@ extern "C" int snnb_conv_lif(const void *x_seq, int64_t x_t_stride, const void *
                              float v_th, float v_reset, float tau, int path, void *stream) {
   using namespace snnb;
   SNNB_CHECK_ARG(x_seq && w && spikes, "conv_lif: null pointer");
-  SNNB_CHECK_ARG(!lif || v_out, "conv_lif: v_out is required when lif != 0");
   SNNB_CHECK_ARG(T >= 1 && B >= 1 && Cin >= 1 && Cout >= 1 && H >= 1 && W >= 1, "conv_lif: sizes must be positive");
   SNNB_CHECK_ARG(KH >= 1 && KW >= 1 && stride >= 1 && pad >= 0, "conv_lif: bad kernel/stride/padding");
   SNNB_CHECK_ARG(is_act_dtype(dtype), "conv_lif: unsupported dtype %d", dtype);
@@ -55,7 +54,7 @@ extern "C" int snnb_linear_lif(const void *x_seq, int64_t x_t_stride, const void
                                int T, int M, int K, int N, int dtype, int spike_dtype, int v_dtype,
                                float v_th, float v_reset, float tau, int path, void *stream) {
   using namespace snnb;
-  SNNB_CHECK_ARG(x_seq && w && spikes && v_out, "linear_lif: null pointer");
+  SNNB_CHECK_ARG(x_seq && w && spikes, "linear_lif: null pointer");
   SNNB_CHECK_ARG(T >= 1 && M >= 1 && K >= 1 && N >= 1, "linear_lif: sizes must be positive");
   SNNB_CHECK_ARG(is_act_dtype(dtype), "linear_lif: unsupported dtype %d", dtype);
   SNNB_CHECK_ARG(spike_dtype == dtype || spike_dtype == SNNB_U8, "linear_lif: spike dtype must be the x dtype or u8");

@@ -428,7 +428,7 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
         __syncwarp();
         if (lane == 0) umma::mbar_arrive(accempty(pair));
       }
-      if (ok && g.lif) {
+      if (ok && g.lif && v_out != nullptr) {
 #pragma unroll
         for (int i = 0; i < 64; ++i)
           if (((pm.rows_ok >> (i >> 3)) & 1) && ((pm.cols_ok >> (i & 7)) & 1))

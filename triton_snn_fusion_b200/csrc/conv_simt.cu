@@ -169,7 +169,7 @@ conv_lif_simt_kernel(const XT *__restrict__ x, int64_t x_t_stride, const XT *__r
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const int n = n0 + tx * 4 + j;
-        if (n < Cout) v_out[m * Cout + n] = DT<VT>::from_f(v[i][j]);
+        if (v_out != nullptr && n < Cout) v_out[m * Cout + n] = DT<VT>::from_f(v[i][j]);
       }
     }
   }

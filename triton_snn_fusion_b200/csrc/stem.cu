@@ -94,7 +94,7 @@ extern "C" int snnb_stem7x7_lif(const void *x_seq, int64_t x_t_stride, const voi
                                 int T, int B, int H, int W, int Cout, int dtype, int spike_dtype, int v_dtype,
                                 float v_th, float v_reset, float tau, void *stream) {
   using namespace snnb;
-  SNNB_CHECK_ARG(x_seq && w_packed && spikes && v_out && scratch, "stem7x7_lif: null pointer");
+  SNNB_CHECK_ARG(x_seq && w_packed && spikes && scratch, "stem7x7_lif: null pointer");
   SNNB_CHECK_ARG(dtype == SNNB_BF16 || dtype == SNNB_F16, "stem7x7_lif: dtype must be bf16 or f16");
   SNNB_CHECK_ARG(T >= 1 && B >= 1 && Cout >= 16 && Cout % 16 == 0, "stem7x7_lif: bad T/B/Cout");
   SNNB_CHECK_ARG(H >= 2 && W >= 2 && H % 2 == 0 && W % 2 == 0, "stem7x7_lif: H and W must be even");

@@ -11,7 +11,7 @@
 //   * the activation chunks of the coming tiles stream through a ring of 16 KB slots;
 //   * accumulators rotate through several TMEM stages, so the MMAs of tile i+1, i+2 run while the
 //     epilogue warps convert and store tile i;
-//   * with 64 output channels and 16-bit spikes a pixel's channels are one 128-byte row: each epilogue
+//   * with 64 output channels a pixel's spikes are one 128-byte row (64 bytes for u8 spikes): each epilogue
 //     warp writes the rows of its 32 pixels for one timestep into a swizzled shared-memory slot of its
 //     own and a TMA store moves them out, with no synchronisation between warps. (A thread owns a
 //     pixel, so direct stores put every lane of a store instruction on a different 128-byte line,
@@ -58,7 +58,9 @@ struct StemGeom {
 // registers is not). The spikes of a step go to a 4 KB slot owned by the warp (128-byte swizzle:
 // 16-byte chunk j of row r sits at chunk j ^ (r & 7)), which lane 0 hands to TMA as one box. The warp
 // synchronises with nobody else. FAST: tau a power of two and hard reset, resolved at compile time.
-template <typename XT, typename VT, bool FAST>
+// One-byte spikes (ST = uint8_t) make 64-byte rows: 16 channels per 16-byte chunk, 64-byte swizzle
+// (chunk j of row r sits at chunk j ^ ((r >> 1) & 3)), slots of 2 KB.
+template <typename XT, typename ST, typename VT, bool FAST>
 __device__ __forceinline__ void staged_tile(const StemGeom &g, const LifParams &p, const CUtensorMap *smap,
                                             uint32_t acc_addr, uint32_t accempty_bar, uint32_t slots, uint32_t &sslot,
                                             const float *bias_s, const VT *__restrict__ v_init, VT *__restrict__ v_out,
@@ -83,13 +85,26 @@ __device__ __forceinline__ void staged_tile(const StemGeom &g, const LifParams &
     // the slot written now was handed to TMA two steps ago: that store must have read it out
     if (lane == 0) umma::bulk_wait_group_read<1>();
     __syncwarp();
-    const uint32_t row = slots + sslot * 4096u + (uint32_t)lane * 128u;
+    constexpr uint32_t kRow = 64u * (uint32_t)sizeof(ST);   // bytes of one pixel's 64 spikes
+    const uint32_t row = slots + sslot * 4096u + (uint32_t)lane * kRow;
     const uint32_t src = acc_addr + (uint32_t)((alias ? 0 : t) * 64);
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
       uint32_t a[16];
       umma::tmem_ld_x16(src + (uint32_t)(q * 16), a);
       umma::tmem_ld_wait();
+      if constexpr (sizeof(ST) == 1) {
+        Pack<uint8_t, 16> pk;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const int c = q * 16 + i;
+          const float y = __uint_as_float(a[i]) + bias_s[c];
+          pk.v[i] = (uint8_t)((FAST ? lif_step_t<1, true>(y, v[c], p) : lif_step(y, v[c], p)) != 0.f);
+        }
+        const uint4 u = *reinterpret_cast<const uint4 *>(&pk);
+        const uint32_t dst = row + ((uint32_t)(q ^ ((lane >> 1) & 3)) << 4);
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(u.x), "r"(u.y), "r"(u.z), "r"(u.w) : "memory");
+      } else {
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
         Pack<XT, 8> pk;
@@ -102,6 +117,7 @@ __device__ __forceinline__ void staged_tile(const StemGeom &g, const LifParams &
         const uint4 u = *reinterpret_cast<const uint4 *>(&pk);
         const uint32_t dst = row + ((uint32_t)((q * 2 + h) ^ (lane & 7)) << 4);
         asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(u.x), "r"(u.y), "r"(u.z), "r"(u.w) : "memory");
+      }
       }
     }
     if (t == g.T - 1) {   // last read of this accumulator stage: the MMA warp may overwrite it
@@ -117,7 +133,7 @@ __device__ __forceinline__ void staged_tile(const StemGeom &g, const LifParams &
     }
     sslot ^= 1u;
   }
-  if (valid) {
+  if (valid && v_out != nullptr) {
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
       float tmp[16];
@@ -248,7 +264,7 @@ stem_gemm_lif_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_cons
     const EpiGeom eg{g.T, g.Tacc, g.Cout, g.Cout, 0};
     const long long frame_out = (long long)g.B * g.Ho * g.Wo * g.Cout;
     bool ok = true;
-    if constexpr (std::is_same<ST, XT>::value) {
+    {
       if (g.staged) {
         // Warps 0-3 take this CTA's even tiles, warps 4-7 the odd ones; a warp converts all 64 channels of
         // its 32 pixels and sends them out by itself, so the epilogue has no block-wide synchronisation.
@@ -272,10 +288,10 @@ stem_gemm_lif_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_cons
           umma::tc_fence_after_sync();
           const uint32_t acc_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * (uint32_t)g.stage_cols;
           if (p.mode == 1 && p.hard)
-            staged_tile<XT, VT, true>(g, p, &smap, acc_addr, accempty(acc), slots, sslot, bias_s, v_init, v_out,
+            staged_tile<XT, ST, VT, true>(g, p, &smap, acc_addr, accempty(acc), slots, sslot, bias_s, v_init, v_out,
                                       w0 + bx_off, h0 + by_off, b, pix, valid);
           else
-            staged_tile<XT, VT, false>(g, p, &smap, acc_addr, accempty(acc), slots, sslot, bias_s, v_init, v_out,
+            staged_tile<XT, ST, VT, false>(g, p, &smap, acc_addr, accempty(acc), slots, sslot, bias_s, v_init, v_out,
                                        w0 + bx_off, h0 + by_off, b, pix, valid);
         }
         // the shared-memory slots must outlive the TMA stores that read them
@@ -343,7 +359,7 @@ int launch(const StemGemmArgs &a, cudaStream_t stream) {
   while (cols < g.nacc * g.stage_cols) cols *= 2;
   g.tmem_cols = cols;
   g.w_chunk_bytes = a.Cout * 128;
-  g.staged = (a.Cout == 64 && std::is_same<ST, XT>::value) ? 1 : 0;
+  g.staged = a.Cout == 64 ? 1 : 0;   // a pixel's spikes are one 128-byte (16-bit) or 64-byte (u8) row
   const int budget = 224 * 1024 - 1024 - 4 * g.w_chunk_bytes - (g.staged ? kStage * kChunkBytes : 0);
   g.ring = budget / kChunkBytes < kMaxRing ? budget / kChunkBytes : kMaxRing;
   int dev = 0, sms = 0;
@@ -369,11 +385,13 @@ int launch(const StemGemmArgs &a, cudaStream_t stream) {
   }
   CUtensorMap sm = xm;
   if (g.staged) {  // spikes [T * B][Ho][Wo][64]: a tile of one step leaves as one box
+    const cuuint64_t ss = sizeof(ST);
     cuuint64_t dims[4] = {64, (cuuint64_t)a.Wo, (cuuint64_t)a.Ho, (cuuint64_t)a.T * a.B};
-    cuuint64_t strides[3] = {(cuuint64_t)64 * es, (cuuint64_t)a.Wo * 64 * es, (cuuint64_t)a.Ho * a.Wo * 64 * es};
+    cuuint64_t strides[3] = {(cuuint64_t)64 * ss, (cuuint64_t)a.Wo * 64 * ss, (cuuint64_t)a.Ho * a.Wo * 64 * ss};
     // a warp stores its 32 tile rows: part of one image row, or 32 / BW whole rows of the tile
     cuuint32_t box[4] = {64, (cuuint32_t)(g.BW >= 32 ? 32 : g.BW), (cuuint32_t)(g.BW >= 32 ? 1 : 32 / g.BW), 1};
-    const int rc = encode_tmap(&sm, a.dtype, 4, a.spikes, dims, strides, box);
+    const int rc = sizeof(ST) == 1 ? encode_tmap(&sm, SNNB_U8, 4, a.spikes, dims, strides, box, 64)
+                                   : encode_tmap(&sm, a.dtype, 4, a.spikes, dims, strides, box);
     if (rc != SNNB_OK) return rc;
   }
   const size_t smem = (size_t)4 * g.w_chunk_bytes + (size_t)g.ring * kChunkBytes + (g.staged ? (size_t)kStage * kChunkBytes : 0) + 1024;

@@ -52,31 +52,59 @@ lif_avgpool_linear_kernel(const XT *__restrict__ x, const VT *__restrict__ v_ini
   for (int s = 0; s < ns; ++s) {
     const int n = n0 + s;
     if constexpr (NHWC) {
+      // Two items (pixel x VEC channels) per trip with the loads of up to four timesteps of both issued
+      // before the first use: the phase is a pure stream, so bytes in flight per thread set its speed.
       const int cvn = (ce - cs) / VEC;
       const int items = HW * cvn;
-      for (int it = tid; it < items; it += NT) {
-        const int pix = it / cvn;
-        const int c = cs + (it % cvn) * VEC;
-        const int64_t e = ((int64_t)n * HW + pix) * C + c;
-        float v[VEC];
-        if (v_init != nullptr) load_pack_stream<VT, VEC>(v_init + e, v);
-        else {
+      for (int it0 = tid; it0 < items; it0 += 2 * NT) {
+        int64_t e[2];
+        int cc[2];
+        bool on[2];
 #pragma unroll
-          for (int i = 0; i < VEC; ++i) v[i] = 0.f;
+        for (int u = 0; u < 2; ++u) {
+          const int it = it0 + u * NT;
+          on[u] = it < items;
+          const int itc = on[u] ? it : it0;
+          const int pix = itc / cvn;
+          cc[u] = cs + (itc % cvn) * VEC;
+          e[u] = ((int64_t)n * HW + pix) * C + cc[u];
         }
-        int k[VEC];
+        float v[2][VEC];
+        int k[2][VEC];
 #pragma unroll
-        for (int i = 0; i < VEC; ++i) k[i] = 0;
-        for (int t = 0; t < T; ++t) {
-          float xv[VEC];
-          load_pack_stream<XT, VEC>(x + (int64_t)t * frame + e, xv);
+        for (int u = 0; u < 2; ++u) {
+          if (v_init != nullptr) load_pack_stream<VT, VEC>(v_init + e[u], v[u]);
+          else {
 #pragma unroll
-          for (int i = 0; i < VEC; ++i) k[i] += (int)lif_step(xv[i], v[i], p);
+            for (int i = 0; i < VEC; ++i) v[u][i] = 0.f;
+          }
+#pragma unroll
+          for (int i = 0; i < VEC; ++i) k[u][i] = 0;
         }
-        store_pack<VT, VEC>(v_out + e, v);
+        for (int t0 = 0; t0 < T; t0 += 4) {
+          float xv[2][4][VEC];
 #pragma unroll
-        for (int i = 0; i < VEC; ++i)
-          if (k[i]) atomicAdd(&cnt[s * C + c + i], k[i]);
+          for (int u = 0; u < 2; ++u)
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              if (t0 + j < T) load_pack_stream<XT, VEC>(x + (int64_t)(t0 + j) * frame + e[u], xv[u][j]);
+#pragma unroll
+          for (int u = 0; u < 2; ++u)
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              if (t0 + j < T) {
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) k[u][i] += (int)lif_step(xv[u][j][i], v[u][i], p);
+              }
+        }
+#pragma unroll
+        for (int u = 0; u < 2; ++u)
+          if (on[u]) {
+            store_pack<VT, VEC>(v_out + e[u], v[u]);
+#pragma unroll
+            for (int i = 0; i < VEC; ++i)
+              if (k[u][i]) atomicAdd(&cnt[s * C + cc[u] + i], k[u][i]);
+          }
       }
     } else {
       const int items = (ce - cs) * HW;
@@ -122,11 +150,30 @@ lif_avgpool_linear_kernel(const XT *__restrict__ x, const VT *__restrict__ v_ini
 #pragma unroll
     for (int s = 0; s < SMAX; ++s) acc[s] = 0.f;
     const XT *wk = fc_w + (int64_t)k * C;
-    for (int c = lane; c < C; c += 32) {
-      const float wv = DT<XT>::to_f(wk[c]);
+    if (VEC > 1 && C % 8 == 0 && (reinterpret_cast<uintptr_t>(fc_w) & 15u) == 0 && sizeof(XT) == 2) {
+      for (int c = lane * 8; c < C; c += 32 * 8) {   // 16 bytes of weights per lane and trip
+        float wv[8];
+        load_pack<XT, 8>(wk + c, wv);
 #pragma unroll
-      for (int s = 0; s < SMAX; ++s)
-        if (s < ns) acc[s] = fmaf(wv, (float)cnt[s * C + c], acc[s]);
+        for (int s = 0; s < SMAX; ++s)
+          if (s < ns) {
+            const int4 c0 = *reinterpret_cast<const int4 *>(&cnt[s * C + c]);
+            const int4 c1 = *reinterpret_cast<const int4 *>(&cnt[s * C + c + 4]);
+            float a = acc[s];
+            a = fmaf(wv[0], (float)c0.x, a); a = fmaf(wv[1], (float)c0.y, a);
+            a = fmaf(wv[2], (float)c0.z, a); a = fmaf(wv[3], (float)c0.w, a);
+            a = fmaf(wv[4], (float)c1.x, a); a = fmaf(wv[5], (float)c1.y, a);
+            a = fmaf(wv[6], (float)c1.z, a); a = fmaf(wv[7], (float)c1.w, a);
+            acc[s] = a;
+          }
+      }
+    } else {
+      for (int c = lane; c < C; c += 32) {
+        const float wv = DT<XT>::to_f(wk[c]);
+#pragma unroll
+        for (int s = 0; s < SMAX; ++s)
+          if (s < ns) acc[s] = fmaf(wv, (float)cnt[s * C + c], acc[s]);
+      }
     }
     const float bk = fc_b != nullptr ? DT<XT>::to_f(fc_b[k]) * (float)T : 0.f;
 #pragma unroll
@@ -142,7 +189,7 @@ lif_avgpool_linear_kernel(const XT *__restrict__ x, const VT *__restrict__ v_ini
 template <typename XT, typename VT, bool NHWC, int VEC>
 int launch(const void *x, const void *v_init, const void *w, const void *b, void *out, void *v_out,
            int T, int N, int C, int HW, int K, const LifParams &p, cudaStream_t stream) {
-  int S = (N * CL + 147) / 148;
+  int S = (N * CL) / (2 * 148);   // samples per cluster: about two CTAs per SM in flight
   S = S < 1 ? 1 : (S > SMAX ? SMAX : S);
   while (S > 1 && (size_t)S * C * sizeof(int) > 48 * 1024) --S;
   const size_t smem = (size_t)S * C * sizeof(int);
@@ -172,7 +219,9 @@ template <typename XT, typename VT>
 int pick(const void *x, const void *v_init, const void *w, const void *b, void *out, void *v_out,
          int T, int N, int C, int HW, int K, int layout, const LifParams &p, cudaStream_t stream) {
   if (layout == SNNB_NHWC) {
-    const bool vec = (C % 4 == 0) && aligned16(x) && aligned16(v_out) && (v_init == nullptr || aligned16(v_init));
+    const bool al = aligned16(x) && aligned16(v_out) && (v_init == nullptr || aligned16(v_init));
+    if (al && sizeof(XT) == 2 && C % 8 == 0) return launch<XT, VT, true, 8>(x, v_init, w, b, out, v_out, T, N, C, HW, K, p, stream);
+    const bool vec = (C % 4 == 0) && al;
     if (vec) return launch<XT, VT, true, 4>(x, v_init, w, b, out, v_out, T, N, C, HW, K, p, stream);
     return launch<XT, VT, true, 1>(x, v_init, w, b, out, v_out, T, N, C, HW, K, p, stream);
   }

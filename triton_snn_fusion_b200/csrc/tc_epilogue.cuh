@@ -76,7 +76,7 @@ __device__ __forceinline__ void epilogue_cols(const EpiArgs<XT, ST, VT> &e, cons
         }
       }
     }
-    if (LIFON && e.valid) store_pack<VT, 16, false>(e.v_out + o0, v);
+    if (LIFON && e.valid && e.v_out != nullptr) store_pack<VT, 16, false>(e.v_out + o0, v);
   }
   umma::tmem_ld_wait();
 }

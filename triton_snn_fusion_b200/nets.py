@@ -164,13 +164,23 @@ class CompiledNet:
         self.x_in = torch.empty((self.B, H, W, 3), dtype=dtype, device=self.device)
         self.bufs["input"] = self.x_in
         self.logits = None
+        # The stem's spikes are the widest activation of a ResNet and are read only by the max-pool: they
+        # are kept as one byte each (spike_dtype U8) and pooled by the u8 variant of the pooling kernel.
+        self.u8_bufs = set()
+        for i, L in enumerate(spec):
+            if (L["op"] == "conv" and i + 1 < len(spec) and spec[i + 1]["op"] == "maxpool" and spec[i + 1]["src"] == L["dst"]
+                    and L["src"] == "input" and self._is_tc_stem(L, H, W) and L["cout"] == 64
+                    and sum(1 for M in spec if M.get("src") == L["dst"] or M.get("residual") == L["dst"]) == 1):
+                self.u8_bufs.add(L["dst"])
         for L in spec:
             h, w_, c = self.shapes[L["src"]]
             if L["op"] == "conv":
                 ho, wo = _out_hw(h, w_, L["k"], L["s"], L["p"])
                 self.shapes[L["dst"]] = (ho, wo, L["cout"])
-                self.bufs[L["dst"]] = torch.empty((self.T, self.B, ho, wo, L["cout"]), dtype=dtype, device=self.device)
-                if L["lif"]:
+                self.bufs[L["dst"]] = torch.empty((self.T, self.B, ho, wo, L["cout"]), device=self.device,
+                                                  dtype=torch.uint8 if L["dst"] in self.u8_bufs else dtype)
+                if L["lif"] and (keep_membranes or L["groups"] != 1):
+                    # dense convs can skip the final membrane (v_out = NULL); the depthwise kernel always writes it
                     self.membranes[L["name"]] = torch.empty((self.B, ho, wo, L["cout"]), dtype=dtype, device=self.device)
             elif L["op"] == "maxpool":
                 ho, wo = _out_hw(h, w_, 3, 2, 1)
@@ -205,7 +215,7 @@ class CompiledNet:
                 wt = self.weights[L["name"]]
                 dst = self.bufs[L["dst"]]
                 res = self.bufs[L["residual"]].data_ptr() if L.get("residual") else None
-                v = self.membranes[L["name"]].data_ptr() if L["lif"] else None
+                v = self.membranes[L["name"]].data_ptr() if L["name"] in self.membranes else None
                 if self._is_tc_stem(L, h, w_):
                     # 7x7/s2 stem on the tensor cores: weights re-packed once, input re-laid into scratch per call
                     frames = B if x_stride == 0 else T * B
@@ -216,8 +226,9 @@ class CompiledNet:
                                "snnb_stem7x7_pack_weight")
                     torch.cuda.synchronize(self.device)
                     wt["w_stem"] = wp
+                    sdt = _lib.dtype_code(torch.uint8) if L["dst"] in self.u8_bufs else dt
                     args = (src.data_ptr(), x_stride, wp.data_ptr(), wt["b"].data_ptr(), None, dst.data_ptr(), v,
-                            self._scratch.data_ptr(), nbytes, T, B, h, w_, L["cout"], dt, dt, dt,
+                            self._scratch.data_ptr(), nbytes, T, B, h, w_, L["cout"], dt, sdt, dt,
                             LIF["v_th"], LIF["v_reset"], LIF["tau"])
                     calls.append((lib.snnb_stem7x7_lif, args, L["name"]))
                     self.extra_launches += 1
@@ -232,7 +243,7 @@ class CompiledNet:
                     calls.append((lib.snnb_dwconv3x3_lif, args, L["name"]))
             elif L["op"] == "maxpool":
                 args = (src.data_ptr(), self.bufs[L["dst"]].data_ptr(), T * B, h, w_, c, dt)
-                calls.append((lib.snnb_maxpool3x3s2, args, L["name"]))
+                calls.append((lib.snnb_maxpool3x3s2_u8 if L["src"] in self.u8_bufs else lib.snnb_maxpool3x3s2, args, L["name"]))
             elif L["op"] == "tail":
                 wt = self.weights[L["name"]]
                 args = (src.data_ptr(), None, wt["w"].data_ptr(), wt["b"].data_ptr(), self.tail_sum.data_ptr(),
@@ -283,6 +294,40 @@ class CompiledNet:
         self.x_in.copy_(x.permute(0, 2, 3, 1), non_blocking=True)
         return self.run()
 
+    def submit(self, host_x: torch.Tensor, host_out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Queue one forward pass on a pinned host batch [B,H,W,3] without waiting for it.
+
+        The host->device copy runs on a side stream into one of two staging buffers, so the copy of
+        the next batch overlaps the kernels of this one; the compute stream moves the staged batch into
+        the graph's input buffer, replays the graph and (if ``host_out`` is given) copies the fp32
+        logits to it. Returns ``self.logits``; results are valid once the current stream is synchronised.
+        """
+        if not hasattr(self, "_stage"):
+            self._stage = [torch.empty_like(self.x_in) for _ in range(2)]
+            self._copy_stream = torch.cuda.Stream(self.device)
+            self._ready = [torch.cuda.Event() for _ in range(2)]
+            self._free = [torch.cuda.Event() for _ in range(2)]
+            self._pipe_idx = 0
+            for e in self._free:
+                e.record(torch.cuda.current_stream(self.device))
+        k = self._pipe_idx
+        self._pipe_idx ^= 1
+        main = torch.cuda.current_stream(self.device)
+        with torch.cuda.stream(self._copy_stream):
+            self._copy_stream.wait_event(self._free[k])      # the staged batch two submits ago has been consumed
+            self._stage[k].copy_(host_x, non_blocking=True)
+            self._ready[k].record(self._copy_stream)
+        main.wait_event(self._ready[k])
+        self.x_in.copy_(self._stage[k], non_blocking=True)
+        self._free[k].record(main)
+        logits = self.run()
+        if host_out is not None:
+            host_out.copy_(logits, non_blocking=True)
+        return logits
+
     def activation(self, name: str) -> torch.Tensor:
         """Named activation as a logical [T,B,C,H,W] tensor (channels-last memory)."""
-        return self.bufs[name].permute(0, 1, 4, 2, 3)
+        buf = self.bufs[name]
+        if buf.dtype == torch.uint8:   # one-byte spikes: hand them out in the compute dtype
+            buf = buf.to(self.dtype)
+        return buf.permute(0, 1, 4, 2, 3)
