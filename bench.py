@@ -149,7 +149,7 @@ def run_reference(args):
         "impl": "reference", "metric": METRIC, "value": ips, "unit": "images/s", "n_gpus": args.gpus,
         "steps": reps, "warmup": 1, "ms_per_step": sec * 1e3 * (GLOBAL_BATCH / batch), "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "spiking ResNet-18 T=4, global batch 512, 3x224x224 N(0,1), direct encoding",
+        "config": {"workload": f"spiking ResNet-18 T=4, global batch {GLOBAL_BATCH}, 3x224x224 N(0,1), direct encoding",
                    "parallelism": "cpu"},
         "cpu_baseline": {"value": ips, "unit": "images/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": ips, "unit": "images/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -160,6 +160,8 @@ def run_reference(args):
 
 def run_ours(args):
     import torch.distributed as dist
+    global GLOBAL_BATCH
+    GLOBAL_BATCH = args.global_batch
 
     from triton_snn_fusion_b200 import _lib, nets
     from triton_snn_fusion_b200.parallel import gather_logits, shard_range
@@ -292,7 +294,7 @@ def run_ours(args):
         "metric": METRIC, "value": GLOBAL_BATCH / (ms_resident * 1e-3), "unit": "images/s", "n_gpus": world,
         "steps": K, "warmup": Wm, "ms_per_step": ms_resident, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": "spiking ResNet-18 T=4, global batch 512, 3x224x224 N(0,1), direct encoding",
+        "config": {"workload": f"spiking ResNet-18 T=4, global batch {GLOBAL_BATCH}, 3x224x224 N(0,1), direct encoding",
                    "parallelism": f"batch-sharded x{world}", "per_gpu_batch": B, "cuda_graph": bool(args.graph),
                    "conv_path": args.path,
                    "l2": "no flush needed: each step streams >3 GB of activations per GPU, far beyond the 126 MB L2"},
@@ -323,6 +325,9 @@ def main():
     ap.add_argument("--no-graph", dest="graph", action="store_false")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--layers", action="store_true", help="also print every layer's device time to stderr")
+    ap.add_argument("--global-batch", type=int, default=GLOBAL_BATCH,
+                    help="images per step over all ranks (the benchmark's configuration is 512; other values are for "
+                         "studying how the kernels behave at the per-GPU batch of an N-GPU run)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

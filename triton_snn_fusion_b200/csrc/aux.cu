@@ -126,40 +126,81 @@ maxpool3x3s2_u8_kernel(const uint8_t *__restrict__ x, XT *__restrict__ y, int64_
   store_pack<XT, 16, false>(y + ((f * Ho + ho) * (int64_t)Wo + wo) * C + cv * 16, out);
 }
 
-// One CTA per group of SB samples: channel sums over (t, pixel) into shared memory, then a
-// warp-per-class mat-vec for the SB samples with the fc row read once.
+// One CTA per (group of SB samples, chunk of classes): channel sums over (t, pixel) into shared memory,
+// then a warp-per-class mat-vec for the SB samples with the fc row read once. The sums are cheap and
+// latency-bound (T*HW strided rows per channel), so the threads of a CTA split the pixels as well as
+// the channels (16 bytes of channels per load, PG pixel groups whose partial sums are added in a fixed
+// order), and CTAs that differ only in their class chunk simply repeat them.
 constexpr int SB = 2;
 template <typename XT>
 __global__ void __launch_bounds__(256)
 avgpool_linear_mean_kernel(const XT *__restrict__ x, const XT *__restrict__ w, const XT *__restrict__ b,
-                           float *__restrict__ out, int T, int N, int C, int HW, int K) {
-  extern __shared__ float sums[];  // [SB][C]
+                           float *__restrict__ out, int T, int N, int C, int HW, int K, int Kc, int PG, int vec) {
+  extern __shared__ float sums[];  // [PG][SB][C]
+  constexpr int V = 16 / sizeof(XT);
   const int n0 = blockIdx.x * SB;
   const int ns = min(SB, N - n0);
   const int tid = threadIdx.x;
   const int64_t frame = (int64_t)N * HW * C;
-  for (int i = tid; i < ns * C; i += 256) {
-    const int s = i / C, c = i % C;
-    // T*HW strided loads per channel: four independent partial sums keep several loads in flight
-    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-    for (int t = 0; t < T; ++t) {
-      const XT *px = x + (int64_t)t * frame + (int64_t)(n0 + s) * HW * C + c;
-      int p = 0;
-      for (; p + 4 <= HW; p += 4) {
-        a0 += DT<XT>::to_f(px[(int64_t)p * C]);
-        a1 += DT<XT>::to_f(px[(int64_t)(p + 1) * C]);
-        a2 += DT<XT>::to_f(px[(int64_t)(p + 2) * C]);
-        a3 += DT<XT>::to_f(px[(int64_t)(p + 3) * C]);
+  if (vec) {
+    const int groups = C / V, rows = T * HW;
+    for (int item = tid; item < ns * PG * groups; item += 256) {
+      const int cg = item % groups;
+      const int pg = (item / groups) % PG;
+      const int s = item / (groups * PG);
+      const XT *px = x + (int64_t)(n0 + s) * HW * C + cg * V;
+      float acc[4][V];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+#pragma unroll
+        for (int i = 0; i < V; ++i) acc[u][i] = 0.f;
+      for (int q0 = pg; q0 < rows; q0 += 4 * PG) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {   // four independent rows in flight
+          const int q = q0 + u * PG;
+          if (q < rows) {
+            const int t = q / HW, pp = q - t * HW;
+            float v[V];
+            load_pack<XT, V>(px + (int64_t)t * frame + (int64_t)pp * C, v);
+#pragma unroll
+            for (int i = 0; i < V; ++i) acc[u][i] += v[i];
+          }
+        }
       }
-      for (; p < HW; ++p) a0 += DT<XT>::to_f(px[(int64_t)p * C]);
+#pragma unroll
+      for (int i = 0; i < V; ++i) sums[(pg * SB + s) * C + cg * V + i] = (acc[0][i] + acc[1][i]) + (acc[2][i] + acc[3][i]);
     }
-    const float a = (a0 + a1) + (a2 + a3);
-    sums[s * C + c] = a;
+  } else {
+    for (int i = tid; i < ns * C; i += 256) {
+      const int s = i / C, c = i % C;
+      float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+      for (int t = 0; t < T; ++t) {
+        const XT *px = x + (int64_t)t * frame + (int64_t)(n0 + s) * HW * C + c;
+        int pp = 0;
+        for (; pp + 4 <= HW; pp += 4) {
+          a0 += DT<XT>::to_f(px[(int64_t)pp * C]);
+          a1 += DT<XT>::to_f(px[(int64_t)(pp + 1) * C]);
+          a2 += DT<XT>::to_f(px[(int64_t)(pp + 2) * C]);
+          a3 += DT<XT>::to_f(px[(int64_t)(pp + 3) * C]);
+        }
+        for (; pp < HW; ++pp) a0 += DT<XT>::to_f(px[(int64_t)pp * C]);
+      }
+      sums[s * C + c] = (a0 + a1) + (a2 + a3);
+    }
   }
   __syncthreads();
+  if (vec && PG > 1) {
+    for (int i = tid; i < ns * C; i += 256) {
+      float a = sums[i];
+      for (int pg = 1; pg < PG; ++pg) a += sums[pg * SB * C + i];
+      sums[i] = a;
+    }
+    __syncthreads();
+  }
   const int warp = tid / 32, lane = tid % 32;
   const float scale = 1.0f / ((float)T * (float)HW);
-  for (int k = warp; k < K; k += 8) {
+  const int k_end = min(K, (int)(blockIdx.y + 1) * Kc);
+  for (int k = blockIdx.y * Kc + warp; k < k_end; k += 8) {
     float acc[SB];
 #pragma unroll
     for (int s = 0; s < SB; ++s) acc[s] = 0.f;
@@ -183,10 +224,22 @@ avgpool_linear_mean_kernel(const XT *__restrict__ x, const XT *__restrict__ w, c
 
 template <typename XT>
 int head(const void *x, const void *w, const void *b, float *out, int T, int N, int C, int HW, int K, cudaStream_t st) {
-  const size_t smem = (size_t)SB * C * sizeof(float);
-  if (smem > 48 * 1024) return fail(SNNB_ERR_UNSUPPORTED, "avgpool_linear_mean: C=%d too large", C);
-  avgpool_linear_mean_kernel<XT><<<(N + SB - 1) / SB, 256, smem, st>>>(
-      static_cast<const XT *>(x), static_cast<const XT *>(w), static_cast<const XT *>(b), out, T, N, C, HW, K);
+  if ((size_t)SB * C * sizeof(float) > 48 * 1024) return fail(SNNB_ERR_UNSUPPORTED, "avgpool_linear_mean: C=%d too large", C);
+  constexpr int V = 16 / sizeof(XT);
+  const int vec = (C % V == 0 && aligned16(x)) ? 1 : 0;
+  int PG = 1;   // pixel groups: fill the 256 threads, within 48 KB of partial sums
+  if (vec) {
+    PG = 256 / (C / V) > 1 ? 256 / (C / V) : 1;
+    if (PG > 8) PG = 8;
+    while (PG > 1 && (size_t)PG * SB * C * sizeof(float) > 48 * 1024) --PG;
+  }
+  const int gx = (N + SB - 1) / SB;
+  int ks = (2 * 148 + gx - 1) / gx;   // class chunks: about two CTAs per SM in flight
+  ks = ks < 1 ? 1 : (ks > 8 ? 8 : ks);
+  const int Kc = (K + ks - 1) / ks;
+  const size_t smem = (size_t)PG * SB * C * sizeof(float);
+  avgpool_linear_mean_kernel<XT><<<dim3((unsigned)gx, (unsigned)((K + Kc - 1) / Kc)), 256, smem, st>>>(
+      static_cast<const XT *>(x), static_cast<const XT *>(w), static_cast<const XT *>(b), out, T, N, C, HW, K, Kc, PG, vec);
   SNNB_CHECK_LAUNCH("avgpool_linear_mean");
   return SNNB_OK;
 }
