@@ -258,7 +258,7 @@ def run_ours(args):
         if L["op"] != "conv":
             return {"maxpool": "maxpool3x3s2", "head": "avgpool_linear_mean"}[L["op"]]
         if L["cin"] == 3:
-            return "stem (s2d + conv_lif_tc)"
+            return "stem (s2d + stem_gemm_lif)"
         ho = net.shapes[L["dst"]][0]
         if L["k"] == 3 and L["s"] == 1:
             return "conv3x3_pair" if ho >= 8 else "conv3x3_halo"
@@ -275,11 +275,24 @@ def run_ours(args):
     d = by_kernel[dom]
     achieved = d["flop"] / (d["ms"] * 1e-3) / 1e12 if d["ms"] > 0 else 0.0
     top = sorted(layer_ms.items(), key=lambda kv: -kv[1])[:6]
+    # DRAM traffic per launch of the dominant kernel: one ncu capture of a 128->128, 56x56, T=4, batch-32
+    # layer read 103.18 MB and wrote 78.09 MB (profiles/conv3x3_pair_128to128_56x56_T4_b32.md). The kernel
+    # moves each activation once, so the figure is scaled by the activation elements (in + out) of the
+    # layers it serves here and averaged over its launches.
+    traffic = None
+    if dom == "conv3x3_pair":
+        cap_bytes, cap_elems = 181.27e6, 4 * 32 * 56 * 56 * (128 + 128)
+        elems = 0
+        for L in spec:
+            if kernel_of(L) == dom:
+                ho, wo, co = net.shapes[L["dst"]]
+                elems += T_STEPS * B * ho * wo * (L["cin"] + co + (co if L.get("residual") else 0))
+        traffic = cap_bytes * elems / cap_elems / d["launches"]
     roofline = {
         "kernel": f"{dom} ({d['launches']} launches per step: the 3x3 stride-1 conv + BN + LIF layers)",
         "bound": "tensor", "achieved": achieved, "peak": peaks["tf_sustained"], "unit": "TFLOP/s",
         "frac": achieved / peaks["tf_sustained"], "peak_source": peaks["source"] + " (sustained bf16)",
-        "traffic": None,
+        "traffic": traffic, "traffic_unit": "bytes per launch (ncu capture of one layer, scaled by activation elements)",
         "share_of_step": d["ms"] / total_ms if total_ms else None,
         "kernels": {k: {"launches": v["launches"], "ms": round(v["ms"], 3), "share": round(v["ms"] / total_ms, 3),
                         "tflops": round(v["flop"] / (v["ms"] * 1e-3) / 1e12, 1) if v["flop"] else None}
