@@ -5,6 +5,7 @@
     python -m triton_snn_fusion_b200.microbench dw   --B 32 --c 128 --hw 56
     python -m triton_snn_fusion_b200.microbench tail --B 256 --c 1024 --hw 7 --classes 1000
     python -m triton_snn_fusion_b200.microbench stem --B 128 --hw 224
+    python -m triton_snn_fusion_b200.microbench linear --M 4096 --K 768 --N 3072
 
 Each case builds seeded synthetic spikes/currents on the GPU (larger than L2 at the default sizes),
 warms the op up three times, times `--reps` launches with CUDA events and prints the algorithmic
@@ -129,6 +130,27 @@ def case_tail(a):
           f"{nbytes / ms / 1e6:.0f} GB/s")
 
 
+def case_linear(a):
+    dt = torch.bfloat16
+    g = torch.Generator(device=DEV).manual_seed(0)
+    x = (torch.rand(a.T, a.M, a.K, device=DEV, generator=g) < 0.15).to(dt)
+    w = (torch.randn(a.N, a.K, device=DEV, generator=g) * a.K ** -0.5 * 2.5).to(dt)
+    b = torch.zeros(a.N, device=DEV, dtype=dt)
+    sp = torch.empty(a.T, a.M, a.N, device=DEV, dtype=dt)
+    v = torch.empty(a.M, a.N, device=DEV, dtype=dt)
+
+    def call():
+        _lib.check(_lib.lib.snnb_linear_lif(x.data_ptr(), x.stride(0), w.data_ptr(), b.data_ptr(), None, sp.data_ptr(),
+                                            v.data_ptr(), a.T, a.M, a.K, a.N, 1, 1, 1, *LIF, a.path, _stream()),
+                   "snnb_linear_lif")
+
+    ms = _time(call, a.reps)
+    flops = 2.0 * a.T * a.M * a.K * a.N
+    nbytes = 2 * (x.numel() + sp.numel() + v.numel() + w.numel())
+    print(f"linear_lif T{a.T} M{a.M} K{a.K} N{a.N} bf16: {ms:.4f} ms  {flops / ms / 1e9:.1f} TFLOP/s  "
+          f"{nbytes / ms / 1e6:.0f} GB/s  spike rate {float(sp.float().mean()):.3f}  device status {_lib.device_status()}")
+
+
 def case_stem(a):
     dt = torch.bfloat16
     ho = a.hw // 2
@@ -188,7 +210,13 @@ def main(argv=None):
     m.add_argument("--hw", type=int, default=224)
     m.add_argument("--cout", type=int, default=64)
     m.set_defaults(fn=case_stem)
-    for p in (c, l, d, t, m):
+    n = sub.add_parser("linear")
+    n.add_argument("--M", type=int, default=4096)
+    n.add_argument("--K", type=int, default=768)
+    n.add_argument("--N", type=int, default=3072)
+    n.add_argument("--path", type=int, default=_lib.PATH_TCGEN05)
+    n.set_defaults(fn=case_linear)
+    for p in (c, l, d, t, m, n):
         p.add_argument("--T", type=int, default=4)
         p.add_argument("--reps", type=int, default=10)
     a = ap.parse_args(argv)
