@@ -259,9 +259,10 @@ def run_ours(args):
             return {"maxpool": "maxpool3x3s2", "head": "avgpool_linear_mean"}[L["op"]]
         if L["cin"] == 3:
             return "stem (s2d + stem_gemm_lif)"
-        ho = net.shapes[L["dst"]][0]
+        ho, wo, _ = net.shapes[L["dst"]]
         if L["k"] == 3 and L["s"] == 1:
-            return "conv3x3_pair" if ho >= 8 else "conv3x3_halo"
+            one_image, two_images = ho >= 8 and wo >= 8, ho <= 7 and wo <= 8 and L["cout"] > 64
+            return "conv3x3_pair" if one_image or two_images else "conv3x3_halo"
         return "conv_lif_tc"
     by_kernel = {}
     for L in spec:

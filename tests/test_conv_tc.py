@@ -74,7 +74,9 @@ CONV = [
     (2, 128, 256, 3, 2, 1, 28, 28),
     (3, 256, 256, 3, 1, 1, 14, 14),
     (3, 256, 512, 3, 2, 1, 14, 14),
-    (5, 512, 512, 3, 1, 1, 7, 7),
+    (5, 512, 512, 3, 1, 1, 7, 7),        # two images per tile in the pair kernel, odd batch
+    (4, 128, 192, 3, 1, 1, 7, 8),        # same, full-width map, partial channel tile
+    (3, 64, 128, 3, 1, 1, 4, 6),         # same, small map
     (2, 64, 128, 1, 1, 0, 28, 28),
     (2, 128, 64, 1, 1, 0, 13, 17),
     (1, 64, 48, 3, 1, 1, 9, 11),

@@ -15,7 +15,11 @@ bool conv3x3_pair_supported(const ConvArgs &a) {
   if (a.Cin % 64 != 0) return false;
   if (a.x_t_stride == 0 && a.T > 1) return false;   // one frame for all steps: left to the other kernels
   if (a.T != 1 && a.T != 2 && a.T != 4) return false;
-  if (a.Ho < 8 || a.Wo < 8) return false;   // small maps: the stacked-image tiles of conv_halo.cu waste fewer rows
+  // maps of at least 8 x 8 (one image per tile) or at most 7 x 8 (two images per tile, Cout > 64); what lies
+  // in between goes to conv_halo.cu
+  const bool one_image = a.Ho >= 8 && a.Wo >= 8;
+  const bool two_images = a.Ho <= 7 && a.Wo <= 8 && a.Cout > 64;
+  if (!one_image && !two_images) return false;
   if (a.xs_w || a.xs_h || a.xs_b || a.xd_w || a.xd_h) return false;
   if (a.x_t_stride % 8 != 0) return false;
   if (!aligned16(a.x) || !aligned16(a.w)) return false;

@@ -16,6 +16,10 @@
 // addresses 32 groups = 16 output rows x 8 pixels for each of the two timesteps (rows 14, 15 of each
 // are junk and never stored). All nine taps are read from that one copy.
 //
+// Maps of at most 7 rows x 8 columns (the last stage of a ResNet) put two images into one tile: image b
+// uses row groups 0..6 and image b + 1 groups 8..14, each loaded as a box of 9 halo rows (rows 0..8 and
+// 8..16 of the region; rows 8 and 16 are zero padding shared with the neighbour).
+//
 // Timestep pairs are processed one after the other: pair 0 (t = 0, 1) is accumulated over all slabs
 // and taps into TMEM columns 0..255, then pair 1 into 256..511. The epilogue warps convert pair 0
 // (bias, residual, LIF steps 0 and 1, spikes out) while the MMA warp works on pair 1, keep the membrane
@@ -53,6 +57,9 @@ struct PairGeom {
   int tmem_cols, lif, has_res, total_tiles;
   int ring;   // halo slots in use
   int wring;  // weight slots in use (<= kWRingP)
+  int stack;  // maps of at most 7 x 8: two images per tile, image b in row groups 0.., image b + 1 in groups 8..
+              // (halo rows 0..8 and 8..16 of a timestep's region: row 8 is the zero padding of both, row 16
+              // is row 0 of the next region, which is the zero top padding of whatever is stored there)
   int dup;    // Cout <= 64: the 64 weight rows are loaded twice (M rows 64..127 repeat 0..63) so that all
               // eight epilogue warps can read the accumulator and split the pixels four ways
 };
@@ -193,6 +200,10 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
   auto decode = [&](int tile, int &n0, int &w0, int &h0, int &b) {
     const int n_tile = tile % g.n_tiles_n;
     int m = tile / g.n_tiles_n;
+    if (g.stack) {   // a tile is a pair of whole images
+      n0 = n_tile * 128; w0 = 0; h0 = 0; b = 2 * m;
+      return;
+    }
     const int strip = m % g.w_strips;
     m /= g.w_strips;
     const int rt = m % g.row_tiles;
@@ -243,6 +254,10 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
 
   if (warp == kHaloWarpP) {
     // ------------------------------------------------- halo producer: lane q loads timestep q of the pair
+    // bytes one slot receives: a full halo per timestep, or (two images per tile) a box of 9 rows per image
+    auto tx_bytes = [&](int b) {
+      return g.stack ? (uint32_t)g.tq * (uint32_t)(b + 1 < g.B ? 2 : 1) * 9u * (uint32_t)kRowBytes : slot_bytes;
+    };
     uint32_t slot = 0, phase = 1;
     bool ok = true;
     for (int tile = blockIdx.x; tile < g.total_tiles && ok; tile += gridDim.x) {
@@ -252,13 +267,16 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
         for (int slab = 0; slab < g.kslabs; ++slab) {
           if (lane == 0) {
             ok = umma::mbar_wait(hempty(slot), phase, abort_flag);
-            if (ok) umma::mbar_expect_tx(hfull(slot), slot_bytes);
+            if (ok) umma::mbar_expect_tx(hfull(slot), tx_bytes(b));
           }
           ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
           if (!ok) break;
-          if (lane < g.tq)
-            umma::tma_load_5d(h_base + slot * slot_bytes + (uint32_t)lane * kHaloT, &xmap, hfull(slot), slab * 64,
-                              w0 - 1, h0 - 1, b, pair * g.tq + lane);
+          if (lane < g.tq) {
+            const uint32_t dst = h_base + slot * slot_bytes + (uint32_t)lane * kHaloT;
+            umma::tma_load_5d(dst, &xmap, hfull(slot), slab * 64, w0 - 1, h0 - 1, b, pair * g.tq + lane);
+            if (g.stack && b + 1 < g.B)
+              umma::tma_load_5d(dst + 8u * kRowBytes, &xmap, hfull(slot), slab * 64, -1, -1, b + 1, pair * g.tq + lane);
+          }
           if (++slot == (uint32_t)g.ring) { slot = 0; phase ^= 1u; }
         }
         // residual tiles of this pair: one per 64-channel half of the output-channel tile
@@ -266,13 +284,16 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
           if (n0 + rs * 64 >= g.Cout) break;
           if (lane == 0) {
             ok = umma::mbar_wait(hempty(slot), phase, abort_flag);
-            if (ok) umma::mbar_expect_tx(hfull(slot), slot_bytes);
+            if (ok) umma::mbar_expect_tx(hfull(slot), tx_bytes(b));
           }
           ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
           if (!ok) break;
-          if (lane < g.tq)
-            umma::tma_load_5d(h_base + slot * slot_bytes + (uint32_t)lane * kHaloT, &rmap, hfull(slot), n0 + rs * 64,
-                              w0 - 1, h0 - 1, b, pair * g.tq + lane);
+          if (lane < g.tq) {
+            const uint32_t dst = h_base + slot * slot_bytes + (uint32_t)lane * kHaloT;
+            umma::tma_load_5d(dst, &rmap, hfull(slot), n0 + rs * 64, w0 - 1, h0 - 1, b, pair * g.tq + lane);
+            if (g.stack && b + 1 < g.B)
+              umma::tma_load_5d(dst + 8u * kRowBytes, &rmap, hfull(slot), n0 + rs * 64, -1, -1, b + 1, pair * g.tq + lane);
+          }
           if (++slot == (uint32_t)g.ring) { slot = 0; phase ^= 1u; }
         }
       }
@@ -372,17 +393,20 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
       int n0, w0, h0, b;
       decode(tile, n0, w0, h0, b);
       const int c = n0 + ch_in_tile;                   // output channel of this thread
-      const bool c_ok = c < g.Cout;
+      const int img = g.stack ? b + (r_begin >> 3) : b;   // two images per tile: row groups 8.. belong to image b + 1
+      const int row_first = g.stack ? 0 : h0 + r_begin;   // image row of this thread's first row group
+      const int row_limit = g.stack ? 8 : kTileRows - r_begin;   // row groups of this thread that can hold outputs
+      const bool c_ok = c < g.Cout && img < g.B;
       const float bias_c = (bias != nullptr && c_ok) ? DT<XT>::to_f(bias[c]) : 0.f;
       PixMap pm;
       pm.Cout = g.Cout;
       pm.row_stride = g.Wo * g.Cout;
-      pm.row0_off = ((long long)b * g.Ho + (h0 + r_begin)) * pm.row_stride + (long long)w0 * g.Cout + c;
+      pm.row0_off = ((long long)img * g.Ho + row_first) * pm.row_stride + (long long)w0 * g.Cout + c;
       pm.rows_ok = 0;
       pm.cols_ok = 0;
 #pragma unroll
       for (int r = 0; r < 8; ++r)
-        if (c_ok && r < my_rows && r_begin + r < kTileRows && h0 + r_begin + r < g.Ho) pm.rows_ok |= 1 << r;
+        if (c_ok && r < my_rows && r < row_limit && row_first + r < g.Ho) pm.rows_ok |= 1 << r;
 #pragma unroll
       for (int j = 0; j < 8; ++j)
         if (w0 + j < g.Wo) pm.cols_ok |= 1 << j;
@@ -404,7 +428,7 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
         const uint32_t taddr = lane_base + (uint32_t)(pair * 256);
         ST *out = spikes + toff;
         const XT *rs = nullptr;   // the residual was already added by the tensor cores
-        const int rows_valid = min(my_rows, kTileRows - r_begin);   // rows 14, 15 of a tile never exist
+        const int rows_valid = min(my_rows, row_limit);   // rows 14, 15 of a one-image tile never exist
         const int rows_want = (1 << rows_valid) - 1;
         const int nchunks = (rows_valid + 1) / 2;
         // warp-uniform choice: the TMEM loads inside are warp-collective
@@ -456,12 +480,14 @@ int launch(const ConvArgs &a, cudaStream_t stream) {
   g.tq = g.Tacc >= 2 ? 2 : 1;
   g.npairs = g.Tacc / g.tq;
   g.n_tiles_n = (a.Cout + 127) / 128;
+  g.stack = (a.Ho <= 7 && a.Wo <= 8) ? 1 : 0;
   g.row_tiles = (a.Ho + kTileRows - 1) / kTileRows;
   g.w_strips = (a.Wo + 7) / 8;
   g.tmem_cols = g.npairs * 256 > 256 ? 512 : (g.tq == 2 ? 256 : 128);
   g.lif = a.lif;
   g.has_res = a.res != nullptr;
-  const long long tiles = (long long)a.B * g.row_tiles * g.w_strips * g.n_tiles_n;
+  const long long tiles = g.stack ? (long long)((a.B + 1) / 2) * g.n_tiles_n
+                                  : (long long)a.B * g.row_tiles * g.w_strips * g.n_tiles_n;
   if (tiles > 0x7fffffffLL) return fail(SNNB_ERR_INVALID, "conv_lif: problem too large for the grid");
   g.total_tiles = (int)tiles;
   int dev = 0, sms = 0;
@@ -475,7 +501,7 @@ int launch(const ConvArgs &a, cudaStream_t stream) {
     const cuuint64_t frame_bytes = (cuuint64_t)a.B * a.H * a.W * a.Cin * es;
     cuuint64_t strides[4] = {(cuuint64_t)a.Cin * es, (cuuint64_t)a.W * a.Cin * es, (cuuint64_t)a.H * a.W * a.Cin * es,
                              g.Tacc > 1 ? (cuuint64_t)a.x_t_stride * es : frame_bytes};
-    cuuint32_t box[5] = {64, (cuuint32_t)kPW, (cuuint32_t)kPH, 1, 1};
+    cuuint32_t box[5] = {64, (cuuint32_t)kPW, (cuuint32_t)(g.stack ? 9 : kPH), 1, 1};
     const int rc = encode_tmap(&xm, a.dtype, 5, a.x, dims, strides, box);
     if (rc != SNNB_OK) return rc;
   }
@@ -502,7 +528,7 @@ int launch(const ConvArgs &a, cudaStream_t stream) {
     cuuint64_t dims[5] = {(cuuint64_t)a.Cout, (cuuint64_t)a.Wo, (cuuint64_t)a.Ho, (cuuint64_t)a.B, (cuuint64_t)a.T};
     cuuint64_t strides[4] = {(cuuint64_t)a.Cout * es, (cuuint64_t)a.Wo * a.Cout * es, (cuuint64_t)a.Ho * a.Wo * a.Cout * es,
                              (cuuint64_t)a.B * a.Ho * a.Wo * a.Cout * es};
-    cuuint32_t box[5] = {64, (cuuint32_t)kPW, (cuuint32_t)kPH, 1, 1};
+    cuuint32_t box[5] = {64, (cuuint32_t)kPW, (cuuint32_t)(g.stack ? 9 : kPH), 1, 1};
     const int rc = encode_tmap(&rm, a.dtype, 5, a.res, dims, strides, box);
     if (rc != SNNB_OK) return rc;
   }
