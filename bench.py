@@ -265,7 +265,13 @@ def run_ours(args):
             return "conv3x3_pair" if one_image or two_images else "conv3x3_halo"
         return "conv_lif_tc"
     by_kernel = {}
+    fused_into = {D["name"]: consumer for consumer, D in net.fused_sc.items()}   # shortcut conv -> the launch it rides in
+    by_name = {L["name"]: L for L in spec}
     for L in spec:
+        if L["name"] in fused_into:   # no launch of its own: its flops count for the consumer's kernel
+            by_kernel.setdefault(kernel_of(by_name[fused_into[L["name"]]]),
+                                 {"launches": 0, "ms": 0.0, "flop": 0.0})["flop"] += flops.get(L["name"], 0.0)
+            continue
         k = kernel_of(L)
         e = by_kernel.setdefault(k, {"launches": 0, "ms": 0.0, "flop": 0.0})
         e["launches"] += 1
@@ -285,7 +291,7 @@ def run_ours(args):
         cap_bytes, cap_elems = 181.27e6, 4 * 32 * 56 * 56 * (128 + 128)
         elems = 0
         for L in spec:
-            if kernel_of(L) == dom:
+            if L["name"] not in fused_into and kernel_of(L) == dom:
                 ho, wo, co = net.shapes[L["dst"]]
                 elems += T_STEPS * B * ho * wo * (L["cin"] + co + (co if L.get("residual") else 0))
         traffic = cap_bytes * elems / cap_elems / d["launches"]

@@ -146,6 +146,28 @@ int snnb_conv_lif(const void *x_seq, int64_t x_t_stride, const void *w, const vo
                   float v_th, float v_reset, float tau, int path, void *stream);
 
 /*
+ * 3x3 / stride 1 / padding 1 conv + a 1x1 shortcut conv with stride sc_stride over a second input,
+ * summed before the LIF: the second conv of a ResNet block whose shortcut is a strided 1x1 conv + BN.
+ * The reference runs the shortcut conv as its own op and feeds it to the residual input of
+ * run_triton_fused_temporal_conv_add_lif_state (runtime/triton_convlif_backend.py:689-817); here the
+ * shortcut is accumulated on the tensor cores as extra K slabs of the same GEMM, so its output is
+ * never written. No counterpart in the reference.
+ *   x_seq [T][B][H][W][Cin], w [Cout][3][3][Cin], b [Cout] = bias of the main conv + bias of the shortcut,
+ *   sc_x [T][B][sc_H][sc_W][sc_cin] (frames sc_t_stride elements apart), sc_w [Cout][sc_cin];
+ *   output pixel (h, w) adds sc_w . sc_x[h * sc_stride][w * sc_stride]; (sc_H - 1) / sc_stride + 1 == H.
+ *   spikes [T][B][H][W][Cout], v_init / v_out [B][H][W][Cout] (either may be NULL).
+ * Tensor-core only (bf16 / f16, Cin % 64 == 0, sc_cin % 64 == 0, Cout > 64, T in {1, 2, 4}); other calls
+ * return SNNB_ERR_UNSUPPORTED and the caller uses the two-op sequence.
+ */
+int snnb_conv3x3_shortcut_lif(const void *x_seq, int64_t x_t_stride, const void *w, const void *b,
+                              const void *sc_x, int64_t sc_t_stride, const void *sc_w,
+                              int sc_cin, int sc_H, int sc_W, int sc_stride,
+                              const void *v_init, void *spikes, void *v_out,
+                              int T, int B, int Cin, int H, int W, int Cout,
+                              int dtype, int spike_dtype, int v_dtype,
+                              float v_th, float v_reset, float tau, void *stream);
+
+/*
  * 7x7 / stride 2 / padding 3 stem conv with 3 input channels (+ folded BN) + LIF over T on the
  * tensor cores. Same reference items as snnb_conv_lif (kernel key k7_s2_p3,
  * kernels/benchmark_conv_lif_temporal_general.py:561-710, runtime/triton_convlif_backend.py:393-430);

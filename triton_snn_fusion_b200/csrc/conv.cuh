@@ -22,6 +22,14 @@ struct ConvArgs {
   // coordinates along W and H. Used to read overlapping windows as if they were pixels.
   long long xs_w = 0, xs_h = 0, xs_b = 0;
   int xd_w = 0, xd_h = 0;
+  // Optional shortcut branch accumulated into the same output before the LIF: a 1x1 conv with stride
+  // sc_stride over a second input sc_x [T][B][sc_H][sc_W][sc_cin] (frames sc_t_stride elements apart),
+  // weights sc_w [Cout][sc_cin]; its bias is folded into b by the caller. Output pixel (h, w) reads
+  // sc_x at (h * sc_stride, w * sc_stride). Only the timestep-pair kernel implements it.
+  const void *sc_x = nullptr;
+  const void *sc_w = nullptr;
+  int64_t sc_t_stride = 0;
+  int sc_cin = 0, sc_H = 0, sc_W = 0, sc_stride = 1;
 };
 
 // CUDA-core implicit GEMM (any shape, fp32 accumulate).

@@ -49,6 +49,39 @@ extern "C" int snnb_conv_lif(const void *x_seq, int64_t x_t_stride, const void *
   return run(a, path, static_cast<cudaStream_t>(stream), "conv_lif");
 }
 
+extern "C" int snnb_conv3x3_shortcut_lif(const void *x_seq, int64_t x_t_stride, const void *w, const void *b,
+                                         const void *sc_x, int64_t sc_t_stride, const void *sc_w,
+                                         int sc_cin, int sc_H, int sc_W, int sc_stride,
+                                         const void *v_init, void *spikes, void *v_out,
+                                         int T, int B, int Cin, int H, int W, int Cout,
+                                         int dtype, int spike_dtype, int v_dtype,
+                                         float v_th, float v_reset, float tau, void *stream) {
+  using namespace snnb;
+  SNNB_CHECK_ARG(x_seq && w && sc_x && sc_w && spikes, "conv3x3_shortcut_lif: null pointer");
+  SNNB_CHECK_ARG(T >= 1 && B >= 1 && Cin >= 1 && Cout >= 1 && H >= 1 && W >= 1, "conv3x3_shortcut_lif: sizes must be positive");
+  SNNB_CHECK_ARG(sc_cin >= 1 && sc_H >= 1 && sc_W >= 1 && sc_stride >= 1, "conv3x3_shortcut_lif: bad shortcut geometry");
+  SNNB_CHECK_ARG(dtype == SNNB_BF16 || dtype == SNNB_F16, "conv3x3_shortcut_lif: dtype must be bf16 or f16");
+  SNNB_CHECK_ARG(spike_dtype == dtype || spike_dtype == SNNB_U8, "conv3x3_shortcut_lif: spike dtype must be the x dtype or u8");
+  SNNB_CHECK_ARG(v_dtype == dtype || v_dtype == SNNB_F32, "conv3x3_shortcut_lif: v dtype must be the x dtype or f32");
+  SNNB_CHECK_ARG(x_t_stride > 0 && sc_t_stride > 0 && tau != 0.0f, "conv3x3_shortcut_lif: bad frame stride or tau");
+  SNNB_CHECK_ARG((int64_t)B * H * W < (1LL << 31), "conv3x3_shortcut_lif: problem too large");
+  ConvArgs a;
+  a.x = x_seq; a.x_t_stride = x_t_stride; a.w = w; a.b = b; a.res = nullptr;
+  a.v_init = v_init; a.spikes = spikes; a.v_out = v_out;
+  a.T = T; a.B = B; a.Cin = Cin; a.H = H; a.W = W; a.Cout = Cout; a.KH = 3; a.KW = 3;
+  a.stride = 1; a.pad = 1; a.Ho = H; a.Wo = W; a.lif = 1;
+  a.dtype = dtype; a.spike_dtype = spike_dtype; a.v_dtype = v_dtype;
+  a.p = make_lif_params(v_th, v_reset, tau);
+  a.sc_x = sc_x; a.sc_w = sc_w; a.sc_t_stride = sc_t_stride;
+  a.sc_cin = sc_cin; a.sc_H = sc_H; a.sc_W = sc_W; a.sc_stride = sc_stride;
+  if (!conv3x3_pair_supported(a))
+    return fail(SNNB_ERR_UNSUPPORTED,
+                "conv3x3_shortcut_lif: needs Cin %% 64 == 0, sc_cin %% 64 == 0, Cout > 64, T in {1, 2, 4}, a map of at "
+                "least 8x8 or at most 7x8 and a shortcut input whose strided size equals the output; run the shortcut "
+                "conv and snnb_conv_lif with a residual instead");
+  return conv3x3_pair(a, static_cast<cudaStream_t>(stream));
+}
+
 extern "C" int snnb_linear_lif(const void *x_seq, int64_t x_t_stride, const void *w, const void *b,
                                const void *v_init, void *spikes, void *v_out,
                                int T, int M, int K, int N, int dtype, int spike_dtype, int v_dtype,

@@ -23,6 +23,11 @@ bool conv3x3_pair_supported(const ConvArgs &a) {
   if (a.xs_w || a.xs_h || a.xs_b || a.xd_w || a.xd_h) return false;
   if (a.x_t_stride % 8 != 0) return false;
   if (!aligned16(a.x) || !aligned16(a.w)) return false;
+  if (a.sc_x != nullptr) {   // fused 1x1 shortcut conv
+    if (a.res != nullptr || a.Cout <= 64 || a.sc_cin % 64 != 0 || a.sc_stride < 1) return false;
+    if ((a.sc_H - 1) / a.sc_stride + 1 != a.Ho || (a.sc_W - 1) / a.sc_stride + 1 != a.Wo) return false;
+    if (a.sc_t_stride % 8 != 0 || a.sc_t_stride <= 0 || !aligned16(a.sc_x) || !aligned16(a.sc_w)) return false;
+  }
   return true;
 }
 

@@ -55,6 +55,8 @@ struct PairGeom {
   int kslabs, npairs, tq;   // tq = timesteps per pair (1 or 2)
   int n_tiles_n, row_tiles, w_strips;
   int tmem_cols, lif, has_res, total_tiles;
+  int sc_slabs;   // > 0: instead of a residual tensor, a 1x1 shortcut conv over sc_slabs 64-channel slabs of a
+                  // second input is accumulated (its pixel tiles come through rmap, its weights through scwmap)
   int ring;   // halo slots in use
   int wring;  // weight slots in use (<= kWRingP)
   int stack;  // maps of at most 7 x 8: two images per tile, image b in row groups 0.., image b + 1 in groups 8..
@@ -171,6 +173,7 @@ template <typename XT, typename ST, typename VT>
 __global__ void __launch_bounds__(kThreadsP)
 conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap,
                     const __grid_constant__ CUtensorMap rmap, const __grid_constant__ CUtensorMap wmap64,
+                    const __grid_constant__ CUtensorMap scwmap,
                     const XT *__restrict__ bias, const VT *__restrict__ v_init,
                     ST *__restrict__ spikes, VT *__restrict__ v_out, const PairGeom g, const LifParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -183,7 +186,7 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
   const uint32_t smem_base = (umma::smem_u32(smem_raw) + 1023u) & ~1023u;
   // [identity block (residual path only)] [weight ring] [halo ring]
   const uint32_t ident_base = smem_base;
-  const uint32_t w_base = smem_base + (g.has_res ? (uint32_t)kIdentBytes : 0u);
+  const uint32_t w_base = smem_base + ((g.has_res && !g.sc_slabs) ? (uint32_t)kIdentBytes : 0u);
   const uint32_t h_base = w_base + (uint32_t)(g.wring * kWSlot);
   const uint32_t slot_bytes = (uint32_t)(g.tq * kHaloT);
   const uint32_t bar_base = umma::smem_u32(bars);
@@ -230,8 +233,9 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
     umma::prefetch_tensormap(&xmap);
     umma::prefetch_tensormap(&wmap);
     if (g.has_res) umma::prefetch_tensormap(&rmap);
+    if (g.sc_slabs) umma::prefetch_tensormap(&scwmap);
   }
-  if (g.has_res && warp < kEpiW) {
+  if (g.has_res && !g.sc_slabs && warp < kEpiW) {
     // Residual add on the tensor cores: D += I . R with a 64x64 identity as the weight operand. The block
     // is 192 rows of 128 bytes: 64 zero rows, the identity (row 64 + k has a one in column k, stored where
     // the 128-byte swizzle puts it), 64 zero rows. Read from row 64 it is [I; 0] (channels n0..n0+63 of the
@@ -279,9 +283,12 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
           }
           if (++slot == (uint32_t)g.ring) { slot = 0; phase ^= 1u; }
         }
-        // residual tiles of this pair: one per 64-channel half of the output-channel tile
-        for (int rs = 0; rs < 2 && g.has_res && ok; ++rs) {
-          if (n0 + rs * 64 >= g.Cout) break;
+        // residual tiles of this pair: one per 64-channel half of the output-channel tile; with a shortcut
+        // conv instead: one pixel tile of the shortcut input per 64-channel slab of ITS channels
+        const int n_res = g.sc_slabs ? g.sc_slabs : 2;
+        for (int rs = 0; rs < n_res && g.has_res && ok; ++rs) {
+          if (!g.sc_slabs && n0 + rs * 64 >= g.Cout) break;
+          const int res_c0 = g.sc_slabs ? rs * 64 : n0 + rs * 64;
           if (lane == 0) {
             ok = umma::mbar_wait(hempty(slot), phase, abort_flag);
             if (ok) umma::mbar_expect_tx(hfull(slot), tx_bytes(b));
@@ -290,9 +297,9 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
           if (!ok) break;
           if (lane < g.tq) {
             const uint32_t dst = h_base + slot * slot_bytes + (uint32_t)lane * kHaloT;
-            umma::tma_load_5d(dst, &rmap, hfull(slot), n0 + rs * 64, w0 - 1, h0 - 1, b, pair * g.tq + lane);
+            umma::tma_load_5d(dst, &rmap, hfull(slot), res_c0, w0 - 1, h0 - 1, b, pair * g.tq + lane);
             if (g.stack && b + 1 < g.B)
-              umma::tma_load_5d(dst + 8u * kRowBytes, &rmap, hfull(slot), n0 + rs * 64, -1, -1, b + 1, pair * g.tq + lane);
+              umma::tma_load_5d(dst + 8u * kRowBytes, &rmap, hfull(slot), res_c0, -1, -1, b + 1, pair * g.tq + lane);
           }
           if (++slot == (uint32_t)g.ring) { slot = 0; phase ^= 1u; }
         }
@@ -305,7 +312,7 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
       bool ok = true;
       for (int tile = blockIdx.x; tile < g.total_tiles && ok; tile += gridDim.x) {
         const int n0 = (tile % g.n_tiles_n) * 128;
-        for (int pair = 0; pair < g.npairs && ok; ++pair)
+        for (int pair = 0; pair < g.npairs && ok; ++pair) {
           for (int slab = 0; slab < g.kslabs && ok; ++slab)
             for (int tap = 0; tap < 9; ++tap) {
               ok = umma::mbar_wait(wempty(ws), wphase, abort_flag);
@@ -319,6 +326,15 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
               }
               if (++ws == (uint32_t)g.wring) { ws = 0; wphase ^= 1u; }
             }
+          // shortcut conv: its weight tiles follow the pair's main-conv tiles, one per slab of the shortcut input
+          for (int rs = 0; rs < g.sc_slabs && ok; ++rs) {
+            ok = umma::mbar_wait(wempty(ws), wphase, abort_flag);
+            if (!ok) break;
+            umma::mbar_expect_tx(wfull(ws), (uint32_t)kWSlot);
+            umma::tma_load_2d(w_base + ws * (uint32_t)kWSlot, &scwmap, wfull(ws), rs * 64, n0);
+            if (++ws == (uint32_t)g.wring) { ws = 0; wphase ^= 1u; }
+          }
+        }
       }
     }
     __syncwarp();
@@ -358,17 +374,30 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
             if (ok) umma::mma_commit(hempty(slot));
             if (++slot == (uint32_t)g.ring) { slot = 0; phase ^= 1u; }
           }
-          // residual: accumulate I . R (centre tap of the residual's halo tile)
+          // residual: accumulate I . R (centre tap of the residual's halo tile); with a shortcut conv the
+          // weight tile of each slab of the shortcut input takes the identity's place
           const int n0 = (tile % g.n_tiles_n) * 128;
-          for (int rs = 0; rs < 2 && g.has_res && ok; ++rs) {
-            if (n0 + rs * 64 >= g.Cout) break;
+          const int n_res = g.sc_slabs ? g.sc_slabs : 2;
+          for (int rs = 0; rs < n_res && g.has_res && ok; ++rs) {
+            if (!g.sc_slabs && n0 + rs * 64 >= g.Cout) break;
             ok = umma::mbar_wait(hfull(slot), phase, abort_flag);
             if (!ok) break;
+            uint64_t adesc;
+            if (g.sc_slabs) {
+              ok = umma::mbar_wait(wfull(ws), wphase, abort_flag);
+              if (!ok) break;
+              adesc = wdesc0 + (uint64_t)((ws * (uint32_t)kWSlot) >> 4);
+            } else {
+              adesc = umma::make_sw128_kmajor_desc(ident_base + ((rs == 0 && !g.dup) ? 64u * 128u : 0u));
+            }
             umma::tc_fence_after_sync();
-            const uint64_t idesc_a = umma::make_sw128_kmajor_desc(ident_base + ((rs == 0 && !g.dup) ? 64u * 128u : 0u));
             const uint64_t xdesc = hdesc0 + (uint64_t)((slot * slot_bytes + (uint32_t)(kPW + 1) * 128u) >> 4);
 #pragma unroll
-            for (int k = 0; k < 4; ++k) umma::mma_f16_ss(d, idesc_a + (uint64_t)(2 * k), xdesc + (uint64_t)(2 * k), idesc, 1u);
+            for (int k = 0; k < 4; ++k) umma::mma_f16_ss(d, adesc + (uint64_t)(2 * k), xdesc + (uint64_t)(2 * k), idesc, 1u);
+            if (g.sc_slabs) {
+              umma::mma_commit(wempty(ws));
+              if (++ws == (uint32_t)g.wring) { ws = 0; wphase ^= 1u; }
+            }
             umma::mma_commit(hempty(slot));
             if (++slot == (uint32_t)g.ring) { slot = 0; phase ^= 1u; }
           }
@@ -485,7 +514,8 @@ int launch(const ConvArgs &a, cudaStream_t stream) {
   g.w_strips = (a.Wo + 7) / 8;
   g.tmem_cols = g.npairs * 256 > 256 ? 512 : (g.tq == 2 ? 256 : 128);
   g.lif = a.lif;
-  g.has_res = a.res != nullptr;
+  g.sc_slabs = a.sc_x != nullptr ? a.sc_cin / 64 : 0;
+  g.has_res = a.res != nullptr || g.sc_slabs > 0;
   const long long tiles = g.stack ? (long long)((a.B + 1) / 2) * g.n_tiles_n
                                   : (long long)a.B * g.row_tiles * g.w_strips * g.n_tiles_n;
   if (tiles > 0x7fffffffLL) return fail(SNNB_ERR_INVALID, "conv_lif: problem too large for the grid");
@@ -523,8 +553,22 @@ int launch(const ConvArgs &a, cudaStream_t stream) {
     const int rc = encode_tmap(&wm64, a.dtype, 2, a.w, dims, strides, box);
     if (rc != SNNB_OK) return rc;
   }
-  CUtensorMap rm = xm;
-  if (g.has_res) {   // the residual has the output's shape: [T][B][Ho][Wo][Cout]
+  CUtensorMap rm = xm, scwm = wm;
+  if (g.sc_slabs) {
+    // the shortcut input seen through its stride: pixel (h, w) of the map is sc_x at (h * s, w * s)
+    const cuuint64_t sC = (cuuint64_t)a.sc_cin, s_ = (cuuint64_t)a.sc_stride;
+    cuuint64_t dims[5] = {sC, (cuuint64_t)a.Wo, (cuuint64_t)a.Ho, (cuuint64_t)a.B, (cuuint64_t)a.T};
+    cuuint64_t strides[4] = {s_ * sC * es, s_ * (cuuint64_t)a.sc_W * sC * es, (cuuint64_t)a.sc_H * a.sc_W * sC * es,
+                             (cuuint64_t)a.sc_t_stride * es};
+    cuuint32_t box[5] = {64, (cuuint32_t)kPW, (cuuint32_t)(g.stack ? 9 : kPH), 1, 1};
+    int rc = encode_tmap(&rm, a.dtype, 5, a.sc_x, dims, strides, box);
+    if (rc != SNNB_OK) return rc;
+    cuuint64_t wdims[2] = {sC, (cuuint64_t)a.Cout};
+    cuuint64_t wstrides[1] = {sC * es};
+    cuuint32_t wbox[2] = {64, 128};
+    rc = encode_tmap(&scwm, a.dtype, 2, a.sc_w, wdims, wstrides, wbox);
+    if (rc != SNNB_OK) return rc;
+  } else if (g.has_res) {   // the residual has the output's shape: [T][B][Ho][Wo][Cout]
     cuuint64_t dims[5] = {(cuuint64_t)a.Cout, (cuuint64_t)a.Wo, (cuuint64_t)a.Ho, (cuuint64_t)a.B, (cuuint64_t)a.T};
     cuuint64_t strides[4] = {(cuuint64_t)a.Cout * es, (cuuint64_t)a.Wo * a.Cout * es, (cuuint64_t)a.Ho * a.Wo * a.Cout * es,
                              (cuuint64_t)a.B * a.Ho * a.Wo * a.Cout * es};
@@ -534,13 +578,14 @@ int launch(const ConvArgs &a, cudaStream_t stream) {
   }
   // [identity block] + weight ring + halo ring + room for the junk rows the last descriptor group reads past a slot
   g.ring = kPairRing;
-  g.wring = g.has_res ? kWRingP - 1 : kWRingP;
-  const size_t smem = (g.has_res ? (size_t)kIdentBytes : 0) + (size_t)g.wring * kWSlot + (size_t)g.ring * g.tq * kHaloT +
+  const bool ident = g.has_res && !g.sc_slabs;
+  g.wring = ident ? kWRingP - 1 : kWRingP;
+  const size_t smem = (ident ? (size_t)kIdentBytes : 0) + (size_t)g.wring * kWSlot + (size_t)g.ring * g.tq * kHaloT +
                       4 * kRowBytes + 1024;
   auto kern = conv3x3_pair_kernel<XT, ST, VT>;
   const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return fail(SNNB_ERR_CUDA, "conv_lif: cannot raise the shared-memory limit: %s", cudaGetErrorString(e));
-  kern<<<(unsigned)grid, kThreadsP, smem, stream>>>(xm, wm, rm, wm64, static_cast<const XT *>(a.b),
+  kern<<<(unsigned)grid, kThreadsP, smem, stream>>>(xm, wm, rm, wm64, scwm, static_cast<const XT *>(a.b),
                                                     static_cast<const VT *>(a.v_init), static_cast<ST *>(a.spikes),
                                                     static_cast<VT *>(a.v_out), g, a.p);
   SNNB_CHECK_LAUNCH("conv3x3_pair");

@@ -80,9 +80,11 @@ NETS = {"cnn_small": spiking_cnn_small, "mobilenet_v1": spiking_mobilenet_v1, "r
 
 
 # ------------------------------------------------------------- parameters ----
-def make_params(spec: List[dict], seed: int = 2026) -> Dict[str, Dict[str, torch.Tensor]]:
+def make_params(spec: List[dict], seed: int = 2026, gain: float = 1.0) -> Dict[str, Dict[str, torch.Tensor]]:
     """Seeded fp32 CPU parameters: Kaiming-normal conv / linear weights, BN gamma U(0.5,1.5),
-    beta N(0,0.1), running mean N(0,0.1), running var U(0.5,1.5)."""
+    beta N(0,0.1), running mean N(0,0.1), running var U(0.5,1.5). With this initialisation a deep
+    spiking net falls silent after a few layers (timing does not depend on it; parity tests of whole
+    networks want spikes everywhere): ``gain`` > 1 scales the conv weights of all but the first layer."""
     g = torch.Generator().manual_seed(seed)
     params: Dict[str, Dict[str, torch.Tensor]] = {}
     for L in spec:
@@ -90,7 +92,8 @@ def make_params(spec: List[dict], seed: int = 2026) -> Dict[str, Dict[str, torch
             fan_in = (L["cin"] // L["groups"]) * L["k"] * L["k"]
             c = L["cout"]
             params[L["name"]] = dict(
-                w=torch.randn(c, L["cin"] // L["groups"], L["k"], L["k"], generator=g) * math.sqrt(2.0 / fan_in),
+                w=torch.randn(c, L["cin"] // L["groups"], L["k"], L["k"], generator=g) * math.sqrt(2.0 / fan_in)
+                * (gain if L["src"] != "input" else 1.0),
                 gamma=torch.rand(c, generator=g) + 0.5,
                 beta=torch.randn(c, generator=g) * 0.1,
                 mean=torch.randn(c, generator=g) * 0.1,
@@ -141,7 +144,8 @@ class CompiledNet:
     """
 
     def __init__(self, spec: List[dict], params, batch: int, T: int, in_hw=(224, 224),
-                 dtype=torch.bfloat16, device="cuda", conv_path: str = "auto", keep_membranes: bool = False):
+                 dtype=torch.bfloat16, device="cuda", conv_path: str = "auto", keep_membranes: bool = False,
+                 fuse_shortcuts: bool = True):
         self.spec, self.B, self.T, self.dtype = spec, int(batch), int(T), dtype
         self.device = torch.device(device)
         self.path = {"auto": _lib.PATH_AUTO, "simt": _lib.PATH_SIMT, "tcgen05": _lib.PATH_TCGEN05,
@@ -164,6 +168,27 @@ class CompiledNet:
         self.x_in = torch.empty((self.B, H, W, 3), dtype=dtype, device=self.device)
         self.bufs["input"] = self.x_in
         self.logits = None
+        # A strided 1x1 shortcut conv (lif = False) that only feeds the residual input of a 3x3 / stride 1 conv
+        # is folded into that conv's launch (snnb_conv3x3_shortcut_lif): its output is never materialised.
+        self.fused_sc: Dict[str, dict] = {}    # consumer layer name -> the shortcut layer
+        self.skipped = set()                   # shortcut layers that no longer run on their own
+        if fuse_shortcuts and dtype in (torch.bfloat16, torch.float16) and conv_path == "auto" and self.T in (1, 2, 4):
+            by_dst = {L.get("dst"): L for L in spec if L["op"] == "conv"}
+            hw = {"input": tuple(in_hw)}   # output size of every layer, to know which maps the fused kernel takes
+            for L in spec:
+                if L["op"] == "conv":
+                    hw[L["dst"]] = _out_hw(*hw[L["src"]], L["k"], L["s"], L["p"])
+                elif L["op"] == "maxpool":
+                    hw[L["dst"]] = _out_hw(*hw[L["src"]], 3, 2, 1)
+            for L in spec:
+                D = by_dst.get(L.get("residual")) if L["op"] == "conv" else None
+                ho, wo = hw.get(L.get("dst"), (0, 0))
+                if (D is not None and ((ho >= 8 and wo >= 8) or (ho <= 7 and wo <= 8)) and not D["lif"] and D["k"] == 1 and D["p"] == 0 and D["groups"] == 1
+                        and D["src"] != "input" and L["k"] == 3 and L["s"] == 1 and L["p"] == 1 and L["groups"] == 1
+                        and L["lif"] and L["cin"] % 64 == 0 and D["cin"] % 64 == 0 and L["cout"] > 64
+                        and sum(1 for M in spec if M.get("src") == D["dst"] or M.get("residual") == D["dst"]) == 1):
+                    self.fused_sc[L["name"]] = D
+                    self.skipped.add(D["name"])
         # The stem's spikes are the widest activation of a ResNet and are read only by the max-pool: they
         # are kept as one byte each (spike_dtype U8) and pooled by the u8 variant of the pooling kernel.
         self.u8_bufs = set()
@@ -177,6 +202,8 @@ class CompiledNet:
             if L["op"] == "conv":
                 ho, wo = _out_hw(h, w_, L["k"], L["s"], L["p"])
                 self.shapes[L["dst"]] = (ho, wo, L["cout"])
+                if L["name"] in self.skipped:
+                    continue
                 self.bufs[L["dst"]] = torch.empty((self.T, self.B, ho, wo, L["cout"]), device=self.device,
                                                   dtype=torch.uint8 if L["dst"] in self.u8_bufs else dtype)
                 if L["lif"] and (keep_membranes or L["groups"] != 1):
@@ -208,9 +235,26 @@ class CompiledNet:
         self.extra_launches = 0
         T, B, dt = self.T, self.B, self.dt
         for L in self.spec:
+            if L["name"] in self.skipped:
+                continue
             src = self.bufs[L["src"]]
             h, w_, c = self.shapes[L["src"]]
             x_stride = 0 if L["src"] == "input" else src.stride(0)
+            if L["op"] == "conv" and L["name"] in self.fused_sc:
+                D = self.fused_sc[L["name"]]
+                wt, wd = self.weights[L["name"]], self.weights[D["name"]]
+                if "b_sum" not in wt:   # one bias for both branches, added in fp32
+                    wt["b_sum"] = (wt["b"].float() + wd["b"].float()).to(self.dtype)
+                    wd["w_sc"] = wd["w"].reshape(D["cout"], D["cin"]).contiguous()
+                sc = self.bufs[D["src"]]
+                sh, sw, _ = self.shapes[D["src"]]
+                v = self.membranes[L["name"]].data_ptr() if L["name"] in self.membranes else None
+                args = (src.data_ptr(), x_stride, wt["w"].data_ptr(), wt["b_sum"].data_ptr(),
+                        sc.data_ptr(), sc.stride(0), wd["w_sc"].data_ptr(), D["cin"], sh, sw, D["s"],
+                        None, self.bufs[L["dst"]].data_ptr(), v, T, B, L["cin"], h, w_, L["cout"], dt, dt, dt,
+                        LIF["v_th"], LIF["v_reset"], LIF["tau"])
+                calls.append((lib.snnb_conv3x3_shortcut_lif, args, L["name"]))
+                continue
             if L["op"] == "conv":
                 wt = self.weights[L["name"]]
                 dst = self.bufs[L["dst"]]
