@@ -99,8 +99,11 @@ extern "C" int snnb_linear_lif(const void *x_seq, int64_t x_t_stride, const void
   ConvArgs a;
   a.x = x_seq; a.x_t_stride = x_t_stride; a.w = w; a.b = b; a.res = nullptr;
   a.v_init = v_init; a.spikes = spikes; a.v_out = v_out;
-  a.T = T; a.B = 1; a.Cin = K; a.H = 1; a.W = M; a.Cout = N; a.KH = 1; a.KW = 1;
-  a.stride = 1; a.pad = 0; a.Ho = 1; a.Wo = M; a.lif = 1;
+  // a 1x1 conv over the tokens laid out as an image: 8 tokens per row when that divides (the shape the
+  // timestep-pair kernel tiles), else one row of M tokens
+  const bool rows8 = M % 8 == 0 && M >= 64;
+  a.T = T; a.B = 1; a.Cin = K; a.H = rows8 ? M / 8 : 1; a.W = rows8 ? 8 : M; a.Cout = N; a.KH = 1; a.KW = 1;
+  a.stride = 1; a.pad = 0; a.Ho = a.H; a.Wo = a.W; a.lif = 1;
   a.dtype = dtype; a.spike_dtype = spike_dtype; a.v_dtype = v_dtype;
   a.p = make_lif_params(v_th, v_reset, tau);
   return run(a, path, static_cast<cudaStream_t>(stream), "linear_lif");

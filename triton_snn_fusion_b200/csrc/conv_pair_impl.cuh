@@ -55,6 +55,7 @@ struct PairGeom {
   int kslabs, npairs, tq;   // tq = timesteps per pair (1 or 2)
   int n_tiles_n, row_tiles, w_strips;
   int tmem_cols, lif, has_res, total_tiles;
+  int ntaps;      // 9 (3x3 conv) or 1 (1x1 conv / linear: only the centre of the halo tile is used)
   int sc_slabs;   // > 0: instead of a residual tensor, a 1x1 shortcut conv over sc_slabs 64-channel slabs of a
                   // second input is accumulated (its pixel tiles come through rmap, its weights through scwmap)
   int ring;   // halo slots in use
@@ -314,7 +315,7 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
         const int n0 = (tile % g.n_tiles_n) * 128;
         for (int pair = 0; pair < g.npairs && ok; ++pair) {
           for (int slab = 0; slab < g.kslabs && ok; ++slab)
-            for (int tap = 0; tap < 9; ++tap) {
+            for (int tap = 0; tap < g.ntaps; ++tap) {
               ok = umma::mbar_wait(wempty(ws), wphase, abort_flag);
               if (!ok) break;
               umma::mbar_expect_tx(wfull(ws), (uint32_t)kWSlot);
@@ -357,11 +358,11 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
           for (int slab = 0; slab < g.kslabs && ok; ++slab) {
             ok = umma::mbar_wait(hfull(slot), phase, abort_flag);
             if (!ok) break;
-            for (int tap = 0; tap < 9; ++tap) {
+            for (int tap = 0; tap < g.ntaps; ++tap) {
               ok = umma::mbar_wait(wfull(ws), wphase, abort_flag);
               if (!ok) break;
               umma::tc_fence_after_sync();
-              const int kh = tap / 3, kw = tap - kh * 3;
+              const int kh = g.ntaps == 1 ? 1 : tap / 3, kw = g.ntaps == 1 ? 1 : tap - kh * 3;
               const uint64_t xdesc = hdesc0 + (uint64_t)((slot * slot_bytes + (uint32_t)(kh * kPW + kw) * 128u) >> 4);
               const uint64_t wdesc = wdesc0 + (uint64_t)((ws * (uint32_t)kWSlot) >> 4);
 #pragma unroll
@@ -506,6 +507,7 @@ int launch(const ConvArgs &a, cudaStream_t stream) {
   g.Tacc = (a.x_t_stride == 0) ? 1 : a.T;
   g.B = a.B; g.Cin = a.Cin; g.Cout = a.Cout; g.Ho = a.Ho; g.Wo = a.Wo;
   g.kslabs = a.Cin / 64;
+  g.ntaps = a.KH * a.KW;
   g.tq = g.Tacc >= 2 ? 2 : 1;
   g.npairs = g.Tacc / g.tq;
   g.n_tiles_n = (a.Cout + 127) / 128;
@@ -536,7 +538,7 @@ int launch(const ConvArgs &a, cudaStream_t stream) {
     if (rc != SNNB_OK) return rc;
   }
   {
-    const cuuint64_t K = (cuuint64_t)9 * a.Cin;
+    const cuuint64_t K = (cuuint64_t)g.ntaps * a.Cin;
     cuuint64_t dims[2] = {K, (cuuint64_t)a.Cout};
     cuuint64_t strides[1] = {K * es};
     cuuint32_t box[2] = {64, 128};
@@ -546,7 +548,7 @@ int launch(const ConvArgs &a, cudaStream_t stream) {
   g.dup = a.Cout <= 64 ? 1 : 0;
   CUtensorMap wm64 = wm;
   if (g.dup) {
-    const cuuint64_t K = (cuuint64_t)9 * a.Cin;
+    const cuuint64_t K = (cuuint64_t)g.ntaps * a.Cin;
     cuuint64_t dims[2] = {K, (cuuint64_t)a.Cout};
     cuuint64_t strides[1] = {K * es};
     cuuint32_t box[2] = {64, 64};
