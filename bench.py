@@ -263,6 +263,8 @@ def run_ours(args):
         if L["k"] == 3 and L["s"] == 1:
             one_image, two_images = ho >= 8 and wo >= 8, ho <= 7 and wo <= 8 and L["cout"] > 64
             return "conv3x3_pair" if one_image or two_images else "conv3x3_halo"
+        if L["k"] == 3 and L["s"] == 2 and L["cout"] > 64 and L["cin"] % 64 == 0:
+            return "conv3x3_pair"   # stride 2 through the four phase views
         return "conv_lif_tc"
     by_kernel = {}
     fused_into = {D["name"]: consumer for consumer, D in net.fused_sc.items()}   # shortcut conv -> the launch it rides in
@@ -283,7 +285,7 @@ def run_ours(args):
     achieved = d["flop"] / (d["ms"] * 1e-3) / 1e12 if d["ms"] > 0 else 0.0
     top = sorted(layer_ms.items(), key=lambda kv: -kv[1])[:6]
     # DRAM traffic per launch of the dominant kernel: one ncu capture of a 128->128, 56x56, T=4, batch-32
-    # layer read 103.18 MB and wrote 78.09 MB (profiles/conv3x3_pair_128to128_56x56_T4_b32.md). The kernel
+    # layer read 103.18 MB and wrote 78.09 MB (its ncu summary is committed with the other profiles). The kernel
     # moves each activation once, so the figure is scaled by the activation elements (in + out) of the
     # layers it serves here and averaged over its launches.
     traffic = None
@@ -296,7 +298,7 @@ def run_ours(args):
                 elems += T_STEPS * B * ho * wo * (L["cin"] + co + (co if L.get("residual") else 0))
         traffic = cap_bytes * elems / cap_elems / d["launches"]
     roofline = {
-        "kernel": f"{dom} ({d['launches']} launches per step: the 3x3 stride-1 conv + BN + LIF layers)",
+        "kernel": f"{dom} ({d['launches']} launches per step: every 3x3 conv + BN + LIF layer after the stem)",
         "bound": "tensor", "achieved": achieved, "peak": peaks["tf_sustained"], "unit": "TFLOP/s",
         "frac": achieved / peaks["tf_sustained"], "peak_source": peaks["source"] + " (sustained bf16)",
         "traffic": traffic, "traffic_unit": "bytes per launch (ncu capture of one layer, scaled by activation elements)",

@@ -81,6 +81,8 @@ CONV = [
     (2, 128, 64, 1, 1, 0, 13, 17),
     (1, 64, 48, 3, 1, 1, 9, 11),
     (2, 64, 64, 3, 2, 1, 15, 13),
+    (2, 64, 128, 3, 2, 1, 17, 19),       # stride 2 on odd sizes through the phase views of the pair kernel
+    (3, 128, 192, 3, 2, 1, 12, 16),      # stride 2 down to a 6x8 map: two images per tile
     (1, 64, 32, 5, 1, 2, 12, 12),
 ]
 

@@ -13,7 +13,9 @@ bool conv3x3_pair_supported(const ConvArgs &a) {
   if (a.dtype != SNNB_BF16 && a.dtype != SNNB_F16) return false;
   const bool k3 = a.KH == 3 && a.KW == 3 && a.stride == 1 && a.pad == 1;
   const bool k1 = a.KH == 1 && a.KW == 1 && a.stride == 1 && a.pad == 0;   // reads only the centre of each halo tile
-  if (!k3 && !k1) return false;
+  // stride 2: four phase views of the input per slab; the base of the odd-column views must stay 16-byte aligned
+  const bool k3s2 = a.KH == 3 && a.KW == 3 && a.stride == 2 && a.pad == 1 && a.Cout > 64 && a.H >= 2 && a.W >= 2;
+  if (!k3 && !k1 && !k3s2) return false;
   if (a.sc_x != nullptr && !k3) return false;
   if (a.Cin % 64 != 0) return false;
   if (a.x_t_stride == 0 && a.T > 1) return false;   // one frame for all steps: left to the other kernels

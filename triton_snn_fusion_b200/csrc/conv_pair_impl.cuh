@@ -55,6 +55,9 @@ struct PairGeom {
   int kslabs, npairs, tq;   // tq = timesteps per pair (1 or 2)
   int n_tiles_n, row_tiles, w_strips;
   int tmem_cols, lif, has_res, total_tiles;
+  int s2;         // 3x3 / stride 2 / padding 1: per slab four halo tiles, one per phase (row parity a, column
+                  // parity b) of the input, each seen through a tensor map with doubled strides; input row
+                  // 2i - 1 + kh is phase row i - 1 (kh = 0, a = 1), i (kh = 1, a = 0) or i (kh = 2, a = 1)
   int ntaps;      // 9 (3x3 conv) or 1 (1x1 conv / linear: only the centre of the halo tile is used)
   int sc_slabs;   // > 0: instead of a residual tensor, a 1x1 shortcut conv over sc_slabs 64-channel slabs of a
                   // second input is accumulated (its pixel tiles come through rmap, its weights through scwmap)
@@ -66,6 +69,29 @@ struct PairGeom {
   int dup;    // Cout <= 64: the 64 weight rows are loaded twice (M rows 64..127 repeat 0..63) so that all
               // eight epilogue warps can read the accumulator and split the pixels four ways
 };
+
+// The taps served by halo tile `ph` of a slab: all of them for stride 1 (ph = 0); for stride 2 the taps
+// whose input rows / columns have the parity of phase ph = 2a + b.
+template <bool S2>
+__device__ __forceinline__ int phase_ntaps(const PairGeom &g, int ph) {
+  return S2 ? ((ph & 2) ? 2 : 1) * ((ph & 1) ? 2 : 1) : g.ntaps;
+}
+// j-th tap of phase ph: its index in the weight tensor (kh * 3 + kw) and its row offset inside the halo tile.
+template <bool S2>
+__device__ __forceinline__ void phase_tap(const PairGeom &g, int ph, int j, int &wtap, int &off) {
+  if constexpr (!S2) {
+    const int kh = g.ntaps == 1 ? 1 : j / 3, kw = g.ntaps == 1 ? 1 : j - kh * 3;
+    wtap = g.ntaps == 1 ? 0 : j;
+    off = kh * kPW + kw;
+  } else {
+    const int a = ph >> 1, b = ph & 1, nc = b ? 2 : 1;
+    const int jr = j / nc, jc = j - jr * nc;
+    const int kh = a ? (jr ? 2 : 0) : 1, kw = b ? (jc ? 2 : 0) : 1;
+    const int du = (a && jr == 0) ? -1 : 0, dv = (b && jc == 0) ? -1 : 0;   // phase pixel relative to the output pixel
+    wtap = kh * 3 + kw;
+    off = (du + 1) * kPW + (dv + 1);
+  }
+}
 
 // LIF flavours compiled into the epilogue: the common one (tau a power of two, hard reset) with its
 // branches resolved at compile time, every other kind through the run-time lif_step, or no LIF.
@@ -170,11 +196,12 @@ __device__ __forceinline__ void pair_epilogue_full(const LifParams &p, uint32_t 
   }
 }
 
-template <typename XT, typename ST, typename VT>
+template <typename XT, typename ST, typename VT, bool S2>
 __global__ void __launch_bounds__(kThreadsP)
 conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap,
                     const __grid_constant__ CUtensorMap rmap, const __grid_constant__ CUtensorMap wmap64,
-                    const __grid_constant__ CUtensorMap scwmap,
+                    const __grid_constant__ CUtensorMap scwmap, const __grid_constant__ CUtensorMap xmap01,
+                    const __grid_constant__ CUtensorMap xmap10, const __grid_constant__ CUtensorMap xmap11,
                     const XT *__restrict__ bias, const VT *__restrict__ v_init,
                     ST *__restrict__ spikes, VT *__restrict__ v_out, const PairGeom g, const LifParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -265,11 +292,14 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
     };
     uint32_t slot = 0, phase = 1;
     bool ok = true;
+    constexpr int nph = S2 ? 4 : 1;
     for (int tile = blockIdx.x; tile < g.total_tiles && ok; tile += gridDim.x) {
       int n0, w0, h0, b;
       decode(tile, n0, w0, h0, b);
       for (int pair = 0; pair < g.npairs && ok; ++pair) {
-        for (int slab = 0; slab < g.kslabs; ++slab) {
+        for (int sp = 0; sp < g.kslabs * nph && ok; ++sp) {
+          const int slab = sp / nph, ph = sp - slab * nph;
+          const CUtensorMap *xm = ph == 0 ? &xmap : (ph == 1 ? &xmap01 : (ph == 2 ? &xmap10 : &xmap11));
           if (lane == 0) {
             ok = umma::mbar_wait(hempty(slot), phase, abort_flag);
             if (ok) umma::mbar_expect_tx(hfull(slot), tx_bytes(b));
@@ -278,9 +308,9 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
           if (!ok) break;
           if (lane < g.tq) {
             const uint32_t dst = h_base + slot * slot_bytes + (uint32_t)lane * kHaloT;
-            umma::tma_load_5d(dst, &xmap, hfull(slot), slab * 64, w0 - 1, h0 - 1, b, pair * g.tq + lane);
+            umma::tma_load_5d(dst, xm, hfull(slot), slab * 64, w0 - 1, h0 - 1, b, pair * g.tq + lane);
             if (g.stack && b + 1 < g.B)
-              umma::tma_load_5d(dst + 8u * kRowBytes, &xmap, hfull(slot), slab * 64, -1, -1, b + 1, pair * g.tq + lane);
+              umma::tma_load_5d(dst + 8u * kRowBytes, xm, hfull(slot), slab * 64, -1, -1, b + 1, pair * g.tq + lane);
           }
           if (++slot == (uint32_t)g.ring) { slot = 0; phase ^= 1u; }
         }
@@ -314,8 +344,11 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
       for (int tile = blockIdx.x; tile < g.total_tiles && ok; tile += gridDim.x) {
         const int n0 = (tile % g.n_tiles_n) * 128;
         for (int pair = 0; pair < g.npairs && ok; ++pair) {
-          for (int slab = 0; slab < g.kslabs && ok; ++slab)
-            for (int tap = 0; tap < g.ntaps; ++tap) {
+          for (int sp = 0; sp < g.kslabs * (S2 ? 4 : 1) && ok; ++sp) {
+            const int slab = S2 ? sp >> 2 : sp, ph = S2 ? sp & 3 : 0;
+            for (int j = 0; j < phase_ntaps<S2>(g, ph); ++j) {
+              int tap, off_unused;
+              phase_tap<S2>(g, ph, j, tap, off_unused);
               ok = umma::mbar_wait(wempty(ws), wphase, abort_flag);
               if (!ok) break;
               umma::mbar_expect_tx(wfull(ws), (uint32_t)kWSlot);
@@ -327,6 +360,7 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
               }
               if (++ws == (uint32_t)g.wring) { ws = 0; wphase ^= 1u; }
             }
+          }
           // shortcut conv: its weight tiles follow the pair's main-conv tiles, one per slab of the shortcut input
           for (int rs = 0; rs < g.sc_slabs && ok; ++rs) {
             ok = umma::mbar_wait(wempty(ws), wphase, abort_flag);
@@ -355,20 +389,22 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
           if (!ok) break;
           umma::tc_fence_after_sync();
           const uint32_t d = tmem_base + (uint32_t)(pair * 256);
-          for (int slab = 0; slab < g.kslabs && ok; ++slab) {
+          for (int sp = 0; sp < g.kslabs * (S2 ? 4 : 1) && ok; ++sp) {
+            const int ph = S2 ? sp & 3 : 0;
             ok = umma::mbar_wait(hfull(slot), phase, abort_flag);
             if (!ok) break;
-            for (int tap = 0; tap < g.ntaps; ++tap) {
+            for (int tap = 0; tap < phase_ntaps<S2>(g, ph); ++tap) {
               ok = umma::mbar_wait(wfull(ws), wphase, abort_flag);
               if (!ok) break;
               umma::tc_fence_after_sync();
-              const int kh = g.ntaps == 1 ? 1 : tap / 3, kw = g.ntaps == 1 ? 1 : tap - kh * 3;
-              const uint64_t xdesc = hdesc0 + (uint64_t)((slot * slot_bytes + (uint32_t)(kh * kPW + kw) * 128u) >> 4);
+              int wtap_unused, off;
+              phase_tap<S2>(g, ph, tap, wtap_unused, off);
+              const uint64_t xdesc = hdesc0 + (uint64_t)((slot * slot_bytes + (uint32_t)off * 128u) >> 4);
               const uint64_t wdesc = wdesc0 + (uint64_t)((ws * (uint32_t)kWSlot) >> 4);
 #pragma unroll
               for (int k = 0; k < 4; ++k)   // A = weights (M = 128 channels), B = pixels (N = 128 per timestep)
                 umma::mma_f16_ss(d, wdesc + (uint64_t)(2 * k), xdesc + (uint64_t)(2 * k), idesc,
-                                 (slab > 0 || tap > 0 || k > 0) ? 1u : 0u);
+                                 (sp > 0 || tap > 0 || k > 0) ? 1u : 0u);
               umma::mma_commit(wempty(ws));
               if (++ws == (uint32_t)g.wring) { ws = 0; wphase ^= 1u; }
             }
@@ -508,6 +544,7 @@ int launch(const ConvArgs &a, cudaStream_t stream) {
   g.B = a.B; g.Cin = a.Cin; g.Cout = a.Cout; g.Ho = a.Ho; g.Wo = a.Wo;
   g.kslabs = a.Cin / 64;
   g.ntaps = a.KH * a.KW;
+  g.s2 = a.stride == 2 ? 1 : 0;
   g.tq = g.Tacc >= 2 ? 2 : 1;
   g.npairs = g.Tacc / g.tq;
   g.n_tiles_n = (a.Cout + 127) / 128;
@@ -527,15 +564,25 @@ int launch(const ConvArgs &a, cudaStream_t stream) {
     return fail(SNNB_ERR_CUDA, "conv_lif: cannot query the SM count");
   const long long grid = tiles < sms ? tiles : sms;   // persistent: one CTA per SM walks the tiles
   const int es = 2;
-  CUtensorMap xm, wm;
+  CUtensorMap xm, wm, xph[4];
   {
-    cuuint64_t dims[5] = {(cuuint64_t)a.Cin, (cuuint64_t)a.W, (cuuint64_t)a.H, (cuuint64_t)a.B, (cuuint64_t)g.Tacc};
+    // stride 1: one map of the frame. Stride 2: four phase views (row parity a, column parity b) with doubled
+    // strides; pixel (u, v) of view (a, b) is x at (2u + a, 2v + b).
+    const int s_ = g.s2 ? 2 : 1;
     const cuuint64_t frame_bytes = (cuuint64_t)a.B * a.H * a.W * a.Cin * es;
-    cuuint64_t strides[4] = {(cuuint64_t)a.Cin * es, (cuuint64_t)a.W * a.Cin * es, (cuuint64_t)a.H * a.W * a.Cin * es,
-                             g.Tacc > 1 ? (cuuint64_t)a.x_t_stride * es : frame_bytes};
-    cuuint32_t box[5] = {64, (cuuint32_t)kPW, (cuuint32_t)(g.stack ? 9 : kPH), 1, 1};
-    const int rc = encode_tmap(&xm, a.dtype, 5, a.x, dims, strides, box);
-    if (rc != SNNB_OK) return rc;
+    for (int ph = 0; ph < (g.s2 ? 4 : 1); ++ph) {
+      const int pa = ph >> 1, pb = ph & 1;
+      cuuint64_t dims[5] = {(cuuint64_t)a.Cin, (cuuint64_t)((a.W - pb + s_ - 1) / s_), (cuuint64_t)((a.H - pa + s_ - 1) / s_),
+                            (cuuint64_t)a.B, (cuuint64_t)g.Tacc};
+      cuuint64_t strides[4] = {(cuuint64_t)s_ * a.Cin * es, (cuuint64_t)s_ * a.W * a.Cin * es, (cuuint64_t)a.H * a.W * a.Cin * es,
+                               g.Tacc > 1 ? (cuuint64_t)a.x_t_stride * es : frame_bytes};
+      cuuint32_t box[5] = {64, (cuuint32_t)kPW, (cuuint32_t)(g.stack ? 9 : kPH), 1, 1};
+      const char *base = static_cast<const char *>(a.x) + ((size_t)pa * a.W + pb) * a.Cin * es;
+      const int rc = encode_tmap(&xph[ph], a.dtype, 5, base, dims, strides, box);
+      if (rc != SNNB_OK) return rc;
+    }
+    xm = xph[0];
+    if (!g.s2) xph[1] = xph[2] = xph[3] = xm;
   }
   {
     const cuuint64_t K = (cuuint64_t)g.ntaps * a.Cin;
@@ -584,10 +631,10 @@ int launch(const ConvArgs &a, cudaStream_t stream) {
   g.wring = ident ? kWRingP - 1 : kWRingP;
   const size_t smem = (ident ? (size_t)kIdentBytes : 0) + (size_t)g.wring * kWSlot + (size_t)g.ring * g.tq * kHaloT +
                       4 * kRowBytes + 1024;
-  auto kern = conv3x3_pair_kernel<XT, ST, VT>;
+  auto kern = g.s2 ? conv3x3_pair_kernel<XT, ST, VT, true> : conv3x3_pair_kernel<XT, ST, VT, false>;
   const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return fail(SNNB_ERR_CUDA, "conv_lif: cannot raise the shared-memory limit: %s", cudaGetErrorString(e));
-  kern<<<(unsigned)grid, kThreadsP, smem, stream>>>(xm, wm, rm, wm64, scwm, static_cast<const XT *>(a.b),
+  kern<<<(unsigned)grid, kThreadsP, smem, stream>>>(xm, wm, rm, wm64, scwm, xph[1], xph[2], xph[3], static_cast<const XT *>(a.b),
                                                     static_cast<const VT *>(a.v_init), static_cast<ST *>(a.spikes),
                                                     static_cast<VT *>(a.v_out), g, a.p);
   SNNB_CHECK_LAUNCH("conv3x3_pair");
