@@ -295,7 +295,8 @@ def run_ours(args):
         for L in spec:
             if L["name"] not in fused_into and kernel_of(L) == dom:
                 ho, wo, co = net.shapes[L["dst"]]
-                elems += T_STEPS * B * ho * wo * (L["cin"] + co + (co if L.get("residual") else 0))
+                hi, wi, _ = net.shapes[L["src"]]
+                elems += T_STEPS * B * (hi * wi * L["cin"] + ho * wo * (co + (co if L.get("residual") else 0)))
         traffic = cap_bytes * elems / cap_elems / d["launches"]
     roofline = {
         "kernel": f"{dom} ({d['launches']} launches per step: every 3x3 conv + BN + LIF layer after the stem)",
