@@ -166,3 +166,14 @@ def test_resnet18_with_live_deep_layers():
     for name in ("l2b1.out", "l3b1.out", "l4b1.out"):
         assert float(teacher[name].float().mean()) > 0.01, name
     torch.testing.assert_close(logits, ref_logits, rtol=2e-2, atol=2e-2)
+
+
+def test_resnet18_eight_timesteps_as_two_windows():
+    """T = 8 runs as two windows of four steps with the membrane carried in fp32: layer-wise parity with the
+    oracle's single eight-step pass."""
+    spec, net, logits, teacher, ref_logits, layers = _run_net("resnet18", 2, 8, 64, torch.bfloat16, 100, gain=4.0)
+    assert net.nwin == 2 and net.Tw == 4
+    assert all(m.dtype == torch.float32 for m in net.membranes.values())
+    _check_layers(spec, net, teacher, layers, torch.bfloat16)
+    assert float(teacher["l3b1.out"][4:].float().mean()) > 0.01      # the second window is alive too
+    torch.testing.assert_close(logits, ref_logits, rtol=2e-2, atol=2e-2)

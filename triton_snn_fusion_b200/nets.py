@@ -147,6 +147,13 @@ class CompiledNet:
                  dtype=torch.bfloat16, device="cuda", conv_path: str = "auto", keep_membranes: bool = False,
                  fuse_shortcuts: bool = True):
         self.spec, self.B, self.T, self.dtype = spec, int(batch), int(T), dtype
+        # Longer sequences run as windows of four timesteps (what the fastest conv kernel holds in tensor
+        # memory) with the membrane handed from window to window in fp32, which is exact. Networks with a
+        # LIF tail or depthwise layers keep one window.
+        simple = all(L["op"] in ("maxpool", "head") or (L["op"] == "conv" and L["groups"] == 1) for L in spec)
+        self.Tw = 4 if (self.T > 4 and self.T % 4 == 0 and dtype in (torch.bfloat16, torch.float16) and simple
+                        and conv_path == "auto") else self.T
+        self.nwin = self.T // self.Tw
         self.device = torch.device(device)
         self.path = {"auto": _lib.PATH_AUTO, "simt": _lib.PATH_SIMT, "tcgen05": _lib.PATH_TCGEN05,
                      "tcgen05_taps": _lib.PATH_TCGEN05_TAPS, "tcgen05_halo": _lib.PATH_TCGEN05_HALO}[conv_path]
@@ -172,7 +179,7 @@ class CompiledNet:
         # is folded into that conv's launch (snnb_conv3x3_shortcut_lif): its output is never materialised.
         self.fused_sc: Dict[str, dict] = {}    # consumer layer name -> the shortcut layer
         self.skipped = set()                   # shortcut layers that no longer run on their own
-        if fuse_shortcuts and dtype in (torch.bfloat16, torch.float16) and conv_path == "auto" and self.T in (1, 2, 4):
+        if fuse_shortcuts and dtype in (torch.bfloat16, torch.float16) and conv_path == "auto" and self.Tw in (1, 2, 4):
             by_dst = {L.get("dst"): L for L in spec if L["op"] == "conv"}
             hw = {"input": tuple(in_hw)}   # output size of every layer, to know which maps the fused kernel takes
             for L in spec:
@@ -206,9 +213,11 @@ class CompiledNet:
                     continue
                 self.bufs[L["dst"]] = torch.empty((self.T, self.B, ho, wo, L["cout"]), device=self.device,
                                                   dtype=torch.uint8 if L["dst"] in self.u8_bufs else dtype)
-                if L["lif"] and (keep_membranes or L["groups"] != 1):
-                    # dense convs can skip the final membrane (v_out = NULL); the depthwise kernel always writes it
-                    self.membranes[L["name"]] = torch.empty((self.B, ho, wo, L["cout"]), dtype=dtype, device=self.device)
+                if L["lif"] and (keep_membranes or L["groups"] != 1 or self.nwin > 1):
+                    # dense convs can skip the final membrane (v_out = NULL); the depthwise kernel always writes it;
+                    # several windows carry it in fp32
+                    self.membranes[L["name"]] = torch.empty((self.B, ho, wo, L["cout"]), device=self.device,
+                                                            dtype=torch.float32 if self.nwin > 1 else dtype)
             elif L["op"] == "maxpool":
                 ho, wo = _out_hw(h, w_, 3, 2, 1)
                 self.shapes[L["dst"]] = (ho, wo, c)
@@ -219,6 +228,8 @@ class CompiledNet:
                 self.logits = torch.empty((self.B, L["classes"]), dtype=torch.float32, device=self.device)
             elif L["op"] == "head":
                 self.logits = torch.empty((self.B, L["classes"]), dtype=torch.float32, device=self.device)
+                if self.nwin > 1:
+                    self.logits_w = torch.empty((self.nwin, self.B, L["classes"]), dtype=torch.float32, device=self.device)
         self._calls = self._plan()
         self.launches_per_forward = (len(self._calls) + self.extra_launches
                                      + (1 if any(L["op"] == "tail" for L in spec) else 0))
@@ -233,10 +244,19 @@ class CompiledNet:
     def _plan(self):
         lib, calls = _lib.lib, []
         self.extra_launches = 0
-        T, B, dt = self.T, self.B, self.dt
-        for L in self.spec:
+        T, B, dt = self.Tw, self.B, self.dt
+        vdt = _lib.dtype_code(torch.float32) if self.nwin > 1 else dt
+        for win, L in ((wi, L) for wi in range(self.nwin) for L in self.spec):
             if L["name"] in self.skipped:
                 continue
+
+            def at(name):   # address of this window's first frame of a [T, ...] activation buffer
+                buf = self.bufs[name]
+                return buf.data_ptr() if name == "input" else buf.data_ptr() + win * T * buf.stride(0) * buf.element_size()
+
+            def v_in(name):   # membrane left by the previous window
+                return self.membranes[name].data_ptr() if win > 0 else None
+
             src = self.bufs[L["src"]]
             h, w_, c = self.shapes[L["src"]]
             x_stride = 0 if L["src"] == "input" else src.stride(0)
@@ -249,44 +269,47 @@ class CompiledNet:
                 sc = self.bufs[D["src"]]
                 sh, sw, _ = self.shapes[D["src"]]
                 v = self.membranes[L["name"]].data_ptr() if L["name"] in self.membranes else None
-                args = (src.data_ptr(), x_stride, wt["w"].data_ptr(), wt["b_sum"].data_ptr(),
-                        sc.data_ptr(), sc.stride(0), wd["w_sc"].data_ptr(), D["cin"], sh, sw, D["s"],
-                        None, self.bufs[L["dst"]].data_ptr(), v, T, B, L["cin"], h, w_, L["cout"], dt, dt, dt,
+                args = (at(L["src"]), x_stride, wt["w"].data_ptr(), wt["b_sum"].data_ptr(),
+                        at(D["src"]), sc.stride(0), wd["w_sc"].data_ptr(), D["cin"], sh, sw, D["s"],
+                        v_in(L["name"]), at(L["dst"]), v, T, B, L["cin"], h, w_, L["cout"], dt, dt, vdt,
                         LIF["v_th"], LIF["v_reset"], LIF["tau"])
                 calls.append((lib.snnb_conv3x3_shortcut_lif, args, L["name"]))
                 continue
             if L["op"] == "conv":
                 wt = self.weights[L["name"]]
                 dst = self.bufs[L["dst"]]
-                res = self.bufs[L["residual"]].data_ptr() if L.get("residual") else None
+                res = at(L["residual"]) if L.get("residual") else None
                 v = self.membranes[L["name"]].data_ptr() if L["name"] in self.membranes else None
                 if self._is_tc_stem(L, h, w_):
                     # 7x7/s2 stem on the tensor cores: weights re-packed once, input re-laid into scratch per call
                     frames = B if x_stride == 0 else T * B
                     nbytes = int(lib.snnb_stem7x7_scratch_bytes(frames, h, w_))
-                    self._scratch = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
-                    wp = torch.empty((L["cout"], 256), dtype=self.dtype, device=self.device)
-                    _lib.check(lib.snnb_stem7x7_pack_weight(wt["w"].data_ptr(), wp.data_ptr(), L["cout"], dt, None),
-                               "snnb_stem7x7_pack_weight")
-                    torch.cuda.synchronize(self.device)
-                    wt["w_stem"] = wp
+                    if "w_stem" not in wt:
+                        self._scratch = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
+                        wp = torch.empty((L["cout"], 256), dtype=self.dtype, device=self.device)
+                        _lib.check(lib.snnb_stem7x7_pack_weight(wt["w"].data_ptr(), wp.data_ptr(), L["cout"], dt, None),
+                                   "snnb_stem7x7_pack_weight")
+                        torch.cuda.synchronize(self.device)
+                        wt["w_stem"] = wp
+                    wp = wt["w_stem"]
                     sdt = _lib.dtype_code(torch.uint8) if L["dst"] in self.u8_bufs else dt
-                    args = (src.data_ptr(), x_stride, wp.data_ptr(), wt["b"].data_ptr(), None, dst.data_ptr(), v,
-                            self._scratch.data_ptr(), nbytes, T, B, h, w_, L["cout"], dt, sdt, dt,
+                    args = (at(L["src"]), x_stride, wp.data_ptr(), wt["b"].data_ptr(), v_in(L["name"]), at(L["dst"]), v,
+                            self._scratch.data_ptr(), nbytes, T, B, h, w_, L["cout"], dt, sdt, vdt,
                             LIF["v_th"], LIF["v_reset"], LIF["tau"])
                     calls.append((lib.snnb_stem7x7_lif, args, L["name"]))
                     self.extra_launches += 1
                 elif L["groups"] == 1:
-                    args = (src.data_ptr(), x_stride, wt["w"].data_ptr(), wt["b"].data_ptr(), res, None, dst.data_ptr(), v,
+                    args = (at(L["src"]), x_stride, wt["w"].data_ptr(), wt["b"].data_ptr(), res,
+                            v_in(L["name"]) if L["lif"] else None, at(L["dst"]), v,
                             T, B, L["cin"], h, w_, L["cout"], L["k"], L["k"], L["s"], L["p"], 1 if L["lif"] else 0,
-                            dt, dt, dt, LIF["v_th"], LIF["v_reset"], LIF["tau"], self.path)
+                            dt, dt, vdt, LIF["v_th"], LIF["v_reset"], LIF["tau"], self.path)
                     calls.append((lib.snnb_conv_lif, args, L["name"]))
                 else:
                     args = (src.data_ptr(), x_stride, wt["w"].data_ptr(), wt["b"].data_ptr(), res, None, dst.data_ptr(), v,
                             T, B, L["cin"], h, w_, L["s"], dt, dt, dt, LIF["v_th"], LIF["v_reset"], LIF["tau"])
                     calls.append((lib.snnb_dwconv3x3_lif, args, L["name"]))
             elif L["op"] == "maxpool":
-                args = (src.data_ptr(), self.bufs[L["dst"]].data_ptr(), T * B, h, w_, c, dt)
+                args = (at(L["src"]), at(L["dst"]), T * B, h, w_, c, dt)
                 calls.append((lib.snnb_maxpool3x3s2_u8 if L["src"] in self.u8_bufs else lib.snnb_maxpool3x3s2, args, L["name"]))
             elif L["op"] == "tail":
                 wt = self.weights[L["name"]]
@@ -296,8 +319,8 @@ class CompiledNet:
                 calls.append((lib.snnb_lif_avgpool_linear, args, L["name"]))
             elif L["op"] == "head":
                 wt = self.weights[L["name"]]
-                args = (src.data_ptr(), wt["w"].data_ptr(), wt["b"].data_ptr(), self.logits.data_ptr(),
-                        T, B, c, h * w_, L["classes"], dt)
+                out = self.logits_w[win].data_ptr() if self.nwin > 1 else self.logits.data_ptr()
+                args = (at(L["src"]), wt["w"].data_ptr(), wt["b"].data_ptr(), out, T, B, c, h * w_, L["classes"], dt)
                 calls.append((lib.snnb_avgpool_linear_mean, args, L["name"]))
         return calls
 
@@ -307,6 +330,8 @@ class CompiledNet:
             st = fn(*args, stream)
             if st != 0:
                 _lib.check(st, f"layer {name}")
+        if self.nwin > 1:   # the head wrote one mean per window
+            torch.mean(self.logits_w, dim=0, out=self.logits)
         if hasattr(self, "tail_sum"):
             # the tail returns sum_t logits in the compute dtype; the network output is their mean
             torch.mul(self.tail_sum, 1.0 / float(self.T), out=self.logits)
