@@ -40,7 +40,6 @@ GLOBAL_BATCH = 512
 T_STEPS = 4
 IN_HW = (224, 224)
 CLASSES = 1000
-METRIC = "spiking_resnet18_T4_images_per_sec"
 
 
 def _peaks():
@@ -114,54 +113,89 @@ def conv_flops(spec, shapes, B, T):
     return out
 
 
-def cpu_eager_images_per_s(batch: int, reps: int, threads: int | None = None):
-    """The reference's un-fused eager CPU path (oracle port) on `batch` images: conv -> BN -> LIF per
-    timestep in fp32 with plain torch ops. Returns (images/s, cores, seconds per pass)."""
-    from oracle import models as omodels
-    from triton_snn_fusion_b200 import nets
+def cpu_eager_images_per_s(batch: int, reps: int, net: str = "resnet18", T: int = 4):
+    """The reference's un-fused eager path on the host cores: the single-step model (conv -> BatchNorm -> LIF)
+    called T times and averaged, fp32, with every LIF update done by the reference's own op
+    (snn_custom.lif_forward_state of its runtime/snn_custom_ops.py, imported unmodified from the staged copy under
+    oracle/_ref). Without that copy the oracle's port of the same loop runs instead. Uses every core this
+    process may run on. Returns (images/s, threads, seconds per pass, kind)."""
+    from triton_snn_fusion_b200 import specs   # plain-torch workload definition; loads no CUDA library
 
-    if threads:
-        torch.set_num_threads(threads)
-    spec = nets.spiking_resnet18(CLASSES)
-    params = nets.make_params(spec, seed=2026)
+    torch.set_num_threads(max(1, len(os.sched_getaffinity(0))))
+    spec = specs.NETS[net](CLASSES)
+    params = specs.make_params(spec, seed=2026)
     x = torch.randn(batch, 3, *IN_HW, generator=torch.Generator().manual_seed(2026))
+    ref_dir = ROOT / "oracle" / "_ref"
+    if (ref_dir / "runtime" / "snn_custom_ops.py").exists():
+        sys.dont_write_bytecode = True
+        sys.path.insert(0, str(ref_dir))
+        import runtime.snn_custom_ops as ref_ops   # the reference's file, with its own backends beneath it
+        from oracle import torch_models
+        ref_ops.configure_fused_op(backend="torch")
+        model = torch_models.build(spec, params, T)
+
+        def one_pass():
+            model.layer.reset()
+            return model(x)
+        kind = "reference"
+    else:
+        from oracle import models as omodels
+
+        def one_pass():
+            return omodels.eager_forward(spec, params, x, T)
+        kind = "port"
     with torch.no_grad():
-        omodels.eager_forward(spec, params, x, T_STEPS)  # warm-up
+        one_pass()  # warm-up
         times = []
         for _ in range(reps):
             t0 = time.perf_counter()
-            omodels.eager_forward(spec, params, x, T_STEPS)
+            one_pass()
             times.append(time.perf_counter() - t0)
     times.sort()
     med = times[len(times) // 2]
-    return batch / med, torch.get_num_threads(), med
+    return batch / med, torch.get_num_threads(), med, kind
 
 
 def run_reference(args):
+    """CPU arm: nothing of this library's CUDA code is loaded or run. One step = one timed pass over a bounded
+    sample (batch 32) of the 512-image workload; images/s does not depend on the sample size."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     batch = 32
-    reps = max(1, min(args.steps, 20))   # about 0.45 s per pass on 16 cores
-    ips, cores, sec = cpu_eager_images_per_s(batch, reps)
-    sample = f"{reps} timed passes of batch {batch} (of the 512-image step), fp32, torch eager on CPU"
+    reps = max(1, min(args.steps, 40))   # about 0.45 s per pass on 16 cores
+    ips, cores, sec, kind = cpu_eager_images_per_s(batch, reps, args.net, args.T)
+    sample = (f"{reps} timed passes of batch {batch} (a sample of the {args.global_batch}-image step), fp32, torch eager on "
+              f"{cores} CPU threads, LIF by the reference's snn_custom.lif_forward_state" if kind == "reference" else
+              f"{reps} timed passes of batch {batch} (a sample of the {args.global_batch}-image step), fp32, oracle port of "
+              f"the eager loop on {cores} CPU threads")
     line = {
-        "impl": "reference", "metric": METRIC, "value": ips, "unit": "images/s", "n_gpus": args.gpus,
-        "steps": reps, "warmup": 1, "ms_per_step": sec * 1e3 * (GLOBAL_BATCH / batch), "higher_is_better": True,
+        "impl": "reference", "metric": metric_name(args.net, args.T), "value": ips, "unit": "images/s", "n_gpus": args.gpus,
+        "steps": reps, "warmup": 1, "ms_per_step": sec * 1e3, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"spiking ResNet-18 T=4, global batch {GLOBAL_BATCH}, 3x224x224 N(0,1), direct encoding",
-                   "parallelism": "cpu"},
-        "cpu_baseline": {"value": ips, "unit": "images/s", "cores": cores, "kind": "port", "sample": sample},
+        "config": {"workload": workload_name(args.T, args.global_batch, args.net), "parallelism": "cpu",
+                   "images_per_step": batch},
+        "cpu_baseline": {"value": ips, "unit": "images/s", "cores": cores, "kind": kind, "sample": sample},
         "e2e": {"value": ips, "unit": "images/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
 
 
+def metric_name(net, T):
+    return f"spiking_{net}_T{T}_images_per_sec"
+
+
+def workload_name(T, batch, net="resnet18"):
+    title = {"resnet18": "spiking ResNet-18", "mobilenet_v1": "spiking MobileNetV1"}[net]
+    return f"{title} T={T}, global batch {batch}, 3x224x224 N(0,1), direct encoding"
+
+
 def run_ours(args):
     import torch.distributed as dist
-    global GLOBAL_BATCH
+    global GLOBAL_BATCH, T_STEPS
     GLOBAL_BATCH = args.global_batch
+    T_STEPS = args.T
 
     from triton_snn_fusion_b200 import _lib, nets
     from triton_snn_fusion_b200.parallel import gather_logits, shard_range
@@ -179,7 +213,7 @@ def run_ours(args):
     B = stop - start
     K, Wm = args.steps, max(args.warmup, 3)
 
-    spec = nets.spiking_resnet18(CLASSES)
+    spec = nets.NETS[args.net](CLASSES)
     params = nets.make_params(spec, seed=2026, gain=args.weight_gain)
     net = nets.CompiledNet(spec, params, batch=B, T=T_STEPS, in_hw=IN_HW, dtype=torch.bfloat16, device=dev,
                            conv_path=args.path)
@@ -234,7 +268,7 @@ def run_ours(args):
     # ---- per-layer device times (un-graphed, CUDA events on the launching stream), after the timed region
     stream = torch.cuda.current_stream(dev).cuda_stream
     reps = 5
-    layer_ms = {}
+    layer_ms, layer_launches = {}, {}
     for fn, a, name in net._calls:
         for _ in range(2):
             fn(*a, stream)
@@ -244,7 +278,8 @@ def run_ours(args):
             fn(*a, stream)
         e1.record()
         torch.cuda.synchronize()
-        layer_ms[name] = e0.elapsed_time(e1) / reps
+        layer_ms[name] = layer_ms.get(name, 0.0) + e0.elapsed_time(e1) / reps   # a layer runs once per window of T
+        layer_launches[name] = layer_launches.get(name, 0) + 1
     status = _lib.device_status()
 
     if rank != 0:
@@ -256,10 +291,14 @@ def run_ours(args):
     # which kernel serves which layer (mirrors the library's dispatch for this network)
     def kernel_of(L):
         if L["op"] != "conv":
-            return {"maxpool": "maxpool3x3s2", "head": "avgpool_linear_mean"}[L["op"]]
+            return {"maxpool": "maxpool3x3s2", "head": "avgpool_linear_mean", "tail": "lif_avgpool_linear"}[L["op"]]
+        if L["groups"] != 1:
+            return "dwconv3x3_lif"
         if L["cin"] == 3:
-            return "stem (s2d + stem_gemm_lif)"
+            return "stem (s2d + stem_gemm_lif)" if L["k"] == 7 else "conv_lif_simt (3-channel stem)"
         ho, wo, _ = net.shapes[L["dst"]]
+        if L["k"] == 1 and L["s"] == 1 and L["cin"] % 64 == 0 and ((ho >= 8 and wo >= 8) or (ho <= 7 and wo <= 8 and L["cout"] > 64)):
+            return "conv3x3_pair"   # 1x1 convs run through the same kernel (centre tap only)
         if L["k"] == 3 and L["s"] == 1:
             one_image, two_images = ho >= 8 and wo >= 8, ho <= 7 and wo <= 8 and L["cout"] > 64
             return "conv3x3_pair" if one_image or two_images else "conv3x3_halo"
@@ -276,9 +315,13 @@ def run_ours(args):
             continue
         k = kernel_of(L)
         e = by_kernel.setdefault(k, {"launches": 0, "ms": 0.0, "flop": 0.0})
-        e["launches"] += 1
+        e["launches"] += layer_launches[L["name"]]
         e["ms"] += layer_ms[L["name"]]
         e["flop"] += flops.get(L["name"], 0.0)
+        if k == "dwconv3x3_lif":   # HBM-bound: input frames + spikes out + the membrane written once, 16-bit each
+            hi, wi, _ = net.shapes[L["src"]]
+            ho, wo, co = net.shapes[L["dst"]]
+            e["bytes"] = e.get("bytes", 0.0) + 2.0 * (T_STEPS * B * co * (hi * wi + ho * wo) + B * co * ho * wo)
     total_ms = sum(layer_ms.values())
     dom = max(by_kernel, key=lambda k: by_kernel[k]["ms"])
     d = by_kernel[dom]
@@ -298,10 +341,14 @@ def run_ours(args):
                 hi, wi, _ = net.shapes[L["src"]]
                 elems += T_STEPS * B * (hi * wi * L["cin"] + ho * wo * (co + (co if L.get("residual") else 0)))
         traffic = cap_bytes * elems / cap_elems / d["launches"]
+    bound, peak, unit, peak_src = "tensor", peaks["tf_sustained"], "TFLOP/s", peaks["source"] + " (sustained bf16)"
+    if d.get("bytes"):
+        bound, peak, unit, peak_src = "hbm", peaks["hbm"], "GB/s", peaks["source"] + " (copy bandwidth)"
+        achieved = d["bytes"] / (d["ms"] * 1e-3) / 1e9
     roofline = {
-        "kernel": f"{dom} ({d['launches']} launches per step: every 3x3 conv + BN + LIF layer after the stem)",
-        "bound": "tensor", "achieved": achieved, "peak": peaks["tf_sustained"], "unit": "TFLOP/s",
-        "frac": achieved / peaks["tf_sustained"], "peak_source": peaks["source"] + " (sustained bf16)",
+        "kernel": f"{dom} ({d['launches']} launches per step)",
+        "bound": bound, "achieved": achieved, "peak": peak, "unit": unit,
+        "frac": achieved / peak, "peak_source": peak_src,
         "traffic": traffic, "traffic_unit": "bytes per launch (ncu capture of one layer, scaled by activation elements)",
         "share_of_step": d["ms"] / total_ms if total_ms else None,
         "kernels": {k: {"launches": v["launches"], "ms": round(v["ms"], 3), "share": round(v["ms"] / total_ms, 3),
@@ -312,12 +359,13 @@ def run_ours(args):
     if args.layers:
         print(json.dumps({"layers_ms": {k: round(v, 4) for k, v in layer_ms.items()}}), file=sys.stderr)
     cpu_batch = 32   # 24 timed passes: about 10 s of CPU work on 16 cores
-    ips_cpu, cores, sec = cpu_eager_images_per_s(cpu_batch, 24) if world == 1 and not args.no_cpu else (None, None, None)
+    ips_cpu, cores, sec, cpu_kind = (cpu_eager_images_per_s(cpu_batch, 24 if T_STEPS <= 4 else 12, args.net, T_STEPS)
+                                     if world == 1 and not args.no_cpu else (None, None, None, None))
     line = {
-        "metric": METRIC, "value": GLOBAL_BATCH / (ms_resident * 1e-3), "unit": "images/s", "n_gpus": world,
+        "metric": metric_name(args.net, T_STEPS), "value": GLOBAL_BATCH / (ms_resident * 1e-3), "unit": "images/s", "n_gpus": world,
         "steps": K, "warmup": Wm, "ms_per_step": ms_resident, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": f"spiking ResNet-18 T=4, global batch {GLOBAL_BATCH}, 3x224x224 N(0,1), direct encoding",
+        "config": {"workload": workload_name(T_STEPS, GLOBAL_BATCH, args.net),
                    "parallelism": f"batch-sharded x{world}", "per_gpu_batch": B, "cuda_graph": bool(args.graph),
                    "conv_path": args.path,
                    "l2": "no flush needed: each step streams >3 GB of activations per GPU, far beyond the 126 MB L2"},
@@ -330,9 +378,10 @@ def run_ours(args):
         "device_status": status,
     }
     if ips_cpu is not None:
-        line["cpu_baseline"] = {"value": ips_cpu, "unit": "images/s", "cores": cores, "kind": "port",
-                                "sample": f"24 timed passes of batch {cpu_batch} of the same network, fp32 torch eager "
-                                          f"(conv->BN->LIF per timestep), {sec:.2f} s per pass"}
+        line["cpu_baseline"] = {"value": ips_cpu, "unit": "images/s", "cores": cores, "kind": cpu_kind,
+                                "sample": f"timed passes of batch {cpu_batch} of the same network, fp32 torch eager "
+                                          f"(conv->BN->LIF per timestep, T calls of the single-step model), "
+                                          f"{sec:.2f} s per pass"}
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -344,6 +393,9 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--T", type=int, default=4, help="timesteps (the headline is T = 4; 8 runs as two windows of four)")
+    ap.add_argument("--net", default="resnet18", choices=["resnet18", "mobilenet_v1"],
+                    help="network (the headline is resnet18; mobilenet_v1 is the depthwise / pointwise workload)")
     ap.add_argument("--path", default="auto", choices=["auto", "simt", "tcgen05", "tcgen05_taps", "tcgen05_halo"])
     ap.add_argument("--no-graph", dest="graph", action="store_false")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")

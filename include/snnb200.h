@@ -7,10 +7,19 @@
  *
  * Conventions shared by all entry points
  *   - plain device pointers, sizes and scalars; no torch types;
- *   - the caller owns every buffer; nothing is allocated, nothing is
- *     synchronised, no mutable global state is kept, so calls are re-entrant
- *     and may be issued on any stream (`stream` is a cudaStream_t passed as
- *     void*; NULL = the legacy default stream);
+ *   - the caller owns every buffer; nothing is allocated and nothing is
+ *     synchronised, so calls are re-entrant and may be issued on any stream
+ *     (`stream` is a cudaStream_t passed as void*; NULL = the legacy default
+ *     stream). The only state the library keeps between calls: the diagnostic
+ *     status words read by snnb_device_status(), per-device constants it
+ *     queries once (SM count, kernel attributes), and the scratch array and
+ *     address cache of snnb_stem7x7_lif_static (see there);
+ *   - v_init and v_out may be the very same buffer (the membrane is then
+ *     updated in place, like the reference's in/out membrane buffer,
+ *     kernels/benchmark_conv_lif_temporal_general.py:422-455): every kernel
+ *     reads and writes each membrane value from one thread only. Two different
+ *     buffers that overlap are rejected (SNNB_ERR_INVALID). No other pair of
+ *     arguments may overlap;
  *   - return value: SNNB_OK or an SNNB_ERR_* code; the text of the last error
  *     on the calling thread is returned by snnb_last_error();
  *   - activations are dense channels-last ("NHWC") unless a layout argument
@@ -68,6 +77,18 @@ const char *snnb_last_error(void);
  * 0 = no kernel reported a problem. Diagnostic only; never called on the hot
  * path. */
 int snnb_device_status(int *status_out);
+
+/*
+ * Self-test of those bounded waits (no counterpart in the reference, whose Triton kernels do not wait on
+ * barriers of their own). Arms the NEXT snnb_conv_lif / snnb_linear_lif / snnb_conv3x3_shortcut_lif call
+ * that runs on the timestep-pair kernel: its waits give up after `limit_cycles` SM cycles (1e3 .. 4e9) instead
+ * of about two seconds, and its first thread block announces one weight tile that it never loads. That block's
+ * waits therefore run out: it records the fact in the status word, releases its tensor memory and returns,
+ * while the other blocks finish normally. Nothing traps, faults or hangs; the armed call returns SNNB_OK, its
+ * output is incomplete, and snnb_device_status() then reports a non-zero status once. The call after it runs
+ * normally again.
+ */
+int snnb_selftest_arm_wait_timeout(long long limit_cycles);
 
 /*
  * Standalone temporal LIF scan.
@@ -152,15 +173,16 @@ int snnb_conv_lif(const void *x_seq, int64_t x_t_stride, const void *w, const vo
  * run_triton_fused_temporal_conv_add_lif_state (runtime/triton_convlif_backend.py:689-817); here the
  * shortcut is accumulated on the tensor cores as extra K slabs of the same GEMM, so its output is
  * never written. No counterpart in the reference.
- *   x_seq [T][B][H][W][Cin], w [Cout][3][3][Cin], b [Cout] = bias of the main conv + bias of the shortcut,
- *   sc_x [T][B][sc_H][sc_W][sc_cin] (frames sc_t_stride elements apart), sc_w [Cout][sc_cin];
+ *   x_seq [T][B][H][W][Cin], w [Cout][3][3][Cin], b [Cout] bias of the main conv (or NULL),
+ *   sc_x [T][B][sc_H][sc_W][sc_cin] (frames sc_t_stride elements apart), sc_w [Cout][sc_cin], sc_b [Cout] bias
+ *   of the shortcut conv (or NULL); the two biases are widened to fp32 before they are added;
  *   output pixel (h, w) adds sc_w . sc_x[h * sc_stride][w * sc_stride]; (sc_H - 1) / sc_stride + 1 == H.
  *   spikes [T][B][H][W][Cout], v_init / v_out [B][H][W][Cout] (either may be NULL).
  * Tensor-core only (bf16 / f16, Cin % 64 == 0, sc_cin % 64 == 0, Cout > 64, T in {1, 2, 4}); other calls
  * return SNNB_ERR_UNSUPPORTED and the caller uses the two-op sequence.
  */
 int snnb_conv3x3_shortcut_lif(const void *x_seq, int64_t x_t_stride, const void *w, const void *b,
-                              const void *sc_x, int64_t sc_t_stride, const void *sc_w,
+                              const void *sc_x, int64_t sc_t_stride, const void *sc_w, const void *sc_b,
                               int sc_cin, int sc_H, int sc_W, int sc_stride,
                               const void *v_init, void *spikes, void *v_out,
                               int T, int B, int Cin, int H, int W, int Cout,

@@ -1,4 +1,6 @@
 """Stateless channels-last helpers against torch on the CPU."""
+import time
+
 import pytest
 import torch
 import torch.nn.functional as F
@@ -72,3 +74,41 @@ def test_avgpool_linear_mean(dtype):
     L.check(L.lib.snnb_avgpool_linear_mean(xd.data_ptr(), wd.data_ptr(), bd.data_ptr(), out.data_ptr(),
                                            T, N, C, H * W, K, L.dtype_code(dtype), None), "head")
     torch.testing.assert_close(out.cpu(), ref, rtol=1e-4, atol=1e-5)
+
+
+@pytest.mark.gpu
+def test_bounded_wait_runs_out_and_reports():
+    """A wait inside the tcgen05 conv kernel that can never complete (a weight tile that is announced but not
+    loaded, limit shortened to about a millisecond) must end by itself: the call returns, the status word says
+    that a wait gave up, and the next call works and leaves the status clean."""
+    from oracle import snn_oracle as orc
+    from triton_snn_fusion_b200 import _lib as L
+    from util import check_parity
+    dtype = torch.bfloat16
+    g = torch.Generator().manual_seed(1)
+    x = (torch.rand(4, 2, 16, 16, 64, generator=g) < 0.2).to(dtype)
+    w = (torch.randn(128, 3, 3, 64, generator=g) * 0.12).to(dtype)
+    b = (torch.randn(128, generator=g) * 0.1).to(dtype)
+    xd, wd, bd = x.cuda(), w.cuda(), b.cuda()
+    spikes = torch.zeros(4, 2, 16, 16, 128, dtype=dtype, device="cuda")
+    v = torch.zeros(2, 16, 16, 128, dtype=dtype, device="cuda")
+
+    def call():
+        L.check(L.lib.snnb_conv_lif(xd.data_ptr(), xd.stride(0), wd.data_ptr(), bd.data_ptr(), None, None,
+                                    spikes.data_ptr(), v.data_ptr(), 4, 2, 64, 16, 16, 128, 3, 3, 1, 1, 1,
+                                    L.BF16, L.BF16, L.BF16, 1.0, 0.0, 2.0, L.PATH_TCGEN05, None), "snnb_conv_lif")
+        torch.cuda.synchronize()
+
+    assert L.device_status() == 0
+    L.check(L.lib.snnb_selftest_arm_wait_timeout(2_000_000), "arm")
+    t0 = time.perf_counter()
+    call()
+    assert time.perf_counter() - t0 < 5.0
+    assert L.device_status() != 0        # reported once ...
+    assert L.device_status() == 0        # ... and cleared by the read
+    call()                               # the hook disarmed itself: a normal run
+    assert L.device_status() == 0
+    rs, rv = orc.temporal_conv_lif([orc.widen(x[t]).permute(0, 3, 1, 2) for t in range(4)],
+                                   orc.widen(w).permute(0, 3, 1, 2), orc.widen(b), None, [1, 1], [1, 1], [1, 1], 1,
+                                   1.0, 0.0, 2.0)
+    check_parity(spikes.permute(0, 1, 4, 2, 3), v.permute(0, 3, 1, 2), rs, rv, dtype, what="after the self-test")

@@ -154,7 +154,7 @@ def test_rejections():
         be.run_triton_fused_temporal_conv_lif_state([x], w[:, :2], b, z, [1, 1], [1, 1], [1, 1], 2, 1.0, 0.0, 2.0, False)
     with pytest.raises(RuntimeError, match="missing_or_unsupported_bias"):
         be.run_triton_fused_temporal_conv_lif_state([x], w, None, z, [1, 1], [1, 1], [1, 1], 1, 1.0, 0.0, 2.0, False)
-    with pytest.raises(RuntimeError, match="cannot dispatch pointwise"):
+    with pytest.raises(RuntimeError, match="was called with a pointwise conv"):
         be.run_triton_fused_temporal_conv_lif_state([x], w[:, :, :1, :1], b, z, [1, 1], [0, 0], [1, 1], 1, 1.0, 0.0, 2.0, False)
     with pytest.raises(RuntimeError, match="non-empty"):
         be.run_triton_fused_temporal_conv_lif_state([], w, b, z, [1, 1], [1, 1], [1, 1], 1, 1.0, 0.0, 2.0, False)

@@ -158,7 +158,7 @@ def test_shortcut_conv_without_lif():
 
 
 def test_config2_layer_properties_full_size():
-    """BASELINE config 2 at full size (T=4, batch 64, 128->128, 56x56, Bernoulli(0.15) spikes): too big for the
+    """The single-layer benchmark shape at full size (T=4, batch 64, 128->128, 56x56, Bernoulli(0.15) spikes): too big for the
     CPU oracle in seconds, so checked through size-independent properties: (a) batch independence - the
     first two images of the batch-64 run equal a batch-2 run (which the oracle checks); (b) window
     chaining - T=4 equals two chained T=2 calls with the membrane handed over."""
@@ -248,3 +248,39 @@ def test_stem_byte_spikes_and_no_membrane_output(hw, alias):
         outs[name] = sp.float().cpu()
     assert torch.equal(outs["wide"], outs["bytes"])
     assert 0.02 < float(outs["wide"].mean()) < 0.6
+
+
+def test_membrane_updated_in_place_on_shifted_tiles():
+    """v_init and v_out as ONE buffer across two chained calls (T = 8 as 4 + 4), on a 28x28 map whose last
+    column strip is shifted back inside the image and with more tiles (12 images x 2 row tiles x 4 strips = 96
+    per channel tile, two channel tiles) than the GPU has SMs, so tiles that recompute each other's pixels run
+    in different waves: every membrane value must still be read and written exactly once per call. Compared
+    with the oracle's single eight-step pass."""
+    from triton_snn_fusion_b200 import _lib as L
+    B, cin, cout, H = 12, 64, 256, 28
+    dtype = torch.bfloat16
+    g = torch.Generator().manual_seed(77)
+    x = (torch.rand(8, B, H, H, cin, generator=g) < 0.2).to(dtype)             # [T][B][H][W][C]
+    w = (torch.randn(cout, 3, 3, cin, generator=g) * 0.12).to(dtype)           # [Cout][KH][KW][Cin]
+    b = (torch.randn(cout, generator=g) * 0.1).to(dtype)
+    rs, rv = orc.temporal_conv_lif([orc.widen(x[t]).permute(0, 3, 1, 2) for t in range(8)],
+                                   orc.widen(w).permute(0, 3, 1, 2), orc.widen(b), None, [1, 1], [1, 1], [1, 1], 1,
+                                   1.0, 0.0, 2.0)
+    xd, wd, bd = x.to(DEV), w.to(DEV), b.to(DEV)
+    spikes = torch.empty(8, B, H, H, cout, dtype=dtype, device=DEV)
+    v = torch.empty(B, H, H, cout, dtype=torch.float32, device=DEV)
+    from triton_snn_fusion_b200.runtime import triton_convlif_backend as be
+    path = be._PATH[be._conv_path]
+    for win in range(2):
+        L.check(L.lib.snnb_conv_lif(xd[4 * win].data_ptr(), xd.stride(0), wd.data_ptr(), bd.data_ptr(), None,
+                                    v.data_ptr() if win else None, spikes[4 * win].data_ptr(), v.data_ptr(),
+                                    4, B, cin, H, H, cout, 3, 3, 1, 1, 1, L.BF16, L.BF16, L.F32, 1.0, 0.0, 2.0, path, None),
+                "snnb_conv_lif")
+    torch.cuda.synchronize()
+    check_parity(spikes.permute(0, 1, 4, 2, 3), v.permute(0, 3, 1, 2), rs, rv, torch.float32, what="in-place membrane")
+    assert float(rs[4:].mean()) > 0.02
+    # two different buffers that overlap are refused before anything is launched
+    st = L.lib.snnb_conv_lif(xd.data_ptr(), xd.stride(0), wd.data_ptr(), bd.data_ptr(), None, v.data_ptr() + 64,
+                             spikes.data_ptr(), v.data_ptr(), 4, B, cin, H, H, cout, 3, 3, 1, 1, 1,
+                             L.BF16, L.BF16, L.F32, 1.0, 0.0, 2.0, path, None)
+    assert st == 1 and b"overlap" in L.lib.snnb_last_error()

@@ -33,7 +33,7 @@ def test_golden(name):
 @pytest.mark.parametrize("T", [1, 2, 3, 4, 8, 16])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
 def test_seeded_vs_oracle(T, dtype):
-    # input distribution of BASELINE config 1: N(0.6, 0.8)
+    # input distribution of the standalone-scan benchmark: N(0.6, 0.8)
     torch.manual_seed(2026 + T)
     shape = (4, 32, 32, 32)  # 2^17 neurons
     x = (torch.randn((T,) + shape) * 0.8 + 0.6).to(dtype)
@@ -81,7 +81,7 @@ def test_channels_last_frames_keep_layout():
 
 
 def test_window_chaining_full_size():
-    """Size-independent property at BASELINE size (T=8, 2^24 neurons): one scan over T=8 equals
+    """Size-independent property at benchmark size (T=8, 2^24 neurons): one scan over T=8 equals
     two chained scans over T=4 with the membrane handed over."""
     torch.manual_seed(5)
     dev = torch.device("cuda")
@@ -108,5 +108,5 @@ def test_rejects_bad_arguments():
         f(x, torch.zeros(2, 3, 4, 5, device=dev), 1.0, 0.0, 2.0, False)
     with pytest.raises(RuntimeError, match="unsupported_tau"):
         f(x, torch.tensor(0.0, device=dev), 1.0, 0.0, 0.0, False)
-    with pytest.raises(RuntimeError, match="not CUDA"):
+    with pytest.raises(RuntimeError, match="unsupported_device"):
         f(x.cpu(), torch.tensor(0.0), 1.0, 0.0, 2.0, False)

@@ -13,12 +13,12 @@ from util import check_parity
 pytestmark = pytest.mark.gpu
 
 
-def _run_net(name, B, T, hw, dtype, classes, path="auto", gain=1.0):
+def _run_net(name, B, T, hw, dtype, classes, path="auto", gain=1.0, fuse_shortcuts=False):
     from triton_snn_fusion_b200 import nets
     spec = nets.NETS[name](classes)
     params = nets.make_params(spec, seed=2026, gain=gain)
     net = nets.CompiledNet(spec, params, batch=B, T=T, in_hw=(hw, hw), dtype=dtype, device="cuda", conv_path=path,
-                           keep_membranes=True, fuse_shortcuts=False)   # every layer's output is compared
+                           keep_membranes=True, fuse_shortcuts=fuse_shortcuts)   # every LIF layer's output is compared
     x = torch.randn(B, 3, hw, hw, generator=torch.Generator().manual_seed(2026)).to(dtype)
     logits = net.forward_nchw(x.cuda()).cpu()
     torch.cuda.synchronize()
@@ -29,12 +29,18 @@ def _run_net(name, B, T, hw, dtype, classes, path="auto", gain=1.0):
 
 
 def _check_layers(spec, net, teacher, layers, dtype):
+    """Every layer against the oracle at the stated bounds (flip rate <= 1e-4, membrane rtol); prints the
+    measured flip rate of every LIF layer and returns the worst."""
     worst = 0.0
     for L in spec:
+        if L["name"] in net.skipped:
+            continue   # a shortcut conv that rides in its consumer's launch: no output of its own
         if L["op"] == "conv" and L["lif"]:
             v = net.membranes[L["name"]].permute(0, 3, 1, 2).cpu()
             rate = check_parity(teacher[L["dst"]], v, layers[L["name"]][0], layers[L["name"]][1], dtype,
-                                flip_max=2e-4, what=L["name"])
+                                what=L["name"])
+            print(f"  {L['name']:12s} {teacher[L['dst']].numel():9d} spikes, flip rate {rate:.2e}, "
+                  f"firing rate {float(teacher[L['dst']].float().mean()):.3f}")
             worst = max(worst, rate)
         elif L["op"] == "conv":
             rtol, atol = (1e-4, 1e-5) if dtype == torch.float32 else (1e-2, 1e-2)
@@ -44,8 +50,9 @@ def _check_layers(spec, net, teacher, layers, dtype):
     return worst
 
 
-def test_cnn_small_fp32_config0():
-    """BASELINE config 0: CNN-small, fp32, T=4, batch 16, 3x32x32."""
+def test_cnn_small_fp32_batch16():
+    """Spiking CNN-small, fp32, T=4, batch 16, 3x32x32 N(0,1) input (the configuration the reference's eager
+    path runs on a CPU)."""
     spec, net, logits, teacher, ref_logits, layers = _run_net("cnn_small", 16, 4, 32, torch.float32, 10)
     _check_layers(spec, net, teacher, layers, torch.float32)
     torch.testing.assert_close(logits, ref_logits, rtol=1e-4, atol=1e-4)
@@ -159,6 +166,21 @@ def test_fused_shortcut_convs_match_the_two_op_sequence(hw):
     assert torch.isfinite(a).all() and torch.isfinite(b).all()
 
 
+@pytest.mark.parametrize("hw,B", [(96, 3), (128, 4)])
+def test_resnet18_fused_shortcuts_against_the_oracle(hw, B):
+    """The executor's default form (strided 1x1 shortcut conv + BN folded into the launch of the 3x3 conv it
+    feeds) layer by layer against the oracle, which adds the un-rounded fp32 shortcut: flip rate <= 1e-4.
+    At 128x128, batch 4, every LIF layer has more than 1e5 outputs, so one flip is below 1e-5."""
+    spec, net, logits, teacher, ref_logits, layers = _run_net("resnet18", B, 4, hw, torch.bfloat16, 100, gain=4.0,
+                                                              fuse_shortcuts=True)
+    assert len(net.fused_sc) == 3 and all(f"l{i}b0.sc" not in teacher for i in (2, 3, 4))
+    worst = _check_layers(spec, net, teacher, layers, torch.bfloat16)
+    assert worst <= 1e-4
+    for name in ("l2b0.out", "l3b0.out", "l4b0.out"):
+        assert float(teacher[name].float().mean()) > 0.01, name
+    torch.testing.assert_close(logits, ref_logits, rtol=2e-2, atol=2e-2)
+
+
 def test_resnet18_with_live_deep_layers():
     """Layer-by-layer (teacher-forced) parity with weights scaled so that all four stages keep spiking."""
     spec, net, logits, teacher, ref_logits, layers = _run_net("resnet18", 3, 4, 96, torch.bfloat16, 100, gain=4.0)
@@ -168,10 +190,14 @@ def test_resnet18_with_live_deep_layers():
     torch.testing.assert_close(logits, ref_logits, rtol=2e-2, atol=2e-2)
 
 
-def test_resnet18_eight_timesteps_as_two_windows():
+@pytest.mark.parametrize("hw,B,fuse", [(64, 2, False), (112, 12, True)])
+def test_resnet18_eight_timesteps_as_two_windows(hw, B, fuse):
     """T = 8 runs as two windows of four steps with the membrane carried in fp32: layer-wise parity with the
-    oracle's single eight-step pass."""
-    spec, net, logits, teacher, ref_logits, layers = _run_net("resnet18", 2, 8, 64, torch.bfloat16, 100, gain=4.0)
+    oracle's single eight-step pass. The 112x112 case has 28x28 and 14x14 maps, whose last column strip is
+    shifted back inside the image, and more tiles per layer than the GPU has SMs (28x28: 12 * 2 * 4 = 192
+    per channel tile), so tiles that recompute each other's pixels run in different waves."""
+    spec, net, logits, teacher, ref_logits, layers = _run_net("resnet18", B, 8, hw, torch.bfloat16, 100, gain=4.0,
+                                                              fuse_shortcuts=fuse)
     assert net.nwin == 2 and net.Tw == 4
     assert all(m.dtype == torch.float32 for m in net.membranes.values())
     _check_layers(spec, net, teacher, layers, torch.bfloat16)

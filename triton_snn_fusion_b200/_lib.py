@@ -25,6 +25,7 @@ SIGNATURES = {
     "snnb_version": (c_int, []),
     "snnb_last_error": (c_char_p, []),
     "snnb_device_status": (c_int, [POINTER(c_int)]),
+    "snnb_selftest_arm_wait_timeout": (c_int, [c_int64]),
     "snnb_lif_scan": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int, c_int, c_int,
                               c_float, c_float, c_float, c_void_p]),
     "snnb_lif_avgpool_linear": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -51,7 +52,7 @@ SIGNATURES = {
     "snnb_nchw_to_nhwc": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_void_p]),
     "snnb_nhwc_to_nchw": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_void_p]),
     "snnb_maxpool3x3s2": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_void_p]),
-    "snnb_conv3x3_shortcut_lif": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_void_p,
+    "snnb_conv3x3_shortcut_lif": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p,
                                           c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
                                           c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                           c_float, c_float, c_float, c_void_p]),

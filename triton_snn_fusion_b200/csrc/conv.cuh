@@ -28,6 +28,7 @@ struct ConvArgs {
   // sc_x at (h * sc_stride, w * sc_stride). Only the timestep-pair kernel implements it.
   const void *sc_x = nullptr;
   const void *sc_w = nullptr;
+  const void *b2 = nullptr;   // bias of the shortcut conv, [Cout] or null: added to b in fp32
   int64_t sc_t_stride = 0;
   int sc_cin = 0, sc_H = 0, sc_W = 0, sc_stride = 1;
 };
@@ -51,6 +52,9 @@ int halo_device_status(int *out);
 bool conv3x3_pair_supported(const ConvArgs &a);
 int conv3x3_pair(const ConvArgs &a, cudaStream_t stream);
 int pair_device_status(int *out);
+// Self-test of the bounded waits (snnb_selftest_arm_wait_timeout): if armed, hands the shortened limit and the
+// "drop one load" switch to the next launch of the timestep-pair kernel and disarms.
+void consume_wait_selftest(long long *limit_cycles, int *drop_load);
 
 // GEMM + LIF stage of the 7x7 / stride 2 stem on the re-laid image (stem.cu): persistent tcgen05 kernel
 // with the packed weight resident in shared memory.

@@ -6,7 +6,18 @@
 namespace snnb {
 namespace {
 
+// v_init and v_out may be one and the same buffer (the membrane is then updated in place, as the reference's
+// in/out membrane buffer is); two different buffers that overlap would be read and written by different threads.
+bool membranes_overlap_partially(const ConvArgs &a) {
+  if (!a.lif || a.v_init == nullptr || a.v_out == nullptr || a.v_init == a.v_out) return false;
+  const size_t bytes = (size_t)a.B * a.Ho * a.Wo * a.Cout * dtype_size(a.v_dtype);
+  const char *p = static_cast<const char *>(a.v_init), *q = static_cast<const char *>(a.v_out);
+  return p < q + bytes && q < p + bytes;
+}
+
 int run(const ConvArgs &a, int path, cudaStream_t stream, const char *what) {
+  if (membranes_overlap_partially(a))
+    return fail(SNNB_ERR_INVALID, "%s: v_init and v_out overlap without being the same buffer", what);
   if (path == SNNB_PATH_SIMT) return conv_lif_simt(a, stream);
   const bool taps_only = path == SNNB_PATH_TCGEN05_TAPS;
   if (!taps_only && path != SNNB_PATH_TCGEN05_HALO && conv3x3_pair_supported(a)) return conv3x3_pair(a, stream);
@@ -50,7 +61,7 @@ extern "C" int snnb_conv_lif(const void *x_seq, int64_t x_t_stride, const void *
 }
 
 extern "C" int snnb_conv3x3_shortcut_lif(const void *x_seq, int64_t x_t_stride, const void *w, const void *b,
-                                         const void *sc_x, int64_t sc_t_stride, const void *sc_w,
+                                         const void *sc_x, int64_t sc_t_stride, const void *sc_w, const void *sc_b,
                                          int sc_cin, int sc_H, int sc_W, int sc_stride,
                                          const void *v_init, void *spikes, void *v_out,
                                          int T, int B, int Cin, int H, int W, int Cout,
@@ -72,13 +83,15 @@ extern "C" int snnb_conv3x3_shortcut_lif(const void *x_seq, int64_t x_t_stride, 
   a.stride = 1; a.pad = 1; a.Ho = H; a.Wo = W; a.lif = 1;
   a.dtype = dtype; a.spike_dtype = spike_dtype; a.v_dtype = v_dtype;
   a.p = make_lif_params(v_th, v_reset, tau);
-  a.sc_x = sc_x; a.sc_w = sc_w; a.sc_t_stride = sc_t_stride;
+  a.sc_x = sc_x; a.sc_w = sc_w; a.b2 = sc_b; a.sc_t_stride = sc_t_stride;
   a.sc_cin = sc_cin; a.sc_H = sc_H; a.sc_W = sc_W; a.sc_stride = sc_stride;
   if (!conv3x3_pair_supported(a))
     return fail(SNNB_ERR_UNSUPPORTED,
                 "conv3x3_shortcut_lif: needs Cin %% 64 == 0, sc_cin %% 64 == 0, Cout > 64, T in {1, 2, 4}, a map of at "
                 "least 8x8 or at most 7x8 and a shortcut input whose strided size equals the output; run the shortcut "
                 "conv and snnb_conv_lif with a residual instead");
+  if (membranes_overlap_partially(a))
+    return fail(SNNB_ERR_INVALID, "conv3x3_shortcut_lif: v_init and v_out overlap without being the same buffer");
   return conv3x3_pair(a, static_cast<cudaStream_t>(stream));
 }
 

@@ -2,7 +2,21 @@
 // routing to the per-dtype translation units.
 #include "conv.cuh"
 
+#include <atomic>
+
 namespace snnb {
+
+namespace {
+std::atomic<long long> g_selftest_limit{0};
+}
+
+void consume_wait_selftest(long long *limit_cycles, int *drop_load) {
+  const long long armed = g_selftest_limit.exchange(0);
+  if (armed > 0) {
+    *limit_cycles = armed;
+    *drop_load = 1;
+  }
+}
 
 int conv3x3_pair_bf16(const ConvArgs &a, cudaStream_t stream);
 int conv3x3_pair_f16(const ConvArgs &a, cudaStream_t stream);
@@ -51,3 +65,10 @@ int pair_device_status(int *out) {
 }
 
 }  // namespace snnb
+
+extern "C" int snnb_selftest_arm_wait_timeout(long long limit_cycles) {
+  using namespace snnb;
+  SNNB_CHECK_ARG(limit_cycles >= 1000 && limit_cycles <= 4000000000ll, "selftest_arm_wait_timeout: limit out of range");
+  g_selftest_limit.store(limit_cycles);
+  return SNNB_OK;
+}

@@ -30,7 +30,7 @@ from typing import Dict, List, Optional, Sequence, Tuple
 import torch
 
 from .. import _lib
-from ._common import (ACT_DTYPES, as_pair, empty_nhwc, is_nhwc_dense, lif_scalars, raise_reasons, stack_frames,
+from ._common import (Gate, as_pair, empty_nhwc, is_nhwc_dense, lif_scalars, raise_reasons, stack_frames,
                       state_or_none, to_nhwc)
 
 
@@ -113,53 +113,47 @@ def classify_conv_lif_runtime_kind(weight, stride, padding, dilation, groups) ->
 
 def check_triton_support(x, weight, bias, v_prev, stride, padding, dilation, groups,
                          v_threshold, v_reset, tau, detach_reset) -> List[str]:
-    """Reasons why this backend cannot take the call (empty list = supported)."""
-    reasons: List[str] = []
-    if not x.is_cuda:
-        reasons.append("unsupported_device: x is not CUDA")
+    """Reasons why this backend cannot take the call (empty list = supported). Same role as the reference's
+    function of this name (runtime/triton_convlif_backend.py:118-211); here bf16 passes and the LIF constants
+    are free."""
+    g = Gate("x", x)
+    if not g:
+        return g.why
+    g.lead_is(rank=4)
     if bias is None:
-        reasons.append("missing_or_unsupported_bias: bias must be a Tensor")
-    if x.dtype not in ACT_DTYPES:
-        reasons.append(f"unsupported_dtype: x dtype must be float32, bfloat16 or float16, got {x.dtype}")
-    if weight.dtype != x.dtype or (bias is not None and bias.dtype != x.dtype):
-        reasons.append(
-            f"unsupported_dtype: x/weight/bias dtypes must match, got x={x.dtype}, weight={weight.dtype}, "
-            f"bias={getattr(bias, 'dtype', None)}")
-    if isinstance(v_prev, torch.Tensor) and v_prev.dim() != 0 and v_prev.dtype not in (x.dtype, torch.float32):
-        reasons.append(f"unsupported_dtype: v_prev dtype must be the x dtype or float32, got {v_prev.dtype}")
-    if x.dim() != 4:
-        reasons.append(f"unsupported_rank: x.dim must be 4, got {x.dim()}")
-    if weight.dim() != 4:
-        reasons.append(f"unsupported_rank: weight.dim must be 4, got {weight.dim()}")
-    if reasons:
-        return reasons
+        g.add("missing_or_unsupported_bias", "the conv carries no bias tensor (a folded BatchNorm always yields one)")
+    else:
+        g.companion("bias", bias)
+    if not g.companion("weight", weight, rank=4):
+        return g.why
+    if g.why:
+        return g.why
     groups = int(groups)
     cin, cout, wcin = int(x.shape[1]), int(weight.shape[0]), int(weight.shape[1])
     depthwise = wcin == 1 and groups == cin == cout and groups > 1
     if groups != 1 and not depthwise:
-        reasons.append(f"unsupported_groups: groups must be 1 or depthwise, got {groups}")
+        g.add("unsupported_groups", f"groups = {groups}: only dense (1) and depthwise (= channels) convs have kernels")
     if groups == 1 and wcin != cin:
-        reasons.append(f"unsupported_shape: weight in_channels {wcin} != x channels {cin}")
+        g.add("unsupported_shape", f"weight reads {wcin} channels, x has {cin}")
     if tuple(as_pair(dilation)) != (1, 1):
-        reasons.append(f"unsupported_dilation: dilation must be (1, 1), got {tuple(as_pair(dilation))}")
+        g.add("unsupported_dilation", f"dilation {tuple(as_pair(dilation))}: only undilated convs have kernels")
     s, p, k = tuple(as_pair(stride)), tuple(as_pair(padding)), tuple(int(d) for d in weight.shape[-2:])
     table = SUPPORTED_CONV_LIF_CONFIGS.get(k)
     if table is None:
-        reasons.append(f"unsupported_kernel: kernel must be one of {tuple(SUPPORTED_CONV_LIF_CONFIGS)}, got {k}")
+        g.add("unsupported_kernel", f"{k[0]}x{k[1]} window; kernels exist for "
+                                    f"{', '.join(f'{a}x{b}' for a, b in SUPPORTED_CONV_LIF_CONFIGS)}")
     elif ((s, p, "depthwise") if depthwise else (s, p)) not in table:
-        strides = sorted({c[0] for c in table if (len(c) == 3) == depthwise})
-        pads = sorted({c[1] for c in table if c[0] == s and (len(c) == 3) == depthwise})
-        if not pads:
-            reasons.append(f"unsupported_stride: {k[0]}x{k[1]} kernel supports stride {strides}, got {s}")
+        same_kind = [c for c in table if (len(c) == 3) == depthwise]
+        if not any(c[0] == s for c in same_kind):
+            g.add("unsupported_stride", f"{k[0]}x{k[1]} window with stride {s}; implemented: "
+                                        f"{sorted({c[0] for c in same_kind})}")
         else:
-            reasons.append(f"unsupported_padding: {k[0]}x{k[1]} kernel with stride {s} supports padding {pads}, got {p}")
-    if float(tau) == 0.0:
-        reasons.append("unsupported_tau: tau must be nonzero")
-    if not reasons and isinstance(v_prev, torch.Tensor) and v_prev.dim() != 0:
-        out_shape = _conv2d_output_shape(x, weight, stride, padding, dilation)
-        if tuple(v_prev.shape) != tuple(out_shape):
-            reasons.append(f"v_prev shape {tuple(v_prev.shape)} does not match conv output shape {out_shape}")
-    return reasons
+            g.add("unsupported_padding", f"{k[0]}x{k[1]} window, stride {s}, padding {p}; implemented: "
+                                         f"{sorted({c[1] for c in same_kind if c[0] == s})}")
+    g.tau(tau)
+    if not g.why:
+        g.state(v_prev, _conv2d_output_shape(x, weight, stride, padding, dilation), fp32_ok=True)
+    return g.why
 
 
 # ------------------------------------------------------------------ weights ----
@@ -205,19 +199,16 @@ def _stem_weight(weight: torch.Tensor, dt: int) -> torch.Tensor:
 
 
 def _validate_kind(kind: str, key: str) -> None:
-    if kind == "regular" and key.startswith("depthwise_"):
-        raise RuntimeError(f"regular conv op cannot dispatch depthwise kernel {key}")
-    if kind == "regular" and key == "k1_s1_p0":
-        raise RuntimeError("regular conv op cannot dispatch pointwise kernel k1_s1_p0")
-    if kind == "pointwise" and key != "k1_s1_p0":
-        raise RuntimeError(f"pointwise conv op requires k1_s1_p0 kernel, got {key}")
-    if kind == "depthwise" and not key.startswith("depthwise_"):
-        raise RuntimeError(f"depthwise conv op requires depthwise kernel, got {key}")
+    """An op that names its conv kind (regular / pointwise / depthwise) must be handed a conv of that kind."""
+    actual = "depthwise" if key.startswith("depthwise_") else ("pointwise" if key == "k1_s1_p0" else "regular")
+    if kind != actual:
+        raise RuntimeError(f"the {kind} conv + LIF op was called with a {actual} conv (kernel key {key})")
 
 
 def _launch(x_base, x_t_stride, T, weight, bias, residual, v_init, stride, padding, groups, v_threshold, v_reset, tau,
-            spikes, v_next, lif=True, spike_dtype=None, v_dtype=None):
-    """One C-ABI call. x_base: [B,Cin,H,W] channels-last frame 0; outputs are channels-last buffers."""
+            spikes, v_next, lif=True, spike_dtype=None, v_dtype=None, t0=0):
+    """One C-ABI call over timesteps t0 .. t0 + T - 1. x_base: [B,Cin,H,W] channels-last frame 0; ``residual`` and
+    ``spikes`` are dense channels-last stacks whose frame t0 is where this call starts."""
     B, Cin, H, W = (int(d) for d in x_base.shape)
     Cout, _, KH, KW = (int(d) for d in weight.shape)
     s = as_pair(stride)[0]
@@ -227,6 +218,11 @@ def _launch(x_base, x_t_stride, T, weight, bias, residual, v_init, stride, paddi
     sdt = _lib.dtype_code(spike_dtype or x_base.dtype)
     vdt = _lib.dtype_code(v_dtype or x_base.dtype)
     stream = _lib.current_stream(x_base.device)
+    x_ptr = _lib.ptr(x_base) + t0 * x_t_stride * x_base.element_size()
+    s_ptr = _lib.ptr(spikes) + t0 * spikes.stride(0) * spikes.element_size() if t0 else _lib.ptr(spikes)
+    r_ptr = _lib.ptr(residual)
+    if residual is not None and t0:
+        r_ptr += t0 * residual.numel() * residual.element_size()
     if (groups == 1 and lif and residual is None and Cin == 3 and KH == 7 and KW == 7 and s == 2 and p == 3
             and x_base.dtype in (torch.bfloat16, torch.float16) and H % 2 == 0 and W % 2 == 0 and Cout % 16 == 0
             and _conv_path != "simt"):
@@ -237,7 +233,7 @@ def _launch(x_base, x_t_stride, T, weight, bias, residual, v_init, stride, paddi
         scratch = torch.empty(nbytes, dtype=torch.uint8, device=x_base.device)
         _lib.check(
             _lib.lib.snnb_stem7x7_lif(
-                _lib.ptr(x_base), x_t_stride, _lib.ptr(wp), _lib.ptr(bias), _lib.ptr(v_init), _lib.ptr(spikes),
+                x_ptr, x_t_stride, _lib.ptr(wp), _lib.ptr(bias), _lib.ptr(v_init), s_ptr,
                 _lib.ptr(v_next), _lib.ptr(scratch), nbytes, T, B, H, W, Cout, dt, sdt, vdt, th, vr, ta, stream),
             "snnb_stem7x7_lif")
         return
@@ -245,17 +241,45 @@ def _launch(x_base, x_t_stride, T, weight, bias, residual, v_init, stride, paddi
         w = _packed_weight(weight)
         _lib.check(
             _lib.lib.snnb_conv_lif(
-                _lib.ptr(x_base), x_t_stride, _lib.ptr(w), _lib.ptr(bias), _lib.ptr(residual), _lib.ptr(v_init),
-                _lib.ptr(spikes), _lib.ptr(v_next), T, B, Cin, H, W, Cout, KH, KW, s, p, 1 if lif else 0,
+                x_ptr, x_t_stride, _lib.ptr(w), _lib.ptr(bias), r_ptr, _lib.ptr(v_init),
+                s_ptr, _lib.ptr(v_next), T, B, Cin, H, W, Cout, KH, KW, s, p, 1 if lif else 0,
                 dt, sdt, vdt, th, vr, ta, _PATH[_conv_path], stream),
             "snnb_conv_lif")
     else:
         w = weight.contiguous()
         _lib.check(
             _lib.lib.snnb_dwconv3x3_lif(
-                _lib.ptr(x_base), x_t_stride, _lib.ptr(w), _lib.ptr(bias), _lib.ptr(residual), _lib.ptr(v_init),
-                _lib.ptr(spikes), _lib.ptr(v_next), T, B, Cin, H, W, s, dt, sdt, vdt, th, vr, ta, stream),
+                x_ptr, x_t_stride, _lib.ptr(w), _lib.ptr(bias), r_ptr, _lib.ptr(v_init),
+                s_ptr, _lib.ptr(v_next), T, B, Cin, H, W, s, dt, sdt, vdt, th, vr, ta, stream),
             "snnb_dwconv3x3_lif")
+
+
+# Sequences longer than the four timesteps the fastest dense-conv kernel keeps in tensor memory run as windows
+# of four with the membrane handed over in fp32: the same arithmetic as one pass over all T (the membrane is
+# fp32 inside a kernel too), where the reference loops its windows inside the kernel
+# (kernels/benchmark_conv_lif_temporal_general.py:649).
+WINDOW = 4
+
+
+def _windowed(T, x_t_stride, groups, dtype) -> bool:
+    return (T > WINDOW and T % WINDOW == 0 and x_t_stride != 0 and groups == 1 and _conv_path == "auto"
+            and dtype in (torch.bfloat16, torch.float16))
+
+
+def _launch_windows(x_base, x_t_stride, T, weight, bias, residual, v_init, stride, padding, v_threshold, v_reset, tau,
+                    spikes, v_next):
+    """T = n * WINDOW timesteps as n chained calls; v_init / v_next keep the dtype the caller gave them."""
+    shape = v_next.permute(0, 2, 3, 1).shape   # channels-last memory order
+    carry = [torch.empty(shape, dtype=torch.float32, device=x_base.device).permute(0, 3, 1, 2) for _ in range(2)]
+    v_in = None
+    if v_init is not None:
+        carry[1].copy_(v_init)
+        v_in = carry[1]
+    for w in range(T // WINDOW):
+        _launch(x_base, x_t_stride, WINDOW, weight, bias, residual, v_in, stride, padding, 1, v_threshold, v_reset, tau,
+                spikes, carry[w % 2], v_dtype=torch.float32, t0=w * WINDOW)
+        v_in = carry[w % 2]
+    v_next.copy_(v_in)   # one rounding to the membrane dtype, as at the end of a single pass
 
 
 def _diagnostics(dtype, key, copied, residual=False):
@@ -345,15 +369,21 @@ def _run_temporal(kind, xs, residuals, weight, bias, v_init, stride, padding, di
     else:
         spikes = empty_nhwc([T, B, cout, ho, wo], first.dtype, first.device)
         v_next = empty_nhwc([B, cout, ho, wo], v_dtype, first.device)
-    _launch(x_base, x_stride, T, weight, bias, res_base, v0, stride, padding, int(groups), v_threshold, v_reset, tau,
-            spikes, v_next, v_dtype=v_dtype)
+    windowed = _windowed(T, x_stride, int(groups), first.dtype)
+    if windowed:
+        _launch_windows(x_base, x_stride, T, weight, bias, res_base, v0, stride, padding, v_threshold, v_reset, tau,
+                        spikes, v_next)
+    else:
+        _launch(x_base, x_stride, T, weight, bias, res_base, v0, stride, padding, int(groups), v_threshold, v_reset,
+                tau, spikes, v_next, v_dtype=v_dtype)
     if spike_out is not None and not direct_out:
         spike_out.copy_(spikes)
         v_out.copy_(v_next)
         spikes, v_next = spike_out, v_out
     return TritonConvLIFResult(
         spikes, v_next, True, kernel_key=key,
-        kernel_temporal_config={"BTILE_T": T, "REUSE_GROUPS": 1, "implementation": "snnb200"},
+        kernel_temporal_config={"BTILE_T": WINDOW if windowed else T, "REUSE_GROUPS": 1,
+                                "kernel_temporal_window": WINDOW if windowed else T, "implementation": "snnb200"},
         kernel_diagnostics=_diagnostics(first.dtype, key, copied, residuals is not None))
 
 

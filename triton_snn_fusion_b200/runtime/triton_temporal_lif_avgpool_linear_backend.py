@@ -15,7 +15,7 @@ from typing import Dict, List, Optional
 import torch
 
 from .. import _lib
-from ._common import ACT_DTYPES, is_nhwc_dense, lif_scalars, raise_reasons, state_or_none
+from ._common import Gate, is_nhwc_dense, lif_scalars, raise_reasons, state_or_none
 
 
 @dataclass
@@ -33,38 +33,25 @@ def strict_temporal_lif_avgpool_linear_enabled(strict: bool = False) -> bool:
 
 
 def check_temporal_lif_avgpool_linear_support(x_seq, v_init, fc_weight, fc_bias, tau) -> List[str]:
-    reasons: List[str] = []
-    if not isinstance(x_seq, torch.Tensor):
-        return ["x_seq must be a tensor"]
-    if not x_seq.is_cuda:
-        reasons.append("unsupported_device: x_seq is not CUDA")
-    if x_seq.dim() != 5:
-        reasons.append(f"unsupported_rank: x_seq.dim must be 5, got {x_seq.dim()}")
-    if x_seq.dtype not in ACT_DTYPES:
-        reasons.append(f"unsupported_dtype: x_seq dtype must be float32, bfloat16 or float16, got {x_seq.dtype}")
-    if not isinstance(v_init, torch.Tensor):
-        reasons.append("v_init must be a tensor")
-    elif v_init.dim() != 0:
-        if x_seq.dim() == 5 and tuple(v_init.shape) != tuple(x_seq.shape[1:]):
-            reasons.append(
-                f"unsupported_membrane_state: v_init shape {tuple(v_init.shape)} does not match {tuple(x_seq.shape[1:])}")
-        if v_init.device != x_seq.device or v_init.dtype != x_seq.dtype:
-            reasons.append("unsupported_dtype: v_init device/dtype must match x_seq")
-    if not isinstance(fc_weight, torch.Tensor) or fc_weight.dim() != 2:
-        reasons.append("fc_weight must be a 2D tensor")
-    elif x_seq.dim() == 5:
-        if int(fc_weight.shape[1]) != int(x_seq.shape[2]):
-            reasons.append(f"unsupported_linear: fc in_features {fc_weight.shape[1]} must match channels {x_seq.shape[2]}")
-        if fc_weight.device != x_seq.device or fc_weight.dtype != x_seq.dtype:
-            reasons.append("unsupported_dtype: fc_weight device/dtype must match x_seq")
+    """Reasons why the tail kernel cannot take this call (empty = it can). Same role as the reference's function
+    of this name (runtime/triton_temporal_lif_avgpool_linear_backend.py:22-55); any T >= 1 passes here."""
+    g = Gate("x_seq", x_seq)
+    if not g:
+        return g.why
+    g.lead_is(rank=5)
+    g.state(v_init, tuple(x_seq.shape[1:]) if x_seq.dim() == 5 else None)
+    classes = None
+    if g.companion("fc_weight", fc_weight, rank=2, code="unsupported_linear"):
+        classes = int(fc_weight.shape[0])
+        if x_seq.dim() == 5 and int(fc_weight.shape[1]) != int(x_seq.shape[2]):
+            g.add("unsupported_linear", f"fc_weight reads {int(fc_weight.shape[1])} features, the pooled map has "
+                                        f"{int(x_seq.shape[2])} channels")
     if isinstance(fc_bias, torch.Tensor) and fc_bias.numel() > 0:
-        if isinstance(fc_weight, torch.Tensor) and fc_bias.numel() != fc_weight.shape[0]:
-            reasons.append("unsupported_linear: fc_bias shape does not match out_features")
-        if fc_bias.device != x_seq.device or fc_bias.dtype != x_seq.dtype:
-            reasons.append("unsupported_dtype: fc_bias device/dtype must match x_seq")
-    if float(tau) == 0.0:
-        reasons.append("unsupported_tau: tau must be nonzero")
-    return reasons
+        if classes is not None and fc_bias.numel() != classes:
+            g.add("unsupported_linear", f"fc_bias holds {fc_bias.numel()} values for {classes} classes")
+        g.companion("fc_bias", fc_bias)
+    g.tau(tau)
+    return g.why
 
 
 def run_triton_fused_temporal_lif_avgpool_linear(x_seq, v_init, fc_weight, fc_bias, v_threshold, v_reset, tau,

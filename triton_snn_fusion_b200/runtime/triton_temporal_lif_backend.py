@@ -16,7 +16,7 @@ from typing import Dict, List, Optional
 import torch
 
 from .. import _lib
-from ._common import ACT_DTYPES, lif_scalars, raise_reasons, state_or_none
+from ._common import Gate, lif_scalars, raise_reasons, state_or_none
 
 
 @dataclass
@@ -35,29 +35,17 @@ def strict_temporal_lif_enabled(strict: bool = False) -> bool:
 
 
 def check_temporal_lif_support(x_seq, v_init, v_threshold, v_reset, tau, detach_reset) -> List[str]:
-    reasons: List[str] = []
-    if not isinstance(x_seq, torch.Tensor):
-        return ["x_seq must be a tensor"]
-    if not x_seq.is_cuda:
-        reasons.append("unsupported_device: x_seq is not CUDA")
-    if x_seq.dim() != 5:
-        reasons.append(f"unsupported_rank: x_seq.dim must be 5, got {x_seq.dim()}")
-    if x_seq.dtype not in ACT_DTYPES:
-        reasons.append(f"unsupported_dtype: x_seq dtype must be float32, bfloat16 or float16, got {x_seq.dtype}")
+    """Reasons why the scan cannot take this call (empty = it can). Same role as the reference's function of
+    this name (runtime/triton_temporal_lif_backend.py:23-54); bf16 and any T >= 1 pass here."""
+    g = Gate("x_seq", x_seq)
+    if not g:
+        return g.why
+    g.lead_is(rank=5)
     if x_seq.dim() >= 1 and int(x_seq.shape[0]) < 1:
-        reasons.append("unsupported_temporal_length: T must be >= 1")
-    if not isinstance(v_init, torch.Tensor):
-        reasons.append("v_init must be a tensor")
-    elif v_init.dim() != 0:
-        if x_seq.dim() == 5 and tuple(v_init.shape) != tuple(x_seq.shape[1:]):
-            reasons.append(
-                f"unsupported_membrane_state: v_init shape {tuple(v_init.shape)} does not match {tuple(x_seq.shape[1:])}")
-        if v_init.device != x_seq.device or v_init.dtype != x_seq.dtype:
-            reasons.append(
-                f"unsupported_dtype: v_init device/dtype must match x_seq, got {v_init.device}/{v_init.dtype}")
-    if float(tau) == 0.0:
-        reasons.append("unsupported_tau: tau must be nonzero")
-    return reasons
+        g.add("unsupported_temporal_length", "x_seq holds no timestep")
+    g.state(v_init, tuple(x_seq.shape[1:]) if x_seq.dim() == 5 else None)
+    g.tau(tau)
+    return g.why
 
 
 def _same_dense_layout(x_seq: torch.Tensor, v: Optional[torch.Tensor]) -> bool:

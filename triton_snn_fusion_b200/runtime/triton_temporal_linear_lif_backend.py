@@ -15,7 +15,7 @@ from typing import Dict, List, Optional
 import torch
 
 from .. import _lib
-from ._common import ACT_DTYPES, lif_scalars, raise_reasons, state_or_none
+from ._common import Gate, lif_scalars, raise_reasons, state_or_none
 from .triton_convlif_backend import _PATH
 from . import triton_convlif_backend as _conv
 
@@ -36,40 +36,25 @@ def strict_temporal_linear_lif_enabled(strict: bool = False) -> bool:
 
 
 def check_temporal_linear_lif_support(x_seq, weight, bias, v_init, v_threshold, v_reset, tau, detach_reset) -> List[str]:
-    reasons: List[str] = []
-    if not isinstance(x_seq, torch.Tensor):
-        return ["x_seq must be a tensor"]
-    if not x_seq.is_cuda:
-        reasons.append("unsupported_device: x_seq is not CUDA")
-    if x_seq.dim() != 3:
-        reasons.append(f"unsupported_rank: x_seq.dim must be 3, got {x_seq.dim()}")
-    if x_seq.dtype not in ACT_DTYPES:
-        reasons.append(f"unsupported_dtype: x_seq dtype must be float32, bfloat16 or float16, got {x_seq.dtype}")
-    if not isinstance(weight, torch.Tensor):
-        reasons.append("weight must be a tensor")
-    elif weight.dim() != 2:
-        reasons.append(f"unsupported_weight_rank: weight.dim must be 2, got {weight.dim()}")
-    elif weight.device != x_seq.device or weight.dtype != x_seq.dtype:
-        reasons.append(f"unsupported_dtype: weight device/dtype must match x_seq, got {weight.device}/{weight.dtype}")
-    elif x_seq.dim() == 3 and int(weight.shape[1]) != int(x_seq.shape[2]):
-        reasons.append(f"unsupported_shape: weight in_features {int(weight.shape[1])} != x_seq {int(x_seq.shape[2])}")
+    """Reasons why the linear + LIF kernel cannot take this call (empty = it can). Same role as the reference's
+    function of this name (runtime/triton_temporal_linear_lif_backend.py:23-71)."""
+    g = Gate("x_seq", x_seq)
+    if not g:
+        return g.why
+    g.lead_is(rank=3)
+    n_out = None
+    if g.companion("weight", weight, rank=2, code="unsupported_weight_rank"):
+        n_out = int(weight.shape[0])
+        if x_seq.dim() == 3 and int(weight.shape[1]) != int(x_seq.shape[2]):
+            g.add("unsupported_shape", f"weight reads {int(weight.shape[1])} features per token, x_seq has "
+                                       f"{int(x_seq.shape[2])}")
     if isinstance(bias, torch.Tensor) and bias.numel() > 0:
-        if isinstance(weight, torch.Tensor) and (bias.dim() != 1 or int(bias.shape[0]) != int(weight.shape[0])):
-            reasons.append(f"unsupported_bias: bias shape {tuple(bias.shape)} does not match out_features")
-        if bias.device != x_seq.device or bias.dtype != x_seq.dtype:
-            reasons.append(f"unsupported_dtype: bias device/dtype must match x_seq, got {bias.device}/{bias.dtype}")
-    if not isinstance(v_init, torch.Tensor):
-        reasons.append("v_init must be a tensor")
-    elif v_init.dim() != 0:
-        if x_seq.dim() == 3 and isinstance(weight, torch.Tensor) and weight.dim() == 2:
-            expected = (int(x_seq.shape[1]), int(weight.shape[0]))
-            if tuple(v_init.shape) != expected:
-                reasons.append(f"unsupported_membrane_state: v_init shape {tuple(v_init.shape)} does not match {expected}")
-        if v_init.device != x_seq.device or v_init.dtype not in (x_seq.dtype, torch.float32):
-            reasons.append(f"unsupported_dtype: v_init device/dtype must match x_seq, got {v_init.device}/{v_init.dtype}")
-    if float(tau) == 0.0:
-        reasons.append("unsupported_tau: tau must be nonzero")
-    return reasons
+        if n_out is not None and tuple(bias.shape) != (n_out,):
+            g.add("unsupported_bias", f"bias is {tuple(bias.shape)}, one value per output feature would be ({n_out},)")
+        g.companion("bias", bias)
+    g.state(v_init, (int(x_seq.shape[1]), n_out) if (x_seq.dim() == 3 and n_out is not None) else None, fp32_ok=True)
+    g.tau(tau)
+    return g.why
 
 
 def _impl(x_seq, weight, bias, v_init, v_threshold, v_reset, tau, detach_reset, strict, verbose,
@@ -105,12 +90,33 @@ def _impl(x_seq, weight, bias, v_init, v_threshold, v_reset, tau, detach_reset, 
     spikes = spike_out.view(T, M, N) if use_out else torch.empty((T, M, N), dtype=x_seq.dtype, device=x_seq.device)
     v_next = v_out.view(M, N) if use_out else torch.empty((M, N), dtype=v_dtype, device=x_seq.device)
     th, vr, ta = lif_scalars(v_threshold, v_reset, tau)
-    _lib.check(
-        _lib.lib.snnb_linear_lif(
-            _lib.ptr(x_seq), x_stride, _lib.ptr(weight), _lib.ptr(b), _lib.ptr(v0), _lib.ptr(spikes), _lib.ptr(v_next),
-            T, M, K, N, _lib.dtype_code(x_seq.dtype), _lib.dtype_code(x_seq.dtype), _lib.dtype_code(v_dtype),
-            th, vr, ta, _PATH[_conv._conv_path], _lib.current_stream(x_seq.device)),
-        "snnb_linear_lif")
+    dt = _lib.dtype_code(x_seq.dtype)
+    stream = _lib.current_stream(x_seq.device)
+
+    def call(t0, steps, v_in, v_to, v_dt):
+        _lib.check(
+            _lib.lib.snnb_linear_lif(
+                _lib.ptr(x_seq) + t0 * x_stride * x_seq.element_size(), x_stride, _lib.ptr(weight), _lib.ptr(b),
+                _lib.ptr(v_in), _lib.ptr(spikes) + t0 * M * N * spikes.element_size(), _lib.ptr(v_to),
+                steps, M, K, N, dt, dt, _lib.dtype_code(v_dt), th, vr, ta, _PATH[_conv._conv_path], stream),
+            "snnb_linear_lif")
+
+    # Longer sequences as windows of four timesteps (what the fastest GEMM kernel keeps in tensor memory) with the
+    # membrane handed over in fp32: the arithmetic of a single pass.
+    windowed = (T > _conv.WINDOW and T % _conv.WINDOW == 0 and _conv._conv_path == "auto"
+                and x_seq.dtype in (torch.bfloat16, torch.float16))
+    if windowed:
+        carry = [torch.empty((M, N), dtype=torch.float32, device=x_seq.device) for _ in range(2)]
+        v_in = None
+        if v0 is not None:
+            carry[1].copy_(v0)
+            v_in = carry[1]
+        for w in range(T // _conv.WINDOW):
+            call(w * _conv.WINDOW, _conv.WINDOW, v_in, carry[w % 2], torch.float32)
+            v_in = carry[w % 2]
+        v_next.copy_(v_in)
+    else:
+        call(0, T, v0, v_next, v_dtype)
     if isinstance(spike_out, torch.Tensor) and not use_out:
         spike_out.copy_(spikes.reshape(spike_out.shape))
         v_out.copy_(v_next.reshape(v_out.shape))
@@ -126,6 +132,7 @@ def _impl(x_seq, weight, bias, v_init, v_threshold, v_reset, tau, detach_reset, 
         "stack_materialized": stack_materialized,
         "flattened_leading_dims": spike_shape is not None,
         "T": T, "M": M, "K": K, "N": N,
+        "kernel_temporal_window": _conv.WINDOW if windowed else T,
     }
     return TritonTemporalLinearLIFResult(
         spikes=spikes, v_next=v_next, used_triton=True, kernel_key="temporal_linear_lif",
