@@ -284,3 +284,25 @@ def test_membrane_updated_in_place_on_shifted_tiles():
                              spikes.data_ptr(), v.data_ptr(), 4, B, cin, H, H, cout, 3, 3, 1, 1, 1,
                              L.BF16, L.BF16, L.F32, 1.0, 0.0, 2.0, path, None)
     assert st == 1 and b"overlap" in L.lib.snnb_last_error()
+
+
+@pytest.mark.parametrize("case", [(2, 32, 64, 28, 28), (2, 96, 128, 16, 16), (3, 40, 192, 14, 14)])
+def test_pointwise_conv_with_a_partial_channel_slab(case):
+    """1x1 convs whose input channels are not a multiple of 64 (MobileNet's first pointwise layer reads 32): the
+    timestep-pair kernel completes the last 64-channel slab of both operands with zeros."""
+    be = _conv_be()
+    if be._conv_path != "tcgen05":
+        pytest.skip("only the timestep-pair kernel takes partial slabs")
+    B, cin, cout, H, W = case
+    T, dtype = 4, torch.bfloat16
+    torch.manual_seed(cin + cout)
+    xs = [(torch.rand(B, cin, H, W) < 0.2).to(dtype) for _ in range(T)]
+    w = (torch.randn(cout, cin, 1, 1) * (2.0 / cin) ** 0.5 * 2).to(dtype)
+    b = (torch.randn(cout) * 0.1).to(dtype)
+    rs, rv = orc.temporal_conv_lif([orc.widen(x) for x in xs], orc.widen(w), orc.widen(b), None,
+                                   [1, 1], [0, 0], [1, 1], 1, 1.0, 0.0, 2.0)
+    r = be.run_triton_fused_temporal_pointwise_conv_lif_state(
+        [x.to(DEV) for x in xs], w.to(DEV), b.to(DEV), torch.tensor(0.0, device=DEV, dtype=dtype),
+        [1, 1], [0, 0], [1, 1], 1, 1.0, 0.0, 2.0, False, strict=True)
+    check_parity(r.spikes, r.v_next, rs, rv, dtype, what=str(case))
+    assert 0.02 < float(rs.mean()) < 0.7

@@ -70,5 +70,6 @@ struct StemGemmArgs {
 bool stem_gemm_supported(const StemGemmArgs &a);
 int stem_gemm_lif(const StemGemmArgs &a, cudaStream_t stream);
 int stem_device_status(int *out);
+int dw_device_status(int *out);   // depthwise tile kernel (dwconv_tile.cu)
 
 }  // namespace snnb

@@ -31,7 +31,11 @@ bool conv3x3_pair_supported(const ConvArgs &a) {
   const bool k3s2 = a.KH == 3 && a.KW == 3 && a.stride == 2 && a.pad == 1 && a.Cout > 64 && a.H >= 2 && a.W >= 2;
   if (!k3 && !k1 && !k3s2) return false;
   if (a.sc_x != nullptr && !k3) return false;
-  if (a.Cin % 64 != 0) return false;
+  // input channels come in slabs of 64; a last slab that is only partly inside the tensor is completed with
+  // zeros by the TMA copies of both operands (activations and weights), so any multiple of 8 channels (the
+  // 16-byte granularity of a copy) works, at the price of multiplying the zeros
+  if (a.Cin % 8 != 0) return false;
+  if (a.Cin % 64 != 0 && (a.KH != 1 || a.sc_x != nullptr)) return false;   // only the 1x1 form has been checked on partial slabs
   if (a.x_t_stride == 0 && a.T > 1) return false;   // one frame for all steps: left to the other kernels
   if (a.T != 1 && a.T != 2 && a.T != 4) return false;
   // maps of at least 8 x 8 (one image per tile) or at most 7 x 8 (two images per tile, Cout > 64); what lies

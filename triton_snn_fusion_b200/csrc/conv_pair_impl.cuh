@@ -557,7 +557,7 @@ int launch(const ConvArgs &a, cudaStream_t stream) {
   g.T = a.T;
   g.Tacc = (a.x_t_stride == 0) ? 1 : a.T;
   g.B = a.B; g.Cin = a.Cin; g.Cout = a.Cout; g.Ho = a.Ho; g.Wo = a.Wo;
-  g.kslabs = a.Cin / 64;
+  g.kslabs = (a.Cin + 63) / 64;
   g.ntaps = a.KH * a.KW;
   g.s2 = a.stride == 2 ? 1 : 0;
   g.tq = g.Tacc >= 2 ? 2 : 1;

@@ -433,7 +433,10 @@ extern "C" int snnb_device_status(int *status_out) {
   int h4 = 0;
   const int rc4 = stem_device_status(&h4);
   if (rc4 != SNNB_OK) return rc4;
-  *status_out = h | h2 | h3 | h4;
+  int h5 = 0;
+  const int rc5 = dw_device_status(&h5);
+  if (rc5 != SNNB_OK) return rc5;
+  *status_out = h | h2 | h3 | h4 | h5;
   return SNNB_OK;
 }
 

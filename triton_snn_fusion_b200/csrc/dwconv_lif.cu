@@ -11,6 +11,14 @@
 #include "common.cuh"
 
 namespace snnb {
+
+// shared-memory tile kernel (dwconv_tile.cu): preferred whenever it applies
+bool dwconv_tile_supported(const void *x, int64_t xts, const void *res, const void *v_init, const void *spikes,
+                           const void *v_out, int C, int H, int W, int dtype);
+int dwconv_tile(const void *x, int64_t xts, const void *w, const void *b, const void *res, const void *v_init,
+                void *spikes, void *v_out, int T, int B, int C, int H, int W, int stride, int dtype, int spike_dtype,
+                int v_dtype, const LifParams &p, cudaStream_t stream);
+
 namespace {
 
 constexpr int NT = 128;
@@ -52,7 +60,7 @@ dwconv3x3_lif_kernel(const XT *__restrict__ x, int64_t x_t_stride, const XT *__r
 #pragma unroll
   for (int s = 0; s < S; ++s) {
     if (v_init != nullptr && wo0 + s < Wo) {
-      load_pack<VT, VEC>(v_init + (orow + wo0 + s) * C + c0, v[s]);
+      load_pack_stream<VT, VEC>(v_init + (orow + wo0 + s) * C + c0, v[s]);
     } else {
 #pragma unroll
       for (int i = 0; i < VEC; ++i) v[s][i] = 0.f;
@@ -213,7 +221,7 @@ dwconv3x3_lif_fast_kernel(const XT *__restrict__ x, int64_t x_t_stride, const XT
 #pragma unroll
   for (int s = 0; s < SS; ++s) {
     if (v_init != nullptr && wo0 + s < Wo) {
-      load_pack<VT, 4>(v_init + (orow + wo0 + s) * C + c0, v[s]);
+      load_pack_stream<VT, 4>(v_init + (orow + wo0 + s) * C + c0, v[s]);
     } else {
 #pragma unroll
       for (int i = 0; i < 4; ++i) v[s][i] = 0.f;
@@ -363,6 +371,14 @@ extern "C" int snnb_dwconv3x3_lif(const void *x_seq, int64_t x_t_stride, const v
   SNNB_CHECK_ARG(tau != 0.0f, "dwconv3x3_lif: unsupported_tau: tau must be nonzero");
   const LifParams p = make_lif_params(v_th, v_reset, tau);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (v_init != nullptr && v_init != v_out) {
+    const size_t bytes = (size_t)B * ((H - 1) / stride + 1) * ((W - 1) / stride + 1) * C * dtype_size(v_dtype);
+    const char *pi = static_cast<const char *>(v_init), *po = static_cast<const char *>(v_out);
+    SNNB_CHECK_ARG(!(pi < po + bytes && po < pi + bytes), "dwconv3x3_lif: v_init and v_out overlap without being the same buffer");
+  }
+  if (dwconv_tile_supported(x_seq, x_t_stride, residual, v_init, spikes, v_out, C, H, W, dtype))
+    return dwconv_tile(x_seq, x_t_stride, w, b, residual, v_init, spikes, v_out, T, B, C, H, W, stride, dtype, spike_dtype,
+                       v_dtype, p, s);
 #define SNNB_ARGS x_seq, x_t_stride, w, b, residual, v_init, spikes, v_out, T, B, C, H, W, stride, spike_dtype, v_dtype, p, s
   switch (dtype) {
     case SNNB_F32: return dispatch<float>(SNNB_ARGS);

@@ -73,7 +73,7 @@ __device__ __forceinline__ void staged_tile(const StemGeom &g, const LifParams &
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
       float tmp[16];
-      load_pack<VT, 16>(v_init + o0 + q * 16, tmp);
+      load_pack_stream<VT, 16>(v_init + o0 + q * 16, tmp);
 #pragma unroll
       for (int i = 0; i < 16; ++i) v[q * 16 + i] = tmp[i];
     }

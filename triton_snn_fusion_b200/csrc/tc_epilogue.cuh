@@ -51,7 +51,7 @@ __device__ __forceinline__ void epilogue_cols(const EpiArgs<XT, ST, VT> &e, cons
 #pragma unroll
     for (int i = 0; i < 16; ++i) v[i] = 0.f;
     const long long o0 = e.pix * g.Cout + n;
-    if (LIFON && e.v_init != nullptr && e.valid) load_pack<VT, 16>(e.v_init + o0, v);
+    if (LIFON && e.v_init != nullptr && e.valid) load_pack_stream<VT, 16>(e.v_init + o0, v);
     for (int t = 0; t < g.T; ++t) {
       float y[16];
       umma::tmem_ld_wait();

@@ -11,8 +11,8 @@ Each case builds seeded synthetic spikes/currents on the GPU (larger than L2 at 
 warms the op up three times, times `--reps` launches with CUDA events and prints the algorithmic
 GB/s and TFLOP/s. With `--reps 1` it is the small case a profiler is pointed at.
 
-The conv case follows the workload of the reference's operator benchmark
-(benchmarks/bench_kernel_fusion.py: conv + folded BN + LIF over T steps, binary spike inputs).
+The conv case follows the workload of the reference's conv + LIF kernel benchmark
+(benchmarks/benchmark_fused_convlif_kernel_configs.py: conv + folded BN + LIF over T steps).
 """
 from __future__ import annotations
 
@@ -91,22 +91,23 @@ def case_lif(a):
 
 def case_dw(a):
     dt = torch.bfloat16
+    ho = (a.hw - 1) // a.s + 1
     g = torch.Generator(device=DEV).manual_seed(0)
     x = (torch.rand(a.T, a.B, a.hw, a.hw, a.c, device=DEV, generator=g) < 0.2).to(dt)
     w = (torch.randn(a.c, 3, 3, device=DEV, generator=g) * 0.3).to(dt)
     b = torch.zeros(a.c, device=DEV, dtype=dt)
-    sp = torch.empty_like(x)
-    v = torch.empty(a.B, a.hw, a.hw, a.c, device=DEV, dtype=dt)
+    sp = torch.empty(a.T, a.B, ho, ho, a.c, device=DEV, dtype=dt)
+    v = torch.empty(a.B, ho, ho, a.c, device=DEV, dtype=dt)
 
     def call():
         _lib.check(_lib.lib.snnb_dwconv3x3_lif(x.data_ptr(), x.stride(0), w.data_ptr(), b.data_ptr(), None, None,
-                                               sp.data_ptr(), v.data_ptr(), a.T, a.B, a.c, a.hw, a.hw, 1,
+                                               sp.data_ptr(), v.data_ptr(), a.T, a.B, a.c, a.hw, a.hw, a.s,
                                                1, 1, 1, *LIF, _stream()), "snnb_dwconv3x3_lif")
 
     ms = _time(call, a.reps)
     nbytes = 2 * (x.numel() + sp.numel() + v.numel())
-    print(f"dwconv3x3_lif B{a.B} C{a.c} {a.hw}^2 T{a.T} bf16: {ms:.4f} ms  {nbytes / ms / 1e6:.0f} GB/s  "
-          f"spike rate {float(sp.float().mean()):.3f}")
+    print(f"dwconv3x3_lif B{a.B} C{a.c} {a.hw}^2 s{a.s} T{a.T} bf16: {ms:.4f} ms  {nbytes / ms / 1e6:.0f} GB/s  "
+          f"spike rate {float(sp.float().mean()):.3f}  device status {_lib.device_status()}")
 
 
 def case_tail(a):
@@ -198,6 +199,7 @@ def main(argv=None):
     d.add_argument("--B", type=int, default=32)
     d.add_argument("--c", type=int, default=128)
     d.add_argument("--hw", type=int, default=56)
+    d.add_argument("--s", type=int, default=1)
     d.set_defaults(fn=case_dw)
     t = sub.add_parser("tail")
     t.add_argument("--B", type=int, default=256)

@@ -102,6 +102,16 @@ class CompiledNet:
                     and L["src"] == "input" and self._is_tc_stem(L, H, W) and L["cout"] == 64
                     and sum(1 for M in spec if M.get("src") == L["dst"] or M.get("residual") == L["dst"]) == 1):
                 self.u8_bufs.add(L["dst"])
+        # With several windows, what does not carry state from window to window runs ONCE over all T steps: the
+        # stem on the (time-invariant) input frame, whose conv is evaluated once anyway, a max-pool fed by such a
+        # layer, and the head.
+        self.whole_seq = set()
+        if self.nwin > 1:
+            for L in spec:
+                if L["op"] == "conv" and L["src"] == "input" and self._is_tc_stem(L, H, W):
+                    self.whole_seq.add(L["dst"])
+                elif L["op"] == "maxpool" and L["src"] in self.whole_seq:
+                    self.whole_seq.add(L["dst"])
         for L in spec:
             h, w_, c = self.shapes[L["src"]]
             if L["op"] == "conv":
@@ -111,7 +121,7 @@ class CompiledNet:
                     continue
                 self.bufs[L["dst"]] = torch.empty((self.T, self.B, ho, wo, L["cout"]), device=self.device,
                                                   dtype=torch.uint8 if L["dst"] in self.u8_bufs else dtype)
-                if L["lif"] and (keep_membranes or L["groups"] != 1 or self.nwin > 1):
+                if L["lif"] and (keep_membranes or L["groups"] != 1 or (self.nwin > 1 and L["dst"] not in self.whole_seq)):
                     # dense convs can skip the final membrane (v_out = NULL); the depthwise kernel always writes it;
                     # several windows carry it in fp32 through two buffers used alternately (window w reads the one
                     # window w - 1 wrote), which keeps every tile of the conv kernel on its unpredicated path
@@ -130,8 +140,6 @@ class CompiledNet:
                 self.logits = torch.empty((self.B, L["classes"]), dtype=torch.float32, device=self.device)
             elif L["op"] == "head":
                 self.logits = torch.empty((self.B, L["classes"]), dtype=torch.float32, device=self.device)
-                if self.nwin > 1:
-                    self.logits_w = torch.empty((self.nwin, self.B, L["classes"]), dtype=torch.float32, device=self.device)
         self._calls = self._plan()
         self.launches_per_forward = (len(self._calls) + self.extra_launches
                                      + (1 if any(L["op"] == "tail" for L in spec) else 0))
@@ -151,17 +159,25 @@ class CompiledNet:
         for win, L in ((wi, L) for wi in range(self.nwin) for L in self.spec):
             if L["name"] in self.skipped:
                 continue
+            T = self.Tw
+            if L.get("dst") in self.whole_seq or (L["op"] == "head" and self.nwin > 1):
+                if win != (self.nwin - 1 if L["op"] == "head" else 0):
+                    continue
+                T = self.T   # all steps in one launch
+            first = 0 if T == self.T else win * T   # first timestep this launch covers
 
-            def at(name):   # address of this window's first frame of a [T, ...] activation buffer
+            def at(name, first=first):   # address of frame `first` of a [T, ...] activation buffer
                 buf = self.bufs[name]
-                return buf.data_ptr() if name == "input" else buf.data_ptr() + win * T * buf.stride(0) * buf.element_size()
+                return buf.data_ptr() if name == "input" else buf.data_ptr() + first * buf.stride(0) * buf.element_size()
 
-            def v_in(name):   # membrane left by the previous window
-                return self._vbufs[name][(win - 1) % 2].data_ptr() if win > 0 else None
+            def v_in(name, T=T):   # membrane left by the previous window
+                return self._vbufs[name][(win - 1) % 2].data_ptr() if (win > 0 and T != self.T) else None
 
-            def v_of(name):   # where this window leaves the membrane (None: not kept)
+            def v_of(name, T=T):   # where this launch leaves the membrane (None: not kept)
                 if name not in self._vbufs:
                     return None
+                if T == self.T:
+                    return self.membranes[name].data_ptr()
                 return self._vbufs[name][win % len(self._vbufs[name])].data_ptr()
 
             src = self.bufs[L["src"]]
@@ -225,8 +241,8 @@ class CompiledNet:
                 calls.append((lib.snnb_lif_avgpool_linear, args, L["name"]))
             elif L["op"] == "head":
                 wt = self.weights[L["name"]]
-                out = self.logits_w[win].data_ptr() if self.nwin > 1 else self.logits.data_ptr()
-                args = (at(L["src"]), wt["w"].data_ptr(), wt["b"].data_ptr(), out, T, B, c, h * w_, L["classes"], dt)
+                args = (at(L["src"]), wt["w"].data_ptr(), wt["b"].data_ptr(), self.logits.data_ptr(), T, B, c, h * w_,
+                        L["classes"], dt)
                 calls.append((lib.snnb_avgpool_linear_mean, args, L["name"]))
         return calls
 
@@ -236,8 +252,6 @@ class CompiledNet:
             st = fn(*args, stream)
             if st != 0:
                 _lib.check(st, f"layer {name}")
-        if self.nwin > 1:   # the head wrote one mean per window
-            torch.mean(self.logits_w, dim=0, out=self.logits)
         if hasattr(self, "tail_sum"):
             # the tail returns sum_t logits in the compute dtype; the network output is their mean
             torch.mul(self.tail_sum, 1.0 / float(self.T), out=self.logits)
