@@ -295,7 +295,7 @@ def run_ours(args):
         if L["groups"] != 1:
             return "dwconv3x3_lif"
         if L["cin"] == 3:
-            return "stem (s2d + stem_gemm_lif)" if L["k"] == 7 else "conv_lif_simt (3-channel stem)"
+            return "stem (s2d + stem_gemm_lif)" if L["k"] == 7 else "conv3x3_smallcin (3-channel stem)"
         ho, wo, _ = net.shapes[L["dst"]]
         if L["k"] == 1 and L["s"] == 1 and L["cin"] % 64 == 0 and ((ho >= 8 and wo >= 8) or (ho <= 7 and wo <= 8 and L["cout"] > 64)):
             return "conv3x3_pair"   # 1x1 convs run through the same kernel (centre tap only)

@@ -58,7 +58,7 @@ typedef enum snnb_layout { SNNB_NCHW = 0, SNNB_NHWC = 1 } snnb_layout;
  * the shape qualifies (16-bit activations, Cin a multiple of 64, see
  * snnb_conv_lif) and the CUDA-core path otherwise. TCGEN05 insists on a tensor-core
  * kernel (error if none applies). Among the tensor-core kernels, 3x3 / stride 1 /
- * padding 1 convs prefer the timestep-pair kernel (T = 1, 2, 4; weights as the M
+ * padding 1 convs prefer the timestep-pair kernel (T = 1 or even; weights as the M
  * operand, 256 pixels as N), then the shared-memory halo kernel; TCGEN05_HALO skips
  * the first, TCGEN05_TAPS forces the general one-load-per-tap kernel (for comparison). */
 typedef enum snnb_path {
@@ -178,7 +178,7 @@ int snnb_conv_lif(const void *x_seq, int64_t x_t_stride, const void *w, const vo
  *   of the shortcut conv (or NULL); the two biases are widened to fp32 before they are added;
  *   output pixel (h, w) adds sc_w . sc_x[h * sc_stride][w * sc_stride]; (sc_H - 1) / sc_stride + 1 == H.
  *   spikes [T][B][H][W][Cout], v_init / v_out [B][H][W][Cout] (either may be NULL).
- * Tensor-core only (bf16 / f16, Cin % 64 == 0, sc_cin % 64 == 0, Cout > 64, T in {1, 2, 4}); other calls
+ * Tensor-core only (bf16 / f16, Cin % 64 == 0, sc_cin % 64 == 0, Cout > 64, T = 1 or even); other calls
  * return SNNB_ERR_UNSUPPORTED and the caller uses the two-op sequence.
  */
 int snnb_conv3x3_shortcut_lif(const void *x_seq, int64_t x_t_stride, const void *w, const void *b,

@@ -47,6 +47,7 @@ CASES = [
     (3, 64, 3, 1, 1, 1, 32, 32),     # CNN-small layer 1
     (64, 128, 3, 2, 1, 1, 32, 32),   # CNN-small layer 2
     (128, 256, 3, 2, 1, 1, 16, 16),  # CNN-small layer 3
+    (3, 32, 3, 2, 1, 1, 30, 34),     # MobileNet stem (direct kernel for few input channels)
     (3, 64, 7, 2, 3, 1, 64, 64),     # ResNet stem
     (64, 64, 1, 1, 0, 1, 14, 14),    # pointwise
     (24, 40, 5, 1, 2, 1, 13, 11),    # k5 key, ragged channels

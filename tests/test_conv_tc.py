@@ -37,7 +37,8 @@ def _lin_be():
 
 
 @pytest.mark.parametrize("shape", [(4, 128, 64, 64), (4, 256, 128, 128), (4, 300, 192, 80), (1, 128, 64, 16),
-                                   (8, 200, 128, 128), (16, 130, 64, 64), (4, 4096, 768, 3072)])
+                                   (8, 200, 128, 128), (16, 130, 64, 64), (4, 4096, 768, 3072), (8, 256, 128, 128),
+                                   (68, 128, 64, 64)])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 def test_linear(shape, dtype):
     T, M, K, N = shape
@@ -115,8 +116,10 @@ def test_conv(case, residual):
     assert 0.01 < float(rs.mean()) < 0.7
 
 
-@pytest.mark.parametrize("T", [1, 2, 8, 16])
+@pytest.mark.parametrize("T", [1, 2, 6, 8, 12, 16, 72])
 def test_conv_other_window_lengths(T):
+    """Sequence lengths other than four: one launch for T = 1 and any even T up to 64 (timestep pairs alternate
+    between two accumulators), windows of four with an fp32 membrane hand-over beyond that (T = 72)."""
     B, cin, cout, H, W = 2, 64, 128, 14, 14
     dtype = torch.bfloat16
     torch.manual_seed(T)

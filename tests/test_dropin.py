@@ -298,8 +298,8 @@ def test_lowered_neighbours_match_aten(dtype):
     mean, var = (torch.randn(128, generator=g) * 0.1).to(dtype).cuda(), (torch.rand(128, generator=g) + 0.5).to(dtype).cuda()
     gamma, beta = (torch.rand(128, generator=g) + 0.5).to(dtype).cuda(), (torch.randn(128, generator=g) * 0.1).to(dtype).cuda()
     got = fx._guarded_shortcut(fx._FoldedShortcut())(x, w, [2, 2], [0, 0], mean, var, gamma, beta, 1e-5)
-    want = F.batch_norm(torch.conv2d(x.float(), w.float(), None, 2, 0), mean.float(), var.float(), gamma.float(),
-                        beta.float(), False, 0.0, 1e-5)
+    cpu = lambda t: t.float().cpu()   # on the CPU: cuDNN would run the fp32 conv in TF32
+    want = F.batch_norm(torch.conv2d(cpu(x), cpu(w), None, 2, 0), cpu(mean), cpu(var), cpu(gamma), cpu(beta), False, 0.0, 1e-5)
     tol = 2e-2 if dtype == torch.bfloat16 else 1e-4
-    torch.testing.assert_close(got.float(), want, rtol=tol, atol=tol)
+    torch.testing.assert_close(got.float().cpu(), want, rtol=tol, atol=tol)
     assert tuple(got.shape) == (8, 128, 14, 14)

@@ -13,12 +13,12 @@ from util import check_parity
 pytestmark = pytest.mark.gpu
 
 
-def _run_net(name, B, T, hw, dtype, classes, path="auto", gain=1.0, fuse_shortcuts=False):
+def _run_net(name, B, T, hw, dtype, classes, path="auto", gain=1.0, fuse_shortcuts=False, window=None):
     from triton_snn_fusion_b200 import nets
     spec = nets.NETS[name](classes)
     params = nets.make_params(spec, seed=2026, gain=gain)
     net = nets.CompiledNet(spec, params, batch=B, T=T, in_hw=(hw, hw), dtype=dtype, device="cuda", conv_path=path,
-                           keep_membranes=True, fuse_shortcuts=fuse_shortcuts)   # every LIF layer's output is compared
+                           keep_membranes=True, fuse_shortcuts=fuse_shortcuts, window=window)   # every LIF layer's output is compared
     x = torch.randn(B, 3, hw, hw, generator=torch.Generator().manual_seed(2026)).to(dtype)
     logits = net.forward_nchw(x.cuda()).cpu()
     torch.cuda.synchronize()
@@ -190,16 +190,20 @@ def test_resnet18_with_live_deep_layers():
     torch.testing.assert_close(logits, ref_logits, rtol=2e-2, atol=2e-2)
 
 
-@pytest.mark.parametrize("hw,B,fuse", [(64, 2, False), (112, 12, True)])
-def test_resnet18_eight_timesteps_as_two_windows(hw, B, fuse):
-    """T = 8 runs as two windows of four steps with the membrane carried in fp32: layer-wise parity with the
-    oracle's single eight-step pass. The 112x112 case has 28x28 and 14x14 maps, whose last column strip is
-    shifted back inside the image, and more tiles per layer than the GPU has SMs (28x28: 12 * 2 * 4 = 192
-    per channel tile), so tiles that recompute each other's pixels run in different waves."""
+@pytest.mark.parametrize("hw,B,fuse,window", [(64, 2, False, 4), (112, 12, True, 4), (112, 12, True, None), (64, 2, False, None)])
+def test_resnet18_eight_timesteps(hw, B, fuse, window):
+    """T = 8 in one launch per layer (the conv kernel alternates timestep pairs between two accumulators) and as
+    two windows of four steps with the membrane carried in fp32: layer-wise parity with the oracle's single
+    eight-step pass. The 112x112 case has 28x28 and 14x14 maps, whose last column strip is shifted back inside
+    the image, and more tiles per layer than the GPU has SMs (28x28: 12 * 2 * 4 = 192 per channel tile), so
+    tiles that recompute each other's pixels run in different waves."""
     spec, net, logits, teacher, ref_logits, layers = _run_net("resnet18", B, 8, hw, torch.bfloat16, 100, gain=4.0,
-                                                              fuse_shortcuts=fuse)
-    assert net.nwin == 2 and net.Tw == 4
-    assert all(m.dtype == torch.float32 for m in net.membranes.values())
+                                                              fuse_shortcuts=fuse, window=window)
+    if window:
+        assert net.nwin == 2 and net.Tw == 4
+        assert all(m.dtype == torch.float32 for m in net.membranes.values())
+    else:
+        assert net.nwin == 1 and net.Tw == 8
     _check_layers(spec, net, teacher, layers, torch.bfloat16)
-    assert float(teacher["l3b1.out"][4:].float().mean()) > 0.01      # the second window is alive too
+    assert float(teacher["l3b1.out"][4:].float().mean()) > 0.01      # the second half is alive too
     torch.testing.assert_close(logits, ref_logits, rtol=2e-2, atol=2e-2)

@@ -234,7 +234,8 @@ int head(const void *x, const void *w, const void *b, float *out, int T, int N, 
     while (PG > 1 && (size_t)PG * SB * C * sizeof(float) > 48 * 1024) --PG;
   }
   const int gx = (N + SB - 1) / SB;
-  int ks = (2 * 148 + gx - 1) / gx;   // class chunks: about two CTAs per SM in flight
+  const int sms = sm_count() > 0 ? sm_count() : 128;
+  int ks = (2 * sms + gx - 1) / gx;   // class chunks: about two CTAs per SM in flight
   ks = ks < 1 ? 1 : (ks > 8 ? 8 : ks);
   const int Kc = (K + ks - 1) / ks;
   const size_t smem = (size_t)PG * SB * C * sizeof(float);

@@ -25,6 +25,17 @@ int fail(int code, const char *fmt, ...) {
 
 const char *last_error() { return g_err; }
 
+int sm_count() {
+  static int cached[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+  if (dev >= 0 && dev < 64 && cached[dev] > 0) return cached[dev];
+  int n = 0;
+  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n < 1) return 0;
+  if (dev >= 0 && dev < 64) cached[dev] = n;
+  return n;
+}
+
 LifParams make_lif_params(float v_th, float v_reset, float tau) {
   LifParams p;
   p.v_th = v_th;

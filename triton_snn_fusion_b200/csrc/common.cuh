@@ -30,6 +30,9 @@ int fail(int code, const char *fmt, ...);
       return ::snnb::fail(SNNB_ERR_CUDA, "%s: launch failed: %s", name, cudaGetErrorString(e__)); \
   } while (0)
 
+// Number of SMs of the current device (queried once per device; 0 if the query fails).
+int sm_count();
+
 inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 inline int dtype_size(int dt) { return dt == SNNB_F32 ? 4 : (dt == SNNB_U8 ? 1 : 2); }
 inline bool is_act_dtype(int dt) { return dt == SNNB_F32 || dt == SNNB_BF16 || dt == SNNB_F16; }

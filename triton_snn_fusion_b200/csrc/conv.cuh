@@ -36,6 +36,10 @@ struct ConvArgs {
 // CUDA-core implicit GEMM (any shape, fp32 accumulate).
 int conv_lif_simt(const ConvArgs &a, cudaStream_t stream);
 
+// Direct CUDA-core kernel for 3x3 convs over images with at most four channels (the first layer of a network).
+bool conv_smallcin_supported(const ConvArgs &a);
+int conv_smallcin(const ConvArgs &a, cudaStream_t stream);
+
 // tcgen05 / TMEM implicit GEMM fed by TMA. `why` receives the reason when unsupported.
 bool conv_lif_tc_supported(const ConvArgs &a, const char **why);
 int conv_lif_tc(const ConvArgs &a, cudaStream_t stream);
@@ -46,7 +50,7 @@ bool conv3x3_halo_supported(const ConvArgs &a);
 int conv3x3_halo(const ConvArgs &a, cudaStream_t stream);
 int halo_device_status(int *out);
 
-// tcgen05 implicit GEMM for 3x3 / stride 1 / padding 1, T in {1, 2, 4}: weights as the M operand and
+// tcgen05 implicit GEMM for 3x3 (stride 1 or 2) and 1x1 convs, T = 1 or even: weights as the M operand and
 // the pixels of two timesteps as a 256-wide N operand (the only shape that runs the tensor pipe at
 // its full rate), halo tiles in shared memory. Preferred over conv3x3_halo when supported.
 bool conv3x3_pair_supported(const ConvArgs &a);

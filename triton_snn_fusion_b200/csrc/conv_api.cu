@@ -18,6 +18,7 @@ bool membranes_overlap_partially(const ConvArgs &a) {
 int run(const ConvArgs &a, int path, cudaStream_t stream, const char *what) {
   if (membranes_overlap_partially(a))
     return fail(SNNB_ERR_INVALID, "%s: v_init and v_out overlap without being the same buffer", what);
+  if (path == SNNB_PATH_AUTO && conv_smallcin_supported(a)) return conv_smallcin(a, stream);   // RGB first layers
   if (path == SNNB_PATH_SIMT) return conv_lif_simt(a, stream);
   const bool taps_only = path == SNNB_PATH_TCGEN05_TAPS;
   if (!taps_only && path != SNNB_PATH_TCGEN05_HALO && conv3x3_pair_supported(a)) return conv3x3_pair(a, stream);
@@ -87,7 +88,7 @@ extern "C" int snnb_conv3x3_shortcut_lif(const void *x_seq, int64_t x_t_stride, 
   a.sc_cin = sc_cin; a.sc_H = sc_H; a.sc_W = sc_W; a.sc_stride = sc_stride;
   if (!conv3x3_pair_supported(a))
     return fail(SNNB_ERR_UNSUPPORTED,
-                "conv3x3_shortcut_lif: needs Cin %% 64 == 0, sc_cin %% 64 == 0, Cout > 64, T in {1, 2, 4}, a map of at "
+                "conv3x3_shortcut_lif: needs Cin %% 64 == 0, sc_cin %% 64 == 0, Cout > 64, T = 1 or even, a map of at "
                 "least 8x8 or at most 7x8 and a shortcut input whose strided size equals the output; run the shortcut "
                 "conv and snnb_conv_lif with a residual instead");
   if (membranes_overlap_partially(a))

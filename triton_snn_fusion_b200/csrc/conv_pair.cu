@@ -37,7 +37,9 @@ bool conv3x3_pair_supported(const ConvArgs &a) {
   if (a.Cin % 8 != 0) return false;
   if (a.Cin % 64 != 0 && (a.KH != 1 || a.sc_x != nullptr)) return false;   // only the 1x1 form has been checked on partial slabs
   if (a.x_t_stride == 0 && a.T > 1) return false;   // one frame for all steps: left to the other kernels
-  if (a.T != 1 && a.T != 2 && a.T != 4) return false;
+  // T = 1, or an even number of steps: they are processed as pairs that alternate between two accumulators in
+  // tensor memory while the membrane stays in registers, so any number of pairs fits
+  if (a.T != 1 && (a.T % 2 != 0 || a.T > 64)) return false;
   // maps of at least 8 x 8 (one image per tile) or at most 7 x 8 (two images per tile, Cout > 64); what lies
   // in between goes to conv_halo.cu
   const bool one_image = a.Ho >= 8 && a.Wo >= 8;

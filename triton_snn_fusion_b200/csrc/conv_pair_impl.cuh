@@ -1,4 +1,4 @@
-// 3x3 / stride 1 / padding 1 conv (+ bias, + residual) + LIF over T <= 4 with the operand roles
+// 3x3 / stride 1 / padding 1 conv (+ bias, + residual) + LIF over T steps (T = 1 or even) with the operand roles
 // swapped so that one tcgen05.mma covers 256 output pixels.
 //
 // Measured on B200: a tcgen05.mma (cta_group::1, K = 16) occupies the tensor pipe for ~128 cycles
@@ -20,10 +20,10 @@
 // uses row groups 0..6 and image b + 1 groups 8..14, each loaded as a box of 9 halo rows (rows 0..8 and
 // 8..16 of the region; rows 8 and 16 are zero padding shared with the neighbour).
 //
-// Timestep pairs are processed one after the other: pair 0 (t = 0, 1) is accumulated over all slabs
-// and taps into TMEM columns 0..255, then pair 1 into 256..511. The epilogue warps convert pair 0
-// (bias, residual, LIF steps 0 and 1, spikes out) while the MMA warp works on pair 1, keep the membrane
-// potentials in registers, and finish with pair 1. TMEM lane = output channel, so a thread owns one
+// Timestep pairs are processed one after the other and alternate between two accumulators: pair 0 (t = 0, 1)
+// is accumulated over all slabs and taps into TMEM columns 0..255, pair 1 into 256..511, pair 2 into 0..255
+// again, and so on for any even T. The epilogue warps convert pair p (bias, residual, two LIF steps, spikes out)
+// while the MMA warp works on pair p + 1 and keep the membrane potentials in registers over all pairs of a tile. TMEM lane = output channel, so a thread owns one
 // channel of 64 pixels and a warp's stores cover 32 consecutive channels of one pixel.
 #pragma once
 #include <type_traits>
@@ -395,11 +395,15 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
       bool ok = true;
       for (int tile = blockIdx.x; tile < g.total_tiles && ok; tile += gridDim.x, ++it) {
         for (int pair = 0; pair < g.npairs && ok; ++pair) {
-          // the epilogue warps must have drained this accumulator (previous tile) before it is overwritten
-          ok = umma::mbar_wait(accempty(pair), (it & 1u) ^ 1u, abort_flag, wl);
+          // Timestep pairs alternate between the two accumulators (columns 0..255 and 256..511). `use` counts
+          // how often this accumulator has been filled so far: even pairs use the first one, odd pairs the second.
+          const uint32_t acc = (uint32_t)(pair & 1);
+          const uint32_t use = it * (uint32_t)((g.npairs + 1 - (int)acc) >> 1) + (uint32_t)(pair >> 1);
+          // the epilogue warps must have drained this accumulator (its previous use) before it is overwritten
+          ok = umma::mbar_wait(accempty(acc), (use & 1u) ^ 1u, abort_flag, wl);
           if (!ok) break;
           umma::tc_fence_after_sync();
-          const uint32_t d = tmem_base + (uint32_t)(pair * 256);
+          const uint32_t d = tmem_base + acc * 256u;
           for (int sp = 0; sp < g.kslabs * (S2 ? 4 : 1) && ok; ++sp) {
             const int ph = S2 ? sp & 3 : 0;
             ok = umma::mbar_wait(hfull(slot), phase, abort_flag, wl);
@@ -449,7 +453,7 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
             umma::mma_commit(hempty(slot));
             if (++slot == (uint32_t)g.ring) { slot = 0; phase ^= 1u; }
           }
-          if (ok) umma::mma_commit(accfull(pair));
+          if (ok) umma::mma_commit(accfull(acc));
         }
       }
     }
@@ -501,12 +505,14 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
             v[i] = DT<VT>::to_f(v_init[pm.row0_off + (long long)(i >> 3) * pm.row_stride + (i & 7) * pm.Cout]);
       }
       for (int pair = 0; pair < g.npairs && ok; ++pair) {
-        if (lane == 0) ok = umma::mbar_wait(accfull(pair), it & 1u, abort_flag, wl);
+        const uint32_t acc = (uint32_t)(pair & 1);
+        const uint32_t use = it * (uint32_t)((g.npairs + 1 - (int)acc) >> 1) + (uint32_t)(pair >> 1);
+        if (lane == 0) ok = umma::mbar_wait(accfull(acc), use & 1u, abort_flag, wl);
         ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
         if (!ok) break;
         umma::tc_fence_after_sync();
         const long long toff = (long long)(pair * g.tq) * frame_out;
-        const uint32_t taddr = lane_base + (uint32_t)(pair * 256);
+        const uint32_t taddr = lane_base + acc * 256u;
         ST *out = spikes + toff;
         const XT *rs = nullptr;   // the residual was already added by the tensor cores
         const int rows_valid = min(my_rows, row_limit);   // rows 14, 15 of a one-image tile never exist
@@ -531,7 +537,7 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
         // this accumulator may now be overwritten by the next tile's MMAs
         umma::tc_fence_before_sync();
         __syncwarp();
-        if (lane == 0) umma::mbar_arrive(accempty(pair));
+        if (lane == 0) umma::mbar_arrive(accempty(acc));
       }
       if (ok && g.lif && v_out != nullptr) {
 #pragma unroll
@@ -566,7 +572,7 @@ int launch(const ConvArgs &a, cudaStream_t stream) {
   g.stack = (a.Ho <= 7 && a.Wo <= 8) ? 1 : 0;
   g.row_tiles = (a.Ho + kTileRows - 1) / kTileRows;
   g.w_strips = (a.Wo + 7) / 8;
-  g.tmem_cols = g.npairs * 256 > 256 ? 512 : (g.tq == 2 ? 256 : 128);
+  g.tmem_cols = g.npairs >= 2 ? 512 : (g.tq == 2 ? 256 : 128);
   g.lif = a.lif;
   g.sc_slabs = a.sc_x != nullptr ? a.sc_cin / 64 : 0;
   g.has_res = a.res != nullptr || g.sc_slabs > 0;

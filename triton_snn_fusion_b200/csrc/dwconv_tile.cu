@@ -35,7 +35,7 @@ struct DwGeom {
   int ns;        // strips per tile row: 1 or 2
   int rows;      // output rows per tile = threads / (cs / 4 * ns)
   int hw, hr;    // halo tile: columns, rows
-  int nct, nrt, nslab;
+  int nct, nrt, nslab, total_tiles;
   int tx_bytes;    // size of one halo tile = bytes one copy delivers
   int buf_pitch;   // distance between the two buffers (tx_bytes rounded up to 128)
 };
@@ -66,27 +66,34 @@ template <> struct Vec4<__half> {
   }
 };
 
-// one LIF step on two channels; FAST: tau a power of two and hard reset (the common case), with the charge
-// step on the packed fp32 pipe. h = v + (y - v) * inv_tau is evaluated as three separately rounded operations
-// exactly as lif_step does (x - v and x + (-v) round identically).
-template <bool FAST>
+// one LIF step on two channels. KIND 0: any LIF (run-time lif_step); 1: tau a power of two and hard reset, with the
+// charge step on the packed fp32 pipe; 2: additionally v_reset == 0, where the reset is one packed multiply-add.
+// h = v + (y - v) * inv_tau is evaluated as three separately rounded operations exactly as lif_step does
+// (x - v and x + (-v) round identically); with s in {0, 1}, h - s * h is exactly 0 or h.
+template <int KIND>
 __device__ __forceinline__ float2 lif2(float2 y, float2 &v, const LifParams &p) {
   float2 s;
-  if constexpr (FAST) {
-    const float2 d = __fadd2_rn(y, make_float2(-v.x, -v.y));
-    const float2 h = __fadd2_rn(v, __fmul2_rn(d, make_float2(p.inv_tau, p.inv_tau)));
-    const bool s0 = h.x >= p.v_th, s1 = h.y >= p.v_th;
-    v.x = s0 ? p.v_reset : h.x;
-    v.y = s1 ? p.v_reset : h.y;
-    s = make_float2(s0 ? 1.f : 0.f, s1 ? 1.f : 0.f);
-  } else {
+  if constexpr (KIND == 0) {
     s.x = lif_step(y.x, v.x, p);
     s.y = lif_step(y.y, v.y, p);
+  } else {
+    const float2 d = __fadd2_rn(y, make_float2(-v.x, -v.y));
+    const float2 h = __fadd2_rn(v, __fmul2_rn(d, make_float2(p.inv_tau, p.inv_tau)));
+    s = make_float2(h.x >= p.v_th ? 1.f : 0.f, h.y >= p.v_th ? 1.f : 0.f);
+    if constexpr (KIND == 2) {
+      v = __ffma2_rn(make_float2(-s.x, -s.y), h, h);
+    } else {
+      v.x = s.x != 0.f ? p.v_reset : h.x;
+      v.y = s.y != 0.f ? p.v_reset : h.y;
+    }
   }
   return s;
 }
 
-template <typename XT, typename ST, typename VT, int STRIDE, int PW, bool FAST>
+// Persistent: a block walks tiles blockIdx.x, blockIdx.x + gridDim.x, ... and treats (tile, timestep) pairs as one
+// stream of work items, so the copy of the next item - the next timestep, or the first timestep of the next tile -
+// always runs under the arithmetic of the current one and only the very first copy of a block is exposed.
+template <typename XT, typename ST, typename VT, int STRIDE, int PW, int KIND>
 __global__ void __launch_bounds__(kDwThreads, PW <= 4 ? 2 : 1)
 dwconv_tile_kernel(const __grid_constant__ CUtensorMap xmap, const XT *__restrict__ w, const XT *__restrict__ bias,
                    const XT *__restrict__ res, const VT *v_init, ST *__restrict__ spikes, VT *v_out,
@@ -98,19 +105,31 @@ dwconv_tile_kernel(const __grid_constant__ CUtensorMap xmap, const XT *__restric
   const uint32_t bar = umma::smem_u32(full);
   volatile int *abort_flag = &abort_s;
 
-  int idx = blockIdx.x;
-  const int ct = idx % g.nct; idx /= g.nct;
-  const int rt = idx % g.nrt; idx /= g.nrt;
-  const int slab = idx % g.nslab;
-  const int b = idx / g.nslab;
   const int cg_n = g.cs >> 2;
   const int tid = threadIdx.x;
   const int cg = tid % cg_n;
   const int strip = (tid / cg_n) % g.ns;
   const int row = tid / (cg_n * g.ns);
-  const int ho = rt * g.rows + row;
-  const int wo0 = (ct * g.ns + strip) * PW;
-  const int c = slab * g.cs + cg * 4;
+
+  // tile index -> (column tile, row tile, image, channel block); the channel block is slowest, so a block's
+  // consecutive tiles nearly always share their weights
+  auto decode = [&](int tile, int &ct, int &rt, int &b, int &slab) {
+    ct = tile % g.nct; tile /= g.nct;
+    rt = tile % g.nrt; tile /= g.nrt;
+    b = tile % g.B;
+    slab = tile / g.B;
+  };
+  const int my_tiles = (int)blockIdx.x < g.total_tiles ? (g.total_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+  const int n_items = my_tiles * g.T;
+  auto issue = [&](int item) {   // one thread: start the copy of work item `item` into buffer item & 1
+    int ct, rt, b, slab;
+    decode((int)blockIdx.x + (item / g.T) * (int)gridDim.x, ct, rt, b, slab);
+    const int t = item - (item / g.T) * g.T;
+    const uint32_t nb = (uint32_t)(item & 1);
+    umma::mbar_expect_tx(bar + 8 * nb, (uint32_t)g.tx_bytes);
+    umma::tma_load_5d(smem + nb * (uint32_t)g.buf_pitch, &xmap, bar + 8 * nb, slab * g.cs,
+                      ct * g.ns * PW * STRIDE - 1, rt * g.rows * STRIDE - 1, b, g.Tx > 1 ? t : 0);
+  };
 
   if (tid == 0) {
     abort_s = 0;
@@ -120,40 +139,7 @@ dwconv_tile_kernel(const __grid_constant__ CUtensorMap xmap, const XT *__restric
     umma::prefetch_tensormap(&xmap);
   }
   __syncthreads();
-  const int h_in0 = rt * g.rows * STRIDE - 1, w_in0 = ct * g.ns * PW * STRIDE - 1;
-  if (tid == 0) {
-    umma::mbar_expect_tx(bar, (uint32_t)g.tx_bytes);
-    umma::tma_load_5d(smem, &xmap, bar, slab * g.cs, w_in0, h_in0, b, 0);
-  }
-
-  // weights and bias of this thread's four channels, as channel pairs
-  float2 wq[9][2];
-#pragma unroll
-  for (int k = 0; k < 9; ++k) {
-    wq[k][0] = make_float2(DT<XT>::to_f(w[(size_t)(c + 0) * 9 + k]), DT<XT>::to_f(w[(size_t)(c + 1) * 9 + k]));
-    wq[k][1] = make_float2(DT<XT>::to_f(w[(size_t)(c + 2) * 9 + k]), DT<XT>::to_f(w[(size_t)(c + 3) * 9 + k]));
-  }
-  float2 bq[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
-  if (bias != nullptr) {
-    bq[0] = make_float2(DT<XT>::to_f(bias[c]), DT<XT>::to_f(bias[c + 1]));
-    bq[1] = make_float2(DT<XT>::to_f(bias[c + 2]), DT<XT>::to_f(bias[c + 3]));
-  }
-
-  const bool row_ok = ho < g.Ho;
-  const size_t frame_out = (size_t)g.B * g.Ho * g.Wo * g.C;
-  const size_t out0 = (((size_t)b * g.Ho + (row_ok ? ho : 0)) * g.Wo) * g.C + c;   // (b, ho, 0, c)
-
-  float2 v[PW][2];
-#pragma unroll
-  for (int j = 0; j < PW; ++j) {
-    v[j][0] = v[j][1] = make_float2(0.f, 0.f);
-    if (v_init != nullptr && row_ok && wo0 + j < g.Wo) {
-      float t4[4];
-      load_pack_stream<VT, 4>(v_init + out0 + (size_t)(wo0 + j) * g.C, t4);
-      v[j][0] = make_float2(t4[0], t4[1]);
-      v[j][1] = make_float2(t4[2], t4[3]);
-    }
-  }
+  if (tid == 0 && n_items > 0) issue(0);
 
   const uint32_t px_bytes = (uint32_t)g.cs * sizeof(XT);
   // this thread's window inside a halo tile: rows row*STRIDE .., columns strip*PW*STRIDE ..
@@ -161,69 +147,105 @@ dwconv_tile_kernel(const __grid_constant__ CUtensorMap xmap, const XT *__restric
                         (uint32_t)cg * 4u * sizeof(XT);
   const uint32_t row_bytes = (uint32_t)g.hw * px_bytes;
   constexpr int NCOL = (PW - 1) * STRIDE + 3;   // input columns a strip needs
+  const size_t frame_out = (size_t)g.B * g.Ho * g.Wo * g.C;
 
+  float2 wq[9][2];   // weights and bias of this thread's four channels, as channel pairs
+  float2 bq[2];
+  int cur_slab = -1;
+  int item = 0;
   bool ok = true;
-  for (int t = 0; t < g.T && ok; ++t) {
-    if (tid == 0 && t + 1 < g.T) {   // buffer (t + 1) & 1 was last read in step t - 1, which ended with a barrier
-      const uint32_t nb = (uint32_t)((t + 1) & 1);
-      umma::mbar_expect_tx(bar + 8 * nb, (uint32_t)g.tx_bytes);
-      umma::tma_load_5d(smem + nb * (uint32_t)g.buf_pitch, &xmap, bar + 8 * nb, slab * g.cs, w_in0, h_in0, b,
-                        g.Tx > 1 ? t + 1 : 0);
+  for (int i = 0; i < my_tiles && ok; ++i) {
+    int ct, rt, b, slab;
+    decode((int)blockIdx.x + i * (int)gridDim.x, ct, rt, b, slab);
+    const int c = slab * g.cs + cg * 4;
+    if (slab != cur_slab) {
+      cur_slab = slab;
+#pragma unroll
+      for (int k = 0; k < 9; ++k) {
+        wq[k][0] = make_float2(DT<XT>::to_f(w[(size_t)(c + 0) * 9 + k]), DT<XT>::to_f(w[(size_t)(c + 1) * 9 + k]));
+        wq[k][1] = make_float2(DT<XT>::to_f(w[(size_t)(c + 2) * 9 + k]), DT<XT>::to_f(w[(size_t)(c + 3) * 9 + k]));
+      }
+      bq[0] = bq[1] = make_float2(0.f, 0.f);
+      if (bias != nullptr) {
+        bq[0] = make_float2(DT<XT>::to_f(bias[c]), DT<XT>::to_f(bias[c + 1]));
+        bq[1] = make_float2(DT<XT>::to_f(bias[c + 2]), DT<XT>::to_f(bias[c + 3]));
+      }
     }
-    ok = umma::mbar_wait(bar + 8 * (uint32_t)(t & 1), (uint32_t)((t >> 1) & 1), abort_flag);
-    if (!ok) break;
-    const uint32_t base = smem + (uint32_t)(t & 1) * (uint32_t)g.buf_pitch + win0;
+    const int ho = rt * g.rows + row;
+    const int wo0 = (ct * g.ns + strip) * PW;
+    const bool row_ok = ho < g.Ho;
+    const size_t out0 = (((size_t)b * g.Ho + (row_ok ? ho : 0)) * g.Wo) * g.C + c;   // (b, ho, 0, c)
 
-    float2 acc[PW][2];
+    float2 v[PW][2];
 #pragma unroll
-    for (int j = 0; j < PW; ++j) { acc[j][0] = bq[0]; acc[j][1] = bq[1]; }
-#pragma unroll
-    for (int kh = 0; kh < 3; ++kh) {
-      const uint32_t rbase = base + (uint32_t)kh * row_bytes;
-#pragma unroll
-      for (int col = 0; col < NCOL; ++col) {
-        float2 x0, x1;
-        Vec4<XT>::load(rbase + (uint32_t)col * px_bytes, x0, x1);
-#pragma unroll
-        for (int kw = 0; kw < 3; ++kw) {
-          // input column col = j * STRIDE + kw
-          if ((col - kw) >= 0 && (col - kw) % STRIDE == 0 && (col - kw) / STRIDE < PW) {   // resolved when unrolled
-            const int j = (col - kw) / STRIDE;
-            acc[j][0] = __ffma2_rn(wq[kh * 3 + kw][0], x0, acc[j][0]);
-            acc[j][1] = __ffma2_rn(wq[kh * 3 + kw][1], x1, acc[j][1]);
-          }
-        }
+    for (int j = 0; j < PW; ++j) {
+      v[j][0] = v[j][1] = make_float2(0.f, 0.f);
+      if (v_init != nullptr && row_ok && wo0 + j < g.Wo) {
+        float t4[4];
+        load_pack_stream<VT, 4>(v_init + out0 + (size_t)(wo0 + j) * g.C, t4);
+        v[j][0] = make_float2(t4[0], t4[1]);
+        v[j][1] = make_float2(t4[2], t4[3]);
       }
     }
 
-    if (row_ok) {
-      const size_t tout = (size_t)t * frame_out + out0;
+    for (int t = 0; t < g.T; ++t, ++item) {
+      // buffer (item + 1) & 1 was last read by item - 1, which ended with a barrier
+      if (tid == 0 && item + 1 < n_items) issue(item + 1);
+      ok = umma::mbar_wait(bar + 8 * (uint32_t)(item & 1), (uint32_t)((item >> 1) & 1), abort_flag);
+      if (!ok) break;
+      const uint32_t base = smem + (uint32_t)(item & 1) * (uint32_t)g.buf_pitch + win0;
+
+      float2 acc[PW][2];
+#pragma unroll
+      for (int j = 0; j < PW; ++j) { acc[j][0] = bq[0]; acc[j][1] = bq[1]; }
+#pragma unroll
+      for (int kh = 0; kh < 3; ++kh) {
+        const uint32_t rbase = base + (uint32_t)kh * row_bytes;
+#pragma unroll
+        for (int col = 0; col < NCOL; ++col) {
+          float2 x0, x1;
+          Vec4<XT>::load(rbase + (uint32_t)col * px_bytes, x0, x1);
+#pragma unroll
+          for (int kw = 0; kw < 3; ++kw) {
+            // input column col = j * STRIDE + kw
+            if ((col - kw) >= 0 && (col - kw) % STRIDE == 0 && (col - kw) / STRIDE < PW) {   // resolved when unrolled
+              const int j = (col - kw) / STRIDE;
+              acc[j][0] = __ffma2_rn(wq[kh * 3 + kw][0], x0, acc[j][0]);
+              acc[j][1] = __ffma2_rn(wq[kh * 3 + kw][1], x1, acc[j][1]);
+            }
+          }
+        }
+      }
+
+      if (row_ok) {
+        const size_t tout = (size_t)t * frame_out + out0;
+#pragma unroll
+        for (int j = 0; j < PW; ++j) {
+          if (wo0 + j < g.Wo) {
+            const size_t o = tout + (size_t)(wo0 + j) * g.C;
+            if (res != nullptr) {
+              float r4[4];
+              load_pack<XT, 4>(res + o, r4);
+              acc[j][0] = __fadd2_rn(acc[j][0], make_float2(r4[0], r4[1]));
+              acc[j][1] = __fadd2_rn(acc[j][1], make_float2(r4[2], r4[3]));
+            }
+            const float2 s0 = lif2<KIND>(acc[j][0], v[j][0], p);
+            const float2 s1 = lif2<KIND>(acc[j][1], v[j][1], p);
+            const float s4[4] = {s0.x, s0.y, s1.x, s1.y};
+            store_pack<ST, 4>(spikes + o, s4);
+          }
+        }
+      }
+      __syncthreads();   // everyone is done with buffer item & 1 before the copy of item + 2 may overwrite it
+    }
+
+    if (ok && row_ok) {
 #pragma unroll
       for (int j = 0; j < PW; ++j) {
         if (wo0 + j < g.Wo) {
-          const size_t o = tout + (size_t)(wo0 + j) * g.C;
-          if (res != nullptr) {
-            float r4[4];
-            load_pack<XT, 4>(res + o, r4);
-            acc[j][0] = __fadd2_rn(acc[j][0], make_float2(r4[0], r4[1]));
-            acc[j][1] = __fadd2_rn(acc[j][1], make_float2(r4[2], r4[3]));
-          }
-          const float2 s0 = lif2<FAST>(acc[j][0], v[j][0], p);
-          const float2 s1 = lif2<FAST>(acc[j][1], v[j][1], p);
-          const float s4[4] = {s0.x, s0.y, s1.x, s1.y};
-          store_pack<ST, 4>(spikes + o, s4);
+          const float v4[4] = {v[j][0].x, v[j][0].y, v[j][1].x, v[j][1].y};
+          store_pack<VT, 4>(v_out + out0 + (size_t)(wo0 + j) * g.C, v4);
         }
-      }
-    }
-    __syncthreads();   // everyone is done with buffer t & 1 before the copy of step t + 2 may overwrite it
-  }
-
-  if (ok && row_ok) {
-#pragma unroll
-    for (int j = 0; j < PW; ++j) {
-      if (wo0 + j < g.Wo) {
-        const float v4[4] = {v[j][0].x, v[j][0].y, v[j][1].x, v[j][1].y};
-        store_pack<VT, 4>(v_out + out0 + (size_t)(wo0 + j) * g.C, v4);
       }
     }
   }
@@ -263,8 +285,12 @@ int launch_tile(const DwCall &a, cudaStream_t stream) {
   g.nslab = a.C / g.cs;
   g.tx_bytes = g.hr * g.hw * g.cs * (int)sizeof(XT);
   g.buf_pitch = (g.tx_bytes + 127) & ~127;
-  const long long grid = (long long)a.B * g.nslab * g.nrt * g.nct;
-  if (grid > 0x7fffffffLL) return fail(SNNB_ERR_INVALID, "dwconv3x3_lif: problem too large");
+  const long long tiles = (long long)a.B * g.nslab * g.nrt * g.nct;
+  if (tiles * a.T > 0x7fffffffLL) return fail(SNNB_ERR_INVALID, "dwconv3x3_lif: problem too large");
+  g.total_tiles = (int)tiles;
+  const int sms = sm_count() > 0 ? sm_count() : 128;
+  const int per_sm = pw <= 4 ? 2 : 1;   // resident blocks per SM (register budget of the instantiation)
+  const long long grid = tiles < (long long)sms * per_sm ? tiles : (long long)sms * per_sm;
   const size_t smem = 2 * (size_t)g.buf_pitch + 128;
   if (smem > 200 * 1024) return fail(SNNB_ERR_UNSUPPORTED, "dwconv3x3_lif: tile does not fit shared memory");
   CUtensorMap xm;
@@ -278,8 +304,8 @@ int launch_tile(const DwCall &a, cudaStream_t stream) {
     if (rc != SNNB_OK) return rc;
   }
   const DwGeom gk = g;
-  const bool fast = a.p.mode == 1 && a.p.hard;
-#define SNNB_DWT(STR, PWV, FASTV)                                                                                   \
+  const int kind = (a.p.mode == 1 && a.p.hard) ? (a.p.v_reset == 0.f ? 2 : 1) : 0;
+#define SNNB_DWT2(STR, PWV, FASTV)                                                                                   \
   do {                                                                                                              \
     auto kern = dwconv_tile_kernel<XT, ST, VT, STR, PWV, FASTV>;                                                    \
     static bool attr_done[16] = {};                                                                                 \
@@ -294,15 +320,18 @@ int launch_tile(const DwCall &a, cudaStream_t stream) {
                                                     static_cast<const XT *>(a.res), static_cast<const VT *>(a.v_init), \
                                                     static_cast<ST *>(a.spikes), static_cast<VT *>(a.v_out), gk, a.p); \
   } while (0)
+#define SNNB_DWT(STR, PWV)                                                           \
+  do {                                                                               \
+    if (kind == 2) SNNB_DWT2(STR, PWV, 2);                                           \
+    else if (kind == 1) SNNB_DWT2(STR, PWV, 1);                                      \
+    else SNNB_DWT2(STR, PWV, 0);                                                     \
+  } while (0)
   if (a.stride == 1) {
-    if (pw == 8) { if (fast) SNNB_DWT(1, 8, true); else SNNB_DWT(1, 8, false); }
-    else if (pw == 7) { if (fast) SNNB_DWT(1, 7, true); else SNNB_DWT(1, 7, false); }
-    else { if (fast) SNNB_DWT(1, 4, true); else SNNB_DWT(1, 4, false); }
+    if (pw == 8) SNNB_DWT(1, 8); else if (pw == 7) SNNB_DWT(1, 7); else SNNB_DWT(1, 4);
   } else {
-    if (pw == 8) { if (fast) SNNB_DWT(2, 8, true); else SNNB_DWT(2, 8, false); }
-    else if (pw == 7) { if (fast) SNNB_DWT(2, 7, true); else SNNB_DWT(2, 7, false); }
-    else { if (fast) SNNB_DWT(2, 4, true); else SNNB_DWT(2, 4, false); }
+    if (pw == 8) SNNB_DWT(2, 8); else if (pw == 7) SNNB_DWT(2, 7); else SNNB_DWT(2, 4);
   }
+#undef SNNB_DWT2
 #undef SNNB_DWT
   SNNB_CHECK_LAUNCH("dwconv3x3_lif (tile kernel)");
   return SNNB_OK;

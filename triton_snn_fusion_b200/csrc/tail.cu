@@ -186,10 +186,170 @@ lif_avgpool_linear_kernel(const XT *__restrict__ x, const VT *__restrict__ v_ini
   }
 }
 
+// ------------------------------------------------------------------------------------------------
+// Streaming form for channels-last input whose channel count splits evenly over the cluster.
+// Same plan (scan + integer counts, DSMEM exchange, warp-per-class mat-vec), laid out for bandwidth:
+//   * scan: the (sample, pixel, channel-vector) items of the CTA's channel slice form ONE index space over all
+//     samples of the group; a thread takes four items per trip and issues their 16-byte loads for up to four
+//     timesteps (and the initial membranes) before the first use, i.e. up to 320 bytes in flight per thread;
+//   * exchange: the peers' count slices are copied with 16-byte DSMEM loads;
+//   * mat-vec: a warp works on four classes at a time, so every count read from shared memory feeds four
+//     dot products, and its four 16-byte weight loads per trip are independent.
+constexpr int NTF = 256;
+
+// a 16-byte vector of XT as loaded (kept packed until it is used, which keeps 16 loads in flight cheap in registers)
+template <typename XT, int VEC>
+__device__ __forceinline__ void unpack16(const int4 &raw, float (&out)[VEC]) {
+  static_assert(sizeof(XT) * VEC == 16, "one 16-byte vector");
+  const XT *e = reinterpret_cast<const XT *>(&raw);
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) out[i] = DT<XT>::to_f(e[i]);
+}
+
+template <typename XT, typename VT, int VEC>
+__global__ void __launch_bounds__(NTF)
+lif_avgpool_linear_stream_kernel(const XT *__restrict__ x, const VT *v_init, const XT *__restrict__ fc_w,
+                                 const XT *__restrict__ fc_b, XT *__restrict__ out, VT *v_out,
+                                 int T, int N, int C, int HW, int K, int S, LifParams p) {
+  extern __shared__ __align__(16) int cnt[];  // [S][C] spike counts summed over t and pixels
+  cg::cluster_group cluster = cg::this_cluster();
+  const int r = (int)cluster.block_rank();
+  const int n0 = (blockIdx.x / CL) * S;
+  const int ns = min(S, N - n0);
+  const int tid = threadIdx.x;
+  for (int i = tid; i < S * C; i += NTF) cnt[i] = 0;
+  __syncthreads();
+
+  const int Cs = C / CL;            // channels of this CTA, a multiple of VEC
+  const int cvn = Cs / VEC;         // vectors per pixel; NTF % cvn == 0, so a thread keeps its channel vector
+  const int cs = r * Cs;
+  const int64_t frame = (int64_t)N * C * HW;
+  const int items = ns * HW * cvn;
+  const int cc = cs + (tid % cvn) * VEC;
+  for (int it0 = tid; it0 < items; it0 += 4 * NTF) {
+    int64_t e[4];
+    int smp[4];
+    bool on[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int it = it0 + u * NTF;
+      on[u] = it < items;
+      const int ps = (on[u] ? it : it0) / cvn;   // (sample, pixel) index
+      smp[u] = ps / HW;
+      e[u] = ((int64_t)(n0 + smp[u]) * HW + (ps - smp[u] * HW)) * C + cc;
+    }
+    float v[4][VEC];
+    int k[4][VEC];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      if (v_init != nullptr) load_pack_stream<VT, VEC>(v_init + e[u], v[u]);
+      else {
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) v[u][i] = 0.f;
+      }
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) k[u][i] = 0;
+    }
+    for (int t0 = 0; t0 < T; t0 += 4) {
+      int4 raw[4][4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (t0 + j < T) raw[u][j] = __ldcs(reinterpret_cast<const int4 *>(x + (int64_t)(t0 + j) * frame + e[u]));
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (t0 + j < T) {
+            float xv[VEC];
+            unpack16<XT, VEC>(raw[u][j], xv);
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) k[u][i] += (int)lif_step(xv[i], v[u][i], p);
+          }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      if (on[u]) {
+        store_pack<VT, VEC>(v_out + e[u], v[u]);
+#pragma unroll
+        for (int i = 0; i < VEC; ++i)
+          if (k[u][i]) atomicAdd(&cnt[smp[u] * C + cc + i], k[u][i]);
+      }
+  }
+
+  // ---- exchange the count slices through distributed shared memory, 16 bytes at a time
+  cluster.sync();
+  {
+    const int q4 = Cs / 4;   // int4 per (peer, sample)
+    for (int i = tid; i < (CL - 1) * ns * q4; i += NTF) {
+      int q = i / (ns * q4);
+      const int rem = i - q * (ns * q4);
+      q += (q >= r) ? 1 : 0;                       // skip this CTA's own slice
+      const int s = rem / q4, j = rem - s * q4;
+      const int off = s * C + q * Cs + j * 4;
+      const int *peer = cluster.map_shared_rank(cnt, q);
+      *reinterpret_cast<int4 *>(&cnt[off]) = *reinterpret_cast<const int4 *>(&peer[off]);
+    }
+  }
+  cluster.sync();  // nobody leaves (or overwrites) before every peer has read its slice
+
+  // ---- linear: this CTA's classes for all samples of the group, four classes per warp and trip
+  const int Ks = (K + CL - 1) / CL;
+  const int ks = r * Ks, ke = min(K, ks + Ks);
+  const int warp = tid / 32, lane = tid % 32;
+  const float inv_hw = 1.0f / (float)HW;
+  for (int k0 = ks + 4 * warp; k0 < ke; k0 += 4 * (NTF / 32)) {
+    float acc[4][SMAX];
+#pragma unroll
+    for (int q = 0; q < 4; ++q)
+#pragma unroll
+      for (int s = 0; s < SMAX; ++s) acc[q][s] = 0.f;
+    for (int c = lane * 8; c < C; c += 32 * 8) {
+      float wv[4][8];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        if (k0 + q < ke) load_pack<XT, 8>(fc_w + (int64_t)(k0 + q) * C + c, wv[q]);
+        else {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) wv[q][i] = 0.f;
+        }
+      }
+#pragma unroll
+      for (int s = 0; s < SMAX; ++s)
+        if (s < ns) {
+          const int4 c0 = *reinterpret_cast<const int4 *>(&cnt[s * C + c]);
+          const int4 c1 = *reinterpret_cast<const int4 *>(&cnt[s * C + c + 4]);
+          const float cf[8] = {(float)c0.x, (float)c0.y, (float)c0.z, (float)c0.w,
+                               (float)c1.x, (float)c1.y, (float)c1.z, (float)c1.w};
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            float a = acc[q][s];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) a = fmaf(wv[q][i], cf[i], a);
+            acc[q][s] = a;
+          }
+        }
+    }
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const float bk = (fc_b != nullptr && k0 + q < ke) ? DT<XT>::to_f(fc_b[k0 + q]) * (float)T : 0.f;
+#pragma unroll
+      for (int s = 0; s < SMAX; ++s) {
+        float a = acc[q][s];
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) a += __shfl_xor_sync(0xffffffffu, a, off);
+        if (lane == 0 && s < ns && k0 + q < ke) out[(int64_t)(n0 + s) * K + k0 + q] = DT<XT>::from_f(a * inv_hw + bk);
+      }
+    }
+  }
+}
+
 template <typename XT, typename VT, bool NHWC, int VEC>
 int launch(const void *x, const void *v_init, const void *w, const void *b, void *out, void *v_out,
            int T, int N, int C, int HW, int K, const LifParams &p, cudaStream_t stream) {
-  int S = (N * CL) / (2 * 148);   // samples per cluster: about two CTAs per SM in flight
+  const int sms = sm_count() > 0 ? sm_count() : 128;
+  int S = (N * CL) / (2 * sms);   // samples per cluster: about two CTAs per SM in flight
   S = S < 1 ? 1 : (S > SMAX ? SMAX : S);
   while (S > 1 && (size_t)S * C * sizeof(int) > 48 * 1024) --S;
   const size_t smem = (size_t)S * C * sizeof(int);
@@ -215,11 +375,49 @@ int launch(const void *x, const void *v_init, const void *w, const void *b, void
   return SNNB_OK;
 }
 
+template <typename XT, typename VT, int VEC>
+int launch_stream(const void *x, const void *v_init, const void *w, const void *b, void *out, void *v_out,
+                  int T, int N, int C, int HW, int K, const LifParams &p, cudaStream_t stream) {
+  const int sms = sm_count() > 0 ? sm_count() : 128;
+  // samples per cluster: as many as keep about two CTAs per SM in flight (each cluster re-reads the weight
+  // matrix from L2, so few large groups beat many small ones), within 48 KB of counts
+  int S = (N * CL + 2 * sms - 1) / (2 * sms);
+  S = S < 1 ? 1 : (S > SMAX ? SMAX : S);
+  while (S > 1 && (size_t)S * C * sizeof(int) > 48 * 1024) --S;
+  const size_t smem = (size_t)S * C * sizeof(int);
+  const int groups = (N + S - 1) / S;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(groups * CL));
+  cfg.blockDim = dim3(NTF);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = CL;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, lif_avgpool_linear_stream_kernel<XT, VT, VEC>,
+                                     static_cast<const XT *>(x), static_cast<const VT *>(v_init),
+                                     static_cast<const XT *>(w), static_cast<const XT *>(b),
+                                     static_cast<XT *>(out), static_cast<VT *>(v_out), T, N, C, HW, K, S, p);
+  if (e != cudaSuccess) return fail(SNNB_ERR_CUDA, "lif_avgpool_linear: launch failed: %s", cudaGetErrorString(e));
+  return SNNB_OK;
+}
+
 template <typename XT, typename VT>
 int pick(const void *x, const void *v_init, const void *w, const void *b, void *out, void *v_out,
          int T, int N, int C, int HW, int K, int layout, const LifParams &p, cudaStream_t stream) {
   if (layout == SNNB_NHWC) {
     const bool al = aligned16(x) && aligned16(v_out) && (v_init == nullptr || aligned16(v_init));
+    {   // streaming form: the channels split evenly over the cluster into 16-byte vectors
+      constexpr int V = 16 / (int)sizeof(XT);
+      const int Cs = C / CL;
+      if (al && aligned16(w) && C % (CL * V) == 0 && C % 8 == 0 && NTF % (Cs / V) == 0 &&
+          (size_t)C * sizeof(int) <= 48 * 1024 && (sizeof(VT) == sizeof(XT)))
+        return launch_stream<XT, VT, V>(x, v_init, w, b, out, v_out, T, N, C, HW, K, p, stream);
+    }
     if (al && sizeof(XT) == 2 && C % 8 == 0) return launch<XT, VT, true, 8>(x, v_init, w, b, out, v_out, T, N, C, HW, K, p, stream);
     const bool vec = (C % 4 == 0) && al;
     if (vec) return launch<XT, VT, true, 4>(x, v_init, w, b, out, v_out, T, N, C, HW, K, p, stream);

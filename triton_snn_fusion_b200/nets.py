@@ -42,14 +42,17 @@ class CompiledNet:
 
     def __init__(self, spec: List[dict], params, batch: int, T: int, in_hw=(224, 224),
                  dtype=torch.bfloat16, device="cuda", conv_path: str = "auto", keep_membranes: bool = False,
-                 fuse_shortcuts: bool = True):
+                 fuse_shortcuts: bool = True, window: Optional[int] = None):
         self.spec, self.B, self.T, self.dtype = spec, int(batch), int(T), dtype
-        # Longer sequences run as windows of four timesteps (what the fastest conv kernel holds in tensor
-        # memory) with the membrane handed from window to window in fp32, which is exact. Networks with a
-        # LIF tail or depthwise layers keep one window.
+        # The conv kernels take any even T in one launch. A sequence can also run as windows of `window` steps
+        # with the membrane handed from window to window in fp32, which is exact (for sequences beyond what one
+        # launch takes, or to bound the activation memory a layer touches at a time). Networks with a LIF tail
+        # or depthwise layers keep one window.
         simple = all(L["op"] in ("maxpool", "head") or (L["op"] == "conv" and L["groups"] == 1) for L in spec)
-        self.Tw = 4 if (self.T > 4 and self.T % 4 == 0 and dtype in (torch.bfloat16, torch.float16) and simple
-                        and conv_path == "auto") else self.T
+        if window is None and self.T > 64 and self.T % 4 == 0:
+            window = 4
+        self.Tw = int(window) if (window and self.T % int(window) == 0 and self.T > int(window) and simple
+                                  and dtype in (torch.bfloat16, torch.float16) and conv_path == "auto") else self.T
         self.nwin = self.T // self.Tw
         self.device = torch.device(device)
         self.path = {"auto": _lib.PATH_AUTO, "simt": _lib.PATH_SIMT, "tcgen05": _lib.PATH_TCGEN05,
@@ -77,7 +80,7 @@ class CompiledNet:
         # is folded into that conv's launch (snnb_conv3x3_shortcut_lif): its output is never materialised.
         self.fused_sc: Dict[str, dict] = {}    # consumer layer name -> the shortcut layer
         self.skipped = set()                   # shortcut layers that no longer run on their own
-        if fuse_shortcuts and dtype in (torch.bfloat16, torch.float16) and conv_path == "auto" and self.Tw in (1, 2, 4):
+        if fuse_shortcuts and dtype in (torch.bfloat16, torch.float16) and conv_path == "auto" and (self.Tw == 1 or self.Tw % 2 == 0):
             by_dst = {L.get("dst"): L for L in spec if L["op"] == "conv"}
             hw = {"input": tuple(in_hw)}   # output size of every layer, to know which maps the fused kernel takes
             for L in spec:

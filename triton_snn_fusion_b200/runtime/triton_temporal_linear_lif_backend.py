@@ -101,9 +101,9 @@ def _impl(x_seq, weight, bias, v_init, v_threshold, v_reset, tau, detach_reset, 
                 steps, M, K, N, dt, dt, _lib.dtype_code(v_dt), th, vr, ta, _PATH[_conv._conv_path], stream),
             "snnb_linear_lif")
 
-    # Longer sequences as windows of four timesteps (what the fastest GEMM kernel keeps in tensor memory) with the
-    # membrane handed over in fp32: the arithmetic of a single pass.
-    windowed = (T > _conv.WINDOW and T % _conv.WINDOW == 0 and _conv._conv_path == "auto"
+    # Sequences beyond what one launch of the GEMM kernel takes run as windows of four timesteps with the membrane
+    # handed over in fp32: the arithmetic of a single pass.
+    windowed = (T > _conv.MAX_STEPS and T % _conv.WINDOW == 0 and _conv._conv_path == "auto"
                 and x_seq.dtype in (torch.bfloat16, torch.float16))
     if windowed:
         carry = [torch.empty((M, N), dtype=torch.float32, device=x_seq.device) for _ in range(2)]
