@@ -2,6 +2,7 @@
 #include "common.cuh"
 
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 
 namespace snnb {
@@ -24,6 +25,14 @@ int fail(int code, const char *fmt, ...) {
 }
 
 const char *last_error() { return g_err; }
+
+bool pdl_enabled() {
+  static const bool on = [] {
+    const char *e = std::getenv("SNNB_PDL");
+    return !(e != nullptr && e[0] == '0');
+  }();
+  return on;
+}
 
 int sm_count() {
   static int cached[64] = {};

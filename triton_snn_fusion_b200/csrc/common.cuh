@@ -30,6 +30,10 @@ int fail(int code, const char *fmt, ...);
       return ::snnb::fail(SNNB_ERR_CUDA, "%s: launch failed: %s", name, cudaGetErrorString(e__)); \
   } while (0)
 
+// Whether kernels that support it are launched with programmatic dependent launch (on unless the environment
+// variable SNNB_PDL is set to 0).
+bool pdl_enabled();
+
 // Number of SMs of the current device (queried once per device; 0 if the query fails).
 int sm_count();
 

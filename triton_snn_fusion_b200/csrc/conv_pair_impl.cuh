@@ -215,6 +215,7 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
   __shared__ int abort_s;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  umma::pdl_trigger();   // the next kernel's blocks may take over SMs as this grid drains; they wait for its end themselves
 
   const uint32_t smem_base = (umma::smem_u32(smem_raw) + 1023u) & ~1023u;
   // [identity block (residual path only)] [weight ring] [halo ring]
@@ -292,6 +293,9 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
   __syncthreads();
   umma::tc_fence_after_sync();
   const uint32_t tmem_base = tmem_base_s;
+  // Set-up (barriers, tensor memory, identity tile, tensor-map prefetch) is done; from here on the kernel reads
+  // what its predecessor in the stream wrote and writes buffers that predecessor may read.
+  umma::pdl_wait();
 
   if (warp == kHaloWarpP) {
     // ------------------------------------------------- halo producer: lane q loads timestep q of the pair
@@ -580,9 +584,9 @@ int launch(const ConvArgs &a, cudaStream_t stream) {
                                   : (long long)a.B * g.row_tiles * g.w_strips * g.n_tiles_n;
   if (tiles > 0x7fffffffLL) return fail(SNNB_ERR_INVALID, "conv_lif: problem too large for the grid");
   g.total_tiles = (int)tiles;
-  int dev = 0, sms = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 1)
-    return fail(SNNB_ERR_CUDA, "conv_lif: cannot query the SM count");
+  int dev = 0;
+  const int sms = sm_count();
+  if (cudaGetDevice(&dev) != cudaSuccess || sms < 1) return fail(SNNB_ERR_CUDA, "conv_lif: cannot query the SM count");
   const long long grid = tiles < sms ? tiles : sms;   // persistent: one CTA per SM walks the tiles
   const int es = 2;
   CUtensorMap xm, wm, xph[4];
@@ -657,12 +661,32 @@ int launch(const ConvArgs &a, cudaStream_t stream) {
   const size_t smem = (ident ? (size_t)kIdentBytes : 0) + (size_t)g.wring * kWSlot + (size_t)g.ring * g.tq * kHaloT +
                       4 * kRowBytes + 1024;
   auto kern = g.s2 ? conv3x3_pair_kernel<XT, ST, VT, true> : conv3x3_pair_kernel<XT, ST, VT, false>;
-  const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  if (e != cudaSuccess) return fail(SNNB_ERR_CUDA, "conv_lif: cannot raise the shared-memory limit: %s", cudaGetErrorString(e));
-  kern<<<(unsigned)grid, kThreadsP, smem, stream>>>(xm, wm, rm, wm64, scwm, xph[1], xph[2], xph[3], static_cast<const XT *>(a.b),
-                                                    static_cast<const XT *>(a.b2), static_cast<const VT *>(a.v_init), static_cast<ST *>(a.spikes),
-                                                    static_cast<VT *>(a.v_out), g, a.p);
-  SNNB_CHECK_LAUNCH("conv3x3_pair");
+  {
+    // once per kernel instantiation and device: allow the largest dynamic shared-memory size any call may ask for
+    static bool raised[2][64] = {};
+    if (dev < 0 || dev >= 64 || !raised[g.s2][dev]) {
+      const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+      if (e != cudaSuccess) return fail(SNNB_ERR_CUDA, "conv_lif: cannot raise the shared-memory limit: %s", cudaGetErrorString(e));
+      if (dev >= 0 && dev < 64) raised[g.s2][dev] = true;
+    }
+  }
+  {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(kThreadsP);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const cudaError_t le = cudaLaunchKernelEx(&cfg, kern, xm, wm, rm, wm64, scwm, xph[1], xph[2], xph[3],
+                                              static_cast<const XT *>(a.b), static_cast<const XT *>(a.b2),
+                                              static_cast<const VT *>(a.v_init), static_cast<ST *>(a.spikes),
+                                              static_cast<VT *>(a.v_out), g, a.p);
+    if (le != cudaSuccess) return fail(SNNB_ERR_CUDA, "conv3x3_pair: launch failed: %s", cudaGetErrorString(le));
+  }
   return SNNB_OK;
 }
 

@@ -93,8 +93,13 @@ __device__ __forceinline__ float2 lif2(float2 y, float2 &v, const LifParams &p) 
 // Persistent: a block walks tiles blockIdx.x, blockIdx.x + gridDim.x, ... and treats (tile, timestep) pairs as one
 // stream of work items, so the copy of the next item - the next timestep, or the first timestep of the next tile -
 // always runs under the arithmetic of the current one and only the very first copy of a block is exposed.
-template <typename XT, typename ST, typename VT, int STRIDE, int PW, int KIND>
-__global__ void __launch_bounds__(kDwThreads, PW <= 4 ? 2 : 1)
+// The tile geometry is fixed at compile time (strips of PW = 4 pixels, NS = 2 strips per tile row, CS channels), so
+// every shared-memory read of the inner loop is "window base + constant": the loop body is the 16-byte-free
+// sequence load, widen, multiply-add with no address arithmetic left in it.
+constexpr int PW = 4, NS = 2;
+
+template <typename XT, typename ST, typename VT, int STRIDE, int CS, int KIND>
+__global__ void __launch_bounds__(kDwThreads, 2)
 dwconv_tile_kernel(const __grid_constant__ CUtensorMap xmap, const XT *__restrict__ w, const XT *__restrict__ bias,
                    const XT *__restrict__ res, const VT *v_init, ST *__restrict__ spikes, VT *v_out,
                    const DwGeom g, const LifParams p) {
@@ -105,31 +110,30 @@ dwconv_tile_kernel(const __grid_constant__ CUtensorMap xmap, const XT *__restric
   const uint32_t bar = umma::smem_u32(full);
   volatile int *abort_flag = &abort_s;
 
-  const int cg_n = g.cs >> 2;
+  constexpr int CGN = CS / 4;                                  // channel quads per pixel
+  constexpr int HWD = (NS * PW - 1) * STRIDE + 3;              // halo tile width in pixels
+  constexpr uint32_t PXB = CS * sizeof(XT);                    // bytes per pixel
+  constexpr uint32_t ROWB = HWD * PXB;                         // bytes per halo row
+  constexpr int NCOL = (PW - 1) * STRIDE + 3;                  // input columns a strip needs
   const int tid = threadIdx.x;
-  const int cg = tid % cg_n;
-  const int strip = (tid / cg_n) % g.ns;
-  const int row = tid / (cg_n * g.ns);
+  const int cg = tid % CGN;
+  const int strip = (tid / CGN) % NS;
+  const int row = tid / (CGN * NS);
+  // copies of the launch constants the loops use (kept in registers instead of re-read from the parameter bank)
+  const int T = g.T, Ho = g.Ho, Wo = g.Wo, C = g.C, nct = g.nct, nrt = g.nrt, nB = g.B, rows = g.rows;
+  const uint32_t pitch = (uint32_t)g.buf_pitch, tx_bytes = (uint32_t)g.tx_bytes;
+  const bool many_frames = g.Tx > 1;
 
   // tile index -> (column tile, row tile, image, channel block); the channel block is slowest, so a block's
   // consecutive tiles nearly always share their weights
   auto decode = [&](int tile, int &ct, int &rt, int &b, int &slab) {
-    ct = tile % g.nct; tile /= g.nct;
-    rt = tile % g.nrt; tile /= g.nrt;
-    b = tile % g.B;
-    slab = tile / g.B;
+    ct = tile % nct; tile /= nct;
+    rt = tile % nrt; tile /= nrt;
+    b = tile % nB;
+    slab = tile / nB;
   };
   const int my_tiles = (int)blockIdx.x < g.total_tiles ? (g.total_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
-  const int n_items = my_tiles * g.T;
-  auto issue = [&](int item) {   // one thread: start the copy of work item `item` into buffer item & 1
-    int ct, rt, b, slab;
-    decode((int)blockIdx.x + (item / g.T) * (int)gridDim.x, ct, rt, b, slab);
-    const int t = item - (item / g.T) * g.T;
-    const uint32_t nb = (uint32_t)(item & 1);
-    umma::mbar_expect_tx(bar + 8 * nb, (uint32_t)g.tx_bytes);
-    umma::tma_load_5d(smem + nb * (uint32_t)g.buf_pitch, &xmap, bar + 8 * nb, slab * g.cs,
-                      ct * g.ns * PW * STRIDE - 1, rt * g.rows * STRIDE - 1, b, g.Tx > 1 ? t : 0);
-  };
+  const int n_items = my_tiles * T;
 
   if (tid == 0) {
     abort_s = 0;
@@ -139,15 +143,22 @@ dwconv_tile_kernel(const __grid_constant__ CUtensorMap xmap, const XT *__restric
     umma::prefetch_tensormap(&xmap);
   }
   __syncthreads();
-  if (tid == 0 && n_items > 0) issue(0);
+  // producer state (thread 0): the next work item to copy, as (tile ordinal, timestep) and its tile coordinates
+  int p_i = 0, p_t = 0, p_ct = 0, p_rt = 0, p_b = 0, p_slab = 0, p_item = 0;
+  auto issue_next = [&]() {   // one thread: start the copy of work item p_item into buffer p_item & 1
+    if (p_t == 0) decode((int)blockIdx.x + p_i * (int)gridDim.x, p_ct, p_rt, p_b, p_slab);
+    const uint32_t nb = (uint32_t)(p_item & 1);
+    umma::mbar_expect_tx(bar + 8 * nb, tx_bytes);
+    umma::tma_load_5d(smem + nb * pitch, &xmap, bar + 8 * nb, p_slab * CS, p_ct * (NS * PW * STRIDE) - 1,
+                      p_rt * rows * STRIDE - 1, p_b, many_frames ? p_t : 0);
+    ++p_item;
+    if (++p_t == T) { p_t = 0; ++p_i; }
+  };
+  if (tid == 0 && n_items > 0) issue_next();
 
-  const uint32_t px_bytes = (uint32_t)g.cs * sizeof(XT);
   // this thread's window inside a halo tile: rows row*STRIDE .., columns strip*PW*STRIDE ..
-  const uint32_t win0 = ((uint32_t)(row * STRIDE) * g.hw + (uint32_t)(strip * PW * STRIDE)) * px_bytes +
-                        (uint32_t)cg * 4u * sizeof(XT);
-  const uint32_t row_bytes = (uint32_t)g.hw * px_bytes;
-  constexpr int NCOL = (PW - 1) * STRIDE + 3;   // input columns a strip needs
-  const size_t frame_out = (size_t)g.B * g.Ho * g.Wo * g.C;
+  const uint32_t win0 = smem + (uint32_t)(row * STRIDE) * ROWB + (uint32_t)(strip * PW * STRIDE) * PXB + (uint32_t)cg * 4u * sizeof(XT);
+  const size_t frame_out = (size_t)nB * Ho * Wo * C;
 
   float2 wq[9][2];   // weights and bias of this thread's four channels, as channel pairs
   float2 bq[2];
@@ -157,7 +168,7 @@ dwconv_tile_kernel(const __grid_constant__ CUtensorMap xmap, const XT *__restric
   for (int i = 0; i < my_tiles && ok; ++i) {
     int ct, rt, b, slab;
     decode((int)blockIdx.x + i * (int)gridDim.x, ct, rt, b, slab);
-    const int c = slab * g.cs + cg * 4;
+    const int c = slab * CS + cg * 4;
     if (slab != cur_slab) {
       cur_slab = slab;
 #pragma unroll
@@ -171,40 +182,45 @@ dwconv_tile_kernel(const __grid_constant__ CUtensorMap xmap, const XT *__restric
         bq[1] = make_float2(DT<XT>::to_f(bias[c + 2]), DT<XT>::to_f(bias[c + 3]));
       }
     }
-    const int ho = rt * g.rows + row;
-    const int wo0 = (ct * g.ns + strip) * PW;
-    const bool row_ok = ho < g.Ho;
-    const size_t out0 = (((size_t)b * g.Ho + (row_ok ? ho : 0)) * g.Wo) * g.C + c;   // (b, ho, 0, c)
+    const int ho = rt * rows + row;
+    const int wo0 = (ct * NS + strip) * PW;
+    // which of the strip's PW outputs exist (bit j), and where the first of them lives in a frame
+    int live = 0;
+#pragma unroll
+    for (int j = 0; j < PW; ++j)
+      if (ho < Ho && wo0 + j < Wo) live |= 1 << j;
+    const size_t out0 = (((size_t)b * Ho + (ho < Ho ? ho : 0)) * Wo + (wo0 < Wo ? wo0 : 0)) * C + c;   // (b, ho, wo0, c)
 
     float2 v[PW][2];
 #pragma unroll
     for (int j = 0; j < PW; ++j) {
       v[j][0] = v[j][1] = make_float2(0.f, 0.f);
-      if (v_init != nullptr && row_ok && wo0 + j < g.Wo) {
+      if (v_init != nullptr && ((live >> j) & 1)) {
         float t4[4];
-        load_pack_stream<VT, 4>(v_init + out0 + (size_t)(wo0 + j) * g.C, t4);
+        load_pack_stream<VT, 4>(v_init + out0 + (size_t)j * C, t4);
         v[j][0] = make_float2(t4[0], t4[1]);
         v[j][1] = make_float2(t4[2], t4[3]);
       }
     }
+    ST *sp = spikes + out0;
+    const XT *rp = res != nullptr ? res + out0 : nullptr;
 
-    for (int t = 0; t < g.T; ++t, ++item) {
+    for (int t = 0; t < T; ++t, ++item) {
       // buffer (item + 1) & 1 was last read by item - 1, which ended with a barrier
-      if (tid == 0 && item + 1 < n_items) issue(item + 1);
+      if (tid == 0 && item + 1 < n_items) issue_next();
       ok = umma::mbar_wait(bar + 8 * (uint32_t)(item & 1), (uint32_t)((item >> 1) & 1), abort_flag);
       if (!ok) break;
-      const uint32_t base = smem + (uint32_t)(item & 1) * (uint32_t)g.buf_pitch + win0;
+      const uint32_t base = win0 + (uint32_t)(item & 1) * pitch;
 
       float2 acc[PW][2];
 #pragma unroll
       for (int j = 0; j < PW; ++j) { acc[j][0] = bq[0]; acc[j][1] = bq[1]; }
 #pragma unroll
       for (int kh = 0; kh < 3; ++kh) {
-        const uint32_t rbase = base + (uint32_t)kh * row_bytes;
 #pragma unroll
         for (int col = 0; col < NCOL; ++col) {
           float2 x0, x1;
-          Vec4<XT>::load(rbase + (uint32_t)col * px_bytes, x0, x1);
+          Vec4<XT>::load(base + (uint32_t)kh * ROWB + (uint32_t)col * PXB, x0, x1);
 #pragma unroll
           for (int kw = 0; kw < 3; ++kw) {
             // input column col = j * STRIDE + kw
@@ -217,34 +233,36 @@ dwconv_tile_kernel(const __grid_constant__ CUtensorMap xmap, const XT *__restric
         }
       }
 
-      if (row_ok) {
-        const size_t tout = (size_t)t * frame_out + out0;
+      ST *spj = sp;
+      const XT *rpj = rp;
 #pragma unroll
-        for (int j = 0; j < PW; ++j) {
-          if (wo0 + j < g.Wo) {
-            const size_t o = tout + (size_t)(wo0 + j) * g.C;
-            if (res != nullptr) {
-              float r4[4];
-              load_pack<XT, 4>(res + o, r4);
-              acc[j][0] = __fadd2_rn(acc[j][0], make_float2(r4[0], r4[1]));
-              acc[j][1] = __fadd2_rn(acc[j][1], make_float2(r4[2], r4[3]));
-            }
-            const float2 s0 = lif2<KIND>(acc[j][0], v[j][0], p);
-            const float2 s1 = lif2<KIND>(acc[j][1], v[j][1], p);
-            const float s4[4] = {s0.x, s0.y, s1.x, s1.y};
-            store_pack<ST, 4>(spikes + o, s4);
+      for (int j = 0; j < PW; ++j) {
+        if ((live >> j) & 1) {
+          if (rpj != nullptr) {
+            float r4[4];
+            load_pack<XT, 4>(rpj, r4);
+            acc[j][0] = __fadd2_rn(acc[j][0], make_float2(r4[0], r4[1]));
+            acc[j][1] = __fadd2_rn(acc[j][1], make_float2(r4[2], r4[3]));
           }
+          const float2 s0 = lif2<KIND>(acc[j][0], v[j][0], p);
+          const float2 s1 = lif2<KIND>(acc[j][1], v[j][1], p);
+          const float s4[4] = {s0.x, s0.y, s1.x, s1.y};
+          store_pack<ST, 4>(spj, s4);
         }
+        spj += C;
+        if (rpj != nullptr) rpj += C;
       }
+      sp += frame_out;
+      if (rp != nullptr) rp += frame_out;
       __syncthreads();   // everyone is done with buffer item & 1 before the copy of item + 2 may overwrite it
     }
 
-    if (ok && row_ok) {
+    if (ok) {
 #pragma unroll
       for (int j = 0; j < PW; ++j) {
-        if (wo0 + j < g.Wo) {
+        if ((live >> j) & 1) {
           const float v4[4] = {v[j][0].x, v[j][0].y, v[j][1].x, v[j][1].y};
-          store_pack<VT, 4>(v_out + out0 + (size_t)(wo0 + j) * g.C, v4);
+          store_pack<VT, 4>(v_out + out0 + (size_t)j * C, v4);
         }
       }
     }
@@ -265,22 +283,15 @@ int launch_tile(const DwCall &a, cudaStream_t stream) {
   g.Ho = (a.H + 2 - 3) / a.stride + 1;
   g.Wo = (a.W + 2 - 3) / a.stride + 1;
   g.cs = a.C % 64 == 0 ? 64 : 32;
-  // strip length 8 or 7, whichever pads the row less (the feature maps of the ImageNet networks are multiples of 7)
-  auto padded = [&](int q) { const int tw = (g.Wo > q ? 2 : 1) * q; return (g.Wo + tw - 1) / tw * tw; };
-  int pw = padded(7) < padded(8) ? 7 : 8;
-  if (const char *e = std::getenv("SNNB_DW_STRIP")) {   // tuning override: 4, 7 or 8 output pixels per thread
-    const int q = std::atoi(e);
-    if (q == 4 || q == 7 || q == 8) pw = q;
-  }
-  g.ns = g.Wo > pw ? 2 : 1;
+  g.ns = NS;
   int threads = kDwThreads;
-  g.rows = threads / ((g.cs / 4) * g.ns);
-  // stride 2 reads four input pixels per output: half the rows keep two buffers of a tile within shared memory
+  g.rows = threads / ((g.cs / 4) * NS);
+  // stride 2 reads four input pixels per output: half the rows keep two buffers of a tile small
   if (a.stride == 2) { g.rows /= 2; threads /= 2; }
   while (g.rows > 1 && g.rows / 2 >= g.Ho) { g.rows /= 2; threads /= 2; }   // short maps: no idle rows
-  g.hw = (g.ns * pw - 1) * a.stride + 3;
+  g.hw = (NS * PW - 1) * a.stride + 3;
   g.hr = (g.rows - 1) * a.stride + 3;
-  g.nct = (g.Wo + g.ns * pw - 1) / (g.ns * pw);
+  g.nct = (g.Wo + NS * PW - 1) / (NS * PW);
   g.nrt = (g.Ho + g.rows - 1) / g.rows;
   g.nslab = a.C / g.cs;
   g.tx_bytes = g.hr * g.hw * g.cs * (int)sizeof(XT);
@@ -289,10 +300,10 @@ int launch_tile(const DwCall &a, cudaStream_t stream) {
   if (tiles * a.T > 0x7fffffffLL) return fail(SNNB_ERR_INVALID, "dwconv3x3_lif: problem too large");
   g.total_tiles = (int)tiles;
   const int sms = sm_count() > 0 ? sm_count() : 128;
-  const int per_sm = pw <= 4 ? 2 : 1;   // resident blocks per SM (register budget of the instantiation)
+  const int per_sm = 2 * (kDwThreads / threads);   // resident blocks per SM (register budget: two blocks of 256 threads)
   const long long grid = tiles < (long long)sms * per_sm ? tiles : (long long)sms * per_sm;
   const size_t smem = 2 * (size_t)g.buf_pitch + 128;
-  if (smem > 200 * 1024) return fail(SNNB_ERR_UNSUPPORTED, "dwconv3x3_lif: tile does not fit shared memory");
+  if (smem > 100 * 1024) return fail(SNNB_ERR_UNSUPPORTED, "dwconv3x3_lif: tile does not fit shared memory");
   CUtensorMap xm;
   {
     const int es = (int)sizeof(XT);
@@ -305,31 +316,31 @@ int launch_tile(const DwCall &a, cudaStream_t stream) {
   }
   const DwGeom gk = g;
   const int kind = (a.p.mode == 1 && a.p.hard) ? (a.p.v_reset == 0.f ? 2 : 1) : 0;
-#define SNNB_DWT2(STR, PWV, FASTV)                                                                                   \
+#define SNNB_DWT2(STR, CSV, KINDV)                                                                                  \
   do {                                                                                                              \
-    auto kern = dwconv_tile_kernel<XT, ST, VT, STR, PWV, FASTV>;                                                    \
-    static bool attr_done[16] = {};                                                                                 \
+    auto kern = dwconv_tile_kernel<XT, ST, VT, STR, CSV, KINDV>;                                                    \
+    static bool attr_done[64] = {};                                                                                 \
     int dev = 0;                                                                                                    \
     cudaGetDevice(&dev);                                                                                            \
-    if (dev < 16 && !attr_done[dev]) {                                                                              \
-      if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess)       \
+    if (dev < 0 || dev >= 64 || !attr_done[dev]) {                                                                  \
+      if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024) != cudaSuccess)       \
         return fail(SNNB_ERR_CUDA, "dwconv3x3_lif: cannot raise the shared-memory limit");                          \
-      attr_done[dev] = true;                                                                                        \
+      if (dev >= 0 && dev < 64) attr_done[dev] = true;                                                              \
     }                                                                                                               \
     kern<<<(unsigned)grid, threads, smem, stream>>>(xm, static_cast<const XT *>(a.w), static_cast<const XT *>(a.b), \
                                                     static_cast<const XT *>(a.res), static_cast<const VT *>(a.v_init), \
                                                     static_cast<ST *>(a.spikes), static_cast<VT *>(a.v_out), gk, a.p); \
   } while (0)
-#define SNNB_DWT(STR, PWV)                                                           \
+#define SNNB_DWT(STR, CSV)                                                           \
   do {                                                                               \
-    if (kind == 2) SNNB_DWT2(STR, PWV, 2);                                           \
-    else if (kind == 1) SNNB_DWT2(STR, PWV, 1);                                      \
-    else SNNB_DWT2(STR, PWV, 0);                                                     \
+    if (kind == 2) SNNB_DWT2(STR, CSV, 2);                                           \
+    else if (kind == 1) SNNB_DWT2(STR, CSV, 1);                                      \
+    else SNNB_DWT2(STR, CSV, 0);                                                     \
   } while (0)
   if (a.stride == 1) {
-    if (pw == 8) SNNB_DWT(1, 8); else if (pw == 7) SNNB_DWT(1, 7); else SNNB_DWT(1, 4);
+    if (g.cs == 64) SNNB_DWT(1, 64); else SNNB_DWT(1, 32);
   } else {
-    if (pw == 8) SNNB_DWT(2, 8); else if (pw == 7) SNNB_DWT(2, 7); else SNNB_DWT(2, 4);
+    if (g.cs == 64) SNNB_DWT(2, 64); else SNNB_DWT(2, 32);
   }
 #undef SNNB_DWT2
 #undef SNNB_DWT

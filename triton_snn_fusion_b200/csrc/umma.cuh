@@ -32,6 +32,15 @@ __device__ __forceinline__ bool elect_one() {
   return pred != 0;
 }
 
+// ------------------------------------------- programmatic dependent launch ----
+// A kernel launched with the programmatic-stream-serialization attribute may start while its predecessor in the
+// stream is still running; pdl_wait() blocks until that predecessor has completed and its writes are visible
+// (a no-op for an ordinary launch). pdl_trigger() lets the successor's blocks be scheduled as soon as resources
+// free up. Everything a block does before pdl_wait() must touch neither the predecessor's outputs nor any buffer
+// an earlier kernel may still read.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ------------------------------------------------------------ mbarrier ----
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));

@@ -255,15 +255,15 @@ def _launch(x_base, x_t_stride, T, weight, bias, residual, v_init, stride, paddi
 
 
 # The fastest dense-conv kernel loops over timestep pairs inside one launch, as the reference loops its windows
-# inside its kernel (kernels/benchmark_conv_lif_temporal_general.py:649), for any even T up to MAX_STEPS. Longer
+# inside its kernel (kernels/benchmark_conv_lif_temporal_general.py:649), for any even T up to MAX_STEPS (what every tensor-core kernel of the library accepts). Longer
 # (or odd, multiple-of-WINDOW) sequences run as windows of WINDOW steps with the membrane handed over in fp32: the
 # same arithmetic as one pass over all T, since the membrane is fp32 inside a kernel too.
 WINDOW = 4
-MAX_STEPS = 64
+MAX_STEPS = 32
 
 
 def _windowed(T, x_t_stride, groups, dtype) -> bool:
-    return (T > MAX_STEPS and T % WINDOW == 0 and x_t_stride != 0 and groups == 1 and _conv_path == "auto"
+    return (T > MAX_STEPS and T % WINDOW == 0 and x_t_stride != 0 and groups == 1 and _conv_path != "simt"
             and dtype in (torch.bfloat16, torch.float16))
 
 

@@ -103,7 +103,7 @@ def _impl(x_seq, weight, bias, v_init, v_threshold, v_reset, tau, detach_reset, 
 
     # Sequences beyond what one launch of the GEMM kernel takes run as windows of four timesteps with the membrane
     # handed over in fp32: the arithmetic of a single pass.
-    windowed = (T > _conv.MAX_STEPS and T % _conv.WINDOW == 0 and _conv._conv_path == "auto"
+    windowed = (T > _conv.MAX_STEPS and T % _conv.WINDOW == 0 and _conv._conv_path != "simt"
                 and x_seq.dtype in (torch.bfloat16, torch.float16))
     if windowed:
         carry = [torch.empty((M, N), dtype=torch.float32, device=x_seq.device) for _ in range(2)]
