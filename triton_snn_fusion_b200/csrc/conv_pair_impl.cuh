@@ -665,7 +665,7 @@ int launch(const ConvArgs &a, cudaStream_t stream) {
     // once per kernel instantiation and device: allow the largest dynamic shared-memory size any call may ask for
     static bool raised[2][64] = {};
     if (dev < 0 || dev >= 64 || !raised[g.s2][dev]) {
-      const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+      const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 225 * 1024);
       if (e != cudaSuccess) return fail(SNNB_ERR_CUDA, "conv_lif: cannot raise the shared-memory limit: %s", cudaGetErrorString(e));
       if (dev >= 0 && dev < 64) raised[g.s2][dev] = true;
     }
