@@ -309,3 +309,31 @@ def test_pointwise_conv_with_a_partial_channel_slab(case):
         [1, 1], [0, 0], [1, 1], 1, 1.0, 0.0, 2.0, False, strict=True)
     check_parity(r.spikes, r.v_next, rs, rv, dtype, what=str(case))
     assert 0.02 < float(rs.mean()) < 0.7
+
+
+@pytest.mark.parametrize("cout,T,soft", [(64, 8, False), (32, 2, True), (48, 1, False)])
+def test_conv3x3_few_output_channels(cout, T, soft):
+    """3x3 / stride 1 convs with at most 64 output channels (the first stage of a ResNet): the timestep-pair kernel
+    computes two kernel rows per MMA and adds the two accumulator halves in its epilogue. Other sequence lengths,
+    soft reset (the general LIF path), a partial channel tile, ragged tile edges, an initial membrane and a
+    residual."""
+    B, cin, H, W = 3, 128, 19, 13
+    dtype = torch.bfloat16
+    torch.manual_seed(cout + T)
+    xs = [(torch.rand(B, cin, H, W) < 0.15).to(dtype) for _ in range(T)]
+    w = (torch.randn(cout, cin, 3, 3) * (2.0 / (cin * 9)) ** 0.5 * 2.5).to(dtype)
+    b = (torch.randn(cout) * 0.1).to(dtype)
+    v0 = (torch.randn(B, cout, H, W) * 0.3).to(dtype)
+    res = [(torch.rand(B, cout, H, W) < 0.2).to(dtype) for _ in range(T)]
+    v_reset = -1.0 if soft else 0.0
+    rs, rv = orc.temporal_conv_lif([orc.widen(x) for x in xs], orc.widen(w), orc.widen(b), orc.widen(v0),
+                                   [1, 1], [1, 1], [1, 1], 1, 1.0, v_reset, 2.0, residuals=[orc.widen(r) for r in res])
+    r = _conv_be().run_triton_fused_temporal_conv_add_lif_state(
+        [x.to(DEV) for x in xs], [q.to(DEV) for q in res], w.to(DEV), b.to(DEV), v0.to(DEV), [1, 1], [1, 1], [1, 1], 1,
+        1.0, v_reset, 2.0, False, strict=True)
+    check_parity(r.spikes, r.v_next, rs, rv, dtype, what=f"cout {cout} T {T}")
+    assert 0.01 < float(rs.mean()) < 0.7
+    # the same conv without the LIF (conv + bias only)
+    ref = orc.temporal_conv_only([orc.widen(x) for x in xs], orc.widen(w), orc.widen(b), [1, 1], [1, 1])
+    out = _conv_be().conv_bias_only([x.to(DEV) for x in xs], w.to(DEV), b.to(DEV), [1, 1], [1, 1])
+    torch.testing.assert_close(out.cpu().float(), ref, rtol=1e-2, atol=1e-2)

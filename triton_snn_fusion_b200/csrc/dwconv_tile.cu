@@ -8,15 +8,11 @@
 //     need - the tile plus its one-pixel halo - into shared memory as a dense [row][col][channel] array;
 //     pixels outside the image arrive as zeros, which is the conv's padding, so no load is predicated.
 //     Two buffers: the copy of step t + 1 runs under the arithmetic of step t;
-//   * a thread owns 2 consecutive channels of a strip of PW = 8 consecutive output pixels of one row. Lanes run
-//     over channels first, so a warp's shared-memory reads and global stores cover whole 128-byte rows (the 64
-//     channels of one pixel). The 3x3 window slides along the strip: every input pair is read from shared memory
-//     and widened to fp32 once and feeds up to three accumulators, both channels in one instruction
-//     (fma.rn.f32x2). Two channels per thread keep the live state (9 weight pairs, 8 accumulator pairs, 8
-//     membrane pairs) far below the register budget of two resident blocks per SM; with four channels the
-//     compiler ran out of registers and re-loaded weights and moved pairs around, which doubled the
-//     instruction count of a kernel that is bound by instruction issue;
-//   * the PW x 2 membrane potentials of a thread stay in registers for all T steps.
+//   * a thread owns 4 consecutive channels of a strip of PW = 4 consecutive output pixels of one row. Lanes run
+//     over channels first, so a warp's shared-memory reads and global stores cover whole 128-byte rows. The
+//     3x3 window slides along the strip: every input vector is read from shared memory and widened to fp32
+//     once and feeds up to three accumulators, two channels per instruction (fma.rn.f32x2);
+//   * the PW x 4 membrane potentials of a thread stay in registers for all T steps.
 // Algorithmic bytes per call: T*B*C*(H*W*s_x + Ho*Wo*s_s [+ Ho*Wo*s_x residual]) + B*C*Ho*Wo*s_v*(1 or 2).
 #include <cstdlib>
 #include <type_traits>
@@ -44,26 +40,29 @@ struct DwGeom {
   int buf_pitch;   // distance between the two buffers (tx_bytes rounded up to 128)
 };
 
-template <typename XT> struct Vec2;   // two consecutive channels in shared memory -> one float2
-template <> struct Vec2<float> {
-  static __device__ __forceinline__ float2 load(uint32_t addr) {
-    float2 r;
-    asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(r.x), "=f"(r.y) : "r"(addr));
-    return r;
+template <typename XT> struct Vec4;   // four consecutive channels in shared memory -> two float2
+template <> struct Vec4<float> {
+  static __device__ __forceinline__ void load(uint32_t addr, float2 &a, float2 &b) {
+    float4 r;
+    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(r.x), "=f"(r.y), "=f"(r.z), "=f"(r.w) : "r"(addr));
+    a = make_float2(r.x, r.y);
+    b = make_float2(r.z, r.w);
   }
 };
-template <> struct Vec2<__nv_bfloat16> {
-  static __device__ __forceinline__ float2 load(uint32_t addr) {
-    uint32_t u;
-    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(u) : "r"(addr));
-    return make_float2(__uint_as_float(u << 16), __uint_as_float(u & 0xffff0000u));
+template <> struct Vec4<__nv_bfloat16> {
+  static __device__ __forceinline__ void load(uint32_t addr, float2 &a, float2 &b) {
+    uint32_t lo, hi;
+    asm volatile("ld.shared.v2.b32 {%0, %1}, [%2];" : "=r"(lo), "=r"(hi) : "r"(addr));
+    a = make_float2(__uint_as_float(lo << 16), __uint_as_float(lo & 0xffff0000u));
+    b = make_float2(__uint_as_float(hi << 16), __uint_as_float(hi & 0xffff0000u));
   }
 };
-template <> struct Vec2<__half> {
-  static __device__ __forceinline__ float2 load(uint32_t addr) {
-    uint32_t u;
-    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(u) : "r"(addr));
-    return __half22float2(*reinterpret_cast<const __half2 *>(&u));
+template <> struct Vec4<__half> {
+  static __device__ __forceinline__ void load(uint32_t addr, float2 &a, float2 &b) {
+    uint32_t lo, hi;
+    asm volatile("ld.shared.v2.b32 {%0, %1}, [%2];" : "=r"(lo), "=r"(hi) : "r"(addr));
+    a = __half22float2(*reinterpret_cast<const __half2 *>(&lo));
+    b = __half22float2(*reinterpret_cast<const __half2 *>(&hi));
   }
 };
 
@@ -94,12 +93,12 @@ __device__ __forceinline__ float2 lif2(float2 y, float2 &v, const LifParams &p) 
 // Persistent: a block walks tiles blockIdx.x, blockIdx.x + gridDim.x, ... and treats (tile, timestep) pairs as one
 // stream of work items, so the copy of the next item - the next timestep, or the first timestep of the next tile -
 // always runs under the arithmetic of the current one and only the very first copy of a block is exposed.
-// The tile geometry is fixed at compile time (strips of PW pixels, NS strips per tile row, CS channels), so every
-// shared-memory read of the inner loop is "window base + constant": the loop body is load, widen, multiply-add
-// with no address arithmetic left in it.
-constexpr int PW = 8;
+// The tile geometry is fixed at compile time (strips of PW = 4 pixels, NS = 2 strips per tile row, CS channels), so
+// every shared-memory read of the inner loop is "window base + constant": the loop body is the 16-byte-free
+// sequence load, widen, multiply-add with no address arithmetic left in it.
+constexpr int PW = 4, NS = 2;
 
-template <typename XT, typename ST, typename VT, int STRIDE, int CS, int NS, int KIND>
+template <typename XT, typename ST, typename VT, int STRIDE, int CS, int KIND>
 __global__ void __launch_bounds__(kDwThreads, 2)
 dwconv_tile_kernel(const __grid_constant__ CUtensorMap xmap, const XT *__restrict__ w, const XT *__restrict__ bias,
                    const XT *__restrict__ res, const VT *v_init, ST *__restrict__ spikes, VT *v_out,
@@ -111,7 +110,7 @@ dwconv_tile_kernel(const __grid_constant__ CUtensorMap xmap, const XT *__restric
   const uint32_t bar = umma::smem_u32(full);
   volatile int *abort_flag = &abort_s;
 
-  constexpr int CGN = CS / 2;                                  // channel pairs per pixel
+  constexpr int CGN = CS / 4;                                  // channel quads per pixel
   constexpr int HWD = (NS * PW - 1) * STRIDE + 3;              // halo tile width in pixels
   constexpr uint32_t PXB = CS * sizeof(XT);                    // bytes per pixel
   constexpr uint32_t ROWB = HWD * PXB;                         // bytes per halo row
@@ -158,24 +157,30 @@ dwconv_tile_kernel(const __grid_constant__ CUtensorMap xmap, const XT *__restric
   if (tid == 0 && n_items > 0) issue_next();
 
   // this thread's window inside a halo tile: rows row*STRIDE .., columns strip*PW*STRIDE ..
-  const uint32_t win0 = smem + (uint32_t)(row * STRIDE) * ROWB + (uint32_t)(strip * PW * STRIDE) * PXB + (uint32_t)cg * 2u * sizeof(XT);
+  const uint32_t win0 = smem + (uint32_t)(row * STRIDE) * ROWB + (uint32_t)(strip * PW * STRIDE) * PXB + (uint32_t)cg * 4u * sizeof(XT);
   const size_t frame_out = (size_t)nB * Ho * Wo * C;
 
-  float2 wq[9];   // weights and bias of this thread's channel pair
-  float2 bq = make_float2(0.f, 0.f);
+  float2 wq[9][2];   // weights and bias of this thread's four channels, as channel pairs
+  float2 bq[2];
   int cur_slab = -1;
   int item = 0;
   bool ok = true;
   for (int i = 0; i < my_tiles && ok; ++i) {
     int ct, rt, b, slab;
     decode((int)blockIdx.x + i * (int)gridDim.x, ct, rt, b, slab);
-    const int c = slab * CS + cg * 2;
+    const int c = slab * CS + cg * 4;
     if (slab != cur_slab) {
       cur_slab = slab;
 #pragma unroll
-      for (int k = 0; k < 9; ++k)
-        wq[k] = make_float2(DT<XT>::to_f(w[(size_t)c * 9 + k]), DT<XT>::to_f(w[(size_t)(c + 1) * 9 + k]));
-      bq = bias != nullptr ? make_float2(DT<XT>::to_f(bias[c]), DT<XT>::to_f(bias[c + 1])) : make_float2(0.f, 0.f);
+      for (int k = 0; k < 9; ++k) {
+        wq[k][0] = make_float2(DT<XT>::to_f(w[(size_t)(c + 0) * 9 + k]), DT<XT>::to_f(w[(size_t)(c + 1) * 9 + k]));
+        wq[k][1] = make_float2(DT<XT>::to_f(w[(size_t)(c + 2) * 9 + k]), DT<XT>::to_f(w[(size_t)(c + 3) * 9 + k]));
+      }
+      bq[0] = bq[1] = make_float2(0.f, 0.f);
+      if (bias != nullptr) {
+        bq[0] = make_float2(DT<XT>::to_f(bias[c]), DT<XT>::to_f(bias[c + 1]));
+        bq[1] = make_float2(DT<XT>::to_f(bias[c + 2]), DT<XT>::to_f(bias[c + 3]));
+      }
     }
     const int ho = rt * rows + row;
     const int wo0 = (ct * NS + strip) * PW;
@@ -186,14 +191,15 @@ dwconv_tile_kernel(const __grid_constant__ CUtensorMap xmap, const XT *__restric
       if (ho < Ho && wo0 + j < Wo) live |= 1 << j;
     const size_t out0 = (((size_t)b * Ho + (ho < Ho ? ho : 0)) * Wo + (wo0 < Wo ? wo0 : 0)) * C + c;   // (b, ho, wo0, c)
 
-    float2 v[PW];
+    float2 v[PW][2];
 #pragma unroll
     for (int j = 0; j < PW; ++j) {
-      v[j] = make_float2(0.f, 0.f);
+      v[j][0] = v[j][1] = make_float2(0.f, 0.f);
       if (v_init != nullptr && ((live >> j) & 1)) {
-        float t2[2];
-        load_pack_stream<VT, 2>(v_init + out0 + (size_t)j * C, t2);
-        v[j] = make_float2(t2[0], t2[1]);
+        float t4[4];
+        load_pack_stream<VT, 4>(v_init + out0 + (size_t)j * C, t4);
+        v[j][0] = make_float2(t4[0], t4[1]);
+        v[j][1] = make_float2(t4[2], t4[3]);
       }
     }
     ST *sp = spikes + out0;
@@ -206,41 +212,58 @@ dwconv_tile_kernel(const __grid_constant__ CUtensorMap xmap, const XT *__restric
       if (!ok) break;
       const uint32_t base = win0 + (uint32_t)(item & 1) * pitch;
 
-      float2 acc[PW];
+      float2 acc[PW][2];
 #pragma unroll
-      for (int j = 0; j < PW; ++j) acc[j] = bq;
+      for (int j = 0; j < PW; ++j) { acc[j][0] = bq[0]; acc[j][1] = bq[1]; }
 #pragma unroll
       for (int kh = 0; kh < 3; ++kh) {
 #pragma unroll
         for (int col = 0; col < NCOL; ++col) {
-          const float2 x = Vec2<XT>::load(base + (uint32_t)kh * ROWB + (uint32_t)col * PXB);
+          float2 x0, x1;
+          Vec4<XT>::load(base + (uint32_t)kh * ROWB + (uint32_t)col * PXB, x0, x1);
 #pragma unroll
           for (int kw = 0; kw < 3; ++kw) {
             // input column col = j * STRIDE + kw
             if ((col - kw) >= 0 && (col - kw) % STRIDE == 0 && (col - kw) / STRIDE < PW) {   // resolved when unrolled
               const int j = (col - kw) / STRIDE;
-              acc[j] = __ffma2_rn(wq[kh * 3 + kw], x, acc[j]);
+              acc[j][0] = __ffma2_rn(wq[kh * 3 + kw][0], x0, acc[j][0]);
+              acc[j][1] = __ffma2_rn(wq[kh * 3 + kw][1], x1, acc[j][1]);
             }
           }
         }
       }
 
-      ST *spj = sp;
-      const XT *rpj = rp;
+      if (live == (1 << PW) - 1 && rp == nullptr) {
+        // the common case: every output of the strip exists and there is no residual: straight-line code
+        ST *spj = sp;
 #pragma unroll
-      for (int j = 0; j < PW; ++j) {
-        if ((live >> j) & 1) {
-          if (rpj != nullptr) {
-            float r2[2];
-            load_pack<XT, 2>(rpj, r2);
-            acc[j] = __fadd2_rn(acc[j], make_float2(r2[0], r2[1]));
-          }
-          const float2 s = lif2<KIND>(acc[j], v[j], p);
-          const float s2[2] = {s.x, s.y};
-          store_pack<ST, 2>(spj, s2);
+        for (int j = 0; j < PW; ++j) {
+          const float2 s0 = lif2<KIND>(acc[j][0], v[j][0], p);
+          const float2 s1 = lif2<KIND>(acc[j][1], v[j][1], p);
+          const float s4[4] = {s0.x, s0.y, s1.x, s1.y};
+          store_pack<ST, 4>(spj, s4);
+          spj += C;
         }
-        spj += C;
-        if (rpj != nullptr) rpj += C;
+      } else {
+        ST *spj = sp;
+        const XT *rpj = rp;
+#pragma unroll
+        for (int j = 0; j < PW; ++j) {
+          if ((live >> j) & 1) {
+            if (rpj != nullptr) {
+              float r4[4];
+              load_pack<XT, 4>(rpj, r4);
+              acc[j][0] = __fadd2_rn(acc[j][0], make_float2(r4[0], r4[1]));
+              acc[j][1] = __fadd2_rn(acc[j][1], make_float2(r4[2], r4[3]));
+            }
+            const float2 s0 = lif2<KIND>(acc[j][0], v[j][0], p);
+            const float2 s1 = lif2<KIND>(acc[j][1], v[j][1], p);
+            const float s4[4] = {s0.x, s0.y, s1.x, s1.y};
+            store_pack<ST, 4>(spj, s4);
+          }
+          spj += C;
+          if (rpj != nullptr) rpj += C;
+        }
       }
       sp += frame_out;
       if (rp != nullptr) rp += frame_out;
@@ -251,8 +274,8 @@ dwconv_tile_kernel(const __grid_constant__ CUtensorMap xmap, const XT *__restric
 #pragma unroll
       for (int j = 0; j < PW; ++j) {
         if ((live >> j) & 1) {
-          const float v2[2] = {v[j].x, v[j].y};
-          store_pack<VT, 2>(v_out + out0 + (size_t)j * C, v2);
+          const float v4[4] = {v[j][0].x, v[j][0].y, v[j][1].x, v[j][1].y};
+          store_pack<VT, 4>(v_out + out0 + (size_t)j * C, v4);
         }
       }
     }
@@ -273,16 +296,15 @@ int launch_tile(const DwCall &a, cudaStream_t stream) {
   g.Ho = (a.H + 2 - 3) / a.stride + 1;
   g.Wo = (a.W + 2 - 3) / a.stride + 1;
   g.cs = a.C % 64 == 0 ? 64 : 32;
-  g.ns = g.Wo > PW ? 2 : 1;
-  const int NSv = g.ns;
+  g.ns = NS;
   int threads = kDwThreads;
-  g.rows = threads / ((g.cs / 2) * NSv);
+  g.rows = threads / ((g.cs / 4) * NS);
   // stride 2 reads four input pixels per output: half the rows keep two buffers of a tile small
   if (a.stride == 2) { g.rows /= 2; threads /= 2; }
   while (g.rows > 1 && g.rows / 2 >= g.Ho) { g.rows /= 2; threads /= 2; }   // short maps: no idle rows
-  g.hw = (NSv * PW - 1) * a.stride + 3;
+  g.hw = (NS * PW - 1) * a.stride + 3;
   g.hr = (g.rows - 1) * a.stride + 3;
-  g.nct = (g.Wo + NSv * PW - 1) / (NSv * PW);
+  g.nct = (g.Wo + NS * PW - 1) / (NS * PW);
   g.nrt = (g.Ho + g.rows - 1) / g.rows;
   g.nslab = a.C / g.cs;
   g.tx_bytes = g.hr * g.hw * g.cs * (int)sizeof(XT);
@@ -306,10 +328,10 @@ int launch_tile(const DwCall &a, cudaStream_t stream) {
     if (rc != SNNB_OK) return rc;
   }
   const DwGeom gk = g;
-  const int kind = (a.p.mode == 1 && a.p.hard && a.p.v_reset == 0.f) ? 2 : 0;
-#define SNNB_DWT2(STR, CSV, NSV, KINDV)                                                                                  \
+  const int kind = (a.p.mode == 1 && a.p.hard) ? (a.p.v_reset == 0.f ? 2 : 1) : 0;
+#define SNNB_DWT2(STR, CSV, KINDV)                                                                                  \
   do {                                                                                                              \
-    auto kern = dwconv_tile_kernel<XT, ST, VT, STR, CSV, NSV, KINDV>;                                                    \
+    auto kern = dwconv_tile_kernel<XT, ST, VT, STR, CSV, KINDV>;                                                    \
     static bool attr_done[64] = {};                                                                                 \
     int dev = 0;                                                                                                    \
     cudaGetDevice(&dev);                                                                                            \
@@ -324,10 +346,9 @@ int launch_tile(const DwCall &a, cudaStream_t stream) {
   } while (0)
 #define SNNB_DWT(STR, CSV)                                                           \
   do {                                                                               \
-    if (kind == 2 && NSv == 2) SNNB_DWT2(STR, CSV, 2, 2);                            \
-    else if (kind == 2) SNNB_DWT2(STR, CSV, 1, 2);                                   \
-    else if (NSv == 2) SNNB_DWT2(STR, CSV, 2, 0);                                    \
-    else SNNB_DWT2(STR, CSV, 1, 0);                                                  \
+    if (kind == 2) SNNB_DWT2(STR, CSV, 2);                                           \
+    else if (kind == 1) SNNB_DWT2(STR, CSV, 1);                                      \
+    else SNNB_DWT2(STR, CSV, 0);                                                     \
   } while (0)
   if (a.stride == 1) {
     if (g.cs == 64) SNNB_DWT(1, 64); else SNNB_DWT(1, 32);
