@@ -313,10 +313,9 @@ def test_pointwise_conv_with_a_partial_channel_slab(case):
 
 @pytest.mark.parametrize("cout,T,soft", [(64, 8, False), (32, 2, True), (48, 1, False)])
 def test_conv3x3_few_output_channels(cout, T, soft):
-    """3x3 / stride 1 convs with at most 64 output channels (the first stage of a ResNet): the timestep-pair kernel
-    computes two kernel rows per MMA and adds the two accumulator halves in its epilogue. Other sequence lengths,
-    soft reset (the general LIF path), a partial channel tile, ragged tile edges, an initial membrane and a
-    residual."""
+    """3x3 / stride 1 convs with at most 64 output channels (the first stage of a ResNet), which fill only half of
+    the timestep-pair kernel's 128 weight rows: other sequence lengths, soft reset (the general LIF path), a
+    partial channel tile, ragged tile edges, an initial membrane and a residual."""
     B, cin, H, W = 3, 128, 19, 13
     dtype = torch.bfloat16
     torch.manual_seed(cout + T)

@@ -33,9 +33,6 @@ int fail(int code, const char *fmt, ...);
 // Whether kernels that support it are launched with programmatic dependent launch (on unless the environment
 // variable SNNB_PDL is set to 0).
 bool pdl_enabled();
-// Whether 3x3 convs with at most 64 output channels use the two-kernel-rows-per-MMA form of the timestep-pair
-// kernel (on unless the environment variable SNNB_TWIN is set to 0; the switch exists to compare the two forms).
-bool twin_enabled();
 
 // Number of SMs of the current device (queried once per device; 0 if the query fails).
 int sm_count();

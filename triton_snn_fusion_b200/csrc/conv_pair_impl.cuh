@@ -47,11 +47,6 @@ constexpr int kIdentBytes = 192 * 128;                 // zero rows / 64x64 iden
 constexpr int kWRingP = 5;                             // weight-tile slots (16 KB each): a load must cover ~1 us of L2 latency
 constexpr int kWSlot = 128 * 128;
 constexpr int kEpiW = 8;
-// "twin" mode (3x3 / stride 1 conv with at most 64 output channels): see PairGeom::twin
-constexpr int kTwinIdentBytes = 128 * 128;             // 64 identity rows followed by 64 zero rows
-constexpr int kStagePitch = 272;                       // bytes per channel row of the exchange buffer (64 floats + 16: conflict-free 16-byte accesses)
-constexpr int kStageHalf = 64 * kStagePitch;           // one tile half (8 output rows) of 64 channels
-constexpr int kStageBytes = 2 * kStageHalf;
 constexpr int kHaloWarpP = kEpiW, kWWarpP = kEpiW + 1, kMmaWarpP = kEpiW + 2;
 constexpr int kThreadsP = 32 * (kEpiW + 3);
 
@@ -71,15 +66,7 @@ struct PairGeom {
   int stack;  // maps of at most 7 x 8: two images per tile, image b in row groups 0.., image b + 1 in groups 8..
               // (halo rows 0..8 and 8..16 of a timestep's region: row 8 is the zero padding of both, row 16
               // is row 0 of the next region, which is the zero top padding of whatever is stored there)
-  int twin;   // 3x3 / stride 1 with Cout <= 64: M rows 0..63 carry the weights of kernel row kh, rows 64..127 those of
-              // kernel row kh + 1, against the SAME pixel operand. Accumulator rows 0..63 (D1) then hold the usual
-              // partial sums and rows 64..127 (D2) the contribution of kernel row kh + 1 to the output pixel one
-              // image row further up, so out[p] = D1[p] + D2[p + one row]. Kernel rows 0 and 1 share their three
-              // MMA groups, row 2 takes three more with zero weights in rows 64..127: 6 groups per slab instead
-              // of 9. The two halves live in different TMEM lanes: the warps that can read lanes 64..127 pass
-              // D2 to the LIF warps through shared memory.
-  int stage_off;   // twin: byte offset of the exchange buffer from the aligned start of dynamic shared memory
-  int dup;    // Cout <= 64 (other shapes): the 64 weight rows are loaded twice (M rows 64..127 repeat 0..63) so that all
+  int dup;    // Cout <= 64: the 64 weight rows are loaded twice (M rows 64..127 repeat 0..63) so that all
               // eight epilogue warps can read the accumulator and split the pixels four ways
   long long wait_limit;   // bound of every mbarrier wait, in SM cycles (about two seconds unless a self-test shortens it)
   int drop_load;          // self-test: CTA 0 announces its first weight tile but never loads it, so that its waits run out
@@ -92,18 +79,12 @@ struct PairGeom {
 // whose input rows / columns have the parity of phase ph = 2a + b.
 template <bool S2>
 __device__ __forceinline__ int phase_ntaps(const PairGeom &g, int ph) {
-  return S2 ? ((ph & 2) ? 2 : 1) * ((ph & 1) ? 2 : 1) : (g.twin ? 6 : g.ntaps);
+  return S2 ? ((ph & 2) ? 2 : 1) * ((ph & 1) ? 2 : 1) : g.ntaps;
 }
 // j-th tap of phase ph: its index in the weight tensor (kh * 3 + kw) and its row offset inside the halo tile.
 template <bool S2>
 __device__ __forceinline__ void phase_tap(const PairGeom &g, int ph, int j, int &wtap, int &off) {
   if constexpr (!S2) {
-    if (g.twin) {   // group j: kernel rows (0, 1) for j < 3, (2, none) for j >= 3; wtap = the tap of M rows 0..63
-      const int kh = j < 3 ? 0 : 2, kw = j < 3 ? j : j - 3;
-      wtap = kh * 3 + kw;
-      off = kh * kPW + kw;
-      return;
-    }
     const int kh = g.ntaps == 1 ? 1 : j / 3, kw = g.ntaps == 1 ? 1 : j - kh * 3;
     wtap = g.ntaps == 1 ? 0 : j;
     off = kh * kPW + kw;
@@ -220,43 +201,6 @@ __device__ __forceinline__ void pair_epilogue_full(const LifParams &p, uint32_t 
   }
 }
 
-// Twin mode, one timestep for the 64 (or 48) pixels of this LIF thread's channel: out[p] = D1[p] (tensor memory,
-// this thread's lane) + D2[p + one row] (passed through shared memory by the warp that can read lanes 64..127)
-// + bias, then LIF / plain store. FULL: every pixel of the thread exists and is owned, nothing is predicated.
-template <typename XT, typename ST, int KIND, bool FULL>
-__device__ __forceinline__ void twin_step(const LifParams &p, uint32_t tmem_addr, uint32_t stage_row, float bias_c,
-                                          ST *__restrict__ out, const PixMap &pm, float (&v)[64], int nchunks) {
-#pragma unroll
-  for (int chunk = 0; chunk < 4; ++chunk) {
-    if (chunk < nchunks) {   // warp-uniform; written as a guard so that the loop stays fully unrolled
-      uint32_t a[16];
-      umma::tmem_ld_x16(tmem_addr + (uint32_t)(chunk * 16), a);
-      float d2[16];
-#pragma unroll
-      for (int q = 0; q < 4; ++q)
-        asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
-                     : "=f"(d2[4 * q]), "=f"(d2[4 * q + 1]), "=f"(d2[4 * q + 2]), "=f"(d2[4 * q + 3])
-                     : "r"(stage_row + (uint32_t)(chunk * 64 + q * 16)));
-      umma::tmem_ld_wait();
-#pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        const int r = chunk * 2 + (i >> 3), j = i & 7;   // a chunk of 16 pixels is two tile rows of 8
-        const bool ok = FULL || (((pm.rows_ok >> r) & 1) && ((pm.cols_ok >> j) & 1));
-        const long long o = pm.row0_off + (long long)r * pm.row_stride + j * pm.Cout;
-        const float y = (__uint_as_float(a[i]) + d2[i]) + bias_c;
-        if (ok) {
-          if constexpr (KIND == kLifOff) {
-            reinterpret_cast<XT *>(out)[o] = DT<XT>::from_f(y);
-          } else {
-            const float s = (KIND == kLifFast) ? lif_step_t<1, true>(y, v[chunk * 16 + i], p) : lif_step(y, v[chunk * 16 + i], p);
-            out[o] = DT<ST>::from_f(s);
-          }
-        }
-      }
-    }
-  }
-}
-
 template <typename XT, typename ST, typename VT, bool S2>
 __global__ void __launch_bounds__(kThreadsP)
 conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap,
@@ -276,7 +220,7 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
   const uint32_t smem_base = (umma::smem_u32(smem_raw) + 1023u) & ~1023u;
   // [identity block (residual path only)] [weight ring] [halo ring]
   const uint32_t ident_base = smem_base;
-  const uint32_t w_base = smem_base + ((g.has_res && !g.sc_slabs) ? (uint32_t)(g.twin ? kTwinIdentBytes : kIdentBytes) : 0u);
+  const uint32_t w_base = smem_base + ((g.has_res && !g.sc_slabs) ? (uint32_t)kIdentBytes : 0u);
   const uint32_t h_base = w_base + (uint32_t)(g.wring * kWSlot);
   const uint32_t slot_bytes = (uint32_t)(g.tq * kHaloT);
   const uint32_t bar_base = umma::smem_u32(bars);
@@ -335,13 +279,11 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
     // the 128-byte swizzle puts it), 64 zero rows. Read from row 64 it is [I; 0] (channels n0..n0+63 of the
     // tile), read from row 0 it is [0; I] (channels n0+64..n0+127).
     uint4 *blk = reinterpret_cast<uint4 *>(smem_raw + (ident_base - umma::smem_u32(smem_raw)));
-    const int ident_bytes = g.twin ? kTwinIdentBytes : kIdentBytes;
-    for (int i = threadIdx.x; i < ident_bytes / 16; i += 32 * kEpiW) blk[i] = make_uint4(0u, 0u, 0u, 0u);
+    for (int i = threadIdx.x; i < kIdentBytes / 16; i += 32 * kEpiW) blk[i] = make_uint4(0u, 0u, 0u, 0u);
     asm volatile("bar.sync 2, %0;" ::"r"(32 * kEpiW) : "memory");
     if (g.dup ? threadIdx.x < 128 : threadIdx.x < 64) {
-      // dup mode: rows 0..127 carry the identity twice (row r has its one in column r % 64); twin mode: the block
-      // is [I; 0], the identity in rows 0..63
-      const int k = threadIdx.x & 63, r = g.dup ? (int)threadIdx.x : (g.twin ? k : 64 + k);
+      // dup mode: rows 0..127 carry the identity twice (row r has its one in column r % 64)
+      const int k = threadIdx.x & 63, r = g.dup ? (int)threadIdx.x : 64 + k;
       uint8_t *row = smem_raw + (ident_base - umma::smem_u32(smem_raw)) + r * 128;
       *reinterpret_cast<XT *>(row + (((k >> 3) ^ (r & 7)) << 4) + (k & 7) * 2) = DT<XT>::from_f(1.0f);
     }
@@ -425,10 +367,6 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
               umma::mbar_expect_tx(wfull(ws), (uint32_t)kWSlot);
               if (g.drop_load && blockIdx.x == 0 && tile == (int)blockIdx.x && pair == 0 && sp == 0 && j == 0) {
                 // self-test of the bounded waits: this tile never arrives
-              } else if (g.twin) {   // rows 0..63: tap (kh, kw); rows 64..127: tap (kh + 1, kw), or zeros for kh = 2
-                const int below = j < 3 ? (tap + 3) * g.Cin + slab * 64 : 9 * g.Cin;   // past the end: filled with zeros
-                umma::tma_load_2d(w_base + ws * (uint32_t)kWSlot, &wmap64, wfull(ws), tap * g.Cin + slab * 64, 0);
-                umma::tma_load_2d(w_base + ws * (uint32_t)kWSlot + 64u * 128u, &wmap64, wfull(ws), below, 0);
               } else if (g.dup) {   // the same 64 rows into both halves of the tile
                 umma::tma_load_2d(w_base + ws * (uint32_t)kWSlot, &wmap64, wfull(ws), tap * g.Cin + slab * 64, 0);
                 umma::tma_load_2d(w_base + ws * (uint32_t)kWSlot + 64u * 128u, &wmap64, wfull(ws), tap * g.Cin + slab * 64, 0);
@@ -506,7 +444,7 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
               if (!ok) break;
               adesc = wdesc0 + (uint64_t)((ws * (uint32_t)kWSlot) >> 4);
             } else {
-              adesc = umma::make_sw128_kmajor_desc(ident_base + ((rs == 0 && !g.dup && !g.twin) ? 64u * 128u : 0u));
+              adesc = umma::make_sw128_kmajor_desc(ident_base + ((rs == 0 && !g.dup) ? 64u * 128u : 0u));
             }
             umma::tc_fence_after_sync();
             const uint64_t xdesc = hdesc0 + (uint64_t)((slot * slot_bytes + (uint32_t)(kPW + 1) * 128u) >> 4);
@@ -524,116 +462,6 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
       }
     }
     __syncwarp();
-  } else if (g.twin) {
-    // ------------------------------------------------- epilogue, twin mode (see PairGeom::twin)
-    // Warps 0, 1, 4, 5 (TMEM lanes 0..63 = D1) run the LIF for channels 0..63: warps 0, 1 for tile rows 0..7, warps
-    // 4, 5 for rows 8..13. Warps 2, 3, 6, 7 (lanes 64..127 = D2) copy the D2 values those rows need - D2 rows 1..8
-    // and 9..14 - into the exchange buffer, one timestep at a time. Both groups meet at two named barriers per
-    // timestep. Whether a wait on the accumulator gave up is agreed on by all eight warps together, so nobody is
-    // left behind at a barrier.
-    const int quarter = warp & 3;
-    const bool mover = quarter >= 2;
-    const int half = warp >> 2;
-    const int ch = (quarter & 1) * 32 + lane;
-    const int r_begin = half * 8, my_rows = 8;
-    const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
-    const uint32_t stage_row = smem_base + (uint32_t)g.stage_off + (uint32_t)half * kStageHalf + (uint32_t)ch * kStagePitch;
-    const long long frame_out = (long long)g.B * g.Ho * g.Wo * g.Cout;
-    bool ok = true;
-    uint32_t it = 0;
-    for (int tile = blockIdx.x; tile < g.total_tiles && ok; tile += gridDim.x, ++it) {
-      int n0, w0, h0, b, wlo, hlo;
-      decode(tile, n0, w0, h0, b, wlo, hlo);
-      if (!g.own) { wlo = w0; hlo = h0; }
-      const int row_first = h0 + r_begin;
-      const int row_limit = kTileRows - r_begin;
-      const bool c_ok = !mover && ch < g.Cout;
-      const float bias_c = (bias != nullptr && c_ok) ? DT<XT>::to_f(bias[ch]) : 0.f;
-      PixMap pm;
-      pm.Cout = g.Cout;
-      pm.row_stride = g.Wo * g.Cout;
-      pm.row0_off = ((long long)b * g.Ho + row_first) * pm.row_stride + (long long)w0 * g.Cout + ch;
-      pm.rows_ok = 0;
-      pm.cols_ok = 0;
-#pragma unroll
-      for (int r = 0; r < 8; ++r)
-        if (c_ok && r < row_limit && row_first + r < g.Ho && row_first + r >= hlo) pm.rows_ok |= 1 << r;
-#pragma unroll
-      for (int j = 0; j < 8; ++j)
-        if (w0 + j < g.Wo && w0 + j >= wlo) pm.cols_ok |= 1 << j;
-      const int rows_valid = min(my_rows, row_limit);   // 8, or 6 for the lower half (rows 14, 15 never exist)
-      const int nchunks = (rows_valid + 1) / 2;          // 16-pixel chunks this thread converts = D2 chunks its mover copies
-      const bool full = __all_sync(0xffffffffu, mover || (pm.rows_ok == (1 << rows_valid) - 1 && pm.cols_ok == 0xFF));
-      float v[64];
-#pragma unroll
-      for (int i = 0; i < 64; ++i) v[i] = 0.f;
-      if (g.lif && v_init != nullptr) {
-#pragma unroll
-        for (int i = 0; i < 64; ++i)
-          if (((pm.rows_ok >> (i >> 3)) & 1) && ((pm.cols_ok >> (i & 7)) & 1))
-            v[i] = DT<VT>::to_f(v_init[pm.row0_off + (long long)(i >> 3) * pm.row_stride + (i & 7) * pm.Cout]);
-      }
-      for (int pair = 0; pair < g.npairs && ok; ++pair) {
-        const uint32_t acc = (uint32_t)(pair & 1);
-        const uint32_t use = it * (uint32_t)((g.npairs + 1 - (int)acc) >> 1) + (uint32_t)(pair >> 1);
-        if (lane == 0) ok = umma::mbar_wait(accfull(acc), use & 1u, abort_flag, wl);
-        ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
-        {   // all eight warps agree: continue only if every one of them saw the accumulator arrive
-          uint32_t all_ok;
-          asm volatile(
-              "{\n\t"
-              ".reg .pred P, Q;\n\t"
-              "setp.ne.b32 P, %1, 0;\n\t"
-              "bar.red.and.pred Q, 3, %2, P;\n\t"
-              "selp.b32 %0, 1, 0, Q;\n\t"
-              "}\n"
-              : "=r"(all_ok) : "r"((int)ok), "r"(32 * kEpiW) : "memory");
-          ok = all_ok != 0;
-        }
-        if (!ok) break;
-        umma::tc_fence_after_sync();
-        for (int q = 0; q < g.tq; ++q) {
-          const uint32_t col0 = acc * 256u + (uint32_t)(q * 128 + r_begin * 8);
-          if (mover) {   // D2 of the image rows below: pixels +8 .. of this half
-#pragma unroll
-            for (int chunk = 0; chunk < 4; ++chunk)
-              if (chunk < nchunks) {
-                uint32_t a[16];
-                umma::tmem_ld_x16(lane_base + col0 + 8u + (uint32_t)(chunk * 16), a);
-                umma::tmem_ld_wait();
-#pragma unroll
-                for (int k = 0; k < 4; ++k)
-                  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stage_row + (uint32_t)(chunk * 64 + k * 16)),
-                               "r"(a[4 * k]), "r"(a[4 * k + 1]), "r"(a[4 * k + 2]), "r"(a[4 * k + 3]) : "memory");
-              }
-          }
-          asm volatile("bar.sync 4, %0;" ::"r"(32 * kEpiW) : "memory");   // the exchange buffer holds timestep q
-          if (!mover) {
-            ST *out = spikes + (long long)(pair * g.tq + q) * frame_out;
-            const uint32_t taddr = lane_base + col0;
-            if (!g.lif) {
-              twin_step<XT, ST, kLifOff, false>(p, taddr, stage_row, bias_c, out, pm, v, nchunks);
-            } else if (p.mode == 1 && p.hard) {
-              if (full) twin_step<XT, ST, kLifFast, true>(p, taddr, stage_row, bias_c, out, pm, v, nchunks);
-              else twin_step<XT, ST, kLifFast, false>(p, taddr, stage_row, bias_c, out, pm, v, nchunks);
-            } else {
-              twin_step<XT, ST, kLifAny, false>(p, taddr, stage_row, bias_c, out, pm, v, nchunks);
-            }
-          }
-          asm volatile("bar.sync 5, %0;" ::"r"(32 * kEpiW) : "memory");   // the buffer may be overwritten
-        }
-        // this accumulator may now be overwritten by later MMAs
-        umma::tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) umma::mbar_arrive(accempty(acc));
-      }
-      if (ok && g.lif && v_out != nullptr) {
-#pragma unroll
-        for (int i = 0; i < 64; ++i)
-          if (((pm.rows_ok >> (i >> 3)) & 1) && ((pm.cols_ok >> (i & 7)) & 1))
-            v_out[pm.row0_off + (long long)(i >> 3) * pm.row_stride + (i & 7) * pm.Cout] = DT<VT>::from_f(v[i]);
-      }
-    }
   } else {
     // ---------------------------------------------------------------- epilogue
     const int quarter = warp & 3;
@@ -789,15 +617,13 @@ int launch(const ConvArgs &a, cudaStream_t stream) {
     const int rc = encode_tmap(&wm, a.dtype, 2, a.w, dims, strides, box);
     if (rc != SNNB_OK) return rc;
   }
-  g.twin = (a.Cout <= 64 && g.ntaps == 9 && !g.s2 && !g.stack && g.sc_slabs == 0 && twin_enabled()) ? 1 : 0;
-  g.dup = (a.Cout <= 64 && !g.twin) ? 1 : 0;
-  g.stage_off = 0;
+  g.dup = a.Cout <= 64 ? 1 : 0;
   g.own = (a.lif && a.v_init != nullptr && a.v_init == a.v_out) ? 1 : 0;
   g.wait_limit = 4000000000ll;
   g.drop_load = 0;
   consume_wait_selftest(&g.wait_limit, &g.drop_load);
   CUtensorMap wm64 = wm;
-  if (g.dup || g.twin) {
+  if (g.dup) {
     const cuuint64_t K = (cuuint64_t)g.ntaps * a.Cin;
     cuuint64_t dims[2] = {K, (cuuint64_t)a.Cout};
     cuuint64_t strides[1] = {K * es};
@@ -832,13 +658,8 @@ int launch(const ConvArgs &a, cudaStream_t stream) {
   g.ring = kPairRing;
   const bool ident = g.has_res && !g.sc_slabs;
   g.wring = ident ? kWRingP - 1 : kWRingP;
-  size_t smem = (ident ? (size_t)kIdentBytes : 0) + (size_t)g.wring * kWSlot + (size_t)g.ring * g.tq * kHaloT +
-                4 * kRowBytes + 1024;
-  if (g.twin) {   // smaller identity block and weight ring make room for the exchange buffer
-    g.wring = ident ? 3 : 4;
-    g.stage_off = (ident ? kTwinIdentBytes : 0) + g.wring * kWSlot + g.ring * g.tq * kHaloT + 4 * kRowBytes;
-    smem = (size_t)g.stage_off + kStageBytes + 1024;
-  }
+  const size_t smem = (ident ? (size_t)kIdentBytes : 0) + (size_t)g.wring * kWSlot + (size_t)g.ring * g.tq * kHaloT +
+                      4 * kRowBytes + 1024;
   auto kern = g.s2 ? conv3x3_pair_kernel<XT, ST, VT, true> : conv3x3_pair_kernel<XT, ST, VT, false>;
   {
     // once per kernel instantiation and device: allow the largest dynamic shared-memory size any call may ask for

@@ -103,7 +103,9 @@ extern "C" int snnb_stem7x7_lif(const void *x_seq, int64_t x_t_stride, const voi
   SNNB_CHECK_ARG(x_t_stride >= 0 && tau != 0.0f, "stem7x7_lif: bad frame stride or tau");
   SNNB_CHECK_ARG(aligned16(scratch) && aligned16(w_packed), "stem7x7_lif: scratch and weights must be 16-byte aligned");
   const int frames = (x_t_stride == 0) ? 1 : T;  // one frame reused for all steps: re-laid (and convolved) once
+  SNNB_CHECK_ARG((int64_t)frames * B <= 0x7fffffffLL, "stem7x7_lif: too many frames");
   const int64_t need = snnb_stem7x7_scratch_bytes(frames * B, H, W);
+  SNNB_CHECK_ARG(need > 0, "stem7x7_lif: bad sizes");
   SNNB_CHECK_ARG(scratch_bytes >= need, "stem7x7_lif: scratch too small: %lld bytes given, %lld needed",
                  (long long)scratch_bytes, (long long)need);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -184,8 +186,11 @@ extern "C" int snnb_stem7x7_lif_static(const void *x_seq, int64_t x_t_stride, co
                                        float v_th, float v_reset, float tau, void *stream) {
   using namespace snnb;
   SNNB_CHECK_ARG(T >= 1 && B >= 1 && H >= 2 && W >= 2, "stem7x7_lif_static: bad sizes");
-  const int frames = (x_t_stride == 0) ? 1 : T;
-  const int64_t need = snnb_stem7x7_scratch_bytes(frames * B, H, W);
+  SNNB_CHECK_ARG(x_t_stride >= 0, "stem7x7_lif_static: negative frame stride");
+  const int64_t frames = (x_t_stride == 0 ? 1 : (int64_t)T) * (int64_t)B;   // 64-bit: T * B may not fit an int
+  SNNB_CHECK_ARG(frames <= 0x7fffffffLL, "stem7x7_lif_static: too many frames");
+  const int64_t need = snnb_stem7x7_scratch_bytes((int)frames, H, W);
+  SNNB_CHECK_ARG(need > 0, "stem7x7_lif_static: bad sizes");
   if (need > (int64_t)SNNB_STEM_STATIC_SCRATCH_BYTES)
     return fail(SNNB_ERR_UNSUPPORTED,
                 "stem7x7_lif_static: this call needs %lld bytes of scratch but the built-in array holds %lld; "
