@@ -51,7 +51,10 @@ extern "C" {
 #define SNNB_ERR_UNSUPPORTED 2 /* valid request this build has no kernel for   */
 #define SNNB_ERR_CUDA 3        /* a CUDA runtime / driver call failed          */
 
-typedef enum snnb_dtype { SNNB_F32 = 0, SNNB_BF16 = 1, SNNB_F16 = 2, SNNB_U8 = 3 } snnb_dtype;
+/* SNNB_B1: spikes packed one bit each along the channel axis: the spikes of channels 32k .. 32k+31 of a pixel
+ * are one little-endian 32-bit word (channel c in bit c % 32 of word c / 32), C % 32 == 0. Written by
+ * snnb_stem7x7_lif (Cout == 64) and read by snnb_maxpool3x3s2_bits. */
+typedef enum snnb_dtype { SNNB_F32 = 0, SNNB_BF16 = 1, SNNB_F16 = 2, SNNB_U8 = 3, SNNB_B1 = 4 } snnb_dtype;
 typedef enum snnb_layout { SNNB_NCHW = 0, SNNB_NHWC = 1 } snnb_layout;
 
 /* Which conv / linear implementation to use. AUTO picks a tcgen05 kernel when
@@ -197,7 +200,8 @@ int snnb_conv3x3_shortcut_lif(const void *x_seq, int64_t x_t_stride, const void 
  *   x_seq [T][B][H][W][3] (x_t_stride elements apart; 0 = one frame for every step, convolved once),
  *   H and W even; w_packed [Cout][4][4][16] produced once by snnb_stem7x7_pack_weight from the
  *   [Cout][7][7][3] channels-last weight; spikes [T][B][H/2][W/2][Cout]; v_init/v_out [B][H/2][W/2][Cout]
- *   (v_out may be NULL, as for snnb_conv_lif).
+ *   (v_out may be NULL, as for snnb_conv_lif). With Cout == 64 spike_dtype may also be SNNB_B1 (bit-packed,
+ *   [T][B][H/2][W/2] 64-bit words).
  *   scratch: snnb_stem7x7_scratch_bytes(frames, H, W) bytes of device memory, 16-byte aligned, where
  *   frames = B if x_t_stride == 0 else T*B. It holds the input re-laid as 2x2-pixel blocks with a
  *   zero border; its contents are overwritten by every call.
@@ -273,6 +277,14 @@ int snnb_maxpool3x3s2(const void *x, void *y, int64_t frames, int H, int W, int 
  */
 int snnb_maxpool3x3s2_u8(const void *x, void *y, int64_t frames, int H, int W, int C, int out_dtype,
                          void *stream);
+/*
+ * The same pooling for bit-packed spikes (SNNB_B1): x [frames][H][W][C / 32] 32-bit words -> y
+ * [frames][Ho][Wo][C] in out_dtype (0.0 / 1.0). The max over a window of 0 / 1 values is the OR of the words, so a
+ * pooled pixel costs nine word loads per 32 channels. With the stem writing SNNB_B1 the widest activation of a
+ * ResNet crosses HBM at one bit per spike. C % 64 == 0. No counterpart in the reference.
+ */
+int snnb_maxpool3x3s2_bits(const void *x, void *y, int64_t frames, int H, int W, int C, int out_dtype,
+                           void *stream);
 /* out[n][k] = (1/T) sum_t ( fc_w . mean_hw x[t][n] + fc_b ), x NHWC [T][N][HW][C], out fp32. */
 int snnb_avgpool_linear_mean(const void *x_seq, const void *fc_w, const void *fc_b, float *out,
                              int T, int N, int C, int HW, int K, int dtype, void *stream);

@@ -112,3 +112,22 @@ def test_bounded_wait_runs_out_and_reports():
                                    orc.widen(w).permute(0, 3, 1, 2), orc.widen(b), None, [1, 1], [1, 1], [1, 1], 1,
                                    1.0, 0.0, 2.0)
     check_parity(spikes.permute(0, 1, 4, 2, 3), v.permute(0, 3, 1, 2), rs, rv, dtype, what="after the self-test")
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("shape", [(5, 14, 18, 64), (2, 7, 9, 128), (3, 112, 112, 64)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_maxpool_of_bit_packed_spikes(shape, dtype):
+    """snnb_maxpool3x3s2_bits (spikes one bit each, 32 channels per word) against torch's max_pool2d."""
+    L = _lib()
+    frames, H, W, C = shape
+    g = torch.Generator().manual_seed(H * W + C)
+    spikes = (torch.rand(frames, H, W, C, generator=g) < 0.2)
+    weights = (1 << torch.arange(8, dtype=torch.int32)).to(torch.uint8)
+    packed = (spikes.reshape(frames, H, W, C // 8, 8).to(torch.uint8) * weights).sum(-1).to(torch.uint8).contiguous()
+    Ho, Wo = (H - 1) // 2 + 1, (W - 1) // 2 + 1
+    y = torch.empty(frames, Ho, Wo, C, dtype=dtype, device=DEV)
+    xd = packed.to(DEV)
+    L.check(L.lib.snnb_maxpool3x3s2_bits(xd.data_ptr(), y.data_ptr(), frames, H, W, C, L.dtype_code(dtype), None), "pool bits")
+    want = F.max_pool2d(spikes.float().permute(0, 3, 1, 2), 3, 2, 1).permute(0, 2, 3, 1)
+    assert torch.equal(y.float().cpu(), want)

@@ -242,14 +242,22 @@ def test_stem_byte_spikes_and_no_membrane_output(hw, alias):
     scratch = torch.empty(nbytes, dtype=torch.uint8, device=DEV)
     xts = 0 if alias else x.stride(0)
     outs = {}
-    for name, sdt, with_v in (("wide", dtype, True), ("bytes", torch.uint8, False)):
+    for name, sdt, with_v in (("wide", dtype, True), ("bytes", torch.uint8, False), ("bits", None, False)):
+        if name == "bits":   # one bit per spike: 8 bytes per pixel, channel c in bit c % 8 of byte c / 8
+            sp = torch.empty(T, B, H // 2, W // 2, cout // 8, dtype=torch.uint8, device=DEV)
+            L.check(L.lib.snnb_stem7x7_lif(x.data_ptr(), xts, wp.data_ptr(), b.data_ptr(), None, sp.data_ptr(), None,
+                                           scratch.data_ptr(), nbytes, T, B, H, W, cout, L.dtype_code(dtype), L.B1,
+                                           L.dtype_code(dtype), 1.0, 0.0, 2.0, None), name)
+            shifts = torch.arange(8, device=DEV, dtype=torch.uint8)
+            outs[name] = ((sp.unsqueeze(-1) >> shifts) & 1).flatten(-2).float().cpu()
+            continue
         sp = torch.empty(T, B, H // 2, W // 2, cout, dtype=sdt, device=DEV)
         v = torch.empty(B, H // 2, W // 2, cout, dtype=dtype, device=DEV) if with_v else None
         L.check(L.lib.snnb_stem7x7_lif(x.data_ptr(), xts, wp.data_ptr(), b.data_ptr(), None, sp.data_ptr(),
                                        v.data_ptr() if with_v else None, scratch.data_ptr(), nbytes, T, B, H, W, cout,
                                        L.dtype_code(dtype), L.dtype_code(sdt), L.dtype_code(dtype), 1.0, 0.0, 2.0, None), name)
         outs[name] = sp.float().cpu()
-    assert torch.equal(outs["wide"], outs["bytes"])
+    assert torch.equal(outs["wide"], outs["bytes"]) and torch.equal(outs["wide"], outs["bits"])
     assert 0.02 < float(outs["wide"].mean()) < 0.6
 
 

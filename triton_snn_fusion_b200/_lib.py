@@ -14,7 +14,7 @@ import torch
 LIB_PATH = Path(__file__).resolve().parent / "libsnnb200.so"
 
 SNNB_OK = 0
-F32, BF16, F16, U8 = 0, 1, 2, 3
+F32, BF16, F16, U8, B1 = 0, 1, 2, 3, 4   # B1: spikes packed one bit each along the channel axis
 NCHW, NHWC = 0, 1
 PATH_AUTO, PATH_SIMT, PATH_TCGEN05, PATH_TCGEN05_TAPS, PATH_TCGEN05_HALO = 0, 1, 2, 3, 4
 
@@ -57,6 +57,7 @@ SIGNATURES = {
                                           c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                           c_float, c_float, c_float, c_void_p]),
     "snnb_maxpool3x3s2_u8": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_void_p]),
+    "snnb_maxpool3x3s2_bits": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_void_p]),
     "snnb_avgpool_linear_mean": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p,
                                          c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
 }

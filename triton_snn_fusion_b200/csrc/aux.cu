@@ -126,6 +126,39 @@ maxpool3x3s2_u8_kernel(const uint8_t *__restrict__ x, XT *__restrict__ y, int64_
   store_pack<XT, 16, false>(y + ((f * Ho + ho) * (int64_t)Wo + wo) * C + cv * 16, out);
 }
 
+// 3x3 / stride 2 / padding 1 max-pool of bit-packed spikes: the max of 0 / 1 values is the OR of the words. A
+// thread produces 16 channels of one output pixel from nine 32-bit word loads (two threads share each word).
+template <typename XT>
+__global__ void __launch_bounds__(256)
+maxpool3x3s2_bits_kernel(const uint32_t *__restrict__ x, XT *__restrict__ y, int64_t frames, int H, int W, int C, int Ho, int Wo) {
+  const int CV = C / 16, WPP = C / 32;   // 16-channel groups and words per pixel
+  const int64_t total = frames * Ho * Wo * CV;
+  int64_t idx = (int64_t)blockIdx.x * 256 + threadIdx.x;
+  if (idx >= total) return;
+  const int cv = (int)(idx % CV); idx /= CV;
+  const int wo = (int)(idx % Wo); idx /= Wo;
+  const int ho = (int)(idx % Ho);
+  const int64_t f = idx / Ho;
+  uint32_t m = 0u;
+  const uint32_t *xf = x + f * (int64_t)H * W * WPP + (cv >> 1);
+#pragma unroll
+  for (int r = 0; r < 3; ++r) {
+    const int hi = ho * 2 - 1 + r;
+    if (hi < 0 || hi >= H) continue;
+#pragma unroll
+    for (int c = 0; c < 3; ++c) {
+      const int wi = wo * 2 - 1 + c;
+      if (wi < 0 || wi >= W) continue;
+      m |= __ldg(xf + ((int64_t)hi * W + wi) * WPP);
+    }
+  }
+  m >>= (cv & 1) * 16;
+  float out[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) out[i] = (float)((m >> i) & 1u);
+  store_pack<XT, 16, false>(y + ((f * Ho + ho) * (int64_t)Wo + wo) * C + cv * 16, out);
+}
+
 // One CTA per (group of SB samples, chunk of classes): channel sums over (t, pixel) into shared memory,
 // then a warp-per-class mat-vec for the SB samples with the fc row read once. The sums are cheap and
 // latency-bound (T*HW strided rows per channel), so the threads of a CTA split the pixels as well as
@@ -286,6 +319,26 @@ extern "C" int snnb_maxpool3x3s2_u8(const void *x, void *y, int64_t frames, int 
   else if (out_dtype == SNNB_BF16) maxpool3x3s2_u8_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, st>>>(xs, static_cast<__nv_bfloat16 *>(y), frames, H, W, C, Ho, Wo);
   else maxpool3x3s2_u8_kernel<__half><<<(unsigned)blocks, 256, 0, st>>>(xs, static_cast<__half *>(y), frames, H, W, C, Ho, Wo);
   SNNB_CHECK_LAUNCH("maxpool3x3s2_u8");
+  return SNNB_OK;
+}
+
+extern "C" int snnb_maxpool3x3s2_bits(const void *x, void *y, int64_t frames, int H, int W, int C, int out_dtype, void *stream) {
+  using namespace snnb;
+  SNNB_CHECK_ARG(x && y, "maxpool3x3s2_bits: null pointer");
+  SNNB_CHECK_ARG(frames >= 0 && H >= 1 && W >= 1 && C >= 64 && C % 64 == 0, "maxpool3x3s2_bits: bad sizes (C must be a multiple of 64)");
+  SNNB_CHECK_ARG(is_act_dtype(out_dtype), "maxpool3x3s2_bits: unsupported output dtype %d", out_dtype);
+  SNNB_CHECK_ARG(aligned16(x) && aligned16(y), "maxpool3x3s2_bits: buffers must be 16-byte aligned");
+  const int Ho = (H - 1) / 2 + 1, Wo = (W - 1) / 2 + 1;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int64_t total = frames * Ho * Wo * (C / 16);
+  const int64_t blocks = (total + 255) / 256;
+  if (blocks > 0x7fffffffLL) return fail(SNNB_ERR_INVALID, "maxpool3x3s2_bits: problem too large");
+  if (blocks == 0) return SNNB_OK;
+  const uint32_t *xs = static_cast<const uint32_t *>(x);
+  if (out_dtype == SNNB_F32) maxpool3x3s2_bits_kernel<float><<<(unsigned)blocks, 256, 0, st>>>(xs, static_cast<float *>(y), frames, H, W, C, Ho, Wo);
+  else if (out_dtype == SNNB_BF16) maxpool3x3s2_bits_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, st>>>(xs, static_cast<__nv_bfloat16 *>(y), frames, H, W, C, Ho, Wo);
+  else maxpool3x3s2_bits_kernel<__half><<<(unsigned)blocks, 256, 0, st>>>(xs, static_cast<__half *>(y), frames, H, W, C, Ho, Wo);
+  SNNB_CHECK_LAUNCH("maxpool3x3s2_bits");
   return SNNB_OK;
 }
 

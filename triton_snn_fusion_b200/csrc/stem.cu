@@ -98,7 +98,8 @@ extern "C" int snnb_stem7x7_lif(const void *x_seq, int64_t x_t_stride, const voi
   SNNB_CHECK_ARG(dtype == SNNB_BF16 || dtype == SNNB_F16, "stem7x7_lif: dtype must be bf16 or f16");
   SNNB_CHECK_ARG(T >= 1 && B >= 1 && Cout >= 16 && Cout % 16 == 0, "stem7x7_lif: bad T/B/Cout");
   SNNB_CHECK_ARG(H >= 2 && W >= 2 && H % 2 == 0 && W % 2 == 0, "stem7x7_lif: H and W must be even");
-  SNNB_CHECK_ARG(spike_dtype == dtype || spike_dtype == SNNB_U8, "stem7x7_lif: spike dtype must be the x dtype or u8");
+  SNNB_CHECK_ARG(spike_dtype == dtype || spike_dtype == SNNB_U8 || (spike_dtype == SNNB_B1 && Cout == 64),
+                 "stem7x7_lif: spike dtype must be the x dtype, u8, or (with 64 output channels) bit-packed");
   SNNB_CHECK_ARG(v_dtype == dtype || v_dtype == SNNB_F32, "stem7x7_lif: v dtype must be the x dtype or f32");
   SNNB_CHECK_ARG(x_t_stride >= 0 && tau != 0.0f, "stem7x7_lif: bad frame stride or tau");
   SNNB_CHECK_ARG(aligned16(scratch) && aligned16(w_packed), "stem7x7_lif: scratch and weights must be 16-byte aligned");

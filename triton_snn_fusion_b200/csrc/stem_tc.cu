@@ -62,7 +62,7 @@ struct StemGeom {
 // (chunk j of row r sits at chunk j ^ ((r >> 1) & 3)), slots of 2 KB.
 template <typename XT, typename ST, typename VT, bool FAST>
 __device__ __forceinline__ void staged_tile(const StemGeom &g, const LifParams &p, const CUtensorMap *smap,
-                                            uint32_t acc_addr, uint32_t accempty_bar, uint32_t slots, uint32_t &sslot,
+                                            ST *__restrict__ spikes, uint32_t acc_addr, uint32_t accempty_bar, uint32_t slots, uint32_t &sslot,
                                             const float *bias_s, const VT *__restrict__ v_init, VT *__restrict__ v_out,
                                             int bx, int by, int b, long long pix, bool valid) {
   const int lane = threadIdx.x & 31;
@@ -80,6 +80,47 @@ __device__ __forceinline__ void staged_tile(const StemGeom &g, const LifParams &
   } else {
 #pragma unroll
     for (int i = 0; i < 64; ++i) v[i] = 0.f;
+  }
+  if constexpr (std::is_same<ST, uint64_t>::value) {
+    // Bit-packed spikes: a thread owns all 64 channels of its pixel, so the spikes of a step are one 64-bit word
+    // (channel c in bit c) that the thread stores itself: the 32 lanes of a warp write consecutive pixels, 256
+    // contiguous bytes per store instruction, and no shared-memory staging or TMA store is involved.
+    ST *dst = spikes;
+    const long long frame_px = (long long)g.B * g.Ho * g.Wo;
+    for (int t = 0; t < g.T; ++t) {
+      const uint32_t src = acc_addr + (uint32_t)((alias ? 0 : t) * 64);
+      uint32_t w0 = 0u, w1 = 0u;
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        uint32_t a[16];
+        umma::tmem_ld_x16(src + (uint32_t)(q * 16), a);
+        umma::tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const int c = q * 16 + i;
+          const float y = __uint_as_float(a[i]) + bias_s[c];
+          const bool sp = (FAST ? lif_step_t<1, true>(y, v[c], p) : lif_step(y, v[c], p)) != 0.f;
+          if (c < 32) w0 |= (sp ? 1u : 0u) << (c & 31);
+          else w1 |= (sp ? 1u : 0u) << (c & 31);
+        }
+      }
+      if (t == g.T - 1) {   // last read of this accumulator stage: the MMA warp may overwrite it
+        umma::tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) umma::mbar_arrive(accempty_bar);
+      }
+      if (valid) dst[(long long)t * frame_px + pix] = (uint64_t)w0 | ((uint64_t)w1 << 32);
+    }
+    if (valid && v_out != nullptr) {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        float tmp[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) tmp[i] = v[q * 16 + i];
+        store_pack<VT, 16, false>(v_out + o0 + q * 16, tmp);
+      }
+    }
+    return;
   }
   for (int t = 0; t < g.T; ++t) {
     // the slot written now was handed to TMA two steps ago: that store must have read it out
@@ -288,10 +329,10 @@ stem_gemm_lif_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_cons
           umma::tc_fence_after_sync();
           const uint32_t acc_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * (uint32_t)g.stage_cols;
           if (p.mode == 1 && p.hard)
-            staged_tile<XT, ST, VT, true>(g, p, &smap, acc_addr, accempty(acc), slots, sslot, bias_s, v_init, v_out,
+            staged_tile<XT, ST, VT, true>(g, p, &smap, spikes, acc_addr, accempty(acc), slots, sslot, bias_s, v_init, v_out,
                                       w0 + bx_off, h0 + by_off, b, pix, valid);
           else
-            staged_tile<XT, ST, VT, false>(g, p, &smap, acc_addr, accempty(acc), slots, sslot, bias_s, v_init, v_out,
+            staged_tile<XT, ST, VT, false>(g, p, &smap, spikes, acc_addr, accempty(acc), slots, sslot, bias_s, v_init, v_out,
                                        w0 + bx_off, h0 + by_off, b, pix, valid);
         }
         // the shared-memory slots must outlive the TMA stores that read them
@@ -311,9 +352,11 @@ stem_gemm_lif_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_cons
       if (!ok) break;
       umma::tc_fence_after_sync();
       const uint32_t acc_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * (uint32_t)g.stage_cols;
-      const EpiArgs<XT, ST, VT> ea{bias, nullptr, v_init, spikes, v_out, acc_addr,
-                                   pix, frame_out, 0, c_begin, c_end, valid};
-      epilogue_dispatch<XT, ST, VT>(ea, eg, 1, p);
+      if constexpr (!std::is_same<ST, uint64_t>::value) {   // bit-packed spikes exist for the staged (64-channel) form only
+        const EpiArgs<XT, ST, VT> ea{bias, nullptr, v_init, spikes, v_out, acc_addr,
+                                     pix, frame_out, 0, c_begin, c_end, valid};
+        epilogue_dispatch<XT, ST, VT>(ea, eg, 1, p);
+      }
       // this stage may now be overwritten
       umma::tc_fence_before_sync();
       __syncwarp();
@@ -384,7 +427,9 @@ int launch(const StemGemmArgs &a, cudaStream_t stream) {
     if (rc != SNNB_OK) return rc;
   }
   CUtensorMap sm = xm;
-  if (g.staged) {  // spikes [T * B][Ho][Wo][64]: a tile of one step leaves as one box
+  constexpr bool kBits = std::is_same<ST, uint64_t>::value;   // one 64-bit word per pixel, stored by the threads themselves
+  if (kBits && !g.staged) return fail(SNNB_ERR_UNSUPPORTED, "stem7x7_lif: bit-packed spikes need Cout == 64");
+  if (g.staged && !kBits) {  // spikes [T * B][Ho][Wo][64]: a tile of one step leaves as one box
     const cuuint64_t ss = sizeof(ST);
     cuuint64_t dims[4] = {64, (cuuint64_t)a.Wo, (cuuint64_t)a.Ho, (cuuint64_t)a.T * a.B};
     cuuint64_t strides[3] = {(cuuint64_t)64 * ss, (cuuint64_t)a.Wo * 64 * ss, (cuuint64_t)a.Ho * a.Wo * 64 * ss};
@@ -408,6 +453,7 @@ template <typename XT>
 int dispatch(const StemGemmArgs &a, cudaStream_t stream) {
   const bool s_u8 = a.spike_dtype == SNNB_U8;
   const bool v_f32 = a.v_dtype == SNNB_F32;
+  if (a.spike_dtype == SNNB_B1) return v_f32 ? launch<XT, uint64_t, float>(a, stream) : launch<XT, uint64_t, XT>(a, stream);
   if (s_u8 && v_f32) return launch<XT, uint8_t, float>(a, stream);
   if (s_u8) return launch<XT, uint8_t, XT>(a, stream);
   if (v_f32) return launch<XT, XT, float>(a, stream);

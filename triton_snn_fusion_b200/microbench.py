@@ -74,19 +74,28 @@ def case_conv(a):
 
 
 def case_lif(a):
+    dt = {"f32": torch.float32, "bf16": torch.bfloat16}[a.dtype]
+    dc = _lib.dtype_code(dt)
+    es = 4 if a.dtype == "f32" else 2
+    # Footprints below the L2 size would be served from L2 on every repetition: rotate through enough copies of the
+    # buffers that a launch never finds its data cached (every copy holds different seeded values).
+    footprint = es * (2 * a.T + 1) * a.n
+    copies = max(1, -(-(400 << 20) // footprint)) if footprint < (256 << 20) else 1
     g = torch.Generator(device=DEV).manual_seed(0)
-    x = torch.randn(a.T, a.n, device=DEV, generator=g) * 0.8 + 0.6
-    sp = torch.empty_like(x)
-    v = torch.empty(a.n, device=DEV)
+    xs = [(torch.randn(a.T, a.n, device=DEV, generator=g) * 0.8 + 0.6).to(dt) for _ in range(copies)]
+    sps = [torch.empty_like(x) for x in xs]
+    vs = [torch.empty(a.n, device=DEV, dtype=dt) for _ in range(copies)]
+    k = [0]
 
     def call():
-        _lib.check(_lib.lib.snnb_lif_scan(x.data_ptr(), None, sp.data_ptr(), v.data_ptr(), a.T, a.n,
-                                          0, 0, 0, *LIF, _stream()), "snnb_lif_scan")
+        i = k[0] % copies
+        k[0] += 1
+        _lib.check(_lib.lib.snnb_lif_scan(xs[i].data_ptr(), None, sps[i].data_ptr(), vs[i].data_ptr(), a.T, a.n,
+                                          dc, dc, dc, *LIF, _stream()), "snnb_lif_scan")
 
-    ms = _time(call, a.reps)
-    nbytes = 4 * (2 * a.T + 1) * a.n
-    print(f"lif_scan T{a.T} n={a.n} f32: {ms:.4f} ms  {nbytes / ms / 1e6:.0f} GB/s  "
-          f"spike rate {float(sp.mean()):.3f}")
+    ms = _time(call, max(a.reps, 2 * copies))
+    print(f"lif_scan T{a.T} n={a.n} {a.dtype}: {ms:.4f} ms  {footprint / ms / 1e6:.0f} GB/s  "
+          f"spike rate {float(sps[0].float().mean()):.3f}  ({copies} rotating buffer sets)")
 
 
 def case_dw(a):
@@ -134,8 +143,12 @@ def case_tail(a):
 def case_linear(a):
     dt = torch.bfloat16
     g = torch.Generator(device=DEV).manual_seed(0)
-    x = (torch.rand(a.T, a.M, a.K, device=DEV, generator=g) < 0.15).to(dt)
-    w = (torch.randn(a.N, a.K, device=DEV, generator=g) * a.K ** -0.5 * 2.5).to(dt)
+    if a.dist == "normal":   # real-valued activations N(0, 1), weights N(0, 1 / sqrt(K))
+        x = torch.randn(a.T, a.M, a.K, device=DEV, generator=g).to(dt)
+        w = (torch.randn(a.N, a.K, device=DEV, generator=g) * a.K ** -0.5).to(dt)
+    else:                    # binary spikes Bernoulli(0.15), as a preceding LIF layer would emit
+        x = (torch.rand(a.T, a.M, a.K, device=DEV, generator=g) < 0.15).to(dt)
+        w = (torch.randn(a.N, a.K, device=DEV, generator=g) * a.K ** -0.5 * 2.5).to(dt)
     b = torch.zeros(a.N, device=DEV, dtype=dt)
     sp = torch.empty(a.T, a.M, a.N, device=DEV, dtype=dt)
     v = torch.empty(a.M, a.N, device=DEV, dtype=dt)
@@ -148,7 +161,7 @@ def case_linear(a):
     ms = _time(call, a.reps)
     flops = 2.0 * a.T * a.M * a.K * a.N
     nbytes = 2 * (x.numel() + sp.numel() + v.numel() + w.numel())
-    print(f"linear_lif T{a.T} M{a.M} K{a.K} N{a.N} bf16: {ms:.4f} ms  {flops / ms / 1e9:.1f} TFLOP/s  "
+    print(f"linear_lif T{a.T} M{a.M} K{a.K} N{a.N} bf16 ({a.dist} inputs): {ms:.4f} ms  {flops / ms / 1e9:.1f} TFLOP/s  "
           f"{nbytes / ms / 1e6:.0f} GB/s  spike rate {float(sp.float().mean()):.3f}  device status {_lib.device_status()}")
 
 
@@ -194,6 +207,7 @@ def main(argv=None):
     c.set_defaults(fn=case_conv)
     l = sub.add_parser("lif")
     l.add_argument("--n", type=int, default=1 << 24)
+    l.add_argument("--dtype", choices=["f32", "bf16"], default="f32")
     l.set_defaults(fn=case_lif)
     d = sub.add_parser("dw")
     d.add_argument("--B", type=int, default=32)
@@ -217,6 +231,7 @@ def main(argv=None):
     n.add_argument("--K", type=int, default=768)
     n.add_argument("--N", type=int, default=3072)
     n.add_argument("--path", type=int, default=_lib.PATH_TCGEN05)
+    n.add_argument("--dist", choices=["bernoulli", "normal"], default="bernoulli")
     n.set_defaults(fn=case_linear)
     for p in (c, l, d, t, m, n):
         p.add_argument("--T", type=int, default=4)

@@ -98,13 +98,14 @@ class CompiledNet:
                     self.fused_sc[L["name"]] = D
                     self.skipped.add(D["name"])
         # The stem's spikes are the widest activation of a ResNet and are read only by the max-pool: they
-        # are kept as one byte each (spike_dtype U8) and pooled by the u8 variant of the pooling kernel.
-        self.u8_bufs = set()
+        # are kept as one BIT each (spike_dtype B1: a 64-bit word per pixel of the 64-channel stem) and pooled by
+        # the bit variant of the pooling kernel, whose OR of nine words is the max of the window.
+        self.bit_bufs = set()   # names of the activations stored bit-packed
         for i, L in enumerate(spec):
             if (L["op"] == "conv" and i + 1 < len(spec) and spec[i + 1]["op"] == "maxpool" and spec[i + 1]["src"] == L["dst"]
                     and L["src"] == "input" and self._is_tc_stem(L, H, W) and L["cout"] == 64
                     and sum(1 for M in spec if M.get("src") == L["dst"] or M.get("residual") == L["dst"]) == 1):
-                self.u8_bufs.add(L["dst"])
+                self.bit_bufs.add(L["dst"])
         # With several windows, what does not carry state from window to window runs ONCE over all T steps: the
         # stem on the (time-invariant) input frame, whose conv is evaluated once anyway, a max-pool fed by such a
         # layer, and the head.
@@ -122,8 +123,11 @@ class CompiledNet:
                 self.shapes[L["dst"]] = (ho, wo, L["cout"])
                 if L["name"] in self.skipped:
                     continue
-                self.bufs[L["dst"]] = torch.empty((self.T, self.B, ho, wo, L["cout"]), device=self.device,
-                                                  dtype=torch.uint8 if L["dst"] in self.u8_bufs else dtype)
+                if L["dst"] in self.bit_bufs:   # [T, B, H, W, C / 8] bytes = C / 64 little-endian 64-bit words per pixel
+                    self.bufs[L["dst"]] = torch.empty((self.T, self.B, ho, wo, L["cout"] // 8), device=self.device,
+                                                      dtype=torch.uint8)
+                else:
+                    self.bufs[L["dst"]] = torch.empty((self.T, self.B, ho, wo, L["cout"]), device=self.device, dtype=dtype)
                 if L["lif"] and (keep_membranes or L["groups"] != 1 or (self.nwin > 1 and L["dst"] not in self.whole_seq)):
                     # dense convs can skip the final membrane (v_out = NULL); the depthwise kernel always writes it;
                     # several windows carry it in fp32 through two buffers used alternately (window w reads the one
@@ -217,7 +221,7 @@ class CompiledNet:
                         torch.cuda.synchronize(self.device)
                         wt["w_stem"] = wp
                     wp = wt["w_stem"]
-                    sdt = _lib.dtype_code(torch.uint8) if L["dst"] in self.u8_bufs else dt
+                    sdt = _lib.B1 if L["dst"] in self.bit_bufs else dt
                     args = (at(L["src"]), x_stride, wp.data_ptr(), wt["b"].data_ptr(), v_in(L["name"]), at(L["dst"]), v,
                             self._scratch.data_ptr(), nbytes, T, B, h, w_, L["cout"], dt, sdt, vdt,
                             LIF["v_th"], LIF["v_reset"], LIF["tau"])
@@ -235,7 +239,7 @@ class CompiledNet:
                     calls.append((lib.snnb_dwconv3x3_lif, args, L["name"]))
             elif L["op"] == "maxpool":
                 args = (at(L["src"]), at(L["dst"]), T * B, h, w_, c, dt)
-                calls.append((lib.snnb_maxpool3x3s2_u8 if L["src"] in self.u8_bufs else lib.snnb_maxpool3x3s2, args, L["name"]))
+                calls.append((lib.snnb_maxpool3x3s2_bits if L["src"] in self.bit_bufs else lib.snnb_maxpool3x3s2, args, L["name"]))
             elif L["op"] == "tail":
                 wt = self.weights[L["name"]]
                 args = (src.data_ptr(), None, wt["w"].data_ptr(), wt["b"].data_ptr(), self.tail_sum.data_ptr(),
@@ -320,6 +324,7 @@ class CompiledNet:
     def activation(self, name: str) -> torch.Tensor:
         """Named activation as a logical [T,B,C,H,W] tensor (channels-last memory)."""
         buf = self.bufs[name]
-        if buf.dtype == torch.uint8:   # one-byte spikes: hand them out in the compute dtype
-            buf = buf.to(self.dtype)
+        if name in self.bit_bufs:   # bit-packed spikes: channel c of a pixel is bit c % 8 of byte c / 8; hand them out unpacked
+            shifts = torch.arange(8, device=buf.device, dtype=torch.uint8)
+            buf = ((buf.unsqueeze(-1) >> shifts) & 1).flatten(-2).to(self.dtype)
         return buf.permute(0, 1, 4, 2, 3)
