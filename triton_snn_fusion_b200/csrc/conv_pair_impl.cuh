@@ -61,6 +61,12 @@ struct PairGeom {
   int ntaps;      // 9 (3x3 conv) or 1 (1x1 conv / linear: only the centre of the halo tile is used)
   int sc_slabs;   // > 0: instead of a residual tensor, a 1x1 shortcut conv over sc_slabs 64-channel slabs of a
                   // second input is accumulated (its pixel tiles come through rmap, its weights through scwmap)
+  int flat;       // 1x1 conv on a map of at least 16 rows: the pixel tile is loaded without a halo (8 x 16 pixels, all
+                  // of them outputs) instead of as the centre of a 10 x 16 halo tile
+  int pw;         // pixels per tile row in shared memory: 10 (with halo) or 8 (flat)
+  int row_bytes;  // pw * 128
+  int halo_t;     // bytes of one timestep's tile: pw * 16 * 128
+  int tile_rows;  // output rows a tile produces: 14 (with halo) or 16 (flat)
   int ring;   // halo slots in use
   int wring;  // weight slots in use (<= kWRingP)
   int stack;  // maps of at most 7 x 8: two images per tile, image b in row groups 0.., image b + 1 in groups 8..
@@ -87,7 +93,7 @@ __device__ __forceinline__ void phase_tap(const PairGeom &g, int ph, int j, int 
   if constexpr (!S2) {
     const int kh = g.ntaps == 1 ? 1 : j / 3, kw = g.ntaps == 1 ? 1 : j - kh * 3;
     wtap = g.ntaps == 1 ? 0 : j;
-    off = kh * kPW + kw;
+    off = g.flat ? 0 : kh * kPW + kw;
   } else {
     const int a = ph >> 1, b = ph & 1, nc = b ? 2 : 1;
     const int jr = j / nc, jc = j - jr * nc;
@@ -222,7 +228,7 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
   const uint32_t ident_base = smem_base;
   const uint32_t w_base = smem_base + ((g.has_res && !g.sc_slabs) ? (uint32_t)kIdentBytes : 0u);
   const uint32_t h_base = w_base + (uint32_t)(g.wring * kWSlot);
-  const uint32_t slot_bytes = (uint32_t)(g.tq * kHaloT);
+  const uint32_t slot_bytes = (uint32_t)(g.tq * g.halo_t);
   const uint32_t bar_base = umma::smem_u32(bars);
   auto hfull = [&](uint32_t s) { return bar_base + 8u * s; };
   auto hempty = [&](uint32_t s) { return bar_base + 8u * ((uint32_t)kPairRing + s); };
@@ -251,9 +257,9 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
     // The last strip / row tile is shifted back inside the image instead of sticking out of it: it then
     // recomputes a few pixels of its neighbour (both write the same values) and every tile is complete.
     w0 = min(strip * 8, max(g.Wo - 8, 0));
-    h0 = min(rt * kTileRows, max(g.Ho - kTileRows, 0));
+    h0 = min(rt * g.tile_rows, max(g.Ho - g.tile_rows, 0));
     wlo = strip * 8;
-    hlo = rt * kTileRows;
+    hlo = rt * g.tile_rows;
   };
 
   if (threadIdx.x == 0) {
@@ -305,6 +311,7 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
     };
     uint32_t slot = 0, phase = 1;
     bool ok = true;
+    const int org = g.flat ? 0 : 1;   // the halo tile starts one pixel up and to the left of the output tile
     constexpr int nph = S2 ? 4 : 1;
     for (int tile = blockIdx.x; tile < g.total_tiles && ok; tile += gridDim.x) {
       int n0, w0, h0, b, wlo_unused, hlo_unused;
@@ -320,8 +327,8 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
           ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
           if (!ok) break;
           if (lane < g.tq) {
-            const uint32_t dst = h_base + slot * slot_bytes + (uint32_t)lane * kHaloT;
-            umma::tma_load_5d(dst, xm, hfull(slot), slab * 64, w0 - 1, h0 - 1, b, pair * g.tq + lane);
+            const uint32_t dst = h_base + slot * slot_bytes + (uint32_t)lane * (uint32_t)g.halo_t;
+            umma::tma_load_5d(dst, xm, hfull(slot), slab * 64, w0 - org, h0 - org, b, pair * g.tq + lane);
             if (g.stack && b + 1 < g.B)
               umma::tma_load_5d(dst + 8u * kRowBytes, xm, hfull(slot), slab * 64, -1, -1, b + 1, pair * g.tq + lane);
           }
@@ -340,8 +347,8 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
           ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
           if (!ok) break;
           if (lane < g.tq) {
-            const uint32_t dst = h_base + slot * slot_bytes + (uint32_t)lane * kHaloT;
-            umma::tma_load_5d(dst, &rmap, hfull(slot), res_c0, w0 - 1, h0 - 1, b, pair * g.tq + lane);
+            const uint32_t dst = h_base + slot * slot_bytes + (uint32_t)lane * (uint32_t)g.halo_t;
+            umma::tma_load_5d(dst, &rmap, hfull(slot), res_c0, w0 - org, h0 - org, b, pair * g.tq + lane);
             if (g.stack && b + 1 < g.B)
               umma::tma_load_5d(dst + 8u * kRowBytes, &rmap, hfull(slot), res_c0, -1, -1, b + 1, pair * g.tq + lane);
           }
@@ -393,7 +400,7 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
     if (lane == 0) {
       const uint32_t idesc = umma::make_idesc_f16(128, 128 * g.tq, std::is_same<XT, __nv_bfloat16>::value);
       uint64_t hdesc0 = umma::make_sw128_kmajor_desc(h_base);
-      hdesc0 = (hdesc0 & ~((uint64_t)0x3FFF << 32)) | ((uint64_t)(kRowBytes >> 4) << 32);
+      hdesc0 = (hdesc0 & ~((uint64_t)0x3FFF << 32)) | ((uint64_t)(g.row_bytes >> 4) << 32);
       const uint64_t wdesc0 = umma::make_sw128_kmajor_desc(w_base);
       uint32_t slot = 0, phase = 0, ws = 0, wphase = 0, it = 0;
       bool ok = true;
@@ -447,7 +454,7 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
               adesc = umma::make_sw128_kmajor_desc(ident_base + ((rs == 0 && !g.dup) ? 64u * 128u : 0u));
             }
             umma::tc_fence_after_sync();
-            const uint64_t xdesc = hdesc0 + (uint64_t)((slot * slot_bytes + (uint32_t)(kPW + 1) * 128u) >> 4);
+            const uint64_t xdesc = hdesc0 + (uint64_t)((slot * slot_bytes + (g.flat ? 0u : (uint32_t)(kPW + 1) * 128u)) >> 4);
 #pragma unroll
             for (int k = 0; k < 4; ++k) umma::mma_f16_ss(d, adesc + (uint64_t)(2 * k), xdesc + (uint64_t)(2 * k), idesc, 1u);
             if (g.sc_slabs) {
@@ -481,7 +488,7 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
       const int c = n0 + ch_in_tile;                   // output channel of this thread
       const int img = g.stack ? b + (r_begin >> 3) : b;   // two images per tile: row groups 8.. belong to image b + 1
       const int row_first = g.stack ? 0 : h0 + r_begin;   // image row of this thread's first row group
-      const int row_limit = g.stack ? 8 : kTileRows - r_begin;   // row groups of this thread that can hold outputs
+      const int row_limit = g.stack ? 8 : g.tile_rows - r_begin;   // row groups of this thread that can hold outputs
       const bool c_ok = c < g.Cout && img < g.B;
       // the two biases of a conv with a fused shortcut conv are widened first and added in fp32
       const float bias_c = ((bias != nullptr && c_ok) ? DT<XT>::to_f(bias[c]) : 0.f) +
@@ -574,7 +581,12 @@ int launch(const ConvArgs &a, cudaStream_t stream) {
   g.npairs = g.Tacc / g.tq;
   g.n_tiles_n = (a.Cout + 127) / 128;
   g.stack = (a.Ho <= 7 && a.Wo <= 8) ? 1 : 0;
-  g.row_tiles = (a.Ho + kTileRows - 1) / kTileRows;
+  g.flat = (g.ntaps == 1 && !g.stack && a.Ho >= 16) ? 1 : 0;
+  g.pw = g.flat ? 8 : kPW;
+  g.row_bytes = g.pw * 128;
+  g.halo_t = g.pw * kPH * 128;
+  g.tile_rows = g.flat ? 16 : kTileRows;
+  g.row_tiles = (a.Ho + g.tile_rows - 1) / g.tile_rows;
   g.w_strips = (a.Wo + 7) / 8;
   g.tmem_cols = g.npairs >= 2 ? 512 : (g.tq == 2 ? 256 : 128);
   g.lif = a.lif;
@@ -601,7 +613,7 @@ int launch(const ConvArgs &a, cudaStream_t stream) {
                             (cuuint64_t)a.B, (cuuint64_t)g.Tacc};
       cuuint64_t strides[4] = {(cuuint64_t)s_ * a.Cin * es, (cuuint64_t)s_ * a.W * a.Cin * es, (cuuint64_t)a.H * a.W * a.Cin * es,
                                g.Tacc > 1 ? (cuuint64_t)a.x_t_stride * es : frame_bytes};
-      cuuint32_t box[5] = {64, (cuuint32_t)kPW, (cuuint32_t)(g.stack ? 9 : kPH), 1, 1};
+      cuuint32_t box[5] = {64, (cuuint32_t)g.pw, (cuuint32_t)(g.stack ? 9 : kPH), 1, 1};
       const char *base = static_cast<const char *>(a.x) + ((size_t)pa * a.W + pb) * a.Cin * es;
       const int rc = encode_tmap(&xph[ph], a.dtype, 5, base, dims, strides, box);
       if (rc != SNNB_OK) return rc;
@@ -638,7 +650,7 @@ int launch(const ConvArgs &a, cudaStream_t stream) {
     cuuint64_t dims[5] = {sC, (cuuint64_t)a.Wo, (cuuint64_t)a.Ho, (cuuint64_t)a.B, (cuuint64_t)a.T};
     cuuint64_t strides[4] = {s_ * sC * es, s_ * (cuuint64_t)a.sc_W * sC * es, (cuuint64_t)a.sc_H * a.sc_W * sC * es,
                              (cuuint64_t)a.sc_t_stride * es};
-    cuuint32_t box[5] = {64, (cuuint32_t)kPW, (cuuint32_t)(g.stack ? 9 : kPH), 1, 1};
+    cuuint32_t box[5] = {64, (cuuint32_t)g.pw, (cuuint32_t)(g.stack ? 9 : kPH), 1, 1};
     int rc = encode_tmap(&rm, a.dtype, 5, a.sc_x, dims, strides, box);
     if (rc != SNNB_OK) return rc;
     cuuint64_t wdims[2] = {sC, (cuuint64_t)a.Cout};
@@ -650,7 +662,7 @@ int launch(const ConvArgs &a, cudaStream_t stream) {
     cuuint64_t dims[5] = {(cuuint64_t)a.Cout, (cuuint64_t)a.Wo, (cuuint64_t)a.Ho, (cuuint64_t)a.B, (cuuint64_t)a.T};
     cuuint64_t strides[4] = {(cuuint64_t)a.Cout * es, (cuuint64_t)a.Wo * a.Cout * es, (cuuint64_t)a.Ho * a.Wo * a.Cout * es,
                              (cuuint64_t)a.B * a.Ho * a.Wo * a.Cout * es};
-    cuuint32_t box[5] = {64, (cuuint32_t)kPW, (cuuint32_t)(g.stack ? 9 : kPH), 1, 1};
+    cuuint32_t box[5] = {64, (cuuint32_t)g.pw, (cuuint32_t)(g.stack ? 9 : kPH), 1, 1};
     const int rc = encode_tmap(&rm, a.dtype, 5, a.res, dims, strides, box);
     if (rc != SNNB_OK) return rc;
   }
@@ -658,7 +670,7 @@ int launch(const ConvArgs &a, cudaStream_t stream) {
   g.ring = kPairRing;
   const bool ident = g.has_res && !g.sc_slabs;
   g.wring = ident ? kWRingP - 1 : kWRingP;
-  const size_t smem = (ident ? (size_t)kIdentBytes : 0) + (size_t)g.wring * kWSlot + (size_t)g.ring * g.tq * kHaloT +
+  const size_t smem = (ident ? (size_t)kIdentBytes : 0) + (size_t)g.wring * kWSlot + (size_t)g.ring * g.tq * g.halo_t +
                       4 * kRowBytes + 1024;
   auto kern = g.s2 ? conv3x3_pair_kernel<XT, ST, VT, true> : conv3x3_pair_kernel<XT, ST, VT, false>;
   {

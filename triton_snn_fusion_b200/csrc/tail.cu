@@ -190,8 +190,9 @@ lif_avgpool_linear_kernel(const XT *__restrict__ x, const VT *__restrict__ v_ini
 // Streaming form for channels-last input whose channel count splits evenly over the cluster.
 // Same plan (scan + integer counts, DSMEM exchange, warp-per-class mat-vec), laid out for bandwidth:
 //   * scan: the (sample, pixel, channel-vector) items of the CTA's channel slice form ONE index space over all
-//     samples of the group; a thread takes four items per trip and issues their 16-byte loads for up to four
-//     timesteps (and the initial membranes) before the first use, i.e. up to 320 bytes in flight per thread;
+//     samples of the group; a thread takes two items per trip and issues their 16-byte loads for up to four
+//     timesteps (and the initial membranes) before the first use, i.e. up to 160 bytes in flight per thread,
+//     with two blocks resident per SM;
 //   * exchange: the peers' count slices are copied with 16-byte DSMEM loads;
 //   * mat-vec: a warp works on four classes at a time, so every count read from shared memory feeds four
 //     dot products, and its four 16-byte weight loads per trip are independent.
@@ -207,7 +208,7 @@ __device__ __forceinline__ void unpack16(const int4 &raw, float (&out)[VEC]) {
 }
 
 template <typename XT, typename VT, int VEC>
-__global__ void __launch_bounds__(NTF)
+__global__ void __launch_bounds__(NTF, 2)
 lif_avgpool_linear_stream_kernel(const XT *__restrict__ x, const VT *v_init, const XT *__restrict__ fc_w,
                                  const XT *__restrict__ fc_b, XT *__restrict__ out, VT *v_out,
                                  int T, int N, int C, int HW, int K, int S, LifParams p) {
@@ -226,22 +227,23 @@ lif_avgpool_linear_stream_kernel(const XT *__restrict__ x, const VT *v_init, con
   const int64_t frame = (int64_t)N * C * HW;
   const int items = ns * HW * cvn;
   const int cc = cs + (tid % cvn) * VEC;
-  for (int it0 = tid; it0 < items; it0 += 4 * NTF) {
-    int64_t e[4];
-    int smp[4];
-    bool on[4];
+  constexpr int IT = 2;   // items per thread and trip
+  for (int it0 = tid; it0 < items; it0 += IT * NTF) {
+    int64_t e[IT];
+    int smp[IT];
+    bool on[IT];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
+    for (int u = 0; u < IT; ++u) {
       const int it = it0 + u * NTF;
       on[u] = it < items;
       const int ps = (on[u] ? it : it0) / cvn;   // (sample, pixel) index
       smp[u] = ps / HW;
       e[u] = ((int64_t)(n0 + smp[u]) * HW + (ps - smp[u] * HW)) * C + cc;
     }
-    float v[4][VEC];
-    int k[4][VEC];
+    float v[IT][VEC];
+    int k[IT][VEC];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
+    for (int u = 0; u < IT; ++u) {
       if (v_init != nullptr) load_pack_stream<VT, VEC>(v_init + e[u], v[u]);
       else {
 #pragma unroll
@@ -251,14 +253,14 @@ lif_avgpool_linear_stream_kernel(const XT *__restrict__ x, const VT *v_init, con
       for (int i = 0; i < VEC; ++i) k[u][i] = 0;
     }
     for (int t0 = 0; t0 < T; t0 += 4) {
-      int4 raw[4][4];
+      int4 raw[IT][4];
 #pragma unroll
       for (int j = 0; j < 4; ++j)
 #pragma unroll
-        for (int u = 0; u < 4; ++u)
+        for (int u = 0; u < IT; ++u)
           if (t0 + j < T) raw[u][j] = __ldcs(reinterpret_cast<const int4 *>(x + (int64_t)(t0 + j) * frame + e[u]));
 #pragma unroll
-      for (int u = 0; u < 4; ++u)
+      for (int u = 0; u < IT; ++u)
 #pragma unroll
         for (int j = 0; j < 4; ++j)
           if (t0 + j < T) {
@@ -269,7 +271,7 @@ lif_avgpool_linear_stream_kernel(const XT *__restrict__ x, const VT *v_init, con
           }
     }
 #pragma unroll
-    for (int u = 0; u < 4; ++u)
+    for (int u = 0; u < IT; ++u)
       if (on[u]) {
         store_pack<VT, VEC>(v_out + e[u], v[u]);
 #pragma unroll
