@@ -127,20 +127,28 @@ maxpool3x3s2_u8_kernel(const uint8_t *__restrict__ x, XT *__restrict__ y, int64_
 }
 
 // 3x3 / stride 2 / padding 1 max-pool of bit-packed spikes: the max of 0 / 1 values is the OR of the words. A
-// thread produces 16 channels of one output pixel from nine 32-bit word loads (two threads share each word).
+// thread produces 8 channels of one output pixel (one 16-byte store for 16-bit data): the threads of a warp that
+// share a pixel read the same nine words (one broadcast each) and the warp's store covers whole 128-byte rows.
+// Spikes are written as the bit patterns of 0.0 / 1.0 directly; all index arithmetic is 32-bit.
+template <typename XT> struct OneBits;
+template <> struct OneBits<__nv_bfloat16> { static constexpr uint32_t v = 0x3F80u; };
+template <> struct OneBits<__half> { static constexpr uint32_t v = 0x3C00u; };
+
 template <typename XT>
 __global__ void __launch_bounds__(256)
-maxpool3x3s2_bits_kernel(const uint32_t *__restrict__ x, XT *__restrict__ y, int64_t frames, int H, int W, int C, int Ho, int Wo) {
-  const int CV = C / 16, WPP = C / 32;   // 16-channel groups and words per pixel
-  const int64_t total = frames * Ho * Wo * CV;
-  int64_t idx = (int64_t)blockIdx.x * 256 + threadIdx.x;
+maxpool3x3s2_bits_kernel(const uint32_t *__restrict__ x, XT *__restrict__ y, int frames_rows, int H, int W, int C, int Ho, int Wo) {
+  const int CV = C >> 3, WPP = C >> 5;   // 8-channel groups and 32-bit words per pixel
+  const unsigned total = (unsigned)frames_rows * (unsigned)Wo * (unsigned)CV;   // frames_rows = frames * Ho
+  const unsigned idx = blockIdx.x * 256u + threadIdx.x;
   if (idx >= total) return;
-  const int cv = (int)(idx % CV); idx /= CV;
-  const int wo = (int)(idx % Wo); idx /= Wo;
-  const int ho = (int)(idx % Ho);
-  const int64_t f = idx / Ho;
+  const int cv = (int)(idx % (unsigned)CV);
+  const unsigned pix = idx / (unsigned)CV;
+  const int wo = (int)(pix % (unsigned)Wo);
+  const unsigned fr = pix / (unsigned)Wo;          // frame * Ho + ho
+  const int ho = (int)(fr % (unsigned)Ho);
+  const unsigned f = fr / (unsigned)Ho;
   uint32_t m = 0u;
-  const uint32_t *xf = x + f * (int64_t)H * W * WPP + (cv >> 1);
+  const uint32_t *xf = x + (size_t)f * H * W * WPP + (cv >> 2);
 #pragma unroll
   for (int r = 0; r < 3; ++r) {
     const int hi = ho * 2 - 1 + r;
@@ -149,14 +157,23 @@ maxpool3x3s2_bits_kernel(const uint32_t *__restrict__ x, XT *__restrict__ y, int
     for (int c = 0; c < 3; ++c) {
       const int wi = wo * 2 - 1 + c;
       if (wi < 0 || wi >= W) continue;
-      m |= __ldg(xf + ((int64_t)hi * W + wi) * WPP);
+      m |= __ldg(xf + (size_t)(hi * W + wi) * WPP);
     }
   }
-  m >>= (cv & 1) * 16;
-  float out[16];
+  m >>= (cv & 3) * 8;
+  XT *dst = y + (size_t)pix * C + cv * 8;
+  if constexpr (sizeof(XT) == 2) {
+    uint32_t o[4];
 #pragma unroll
-  for (int i = 0; i < 16; ++i) out[i] = (float)((m >> i) & 1u);
-  store_pack<XT, 16, false>(y + ((f * Ho + ho) * (int64_t)Wo + wo) * C + cv * 16, out);
+    for (int i = 0; i < 4; ++i)
+      o[i] = ((m >> (2 * i)) & 1u) * OneBits<XT>::v | ((m >> (2 * i + 1)) & 1u) * (OneBits<XT>::v << 16);
+    *reinterpret_cast<uint4 *>(dst) = make_uint4(o[0], o[1], o[2], o[3]);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+      *reinterpret_cast<float4 *>(dst + 4 * i) = make_float4(((m >> (4 * i)) & 1u) ? 1.f : 0.f, ((m >> (4 * i + 1)) & 1u) ? 1.f : 0.f,
+                                                              ((m >> (4 * i + 2)) & 1u) ? 1.f : 0.f, ((m >> (4 * i + 3)) & 1u) ? 1.f : 0.f);
+  }
 }
 
 // One CTA per (group of SB samples, chunk of classes): channel sums over (t, pixel) into shared memory,
@@ -330,14 +347,15 @@ extern "C" int snnb_maxpool3x3s2_bits(const void *x, void *y, int64_t frames, in
   SNNB_CHECK_ARG(aligned16(x) && aligned16(y), "maxpool3x3s2_bits: buffers must be 16-byte aligned");
   const int Ho = (H - 1) / 2 + 1, Wo = (W - 1) / 2 + 1;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const int64_t total = frames * Ho * Wo * (C / 16);
+  const int64_t total = frames * Ho * Wo * (C / 8);
+  if (total >= (1LL << 32) || frames * Ho >= (1LL << 31)) return fail(SNNB_ERR_INVALID, "maxpool3x3s2_bits: problem too large");
   const int64_t blocks = (total + 255) / 256;
-  if (blocks > 0x7fffffffLL) return fail(SNNB_ERR_INVALID, "maxpool3x3s2_bits: problem too large");
   if (blocks == 0) return SNNB_OK;
   const uint32_t *xs = static_cast<const uint32_t *>(x);
-  if (out_dtype == SNNB_F32) maxpool3x3s2_bits_kernel<float><<<(unsigned)blocks, 256, 0, st>>>(xs, static_cast<float *>(y), frames, H, W, C, Ho, Wo);
-  else if (out_dtype == SNNB_BF16) maxpool3x3s2_bits_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, st>>>(xs, static_cast<__nv_bfloat16 *>(y), frames, H, W, C, Ho, Wo);
-  else maxpool3x3s2_bits_kernel<__half><<<(unsigned)blocks, 256, 0, st>>>(xs, static_cast<__half *>(y), frames, H, W, C, Ho, Wo);
+  const int fr = (int)(frames * Ho);
+  if (out_dtype == SNNB_F32) maxpool3x3s2_bits_kernel<float><<<(unsigned)blocks, 256, 0, st>>>(xs, static_cast<float *>(y), fr, H, W, C, Ho, Wo);
+  else if (out_dtype == SNNB_BF16) maxpool3x3s2_bits_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, st>>>(xs, static_cast<__nv_bfloat16 *>(y), fr, H, W, C, Ho, Wo);
+  else maxpool3x3s2_bits_kernel<__half><<<(unsigned)blocks, 256, 0, st>>>(xs, static_cast<__half *>(y), fr, H, W, C, Ho, Wo);
   SNNB_CHECK_LAUNCH("maxpool3x3s2_bits");
   return SNNB_OK;
 }

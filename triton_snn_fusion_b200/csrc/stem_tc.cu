@@ -57,10 +57,19 @@ struct StemGeom {
 // accumulator re-read from tensor memory at every step (that is cheap; keeping 64 more values in
 // registers is not). The spikes of a step go to a 4 KB slot owned by the warp (128-byte swizzle:
 // 16-byte chunk j of row r sits at chunk j ^ (r & 7)), which lane 0 hands to TMA as one box. The warp
-// synchronises with nobody else. FAST: tau a power of two and hard reset, resolved at compile time.
+// synchronises with nobody else.
 // One-byte spikes (ST = uint8_t) make 64-byte rows: 16 channels per 16-byte chunk, 64-byte swizzle
 // (chunk j of row r sits at chunk j ^ ((r >> 1) & 3)), slots of 2 KB.
-template <typename XT, typename ST, typename VT, bool FAST>
+// spike as 0.0f / 1.0f (bit pattern 0 / 0x3F800000) -> bit `pos` of a word
+__device__ __forceinline__ uint32_t spike_bit(float s, int pos) {
+  const uint32_t u = __float_as_uint(s);
+  return pos <= 23 ? ((u >> (23 - pos)) & (1u << pos)) : ((u << (pos - 23)) & (1u << pos));
+}
+
+// KIND 0: any LIF (run-time lif_step); 1: tau a power of two and hard reset; 2: additionally v_reset == 0, which the
+// bit-packed path evaluates two channels at a time on the packed fp32 pipe (same roundings as lif_step: h = v +
+// (y - v) * inv_tau in three steps, and h - s * h is exactly 0 or h for s in {0, 1}).
+template <typename XT, typename ST, typename VT, int KIND>
 __device__ __forceinline__ void staged_tile(const StemGeom &g, const LifParams &p, const CUtensorMap *smap,
                                             ST *__restrict__ spikes, uint32_t acc_addr, uint32_t accempty_bar, uint32_t slots, uint32_t &sslot,
                                             const float *bias_s, const VT *__restrict__ v_init, VT *__restrict__ v_out,
@@ -95,13 +104,31 @@ __device__ __forceinline__ void staged_tile(const StemGeom &g, const LifParams &
         uint32_t a[16];
         umma::tmem_ld_x16(src + (uint32_t)(q * 16), a);
         umma::tmem_ld_wait();
+        if constexpr (KIND == 2) {
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const int c = q * 16 + i;
-          const float y = __uint_as_float(a[i]) + bias_s[c];
-          const bool sp = (FAST ? lif_step_t<1, true>(y, v[c], p) : lif_step(y, v[c], p)) != 0.f;
-          if (c < 32) w0 |= (sp ? 1u : 0u) << (c & 31);
-          else w1 |= (sp ? 1u : 0u) << (c & 31);
+          for (int i = 0; i < 16; i += 2) {
+            const int c = q * 16 + i;
+            const float2 y = __fadd2_rn(make_float2(__uint_as_float(a[i]), __uint_as_float(a[i + 1])),
+                                        make_float2(bias_s[c], bias_s[c + 1]));
+            const float2 vv = make_float2(v[c], v[c + 1]);
+            const float2 d = __fadd2_rn(y, make_float2(-vv.x, -vv.y));
+            const float2 h = __fadd2_rn(vv, __fmul2_rn(d, make_float2(p.inv_tau, p.inv_tau)));
+            const float2 sp = make_float2(h.x >= p.v_th ? 1.f : 0.f, h.y >= p.v_th ? 1.f : 0.f);
+            const float2 vn = __ffma2_rn(make_float2(-sp.x, -sp.y), h, h);
+            v[c] = vn.x;
+            v[c + 1] = vn.y;
+            if (c < 32) w0 |= spike_bit(sp.x, c & 31) | spike_bit(sp.y, (c + 1) & 31);
+            else w1 |= spike_bit(sp.x, c & 31) | spike_bit(sp.y, (c + 1) & 31);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const int c = q * 16 + i;
+            const float y = __uint_as_float(a[i]) + bias_s[c];
+            const bool sp = (KIND != 0 ? lif_step_t<1, true>(y, v[c], p) : lif_step(y, v[c], p)) != 0.f;
+            if (c < 32) w0 |= (sp ? 1u : 0u) << (c & 31);
+            else w1 |= (sp ? 1u : 0u) << (c & 31);
+          }
         }
       }
       if (t == g.T - 1) {   // last read of this accumulator stage: the MMA warp may overwrite it
@@ -140,7 +167,7 @@ __device__ __forceinline__ void staged_tile(const StemGeom &g, const LifParams &
         for (int i = 0; i < 16; ++i) {
           const int c = q * 16 + i;
           const float y = __uint_as_float(a[i]) + bias_s[c];
-          pk.v[i] = (uint8_t)((FAST ? lif_step_t<1, true>(y, v[c], p) : lif_step(y, v[c], p)) != 0.f);
+          pk.v[i] = (uint8_t)((KIND != 0 ? lif_step_t<1, true>(y, v[c], p) : lif_step(y, v[c], p)) != 0.f);
         }
         const uint4 u = *reinterpret_cast<const uint4 *>(&pk);
         const uint32_t dst = row + ((uint32_t)(q ^ ((lane >> 1) & 3)) << 4);
@@ -153,7 +180,7 @@ __device__ __forceinline__ void staged_tile(const StemGeom &g, const LifParams &
         for (int i = 0; i < 8; ++i) {
           const int c = q * 16 + h * 8 + i;
           const float y = __uint_as_float(a[h * 8 + i]) + bias_s[c];
-          pk.v[i] = DT<XT>::from_f(FAST ? lif_step_t<1, true>(y, v[c], p) : lif_step(y, v[c], p));
+          pk.v[i] = DT<XT>::from_f(KIND != 0 ? lif_step_t<1, true>(y, v[c], p) : lif_step(y, v[c], p));
         }
         const uint4 u = *reinterpret_cast<const uint4 *>(&pk);
         const uint32_t dst = row + ((uint32_t)((q * 2 + h) ^ (lane & 7)) << 4);
@@ -328,11 +355,14 @@ stem_gemm_lif_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_cons
           if (!ok) break;
           umma::tc_fence_after_sync();
           const uint32_t acc_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * (uint32_t)g.stage_cols;
-          if (p.mode == 1 && p.hard)
-            staged_tile<XT, ST, VT, true>(g, p, &smap, spikes, acc_addr, accempty(acc), slots, sslot, bias_s, v_init, v_out,
+          if (p.mode == 1 && p.hard && p.v_reset == 0.f && std::is_same<ST, uint64_t>::value)
+            staged_tile<XT, ST, VT, 2>(g, p, &smap, spikes, acc_addr, accempty(acc), slots, sslot, bias_s, v_init, v_out,
+                                       w0 + bx_off, h0 + by_off, b, pix, valid);
+          else if (p.mode == 1 && p.hard)
+            staged_tile<XT, ST, VT, 1>(g, p, &smap, spikes, acc_addr, accempty(acc), slots, sslot, bias_s, v_init, v_out,
                                       w0 + bx_off, h0 + by_off, b, pix, valid);
           else
-            staged_tile<XT, ST, VT, false>(g, p, &smap, spikes, acc_addr, accempty(acc), slots, sslot, bias_s, v_init, v_out,
+            staged_tile<XT, ST, VT, 0>(g, p, &smap, spikes, acc_addr, accempty(acc), slots, sslot, bias_s, v_init, v_out,
                                        w0 + bx_off, h0 + by_off, b, pix, valid);
         }
         // the shared-memory slots must outlive the TMA stores that read them
