@@ -126,53 +126,67 @@ maxpool3x3s2_u8_kernel(const uint8_t *__restrict__ x, XT *__restrict__ y, int64_
   store_pack<XT, 16, false>(y + ((f * Ho + ho) * (int64_t)Wo + wo) * C + cv * 16, out);
 }
 
-// 3x3 / stride 2 / padding 1 max-pool of bit-packed spikes: the max of 0 / 1 values is the OR of the words. A
-// thread produces 8 channels of one output pixel (one 16-byte store for 16-bit data): the threads of a warp that
-// share a pixel read the same nine words (one broadcast each) and the warp's store covers whole 128-byte rows.
-// Spikes are written as the bit patterns of 0.0 / 1.0 directly; all index arithmetic is 32-bit.
+// 3x3 / stride 2 / padding 1 max-pool of bit-packed spikes: the max of 0 / 1 values is the OR of the words.
+// A thread ORs the nine 64-bit words (64 channels) of one output pixel: a warp's load covers 32 neighbouring
+// pixels, i.e. a few contiguous lines. The 64 results of a pixel are 128 bytes of 16-bit output, so the warp then
+// writes its 32 pixels as 4096 contiguous bytes in eight fully coalesced 16-byte-per-lane stores, each lane
+// fetching the eight bits it needs from the lane that owns the pixel (two shuffles per store). Spikes are written
+// as the bit patterns of 0.0 / 1.0 directly; all index arithmetic is 32-bit.
 template <typename XT> struct OneBits;
 template <> struct OneBits<__nv_bfloat16> { static constexpr uint32_t v = 0x3F80u; };
 template <> struct OneBits<__half> { static constexpr uint32_t v = 0x3C00u; };
 
 template <typename XT>
 __global__ void __launch_bounds__(256)
-maxpool3x3s2_bits_kernel(const uint32_t *__restrict__ x, XT *__restrict__ y, int frames_rows, int H, int W, int C, int Ho, int Wo) {
-  const int CV = C >> 3, WPP = C >> 5;   // 8-channel groups and 32-bit words per pixel
-  const unsigned total = (unsigned)frames_rows * (unsigned)Wo * (unsigned)CV;   // frames_rows = frames * Ho
-  const unsigned idx = blockIdx.x * 256u + threadIdx.x;
-  if (idx >= total) return;
-  const int cv = (int)(idx % (unsigned)CV);
-  const unsigned pix = idx / (unsigned)CV;
-  const int wo = (int)(pix % (unsigned)Wo);
-  const unsigned fr = pix / (unsigned)Wo;          // frame * Ho + ho
+maxpool3x3s2_bits_kernel(const uint2 *__restrict__ x, XT *__restrict__ y, unsigned npix, int H, int W, int G, int Ho, int Wo) {
+  // x: [frames][H][W][G] 64-bit words (G = C / 64 channel groups); y: [frames][Ho][Wo][C]; blockIdx.y = channel group
+  const int g = blockIdx.y;
+  const unsigned pix = blockIdx.x * 256u + threadIdx.x;     // this thread's output pixel (frame, ho, wo) flattened
+  const unsigned pc = pix < npix ? pix : npix - 1;          // lanes past the end repeat the last pixel and store nothing
+  const int wo = (int)(pc % (unsigned)Wo);
+  const unsigned fr = pc / (unsigned)Wo;
   const int ho = (int)(fr % (unsigned)Ho);
   const unsigned f = fr / (unsigned)Ho;
-  uint32_t m = 0u;
-  const uint32_t *xf = x + (size_t)f * H * W * WPP + (cv >> 2);
+  uint32_t lo = 0u, hi = 0u;
+  const uint2 *xf = x + (size_t)f * H * W * G + g;
 #pragma unroll
   for (int r = 0; r < 3; ++r) {
-    const int hi = ho * 2 - 1 + r;
-    if (hi < 0 || hi >= H) continue;
+    const int hi_ = ho * 2 - 1 + r;
+    if (hi_ < 0 || hi_ >= H) continue;
 #pragma unroll
     for (int c = 0; c < 3; ++c) {
       const int wi = wo * 2 - 1 + c;
       if (wi < 0 || wi >= W) continue;
-      m |= __ldg(xf + (size_t)(hi * W + wi) * WPP);
+      const uint2 v = __ldg(xf + (size_t)(hi_ * W + wi) * G);
+      lo |= v.x;
+      hi |= v.y;
     }
   }
-  m >>= (cv & 3) * 8;
-  XT *dst = y + (size_t)pix * C + cv * 8;
-  if constexpr (sizeof(XT) == 2) {
-    uint32_t o[4];
+  const int lane = threadIdx.x & 31;
+  const unsigned warp_pix0 = pix - (unsigned)lane;          // first pixel of this warp
+  const int C = G * 64;
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
-      o[i] = ((m >> (2 * i)) & 1u) * OneBits<XT>::v | ((m >> (2 * i + 1)) & 1u) * (OneBits<XT>::v << 16);
-    *reinterpret_cast<uint4 *>(dst) = make_uint4(o[0], o[1], o[2], o[3]);
-  } else {
+  for (int k = 0; k < 8; ++k) {
+    // store k of the warp: lane L writes channels 8 * (L % 8) .. + 7 of pixel warp_pix0 + 4 * k + L / 8
+    const int src = 4 * k + (lane >> 3);
+    const uint32_t wl = __shfl_sync(0xffffffffu, lo, src), wh = __shfl_sync(0xffffffffu, hi, src);
+    const uint32_t m = (((lane & 4) ? wh : wl) >> ((lane & 3) * 8)) & 0xffu;
+    const unsigned p = warp_pix0 + (unsigned)src;
+    if (p < npix) {
+      XT *dst = y + (size_t)p * C + g * 64 + (lane & 7) * 8;
+      if constexpr (sizeof(XT) == 2) {
+        uint32_t o[4];
 #pragma unroll
-    for (int i = 0; i < 2; ++i)
-      *reinterpret_cast<float4 *>(dst + 4 * i) = make_float4(((m >> (4 * i)) & 1u) ? 1.f : 0.f, ((m >> (4 * i + 1)) & 1u) ? 1.f : 0.f,
-                                                              ((m >> (4 * i + 2)) & 1u) ? 1.f : 0.f, ((m >> (4 * i + 3)) & 1u) ? 1.f : 0.f);
+        for (int i = 0; i < 4; ++i)
+          o[i] = ((m >> (2 * i)) & 1u) * OneBits<XT>::v | ((m >> (2 * i + 1)) & 1u) * (OneBits<XT>::v << 16);
+        *reinterpret_cast<uint4 *>(dst) = make_uint4(o[0], o[1], o[2], o[3]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 2; ++i)
+          *reinterpret_cast<float4 *>(dst + 4 * i) = make_float4(((m >> (4 * i)) & 1u) ? 1.f : 0.f, ((m >> (4 * i + 1)) & 1u) ? 1.f : 0.f,
+                                                                  ((m >> (4 * i + 2)) & 1u) ? 1.f : 0.f, ((m >> (4 * i + 3)) & 1u) ? 1.f : 0.f);
+      }
+    }
   }
 }
 
@@ -347,15 +361,14 @@ extern "C" int snnb_maxpool3x3s2_bits(const void *x, void *y, int64_t frames, in
   SNNB_CHECK_ARG(aligned16(x) && aligned16(y), "maxpool3x3s2_bits: buffers must be 16-byte aligned");
   const int Ho = (H - 1) / 2 + 1, Wo = (W - 1) / 2 + 1;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const int64_t total = frames * Ho * Wo * (C / 8);
-  if (total >= (1LL << 32) || frames * Ho >= (1LL << 31)) return fail(SNNB_ERR_INVALID, "maxpool3x3s2_bits: problem too large");
-  const int64_t blocks = (total + 255) / 256;
-  if (blocks == 0) return SNNB_OK;
-  const uint32_t *xs = static_cast<const uint32_t *>(x);
-  const int fr = (int)(frames * Ho);
-  if (out_dtype == SNNB_F32) maxpool3x3s2_bits_kernel<float><<<(unsigned)blocks, 256, 0, st>>>(xs, static_cast<float *>(y), fr, H, W, C, Ho, Wo);
-  else if (out_dtype == SNNB_BF16) maxpool3x3s2_bits_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, st>>>(xs, static_cast<__nv_bfloat16 *>(y), fr, H, W, C, Ho, Wo);
-  else maxpool3x3s2_bits_kernel<__half><<<(unsigned)blocks, 256, 0, st>>>(xs, static_cast<__half *>(y), fr, H, W, C, Ho, Wo);
+  const int64_t npix = frames * Ho * Wo;
+  if (npix >= (1LL << 31)) return fail(SNNB_ERR_INVALID, "maxpool3x3s2_bits: problem too large");
+  if (npix == 0) return SNNB_OK;
+  const dim3 grid((unsigned)((npix + 255) / 256), (unsigned)(C / 64));
+  const uint2 *xs = static_cast<const uint2 *>(x);
+  if (out_dtype == SNNB_F32) maxpool3x3s2_bits_kernel<float><<<grid, 256, 0, st>>>(xs, static_cast<float *>(y), (unsigned)npix, H, W, C / 64, Ho, Wo);
+  else if (out_dtype == SNNB_BF16) maxpool3x3s2_bits_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(xs, static_cast<__nv_bfloat16 *>(y), (unsigned)npix, H, W, C / 64, Ho, Wo);
+  else maxpool3x3s2_bits_kernel<__half><<<grid, 256, 0, st>>>(xs, static_cast<__half *>(y), (unsigned)npix, H, W, C / 64, Ho, Wo);
   SNNB_CHECK_LAUNCH("maxpool3x3s2_bits");
   return SNNB_OK;
 }

@@ -176,18 +176,26 @@ def case_stem(a):
     _lib.check(_lib.lib.snnb_stem7x7_pack_weight(w.data_ptr(), wp.data_ptr(), a.cout, 1, _stream()), "pack")
     nscratch = int(_lib.lib.snnb_stem7x7_scratch_bytes(a.B, a.hw, a.hw))
     scratch = torch.empty(nscratch, device=DEV, dtype=torch.uint8)
-    sp = torch.empty(a.T, a.B, ho, ho, a.cout, device=DEV, dtype=dt)
-    v = torch.empty(a.B, ho, ho, a.cout, device=DEV, dtype=dt)
+    # spikes in the activation dtype with a membrane output (the drop-in form), or one byte / one bit each without
+    # one (the executor's form)
+    if a.spikes == "same":
+        sp = torch.empty(a.T, a.B, ho, ho, a.cout, device=DEV, dtype=dt)
+        v, sdt = torch.empty(a.B, ho, ho, a.cout, device=DEV, dtype=dt), 1
+    elif a.spikes == "u8":
+        sp, v, sdt = torch.empty(a.T, a.B, ho, ho, a.cout, device=DEV, dtype=torch.uint8), None, _lib.U8
+    else:
+        sp, v, sdt = torch.empty(a.T, a.B, ho, ho, a.cout // 8, device=DEV, dtype=torch.uint8), None, _lib.B1
 
     def call():   # one frame for all T steps (direct encoding)
         _lib.check(_lib.lib.snnb_stem7x7_lif(x.data_ptr(), 0, wp.data_ptr(), b.data_ptr(), None, sp.data_ptr(),
-                                             v.data_ptr(), scratch.data_ptr(), nscratch, a.T, a.B, a.hw, a.hw,
-                                             a.cout, 1, 1, 1, *LIF, _stream()), "snnb_stem7x7_lif")
+                                             v.data_ptr() if v is not None else None, scratch.data_ptr(), nscratch,
+                                             a.T, a.B, a.hw, a.hw, a.cout, 1, sdt, 1, *LIF, _stream()), "snnb_stem7x7_lif")
 
     ms = _time(call, a.reps)
-    nbytes = 2 * (x.numel() + sp.numel() + v.numel()) + 2 * nscratch
-    print(f"stem7x7_lif B{a.B} 3->{a.cout} {a.hw}^2 T{a.T} bf16 (s2d + GEMM): {ms:.4f} ms  {nbytes / ms / 1e6:.0f} GB/s  "
-          f"spike rate {float(sp.float().mean()):.3f}  device status {_lib.device_status()}")
+    nbytes = 2 * x.numel() + sp.numel() * sp.element_size() + (2 * v.numel() if v is not None else 0) + 2 * nscratch
+    rate = float(sp.float().mean()) if a.spikes != "bits" else float("nan")
+    print(f"stem7x7_lif B{a.B} 3->{a.cout} {a.hw}^2 T{a.T} bf16, spikes {a.spikes} (s2d + GEMM): {ms:.4f} ms  "
+          f"{nbytes / ms / 1e6:.0f} GB/s  spike rate {rate:.3f}  device status {_lib.device_status()}")
 
 
 def main(argv=None):
@@ -225,6 +233,7 @@ def main(argv=None):
     m.add_argument("--B", type=int, default=128)
     m.add_argument("--hw", type=int, default=224)
     m.add_argument("--cout", type=int, default=64)
+    m.add_argument("--spikes", choices=["same", "u8", "bits"], default="same")
     m.set_defaults(fn=case_stem)
     n = sub.add_parser("linear")
     n.add_argument("--M", type=int, default=4096)
