@@ -41,6 +41,20 @@ inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 
 inline int dtype_size(int dt) { return dt == SNNB_F32 ? 4 : (dt == SNNB_U8 ? 1 : 2); }
 inline bool is_act_dtype(int dt) { return dt == SNNB_F32 || dt == SNNB_BF16 || dt == SNNB_F16; }
 
+// Raises the dynamic shared-memory limit of kernel `Kern` to `bytes` once per device (the kernel is a template
+// argument, so every kernel has its own flags).
+template <auto Kern>
+inline cudaError_t raise_smem_limit_once(int bytes) {
+  static bool done[64] = {};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev >= 0 && dev < 64 && done[dev]) return cudaSuccess;
+  e = cudaFuncSetAttribute(Kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e == cudaSuccess && dev >= 0 && dev < 64) done[dev] = true;
+  return e;
+}
+
 // ---------------------------------------------------------------- dtypes ----
 template <typename T> struct DT;
 template <> struct DT<float> {

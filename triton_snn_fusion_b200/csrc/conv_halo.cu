@@ -318,7 +318,7 @@ int launch(const ConvArgs &a, cudaStream_t stream) {
   }
   const size_t smem = (size_t)g.halo_slots * kHaloBytes + (size_t)kWRing * g.w_slot_bytes + 1024;
   auto kern = conv3x3_halo_kernel<XT, ST, VT>;
-  const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  const cudaError_t e = raise_smem_limit_once<conv3x3_halo_kernel<XT, ST, VT>>(225 * 1024);
   if (e != cudaSuccess) return fail(SNNB_ERR_CUDA, "conv_lif: cannot raise the shared-memory limit: %s", cudaGetErrorString(e));
   kern<<<(unsigned)grid, kThreadsH, smem, stream>>>(xm, wm, static_cast<const XT *>(a.b), static_cast<const XT *>(a.res),
                                                     static_cast<const VT *>(a.v_init), static_cast<ST *>(a.spikes),

@@ -363,8 +363,8 @@ int launch(const ConvArgs &a, cudaStream_t stream) {
   }
   const size_t smem = (size_t)g.slots * kSlotBytes + kWSlots * (size_t)g.w_slot_bytes + 1024;
   auto kern = conv_lif_tc_kernel<XT, ST, VT>;
-  {  // per device and per kernel; cheap enough to repeat on every launch
-    const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  {
+    const cudaError_t e = raise_smem_limit_once<conv_lif_tc_kernel<XT, ST, VT>>(225 * 1024);
     if (e != cudaSuccess) return fail(SNNB_ERR_CUDA, "conv_lif: cannot raise the shared-memory limit: %s", cudaGetErrorString(e));
   }
   kern<<<(unsigned)grid, kThreads, smem, stream>>>(

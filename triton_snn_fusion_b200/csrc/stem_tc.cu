@@ -471,7 +471,7 @@ int launch(const StemGemmArgs &a, cudaStream_t stream) {
   }
   const size_t smem = (size_t)4 * g.w_chunk_bytes + (size_t)g.ring * kChunkBytes + (g.staged ? (size_t)kStage * kChunkBytes : 0) + 1024;
   auto kern = stem_gemm_lif_kernel<XT, ST, VT>;
-  const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  const cudaError_t e = raise_smem_limit_once<stem_gemm_lif_kernel<XT, ST, VT>>(225 * 1024);
   if (e != cudaSuccess) return fail(SNNB_ERR_CUDA, "stem7x7_lif: cannot raise the shared-memory limit: %s", cudaGetErrorString(e));
   kern<<<(unsigned)grid, kThreadsS, smem, stream>>>(xm, wm, sm, static_cast<const XT *>(a.b), static_cast<const VT *>(a.v_init),
                                                     static_cast<ST *>(a.spikes), static_cast<VT *>(a.v_out), g, a.p);
