@@ -170,6 +170,16 @@ int snnb_conv_lif(const void *x_seq, int64_t x_t_stride, const void *w, const vo
                   float v_th, float v_reset, float tau, int path, void *stream);
 
 /*
+ * Diagnostic: the name of the kernel snnb_conv_lif would run for a call of this shape ("conv3x3_pair",
+ * "conv3x3_halo", "conv_lif_tc", "conv3x3_smallcin" or "conv_lif_simt"), assuming 16-byte aligned dense buffers.
+ * one_frame != 0: the same input frame at every step (x_t_stride == 0). Launches nothing. The reference reports
+ * its kernel choice through kernel_key / kernel_temporal_config of its result objects
+ * (runtime/triton_convlif_backend.py:7-15); this is the C-level counterpart.
+ */
+int snnb_conv_lif_which(int T, int B, int Cin, int H, int W, int Cout, int KH, int KW, int stride, int pad,
+                        int lif, int dtype, int one_frame, int has_residual, int path, char *name, int name_len);
+
+/*
  * 3x3 / stride 1 / padding 1 conv + a 1x1 shortcut conv with stride sc_stride over a second input,
  * summed before the LIF: the second conv of a ResNet block whose shortcut is a strided 1x1 conv + BN.
  * The reference runs the shortcut conv as its own op and feeds it to the residual input of

@@ -217,3 +217,31 @@ def test_depthwise_tile_kernel_one_frame_for_all_steps_and_soft_reset():
                                      T, B, C, H, W, 1, L.BF16, L.BF16, L.BF16, 0.8, -1.0, 3.0, None), "snnb_dwconv3x3_lif")
     torch.cuda.synchronize()
     check_parity(sp.permute(0, 1, 4, 2, 3), v.permute(0, 3, 1, 2), rs, rv, dtype, what="soft reset, tau 3")
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_packed_out_writes_channels_last_buffers_in_place(dtype):
+    """Caller-owned outputs that already are channels-last (what this backend's own outputs and the graph executor's
+    buffers are): the kernel writes straight into them - the result object holds the caller's tensors, poisoned
+    buffers come back fully overwritten, and a pre-stacked channels-last input is read without a copy."""
+    be = _be()
+    torch.manual_seed(5)
+    T, B, cin, cout, H, W = 4, 2, 64, 128, 12, 9
+    x = (torch.rand(T, B, cin, H, W) < 0.2).to(dtype)
+    w = (torch.randn(cout, cin, 3, 3) * 0.15).to(dtype)
+    b = (torch.randn(cout) * 0.1).to(dtype)
+    v0 = (torch.randn(B, cout, H, W) * 0.3).to(dtype)
+    rs, rv = orc.temporal_conv_lif([orc.widen(x[t]) for t in range(T)], orc.widen(w), orc.widen(b), orc.widen(v0),
+                                   [1, 1], [1, 1], [1, 1], 1, 1.0, 0.0, 2.0)
+    x_seq = be.empty_nhwc([T, B, cin, H, W], dtype, DEV)
+    x_seq.copy_(x)
+    spike_out = be.empty_nhwc([T, B, cout, H, W], dtype, DEV)
+    v_out = be.empty_nhwc([B, cout, H, W], dtype, DEV)
+    spike_out.fill_(7.0)
+    v_out.fill_(7.0)
+    r = be.run_triton_fused_temporal_conv_lif_state_packed_out(
+        x_seq, w.to(DEV), b.to(DEV), be.to_nhwc(v0.to(DEV)), [1, 1], [1, 1], [1, 1], 1, 1.0, 0.0, 2.0, False,
+        spike_out, v_out, strict=True)
+    assert r.spikes.data_ptr() == spike_out.data_ptr() and r.v_next.data_ptr() == v_out.data_ptr()
+    assert r.kernel_diagnostics["stack_materialized"] is False
+    check_parity(spike_out, v_out, rs, rv, dtype, what="packed_out, channels-last buffers")

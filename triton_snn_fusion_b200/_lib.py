@@ -37,6 +37,7 @@ SIGNATURES = {
     "snnb_conv_lif": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                               c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                               c_int, c_int, c_int, c_float, c_float, c_float, c_int, c_void_p]),
+    "snnb_conv_lif_which": (c_int, [c_int] * 15 + [c_char_p, c_int]),
     "snnb_linear_lif": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                 c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                 c_float, c_float, c_float, c_int, c_void_p]),
@@ -106,6 +107,15 @@ def ptr(t) -> int | None:
 
 def current_stream(device) -> int:
     return torch.cuda.current_stream(device).cuda_stream
+
+
+def conv_kernel_name(T, B, Cin, H, W, Cout, k, stride, pad, dtype, lif=True, one_frame=False, residual=False,
+                     path=PATH_AUTO) -> str:
+    """Which kernel snnb_conv_lif would run for this shape (no launch)."""
+    buf = ctypes.create_string_buffer(64)
+    check(lib.snnb_conv_lif_which(T, B, Cin, H, W, Cout, k, k, stride, pad, int(lif), dtype_code(dtype), int(one_frame),
+                                  int(residual), path, buf, 64), "snnb_conv_lif_which")
+    return buf.value.decode()
 
 
 def device_status() -> int:

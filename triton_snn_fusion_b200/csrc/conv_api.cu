@@ -61,6 +61,37 @@ extern "C" int snnb_conv_lif(const void *x_seq, int64_t x_t_stride, const void *
   return run(a, path, static_cast<cudaStream_t>(stream), "conv_lif");
 }
 
+extern "C" int snnb_conv_lif_which(int T, int B, int Cin, int H, int W, int Cout, int KH, int KW, int stride, int pad,
+                                   int lif, int dtype, int one_frame, int has_residual, int path, char *name, int name_len) {
+  using namespace snnb;
+  SNNB_CHECK_ARG(name != nullptr && name_len >= 8, "conv_lif_which: name buffer too small");
+  SNNB_CHECK_ARG(T >= 1 && B >= 1 && Cin >= 1 && Cout >= 1 && H >= 1 && W >= 1 && KH >= 1 && KW >= 1 && stride >= 1 && pad >= 0,
+                 "conv_lif_which: bad sizes");
+  SNNB_CHECK_ARG(is_act_dtype(dtype), "conv_lif_which: unsupported dtype %d", dtype);
+  ConvArgs a;
+  // stand-in addresses: 16-byte aligned and distinct, which is all the support gates look at
+  a.x = reinterpret_cast<const void *>(uintptr_t(0x1000)); a.w = reinterpret_cast<const void *>(uintptr_t(0x2000));
+  a.b = reinterpret_cast<const void *>(uintptr_t(0x3000)); a.res = has_residual ? reinterpret_cast<const void *>(uintptr_t(0x4000)) : nullptr;
+  a.v_init = nullptr; a.spikes = reinterpret_cast<void *>(uintptr_t(0x5000)); a.v_out = reinterpret_cast<void *>(uintptr_t(0x6000));
+  a.T = T; a.B = B; a.Cin = Cin; a.H = H; a.W = W; a.Cout = Cout; a.KH = KH; a.KW = KW; a.stride = stride; a.pad = pad;
+  a.Ho = (H + 2 * pad - KH) / stride + 1; a.Wo = (W + 2 * pad - KW) / stride + 1;
+  SNNB_CHECK_ARG(a.Ho >= 1 && a.Wo >= 1, "conv_lif_which: empty output");
+  a.x_t_stride = one_frame ? 0 : (int64_t)B * H * W * Cin;
+  a.lif = lif ? 1 : 0; a.dtype = dtype; a.spike_dtype = dtype; a.v_dtype = dtype;
+  a.p = make_lif_params(1.0f, 0.0f, 2.0f);
+  const char *k = "conv_lif_simt";
+  const bool taps_only = path == SNNB_PATH_TCGEN05_TAPS;
+  const char *why = "";
+  if (path == SNNB_PATH_AUTO && conv_smallcin_supported(a)) k = "conv3x3_smallcin";
+  else if (path == SNNB_PATH_SIMT) k = "conv_lif_simt";
+  else if (!taps_only && path != SNNB_PATH_TCGEN05_HALO && conv3x3_pair_supported(a)) k = "conv3x3_pair";
+  else if (!taps_only && conv3x3_halo_supported(a)) k = "conv3x3_halo";
+  else if (conv_lif_tc_supported(a, &why)) k = "conv_lif_tc";
+  else if (path != SNNB_PATH_AUTO) return fail(SNNB_ERR_UNSUPPORTED, "conv_lif_which: no tensor-core kernel takes this call: %s", why);
+  snprintf(name, (size_t)name_len, "%s", k);
+  return SNNB_OK;
+}
+
 extern "C" int snnb_conv3x3_shortcut_lif(const void *x_seq, int64_t x_t_stride, const void *w, const void *b,
                                          const void *sc_x, int64_t sc_t_stride, const void *sc_w, const void *sc_b,
                                          int sc_cin, int sc_H, int sc_W, int sc_stride,
