@@ -116,6 +116,21 @@ def test_conv(case, residual):
     assert 0.01 < float(rs.mean()) < 0.7
 
 
+def test_conv_few_output_channels_duplicated_rows_form():
+    """3x3 / stride 1 convs with at most 64 output channels run the two-kernel-rows form of the pair kernel by
+    default; SNNB_TWIN=0 selects the form that duplicates the weight rows. The switch is read once per process,
+    so that form is checked in a child process on the two such shapes of the list above (64->64 on 56x56 with and
+    without residual, 64->48 on 9x11)."""
+    import os
+    import subprocess
+    import sys
+    env = dict(os.environ, SNNB_TWIN="0")
+    r = subprocess.run([sys.executable, "-m", "pytest", __file__, "-q", "-x", "-m", "gpu", "-p", "no:cacheprovider",
+                        "-k", "test_conv and (case0 or case11)"], env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert " passed" in r.stdout
+
+
 @pytest.mark.parametrize("T", [1, 2, 6, 8, 12, 16, 72])
 def test_conv_other_window_lengths(T):
     """Sequence lengths other than four: one launch for T = 1 and any even T up to 64 (timestep pairs alternate

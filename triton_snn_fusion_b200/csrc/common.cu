@@ -34,6 +34,14 @@ bool pdl_enabled() {
   return on;
 }
 
+bool twin_enabled() {
+  static const bool on = [] {
+    const char *e = std::getenv("SNNB_TWIN");
+    return e == nullptr || e[0] != '0';
+  }();
+  return on;
+}
+
 int sm_count() {
   static int cached[64] = {};
   int dev = 0;

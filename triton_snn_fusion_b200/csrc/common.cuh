@@ -33,6 +33,9 @@ int fail(int code, const char *fmt, ...);
 // Whether kernels that support it are launched with programmatic dependent launch (on unless the environment
 // variable SNNB_PDL is set to 0).
 bool pdl_enabled();
+// Whether 3x3 / stride 1 convs with at most 64 output channels use the two-kernel-rows-per-MMA form of the
+// timestep-pair kernel (default; SNNB_TWIN=0 in the environment selects the form that duplicates the weight rows).
+bool twin_enabled();
 
 // Number of SMs of the current device (queried once per device; 0 if the query fails).
 int sm_count();

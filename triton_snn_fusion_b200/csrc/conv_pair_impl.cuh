@@ -47,8 +47,17 @@ constexpr int kIdentBytes = 192 * 128;                 // zero rows / 64x64 iden
 constexpr int kWRingP = 5;                             // weight-tile slots (16 KB each): a load must cover ~1 us of L2 latency
 constexpr int kWSlot = 128 * 128;
 constexpr int kEpiW = 8;
-constexpr int kHaloWarpP = kEpiW, kWWarpP = kEpiW + 1, kMmaWarpP = kEpiW + 2;
-constexpr int kThreadsP = 32 * (kEpiW + 3);
+// "twin" mode (3x3 / stride 1 conv with at most 64 output channels): see PairGeom::twin
+constexpr int kTwinIdentBytes = 128 * 128;             // identity rows for D1, zero rows for D2
+constexpr int kEpiWTwin = 16;                          // twin mode runs 16 epilogue warps of 16 pixels each
+constexpr int kXchgWarp = 32 * 64;                     // one epilogue warp's outgoing values of one timestep: 16 floats per lane
+constexpr int kXchgBytes = kEpiWTwin * kXchgWarp;      // 32768
+// warp roles: epilogue warps first, then halo producer, weight producer, MMA issuer
+template <bool TWIN> struct Roles {
+  static constexpr int kEpi = TWIN ? kEpiWTwin : kEpiW;
+  static constexpr int kHalo = kEpi, kW = kEpi + 1, kMma = kEpi + 2;
+  static constexpr int kThreads = 32 * (kEpi + 3);
+};
 
 struct PairGeom {
   int T, Tacc, B, Cin, Cout, Ho, Wo;
@@ -72,7 +81,16 @@ struct PairGeom {
   int stack;  // maps of at most 7 x 8: two images per tile, image b in row groups 0.., image b + 1 in groups 8..
               // (halo rows 0..8 and 8..16 of a timestep's region: row 8 is the zero padding of both, row 16
               // is row 0 of the next region, which is the zero top padding of whatever is stored there)
-  int dup;    // Cout <= 64: the 64 weight rows are loaded twice (M rows 64..127 repeat 0..63) so that all
+  int twin;   // 3x3 / stride 1 with Cout <= 64 (the TWIN instantiation of the kernel): instead of duplicating the 64
+              // weight rows, the M rows carry the weights of TWO kernel rows against the same pixel operand. M rows
+              // [0,32) and [64,96) ("D1", channels 0..31 / 32..63) hold kernel row 0, rows [32,64) and [96,128)
+              // ("D2", same channels) kernel row 1, both multiplied with halo row R for pixel row R; three more
+              // groups hold zeros in D1 and kernel row 2 in D2 and read halo row R + 1. Then
+              // out[R] = D1[R] + D2[R + 1]: 6 MMA groups per slab instead of 9. In TMEM each lane quarter holds one
+              // of D1 / D2 for 32 channels; the warps of quarters q and q ^ 1 pass each other through shared memory
+              // the halves the other one needs and each runs the LIF for a quarter of the tile's rows.
+  int stage_off;   // twin: byte offset of the exchange buffers from the aligned start of dynamic shared memory
+  int dup;    // Cout <= 64 (shapes twin mode does not take): the 64 weight rows are loaded twice (M rows 64..127 repeat 0..63) so that all
               // eight epilogue warps can read the accumulator and split the pixels four ways
   long long wait_limit;   // bound of every mbarrier wait, in SM cycles (about two seconds unless a self-test shortens it)
   int drop_load;          // self-test: CTA 0 announces its first weight tile but never loads it, so that its waits run out
@@ -83,14 +101,23 @@ struct PairGeom {
 
 // The taps served by halo tile `ph` of a slab: all of them for stride 1 (ph = 0); for stride 2 the taps
 // whose input rows / columns have the parity of phase ph = 2a + b.
-template <bool S2>
+template <bool S2, bool TWIN>
 __device__ __forceinline__ int phase_ntaps(const PairGeom &g, int ph) {
-  return S2 ? ((ph & 2) ? 2 : 1) * ((ph & 1) ? 2 : 1) : g.ntaps;
+  return S2 ? ((ph & 2) ? 2 : 1) * ((ph & 1) ? 2 : 1) : (TWIN ? 6 : g.ntaps);
 }
 // j-th tap of phase ph: its index in the weight tensor (kh * 3 + kw) and its row offset inside the halo tile.
-template <bool S2>
+template <bool S2, bool TWIN>
 __device__ __forceinline__ void phase_tap(const PairGeom &g, int ph, int j, int &wtap, int &off) {
   if constexpr (!S2) {
+    if constexpr (TWIN) {
+      // group j < 3: kernel rows 0 (D1 rows) and 1 (D2 rows) against halo row R of pixel row R; group j >= 3:
+      // zero weights (D1 rows) and kernel row 2 (D2 rows) against halo row R + 1. With out[R] = D1[R] + D2[R + 1]
+      // every (kernel row, halo row) product lands once, and no accumulator that is used reads past the halo
+      // tile. wtap = kernel column.
+      wtap = j < 3 ? j : j - 3;
+      off = (j < 3 ? 0 : kPW) + wtap;
+      return;
+    }
     const int kh = g.ntaps == 1 ? 1 : j / 3, kw = g.ntaps == 1 ? 1 : j - kh * 3;
     wtap = g.ntaps == 1 ? 0 : j;
     off = g.flat ? 0 : kh * kPW + kw;
@@ -207,14 +234,147 @@ __device__ __forceinline__ void pair_epilogue_full(const LifParams &p, uint32_t 
   }
 }
 
-template <typename XT, typename ST, typename VT, bool S2>
-__global__ void __launch_bounds__(kThreadsP)
+// ---------------------------------------------------------------------------------------------------------
+// Lean epilogue bodies for the common case: two timesteps per pair, tau a power of two, hard reset to zero, a
+// tile that lies completely inside the image. Two neighbouring pixels share each packed-fp32 instruction, the
+// chunk loop is unrolled (no register rotation), and with COUT known at compile time every store address is
+// "row pointer + constant" (COUT = 0: the stride is a run-time value).
+//
+// h = v + (y - v) * inv_tau: the product with a power of two is exact, so the fused multiply-add rounds the same
+// sum as lif_step's separately rounded multiply and add; with s in {0, 1}, h - s * h is exactly 0 or h.
+__device__ __forceinline__ float2 lif_fast2(float2 y, float &vx, float &vy, float v_th, float2 inv_tau2) {
+  const float2 v = make_float2(vx, vy);
+  const float2 d = __fadd2_rn(y, make_float2(-vx, -vy));
+  const float2 h = __ffma2_rn(d, inv_tau2, v);
+  const float2 s = make_float2(h.x >= v_th ? 1.f : 0.f, h.y >= v_th ? 1.f : 0.f);
+  const float2 vn = __ffma2_rn(make_float2(-s.x, -s.y), h, h);
+  vx = vn.x;
+  vy = vn.y;
+  return s;
+}
+
+template <typename ST, int NROWS, int COUT>
+__device__ __forceinline__ void pair_epilogue_lean(const LifParams &p, uint32_t tmem_addr, float bias_c,
+                                                   ST *__restrict__ out, long long frame_out, const PixMap &pm,
+                                                   float (&v)[64]) {
+  constexpr int NCH = NROWS / 2;   // chunks of 16 pixels = two tile rows
+  const float2 b2 = make_float2(bias_c, bias_c), it2 = make_float2(p.inv_tau, p.inv_tau);
+  const float v_th = p.v_th;
+  const int cs = COUT ? COUT : pm.Cout;
+  ST *row = out + pm.row0_off;
+#pragma unroll
+  for (int c = 0; c < NCH; ++c) {
+    uint32_t a[2][16];   // [timestep][pixel]
+    umma::tmem_ld_x16(tmem_addr + (uint32_t)(c * 16), a[0]);
+    umma::tmem_ld_x16(tmem_addr + (uint32_t)(128 + c * 16), a[1]);
+    umma::tmem_ld_wait();
+#pragma unroll
+    for (int rr = 0; rr < 2; ++rr) {
+      ST *q0 = row, *q1 = row + frame_out;
+#pragma unroll
+      for (int j = 0; j < 8; j += 2) {
+        const int i = rr * 8 + j, k = c * 16 + i;
+        const float2 y0 = __fadd2_rn(make_float2(__uint_as_float(a[0][i]), __uint_as_float(a[0][i + 1])), b2);
+        const float2 y1 = __fadd2_rn(make_float2(__uint_as_float(a[1][i]), __uint_as_float(a[1][i + 1])), b2);
+        const float2 s0 = lif_fast2(y0, v[k], v[k + 1], v_th, it2);
+        const float2 s1 = lif_fast2(y1, v[k], v[k + 1], v_th, it2);
+        q0[j * cs] = DT<ST>::from_f(s0.x);
+        q0[(j + 1) * cs] = DT<ST>::from_f(s0.y);
+        q1[j * cs] = DT<ST>::from_f(s1.x);
+        q1[(j + 1) * cs] = DT<ST>::from_f(s1.y);
+      }
+      row += pm.row_stride;
+    }
+  }
+}
+
+template <typename ST, int NROWS>
+__device__ __forceinline__ void pair_epilogue_lean_any(const LifParams &p, uint32_t tmem_addr, float bias_c,
+                                                       ST *__restrict__ out, long long frame_out, const PixMap &pm,
+                                                       float (&v)[64]) {
+  switch (pm.Cout) {
+    case 128: pair_epilogue_lean<ST, NROWS, 128>(p, tmem_addr, bias_c, out, frame_out, pm, v); break;
+    default: pair_epilogue_lean<ST, NROWS, 0>(p, tmem_addr, bias_c, out, frame_out, pm, v); break;
+  }
+}
+
+// Exchange buffers of twin mode: 64 bytes per lane (16 floats), the four 16-byte pieces of a lane stored at
+// piece ^ ((lane >> 1) & 3) so that the 16-byte accesses of eight neighbouring lanes fall on different banks.
+__device__ __forceinline__ uint32_t xchg_piece(uint32_t lane_row, int lane, int q) {
+  return lane_row + (uint32_t)((q ^ ((lane >> 1) & 3)) << 4);
+}
+
+// Twin mode, same case: one timestep for this thread's 16 pixels (64 output channels: the pixel stride is a
+// constant). Own accumulator half (tensor memory) + the partner's half (shared memory) + bias -> LIF -> spikes.
+template <typename ST>
+__device__ __forceinline__ void twin_step_lean(const LifParams &p, uint32_t tmem_addr, uint32_t in_row, int lane,
+                                               float bias_c, ST *__restrict__ out, const PixMap &pm, float (&v)[16]) {
+  constexpr int cs = 64;
+  const float2 b2 = make_float2(bias_c, bias_c), it2 = make_float2(p.inv_tau, p.inv_tau);
+  const float v_th = p.v_th;
+  uint32_t a[16];
+  float d[16];
+  umma::tmem_ld_x16(tmem_addr, a);
+#pragma unroll
+  for (int q = 0; q < 4; ++q)
+    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(d[4 * q]), "=f"(d[4 * q + 1]), "=f"(d[4 * q + 2]), "=f"(d[4 * q + 3])
+                 : "r"(xchg_piece(in_row, lane, q)));
+  umma::tmem_ld_wait();
+  ST *row = out + pm.row0_off;
+#pragma unroll
+  for (int rr = 0; rr < 2; ++rr) {
+#pragma unroll
+    for (int j = 0; j < 8; j += 2) {
+      const int i = rr * 8 + j;
+      const float2 acc = __fadd2_rn(make_float2(__uint_as_float(a[i]), __uint_as_float(a[i + 1])), make_float2(d[i], d[i + 1]));
+      const float2 s = lif_fast2(__fadd2_rn(acc, b2), v[i], v[i + 1], v_th, it2);
+      row[j * cs] = DT<ST>::from_f(s.x);
+      row[(j + 1) * cs] = DT<ST>::from_f(s.y);
+    }
+    row += pm.row_stride;
+  }
+}
+
+// Twin mode, any case: every pixel predicated on the tile / image edges and on the channel count.
+template <typename XT, typename ST, int KIND>
+__device__ __forceinline__ void twin_step(const LifParams &p, uint32_t tmem_addr, uint32_t in_row, int lane, float bias_c,
+                                          ST *__restrict__ out, const PixMap &pm, float (&v)[16]) {
+  uint32_t a[16];
+  float d[16];
+  umma::tmem_ld_x16(tmem_addr, a);
+#pragma unroll
+  for (int q = 0; q < 4; ++q)
+    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(d[4 * q]), "=f"(d[4 * q + 1]), "=f"(d[4 * q + 2]), "=f"(d[4 * q + 3])
+                 : "r"(xchg_piece(in_row, lane, q)));
+  umma::tmem_ld_wait();
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const int r = i >> 3, j = i & 7;   // 16 pixels are two tile rows of 8
+    const bool ok = ((pm.rows_ok >> r) & 1) && ((pm.cols_ok >> j) & 1);
+    const long long o = pm.row0_off + (long long)r * pm.row_stride + j * pm.Cout;
+    const float y = (__uint_as_float(a[i]) + d[i]) + bias_c;
+    if (ok) {
+      if constexpr (KIND == kLifOff) {
+        reinterpret_cast<XT *>(out)[o] = DT<XT>::from_f(y);
+      } else {
+        const float s = (KIND == kLifFast) ? lif_step_t<1, true>(y, v[i], p) : lif_step(y, v[i], p);
+        out[o] = DT<ST>::from_f(s);
+      }
+    }
+  }
+}
+
+template <typename XT, typename ST, typename VT, bool S2, bool TWIN>
+__global__ void __launch_bounds__(Roles<TWIN>::kThreads)
 conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap,
                     const __grid_constant__ CUtensorMap rmap, const __grid_constant__ CUtensorMap wmap64,
                     const __grid_constant__ CUtensorMap scwmap, const __grid_constant__ CUtensorMap xmap01,
                     const __grid_constant__ CUtensorMap xmap10, const __grid_constant__ CUtensorMap xmap11,
                     const XT *__restrict__ bias, const XT *__restrict__ bias2, const VT *v_init,
                     ST *__restrict__ spikes, VT *v_out, const PairGeom g, const LifParams p) {
+  using R = Roles<TWIN>;
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bars[2 * kPairRing + 2 * kWRingP + 4];
   __shared__ uint32_t tmem_base_s;
@@ -226,7 +386,7 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
   const uint32_t smem_base = (umma::smem_u32(smem_raw) + 1023u) & ~1023u;
   // [identity block (residual path only)] [weight ring] [halo ring]
   const uint32_t ident_base = smem_base;
-  const uint32_t w_base = smem_base + ((g.has_res && !g.sc_slabs) ? (uint32_t)kIdentBytes : 0u);
+  const uint32_t w_base = smem_base + ((g.has_res && !g.sc_slabs) ? (uint32_t)(TWIN ? kTwinIdentBytes : kIdentBytes) : 0u);
   const uint32_t h_base = w_base + (uint32_t)(g.wring * kWSlot);
   const uint32_t slot_bytes = (uint32_t)(g.tq * g.halo_t);
   const uint32_t bar_base = umma::smem_u32(bars);
@@ -266,30 +426,32 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
     abort_s = 0;
     for (int s = 0; s < g.ring; ++s) { umma::mbar_init(hfull(s), 1); umma::mbar_init(hempty(s), 1); }
     for (int s = 0; s < g.wring; ++s) { umma::mbar_init(wfull(s), 1); umma::mbar_init(wempty(s), 1); }
-    for (int s = 0; s < 2; ++s) { umma::mbar_init(accfull(s), 1); umma::mbar_init(accempty(s), kEpiW); }
+    for (int s = 0; s < 2; ++s) { umma::mbar_init(accfull(s), 1); umma::mbar_init(accempty(s), R::kEpi); }
     umma::fence_mbar_init();
   }
-  if (warp == kMmaWarpP) {
+  if (warp == R::kMma) {
     umma::tmem_alloc(umma::smem_u32(&tmem_base_s), (uint32_t)g.tmem_cols);
     umma::tmem_relinquish();
   }
-  if (warp == kHaloWarpP && lane == 0) {
+  if (warp == R::kHalo && lane == 0) {
     umma::prefetch_tensormap(&xmap);
     umma::prefetch_tensormap(&wmap);
     if (g.has_res) umma::prefetch_tensormap(&rmap);
     if (g.sc_slabs) umma::prefetch_tensormap(&scwmap);
   }
-  if (g.has_res && !g.sc_slabs && warp < kEpiW) {
+  if (g.has_res && !g.sc_slabs && warp < R::kEpi) {
     // Residual add on the tensor cores: D += I . R with a 64x64 identity as the weight operand. The block
     // is 192 rows of 128 bytes: 64 zero rows, the identity (row 64 + k has a one in column k, stored where
     // the 128-byte swizzle puts it), 64 zero rows. Read from row 64 it is [I; 0] (channels n0..n0+63 of the
     // tile), read from row 0 it is [0; I] (channels n0+64..n0+127).
     uint4 *blk = reinterpret_cast<uint4 *>(smem_raw + (ident_base - umma::smem_u32(smem_raw)));
-    for (int i = threadIdx.x; i < kIdentBytes / 16; i += 32 * kEpiW) blk[i] = make_uint4(0u, 0u, 0u, 0u);
-    asm volatile("bar.sync 2, %0;" ::"r"(32 * kEpiW) : "memory");
+    const int ident_bytes = TWIN ? kTwinIdentBytes : kIdentBytes;
+    for (int i = threadIdx.x; i < ident_bytes / 16; i += 32 * R::kEpi) blk[i] = make_uint4(0u, 0u, 0u, 0u);
+    asm volatile("bar.sync 2, %0;" ::"r"(32 * R::kEpi) : "memory");
     if (g.dup ? threadIdx.x < 128 : threadIdx.x < 64) {
-      // dup mode: rows 0..127 carry the identity twice (row r has its one in column r % 64)
-      const int k = threadIdx.x & 63, r = g.dup ? (int)threadIdx.x : 64 + k;
+      // dup mode: rows 0..127 carry the identity twice (row r has its one in column r % 64); twin mode: the D1 row
+      // of channel k (row k for k < 32, row k + 32 above) has its one in column k, the D2 rows stay zero
+      const int k = threadIdx.x & 63, r = g.dup ? (int)threadIdx.x : (TWIN ? (k < 32 ? k : k + 32) : 64 + k);
       uint8_t *row = smem_raw + (ident_base - umma::smem_u32(smem_raw)) + r * 128;
       *reinterpret_cast<XT *>(row + (((k >> 3) ^ (r & 7)) << 4) + (k & 7) * 2) = DT<XT>::from_f(1.0f);
     }
@@ -303,7 +465,7 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
   // what its predecessor in the stream wrote and writes buffers that predecessor may read.
   umma::pdl_wait();
 
-  if (warp == kHaloWarpP) {
+  if (warp == R::kHalo) {
     // ------------------------------------------------- halo producer: lane q loads timestep q of the pair
     // bytes one slot receives: a full halo per timestep, or (two images per tile) a box of 9 rows per image
     auto tx_bytes = [&](int b) {
@@ -356,7 +518,7 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
         }
       }
     }
-  } else if (warp == kWWarpP) {
+  } else if (warp == R::kW) {
     // ---------------------------------------------------------- weight producer
     if (lane == 0) {
       uint32_t ws = 0, wphase = 1;
@@ -366,14 +528,25 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
         for (int pair = 0; pair < g.npairs && ok; ++pair) {
           for (int sp = 0; sp < g.kslabs * (S2 ? 4 : 1) && ok; ++sp) {
             const int slab = S2 ? sp >> 2 : sp, ph = S2 ? sp & 3 : 0;
-            for (int j = 0; j < phase_ntaps<S2>(g, ph); ++j) {
+            for (int j = 0; j < phase_ntaps<S2, TWIN>(g, ph); ++j) {
               int tap, off_unused;
-              phase_tap<S2>(g, ph, j, tap, off_unused);
+              phase_tap<S2, TWIN>(g, ph, j, tap, off_unused);
               ok = umma::mbar_wait(wempty(ws), wphase, abort_flag, wl);
               if (!ok) break;
               umma::mbar_expect_tx(wfull(ws), (uint32_t)kWSlot);
               if (g.drop_load && blockIdx.x == 0 && tile == (int)blockIdx.x && pair == 0 && sp == 0 && j == 0) {
                 // self-test of the bounded waits: this tile never arrives
+              } else if (TWIN) {
+                // M rows [0,32) / [64,96) (D1 of channels 0..31 / 32..63): kernel tap (0, kw), or zeros (a box past
+                // the end of the tensor) in the second three groups; rows [32,64) / [96,128) (D2 of the same
+                // channels): tap (1, kw), then tap (2, kw)
+                const int kx = j < 3 ? tap * g.Cin + slab * 64 : 9 * g.Cin;
+                const int kx2 = ((j < 3 ? 3 : 6) + tap) * g.Cin + slab * 64;
+                const uint32_t dst = w_base + ws * (uint32_t)kWSlot;
+                umma::tma_load_2d(dst, &wmap64, wfull(ws), kx, 0);
+                umma::tma_load_2d(dst + 32u * 128u, &wmap64, wfull(ws), kx2, 0);
+                umma::tma_load_2d(dst + 64u * 128u, &wmap64, wfull(ws), kx, 32);
+                umma::tma_load_2d(dst + 96u * 128u, &wmap64, wfull(ws), kx2, 32);
               } else if (g.dup) {   // the same 64 rows into both halves of the tile
                 umma::tma_load_2d(w_base + ws * (uint32_t)kWSlot, &wmap64, wfull(ws), tap * g.Cin + slab * 64, 0);
                 umma::tma_load_2d(w_base + ws * (uint32_t)kWSlot + 64u * 128u, &wmap64, wfull(ws), tap * g.Cin + slab * 64, 0);
@@ -395,7 +568,7 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
       }
     }
     __syncwarp();
-  } else if (warp == kMmaWarpP) {
+  } else if (warp == R::kMma) {
     // -------------------------------------------------------------- MMA issuer
     if (lane == 0) {
       const uint32_t idesc = umma::make_idesc_f16(128, 128 * g.tq, std::is_same<XT, __nv_bfloat16>::value);
@@ -419,12 +592,12 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
             const int ph = S2 ? sp & 3 : 0;
             ok = umma::mbar_wait(hfull(slot), phase, abort_flag, wl);
             if (!ok) break;
-            for (int tap = 0; tap < phase_ntaps<S2>(g, ph); ++tap) {
+            for (int tap = 0; tap < phase_ntaps<S2, TWIN>(g, ph); ++tap) {
               ok = umma::mbar_wait(wfull(ws), wphase, abort_flag, wl);
               if (!ok) break;
               umma::tc_fence_after_sync();
               int wtap_unused, off;
-              phase_tap<S2>(g, ph, tap, wtap_unused, off);
+              phase_tap<S2, TWIN>(g, ph, tap, wtap_unused, off);
               const uint64_t xdesc = hdesc0 + (uint64_t)((slot * slot_bytes + (uint32_t)off * 128u) >> 4);
               const uint64_t wdesc = wdesc0 + (uint64_t)((ws * (uint32_t)kWSlot) >> 4);
 #pragma unroll
@@ -451,7 +624,7 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
               if (!ok) break;
               adesc = wdesc0 + (uint64_t)((ws * (uint32_t)kWSlot) >> 4);
             } else {
-              adesc = umma::make_sw128_kmajor_desc(ident_base + ((rs == 0 && !g.dup) ? 64u * 128u : 0u));
+              adesc = umma::make_sw128_kmajor_desc(ident_base + ((rs == 0 && !g.dup && !TWIN) ? 64u * 128u : 0u));
             }
             umma::tc_fence_after_sync();
             const uint64_t xdesc = hdesc0 + (uint64_t)((slot * slot_bytes + (g.flat ? 0u : (uint32_t)(kPW + 1) * 128u)) >> 4);
@@ -469,6 +642,115 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
       }
     }
     __syncwarp();
+  } else if constexpr (TWIN) {
+    // ------------------------------------------------- epilogue, twin mode (see PairGeom::twin)
+    // Lane quarter q holds D1 (q even) or D2 (q odd) of channels 32 * (q / 2) .. + 31 and is read by four warps
+    // (w, w + 4, w + 8, w + 12). The eight warps of a channel group each run the LIF for two tile rows:
+    // part = 2 * (w / 4) + kind, rows 2 * part and 2 * part + 1 (part 7 holds rows 14, 15, which never exist).
+    // A D1 warp needs D2 of the rows below its own, a D2 warp needs D1 of its own rows: partners (w, w ^ 1) pass
+    // each other those 16 pixels per timestep through shared memory and meet at a barrier of their own. Whether
+    // a wait on the accumulator gave up is agreed on by all sixteen warps together, so nobody is left behind at
+    // a barrier.
+    const int quarter = warp & 3, kind = quarter & 1;
+    const int part = 2 * (warp >> 2) + kind, r_begin = 2 * part;
+    const int ch = (quarter >> 1) * 32 + lane;
+    const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    const uint32_t xchg = smem_base + (uint32_t)g.stage_off;
+    const uint32_t out_row = xchg + (uint32_t)warp * kXchgWarp + (uint32_t)lane * 64u;        // what I pass on
+    const uint32_t in_row = xchg + (uint32_t)(warp ^ 1) * kXchgWarp + (uint32_t)lane * 64u;   // what my partner passed
+    const int bar_id = 4 + (warp >> 1);   // warps (0,1) (2,3) .. (14,15): barriers 4..11
+    const uint32_t own_col = (uint32_t)((r_begin + kind) * 8);               // my half for my rows: D1[R] or D2[R + 1]
+    const uint32_t send_col = (uint32_t)(((part ^ 1) * 2 + kind) * 8);       // my half for my partner's rows
+    const bool has_rows = r_begin < kTileRows;   // false for part 7: it only passes its half on
+    const long long frame_out = (long long)g.B * g.Ho * g.Wo * g.Cout;
+    bool ok = true;
+    uint32_t it = 0;
+    for (int tile = blockIdx.x; tile < g.total_tiles && ok; tile += gridDim.x, ++it) {
+      int n0, w0, h0, b, wlo, hlo;
+      decode(tile, n0, w0, h0, b, wlo, hlo);
+      if (!g.own) { wlo = w0; hlo = h0; }
+      const int row_first = h0 + r_begin;
+      const bool c_ok = ch < g.Cout && has_rows;
+      const float bias_c = (bias != nullptr && c_ok) ? DT<XT>::to_f(bias[ch]) : 0.f;
+      PixMap pm;
+      pm.Cout = g.Cout;
+      pm.row_stride = g.Wo * g.Cout;
+      pm.row0_off = ((long long)b * g.Ho + row_first) * pm.row_stride + (long long)w0 * g.Cout + ch;
+      pm.rows_ok = 0;
+      pm.cols_ok = 0;
+#pragma unroll
+      for (int r = 0; r < 2; ++r)
+        if (c_ok && row_first + r < g.Ho && row_first + r >= hlo) pm.rows_ok |= 1 << r;
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (w0 + j < g.Wo && w0 + j >= wlo) pm.cols_ok |= 1 << j;
+      const bool full = __all_sync(0xffffffffu, pm.rows_ok == 3 && pm.cols_ok == 0xFF);
+      float v[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) v[i] = 0.f;
+      if (g.lif && v_init != nullptr) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+          if (((pm.rows_ok >> (i >> 3)) & 1) && ((pm.cols_ok >> (i & 7)) & 1))
+            v[i] = DT<VT>::to_f(v_init[pm.row0_off + (long long)(i >> 3) * pm.row_stride + (i & 7) * pm.Cout]);
+      }
+      for (int pair = 0; pair < g.npairs && ok; ++pair) {
+        const uint32_t acc = (uint32_t)(pair & 1);
+        const uint32_t use = it * (uint32_t)((g.npairs + 1 - (int)acc) >> 1) + (uint32_t)(pair >> 1);
+        if (lane == 0) ok = umma::mbar_wait(accfull(acc), use & 1u, abort_flag, wl);
+        ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+        {   // all epilogue warps agree: continue only if every one of them saw the accumulator arrive
+          uint32_t all_ok;
+          asm volatile(
+              "{\n\t"
+              ".reg .pred P, Q;\n\t"
+              "setp.ne.b32 P, %1, 0;\n\t"
+              "bar.red.and.pred Q, 3, %2, P;\n\t"
+              "selp.b32 %0, 1, 0, Q;\n\t"
+              "}\n"
+              : "=r"(all_ok) : "r"((int)ok), "r"(32 * R::kEpi) : "memory");
+          ok = all_ok != 0;
+        }
+        if (!ok) break;
+        umma::tc_fence_after_sync();
+        for (int q = 0; q < g.tq; ++q) {
+          const uint32_t tcol = lane_base + acc * 256u + (uint32_t)(q * 128);
+          {
+            uint32_t a[16];
+            umma::tmem_ld_x16(tcol + send_col, a);
+            umma::tmem_ld_wait();
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(xchg_piece(out_row, lane, k)),
+                           "r"(a[4 * k]), "r"(a[4 * k + 1]), "r"(a[4 * k + 2]), "r"(a[4 * k + 3]) : "memory");
+          }
+          asm volatile("bar.sync %0, 64;" ::"r"(bar_id) : "memory");   // both partners have written timestep q
+          if (has_rows) {   // warp-uniform
+            ST *out = spikes + (long long)(pair * g.tq + q) * frame_out;
+            const uint32_t taddr = tcol + own_col;
+            if (!g.lif) {
+              twin_step<XT, ST, kLifOff>(p, taddr, in_row, lane, bias_c, out, pm, v);
+            } else if (p.mode == 1 && p.hard) {
+              if (full && p.v_reset == 0.f && g.Cout == 64) twin_step_lean<ST>(p, taddr, in_row, lane, bias_c, out, pm, v);
+              else twin_step<XT, ST, kLifFast>(p, taddr, in_row, lane, bias_c, out, pm, v);
+            } else {
+              twin_step<XT, ST, kLifAny>(p, taddr, in_row, lane, bias_c, out, pm, v);
+            }
+          }
+          asm volatile("bar.sync %0, 64;" ::"r"(bar_id) : "memory");   // both have read: the buffers may be overwritten
+        }
+        // this accumulator may now be overwritten by later MMAs
+        umma::tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) umma::mbar_arrive(accempty(acc));
+      }
+      if (ok && g.lif && v_out != nullptr) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+          if (((pm.rows_ok >> (i >> 3)) & 1) && ((pm.cols_ok >> (i & 7)) & 1))
+            v_out[pm.row0_off + (long long)(i >> 3) * pm.row_stride + (i & 7) * pm.Cout] = DT<VT>::from_f(v[i]);
+      }
+    }
   } else {
     // ---------------------------------------------------------------- epilogue
     const int quarter = warp & 3;
@@ -531,7 +813,10 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
         const int nchunks = (rows_valid + 1) / 2;
         // warp-uniform choice: the TMEM loads inside are warp-collective
         const bool full = __all_sync(0xffffffffu, pm.rows_ok == rows_want && pm.cols_ok == 0xFF);
-        if (g.lif && p.mode == 1 && p.hard && g.tq == 2 && full) {
+        if (g.lif && p.mode == 1 && p.hard && p.v_reset == 0.f && g.tq == 2 && full && rows_valid >= 6) {
+          if (rows_valid == 8) pair_epilogue_lean_any<ST, 8>(p, taddr, bias_c, out, frame_out, pm, v);
+          else pair_epilogue_lean_any<ST, 6>(p, taddr, bias_c, out, frame_out, pm, v);
+        } else if (g.lif && p.mode == 1 && p.hard && g.tq == 2 && full) {
           if (rows_valid == 8) pair_epilogue_full<XT, ST, 8>(p, taddr, bias_c, out, frame_out, pm, v);
           else if (rows_valid == 6) pair_epilogue_full<XT, ST, 6>(p, taddr, bias_c, out, frame_out, pm, v);
           else if (rows_valid == 4) pair_epilogue_full<XT, ST, 4>(p, taddr, bias_c, out, frame_out, pm, v);
@@ -562,7 +847,7 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
   umma::tc_fence_before_sync();
   __syncthreads();
   if (abort_s && threadIdx.x == 0) atomicExch(&g_pair_status, 1);
-  if (warp == kMmaWarpP) {
+  if (warp == R::kMma) {
     umma::tc_fence_after_sync();
     umma::tmem_dealloc(tmem_base, (uint32_t)g.tmem_cols);
   }
@@ -629,17 +914,19 @@ int launch(const ConvArgs &a, cudaStream_t stream) {
     const int rc = encode_tmap(&wm, a.dtype, 2, a.w, dims, strides, box);
     if (rc != SNNB_OK) return rc;
   }
-  g.dup = a.Cout <= 64 ? 1 : 0;
+  g.twin = (a.Cout <= 64 && g.ntaps == 9 && !g.s2 && !g.stack && g.sc_slabs == 0 && twin_enabled()) ? 1 : 0;
+  g.dup = (a.Cout <= 64 && !g.twin) ? 1 : 0;
+  g.stage_off = 0;
   g.own = (a.lif && a.v_init != nullptr && a.v_init == a.v_out) ? 1 : 0;
   g.wait_limit = 4000000000ll;
   g.drop_load = 0;
   consume_wait_selftest(&g.wait_limit, &g.drop_load);
   CUtensorMap wm64 = wm;
-  if (g.dup) {
+  if (g.dup || g.twin) {
     const cuuint64_t K = (cuuint64_t)g.ntaps * a.Cin;
     cuuint64_t dims[2] = {K, (cuuint64_t)a.Cout};
     cuuint64_t strides[1] = {K * es};
-    cuuint32_t box[2] = {64, 64};
+    cuuint32_t box[2] = {64, (cuuint32_t)(g.twin ? 32 : 64)};
     const int rc = encode_tmap(&wm64, a.dtype, 2, a.w, dims, strides, box);
     if (rc != SNNB_OK) return rc;
   }
@@ -670,22 +957,31 @@ int launch(const ConvArgs &a, cudaStream_t stream) {
   g.ring = kPairRing;
   const bool ident = g.has_res && !g.sc_slabs;
   g.wring = ident ? kWRingP - 1 : kWRingP;
-  const size_t smem = (ident ? (size_t)kIdentBytes : 0) + (size_t)g.wring * kWSlot + (size_t)g.ring * g.tq * g.halo_t +
-                      4 * kRowBytes + 1024;
-  auto kern = g.s2 ? conv3x3_pair_kernel<XT, ST, VT, true> : conv3x3_pair_kernel<XT, ST, VT, false>;
+  size_t smem = (ident ? (size_t)kIdentBytes : 0) + (size_t)g.wring * kWSlot + (size_t)g.ring * g.tq * g.halo_t +
+                4 * kRowBytes + 1024;
+  if (g.twin) {   // a smaller identity block and weight ring make room for the exchange buffers
+    g.wring = ident ? 3 : 4;
+    // (the junk rows read past the last halo slot fall into the exchange buffers, which only the epilogue writes)
+    g.stage_off = (ident ? kTwinIdentBytes : 0) + g.wring * kWSlot + g.ring * g.tq * g.halo_t;
+    smem = (size_t)g.stage_off + kXchgBytes + 1024;
+    static_assert(kTwinIdentBytes + 3 * kWSlot + kPairRing * 2 * kHaloT + kXchgBytes + 1024 <= 225 * 1024, "twin mode: shared memory");
+    static_assert(4 * kWSlot + kPairRing * 2 * kHaloT + kXchgBytes + 1024 <= 225 * 1024, "twin mode: shared memory");
+  }
+  auto kern = g.s2 ? conv3x3_pair_kernel<XT, ST, VT, true, false>
+                   : (g.twin ? conv3x3_pair_kernel<XT, ST, VT, false, true> : conv3x3_pair_kernel<XT, ST, VT, false, false>);
   {
     // once per kernel instantiation and device: allow the largest dynamic shared-memory size any call may ask for
-    static bool raised[2][64] = {};
-    if (dev < 0 || dev >= 64 || !raised[g.s2][dev]) {
+    static bool raised[3][64] = {};
+    if (dev < 0 || dev >= 64 || !raised[g.s2 + 2 * g.twin][dev]) {
       const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 225 * 1024);
       if (e != cudaSuccess) return fail(SNNB_ERR_CUDA, "conv_lif: cannot raise the shared-memory limit: %s", cudaGetErrorString(e));
-      if (dev >= 0 && dev < 64) raised[g.s2][dev] = true;
+      if (dev >= 0 && dev < 64) raised[g.s2 + 2 * g.twin][dev] = true;
     }
   }
   {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid);
-    cfg.blockDim = dim3(kThreadsP);
+    cfg.blockDim = dim3(g.twin ? Roles<true>::kThreads : Roles<false>::kThreads);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
