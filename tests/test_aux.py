@@ -77,6 +77,28 @@ def test_avgpool_linear_mean(dtype):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("N", [3, 64, 301])
+def test_avgpool_linear_mean_arbitrary_values(N):
+    """bf16 inputs that are not spikes: the tensor-core form keeps each pooled sum as two bf16 parts."""
+    L = _lib()
+    T, C, HW, K = 4, 512, 49, 1000
+    torch.manual_seed(N)
+    x = (torch.randn(T, N, HW, C) * 0.7 + 0.2).to(torch.bfloat16)
+    w = (torch.randn(K, C) * 0.05).to(torch.bfloat16)
+    b = (torch.randn(K) * 0.05).to(torch.bfloat16)
+    ref = x.float().mean(dim=(0, 2)) @ w.float().t() + b.float()
+    xd, wd, bd = x.to(DEV), w.to(DEV), b.to(DEV)
+    out = torch.empty(N, K, device=DEV)
+    L.check(L.lib.snnb_avgpool_linear_mean(xd.data_ptr(), wd.data_ptr(), bd.data_ptr(), out.data_ptr(),
+                                           T, N, C, HW, K, L.BF16, None), "head")
+    torch.testing.assert_close(out.cpu(), ref, rtol=1e-3, atol=1e-4)
+    out2 = torch.empty_like(out)
+    L.check(L.lib.snnb_avgpool_linear_mean(xd.data_ptr(), wd.data_ptr(), bd.data_ptr(), out2.data_ptr(),
+                                           T, N, C, HW, K, L.BF16, None), "head")
+    assert torch.equal(out, out2)   # fixed summation order
+
+
+@pytest.mark.gpu
 def test_bounded_wait_runs_out_and_reports():
     """A wait inside the tcgen05 conv kernel that can never complete (a weight tile that is announced but not
     loaded, limit shortened to about a millisecond) must end by itself: the call returns, the status word says

@@ -381,7 +381,12 @@ extern "C" int snnb_avgpool_linear_mean(const void *x_seq, const void *fc_w, con
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   switch (dtype) {
     case SNNB_F32: return head<float>(x_seq, fc_w, fc_b, out, T, N, C, HW, K, st);
-    case SNNB_BF16: return head<__nv_bfloat16>(x_seq, fc_w, fc_b, out, T, N, C, HW, K, st);
+    case SNNB_BF16: {
+      bool taken = false;
+      const int rc = head_pool_linear_bf16(x_seq, fc_w, fc_b, out, T, N, C, HW, K, st, &taken);
+      if (taken || rc != SNNB_OK) return rc;
+      return head<__nv_bfloat16>(x_seq, fc_w, fc_b, out, T, N, C, HW, K, st);
+    }
     case SNNB_F16: return head<__half>(x_seq, fc_w, fc_b, out, T, N, C, HW, K, st);
     default: return fail(SNNB_ERR_INVALID, "avgpool_linear_mean: unsupported dtype %d", dtype);
   }

@@ -33,6 +33,9 @@ int fail(int code, const char *fmt, ...);
 // Whether kernels that support it are launched with programmatic dependent launch (on unless the environment
 // variable SNNB_PDL is set to 0).
 bool pdl_enabled();
+// tail.cu: average pool + linear + mean over T on the tensor cores (bf16, channels-last); see its definition
+int head_pool_linear_bf16(const void *x, const void *w, const void *b, float *out, int T, int N, int C, int HW, int K,
+                          cudaStream_t stream, bool *taken);
 // Whether 3x3 / stride 1 convs with at most 64 output channels use the two-kernel-rows-per-MMA form of the
 // timestep-pair kernel (default; SNNB_TWIN=0 in the environment selects the form that duplicates the weight rows).
 bool twin_enabled();

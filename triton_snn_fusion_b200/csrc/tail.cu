@@ -12,6 +12,8 @@
 // which equals sum_t (W . mean_hw(spike_t) + b).
 #include <cooperative_groups.h>
 
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace cg = cooperative_groups;
@@ -347,6 +349,264 @@ lif_avgpool_linear_stream_kernel(const XT *__restrict__ x, const VT *v_init, con
   }
 }
 
+// ------------------------------------------------------------------------------------------------
+// Second streaming form, 16-bit activations: register sums and a warp-level tensor-core mat-vec.
+//   * scan: a thread keeps ONE (sample, pixel group, channel vector) and walks that sample's pixels (pixel pg,
+//     pg + PG, ...), two pixels per trip with the 16-byte loads of up to four timesteps of both issued before
+//     the first use; its spike counts stay in registers (packed fp32 adds) until it is done and then go to a
+//     shared-memory row of its own, so there are no atomics and no index arithmetic per item. The rows of a
+//     sample's pixel groups are added in a fixed order: the result is deterministic. tau a power of two with
+//     hard reset to zero runs the packed-fp32 LIF (same operation order and rounding as lif_step). MODE 2 skips
+//     the LIF and sums the inputs themselves (the network head: average pool + linear over spikes that exist
+//     already).
+//   * exchange: every CTA gathers the eight slices of sums through DSMEM and stores them as 16-bit floats.
+//     Spike counts are at most T * HW: exact in bf16 up to 256 and in fp16 up to 2048 (larger counts take the
+//     first streaming form). SPLIT stores a second 16-bit float with the rounding error of the first, for sums
+//     of arbitrary values (relative error 2^-16 instead of 2^-8).
+//   * linear: out[s][k] = sum_c sum[s][c] * w[k][c] as mma.sync m16n8k16 with the samples as the M rows
+//     (rows 8..15 are zero) and eight classes as N. A thread's 16-byte load of w[k][c .. c + 7] and its
+//     16-byte shared-memory read of sum[s][c .. c + 7] are the operands of two MMAs (the channel order
+//     inside a K block is permuted the same way on both sides, which a dot product does not see).
+template <typename XT> struct Mma16;
+template <> struct Mma16<__nv_bfloat16> {
+  static __device__ __forceinline__ void run(float (&d)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
+  }
+};
+template <> struct Mma16<__half> {
+  static __device__ __forceinline__ void run(float (&d)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
+  }
+};
+
+enum : int { kScanLif = 0, kScanLifFast = 1, kScanSum = 2 };
+
+// Two LIF steps side by side; kScanLifFast: h = v + (y - v) * inv_tau as three separately rounded packed
+// operations (what lif_step does one lane at a time), reset to zero as h - s * h.
+template <int MODE>
+__device__ __forceinline__ float2 scan_two(float2 y, float2 &v, const LifParams &p) {
+  if constexpr (MODE == kScanSum) {
+    return y;
+  } else if constexpr (MODE == kScanLifFast) {
+    const float2 d = __fadd2_rn(y, make_float2(-v.x, -v.y));
+    const float2 h = __fadd2_rn(v, __fmul2_rn(d, make_float2(p.inv_tau, p.inv_tau)));
+    const float2 s = make_float2(h.x >= p.v_th ? 1.f : 0.f, h.y >= p.v_th ? 1.f : 0.f);
+    v = __ffma2_rn(make_float2(-s.x, -s.y), h, h);
+    return s;
+  } else {
+    float2 s;
+    s.x = lif_step(y.x, v.x, p);
+    s.y = lif_step(y.y, v.y, p);
+    return s;
+  }
+}
+
+// out[n][k] = out_scale * sum_c w[k][c] * (sum over t and pixels of spikes or inputs)[n][c] + bias_mul * b[k]
+template <typename XT, typename OT, int MODE, bool SPLIT>
+__global__ void __launch_bounds__(NTF, 2)
+pool_linear_mma_kernel(const XT *__restrict__ x, const XT *v_init, const XT *__restrict__ fc_w,
+                       const XT *__restrict__ fc_b, OT *__restrict__ out, XT *v_out,
+                       int T, int N, int C, int HW, int K, int S, float out_scale, float bias_mul, LifParams p) {
+  constexpr int VEC = 8, NP = SPLIT ? 2 : 1;
+  extern __shared__ __align__(16) float tail_smem_f[];
+  cg::cluster_group cluster = cg::this_cluster();
+  const int r = (int)cluster.block_rank();
+  const int n0 = (blockIdx.x / CL) * S;
+  const int ns = min(S, N - n0);
+  const int tid = threadIdx.x;
+  const int Cs = C / CL;            // channels of this CTA, a multiple of VEC
+  const int cvn = Cs / VEC;         // vectors per pixel; NTF % cvn == 0
+  const int slots = NTF / cvn;      // (sample, pixel group) pairs that run side by side
+  const int PG = max(1, slots / ns);   // pixel groups per sample
+  const int AP = C + 8;             // row pitch of the gathered sums in elements: rows 16 bytes apart in the banks
+  float *part = tail_smem_f;                                   // [max(slots, S)][Cs] one row per (sample, pixel group)
+  float *sums = part + max(slots, S) * Cs;                     // [S][Cs] this CTA's slice
+  XT *amat = reinterpret_cast<XT *>(sums + S * Cs);            // [NP][S][AP] all slices as 16-bit floats
+
+  // ---- scan
+  {
+    const int cv = tid % cvn;
+    const int cc = r * Cs + cv * VEC;
+    const int64_t frame = (int64_t)N * C * HW;
+    for (int sp = tid / cvn; sp < ns * PG; sp += slots) {
+      const int smp = sp / PG, pg = sp - smp * PG;
+      const int64_t e0 = (int64_t)(n0 + smp) * HW * C + cc;
+      float2 k2[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) k2[i] = make_float2(0.f, 0.f);
+      for (int p0 = pg; p0 < HW; p0 += 2 * PG) {
+        const bool two = p0 + PG < HW;
+        const int64_t e[2] = {e0 + (int64_t)p0 * C, e0 + (int64_t)(two ? p0 + PG : p0) * C};
+        float2 v[2][4];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          if (MODE != kScanSum && v_init != nullptr) {
+            float vv[VEC];
+            load_pack_stream<XT, VEC>(v_init + e[u], vv);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) v[u][i] = make_float2(vv[2 * i], vv[2 * i + 1]);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) v[u][i] = make_float2(0.f, 0.f);
+          }
+        }
+        for (int t0 = 0; t0 < T; t0 += 4) {
+          int4 raw[2][4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int u = 0; u < 2; ++u)
+              if (t0 + j < T) raw[u][j] = __ldcs(reinterpret_cast<const int4 *>(x + (int64_t)(t0 + j) * frame + e[u]));
+#pragma unroll
+          for (int u = 0; u < 2; ++u)
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              if (t0 + j < T && (u == 0 || two)) {
+                float xv[VEC];
+                unpack16<XT, VEC>(raw[u][j], xv);
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                  k2[i] = __fadd2_rn(k2[i], scan_two<MODE>(make_float2(xv[2 * i], xv[2 * i + 1]), v[u][i], p));
+              }
+        }
+        if constexpr (MODE != kScanSum) {
+#pragma unroll
+          for (int u = 0; u < 2; ++u)
+            if (u == 0 || two) {
+              const float vv[VEC] = {v[u][0].x, v[u][0].y, v[u][1].x, v[u][1].y, v[u][2].x, v[u][2].y, v[u][3].x, v[u][3].y};
+              store_pack<XT, VEC>(v_out + e[u], vv);
+            }
+        }
+      }
+      float4 *row = reinterpret_cast<float4 *>(part + sp * Cs + cv * VEC);
+      row[0] = make_float4(k2[0].x, k2[0].y, k2[1].x, k2[1].y);
+      row[1] = make_float4(k2[2].x, k2[2].y, k2[3].x, k2[3].y);
+    }
+  }
+  __syncthreads();
+  for (int i = tid; i < ns * Cs; i += NTF) {   // a sample's pixel groups, added in a fixed order
+    const int smp = i / Cs, j = i - smp * Cs;
+    float a = part[(smp * PG) * Cs + j];
+    for (int pg = 1; pg < PG; ++pg) a += part[(smp * PG + pg) * Cs + j];
+    sums[i] = a;
+  }
+
+  // ---- gather all slices through distributed shared memory, as 16-bit floats
+  cluster.sync();
+  {
+    const int q4 = Cs / 4;  // float4 per (peer, sample)
+    for (int i = tid; i < CL * ns * q4; i += NTF) {
+      const int q = i / (ns * q4);
+      const int rem = i - q * (ns * q4);
+      const int smp = rem / q4, j = rem - smp * q4;
+      const float *peer = cluster.map_shared_rank(sums, q);
+      const float4 c4 = *reinterpret_cast<const float4 *>(&peer[smp * Cs + j * 4]);
+      const float cf[4] = {c4.x, c4.y, c4.z, c4.w};
+      XT *dst = amat + smp * AP + q * Cs + j * 4;
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const XT hi = DT<XT>::from_f(cf[u]);
+        dst[u] = hi;
+        if (SPLIT) dst[S * AP + u] = DT<XT>::from_f(cf[u] - DT<XT>::to_f(hi));
+      }
+    }
+    for (int part_i = 0; part_i < NP; ++part_i)   // unused sample rows
+      for (int i = tid; i < (S - ns) * AP; i += NTF) amat[(part_i * S + ns) * AP + i] = DT<XT>::from_f(0.f);
+  }
+  cluster.sync();  // nobody leaves before every peer has read its slice; amat is complete
+
+  // ---- linear on the tensor cores: a warp takes eight classes at a time
+  {
+    const int Ks = (K + CL - 1) / CL;
+    const int ks = r * Ks, ke = min(K, ks + Ks);
+    const int warp = tid / 32, lane = tid % 32;
+    const int g = lane >> 2, t4 = lane & 3;
+    const XT *arow = amat + (g < S ? g : 0) * AP;   // sample g (rows past S never reach the output)
+    for (int k0 = ks + 8 * warp; k0 < ke; k0 += 8 * (NTF / 32)) {
+      const int kc = min(k0 + g, ke - 1);   // classes past the end repeat the last one and are not stored
+      const XT *wrow = fc_w + (int64_t)kc * C;
+      float d[4] = {0.f, 0.f, 0.f, 0.f};
+      for (int c0 = 0; c0 < C; c0 += 128) {   // four independent 16-byte weight loads per trip
+        int4 wv[4], av[4], al[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (c0 + u * 32 < C) wv[u] = __ldg(reinterpret_cast<const int4 *>(wrow + c0 + u * 32 + t4 * 8));
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (c0 + u * 32 < C) {
+            av[u] = *reinterpret_cast<const int4 *>(arow + c0 + u * 32 + t4 * 8);
+            if (SPLIT) al[u] = *reinterpret_cast<const int4 *>(arow + S * AP + c0 + u * 32 + t4 * 8);
+          }
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (c0 + u * 32 < C) {
+            if (SPLIT) {   // the small parts first
+              Mma16<XT>::run(d, (uint32_t)al[u].x, (uint32_t)al[u].y, (uint32_t)wv[u].x, (uint32_t)wv[u].y);
+              Mma16<XT>::run(d, (uint32_t)al[u].z, (uint32_t)al[u].w, (uint32_t)wv[u].z, (uint32_t)wv[u].w);
+            }
+            Mma16<XT>::run(d, (uint32_t)av[u].x, (uint32_t)av[u].y, (uint32_t)wv[u].x, (uint32_t)wv[u].y);
+            Mma16<XT>::run(d, (uint32_t)av[u].z, (uint32_t)av[u].w, (uint32_t)wv[u].z, (uint32_t)wv[u].w);
+          }
+      }
+      // d[0], d[1]: sample g, classes k0 + 2 * t4, k0 + 2 * t4 + 1
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int k = k0 + 2 * t4 + j;
+        if (g < ns && k < ke) {
+          const float bk = fc_b != nullptr ? DT<XT>::to_f(fc_b[k]) * bias_mul : 0.f;
+          out[(int64_t)(n0 + g) * K + k] = DT<OT>::from_f(d[j] * out_scale + bk);
+        }
+      }
+    }
+  }
+}
+
+// Whether the tensor-core form takes the shape (the stricter count limit for spike counts is the caller's).
+inline bool pool_linear_mma_ok(const void *x, const void *w, int C) {
+  const int Cs = C / CL;
+  return aligned16(x) && aligned16(w) && C % (CL * 8) == 0 && C % 32 == 0 && NTF % (Cs / 8) == 0 && Cs / 8 <= NTF &&
+         C <= 4096;
+}
+
+template <typename XT, typename OT, bool SPLIT>
+int launch_mma(const void *x, const void *v_init, const void *w, const void *b, void *out, void *v_out,
+               int T, int N, int C, int HW, int K, int mode, float out_scale, float bias_mul, const LifParams &p,
+               cudaStream_t stream) {
+  const int sms = sm_count() > 0 ? sm_count() : 128;
+  int S = (N * CL + 2 * sms - 1) / (2 * sms);   // samples per cluster: about two CTAs per SM in flight
+  S = S < 1 ? 1 : (S > SMAX ? SMAX : S);
+  const int Cs = C / CL, slots = NTF / (Cs / 8);
+  const size_t smem = (size_t)((slots > S ? slots : S) + S) * Cs * sizeof(float) + (size_t)(SPLIT ? 2 : 1) * S * (C + 8) * sizeof(XT);
+  const int groups = (N + S - 1) / S;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(groups * CL));
+  cfg.blockDim = dim3(NTF);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = CL;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  auto kern = mode == kScanSum ? pool_linear_mma_kernel<XT, OT, kScanSum, SPLIT>
+                               : (mode == kScanLifFast ? pool_linear_mma_kernel<XT, OT, kScanLifFast, SPLIT>
+                                                       : pool_linear_mma_kernel<XT, OT, kScanLif, SPLIT>);
+  if (smem > 48 * 1024) {
+    const cudaError_t ea = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (ea != cudaSuccess) return fail(SNNB_ERR_CUDA, "pool_linear: cannot raise the shared-memory limit: %s", cudaGetErrorString(ea));
+  }
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, static_cast<const XT *>(x), static_cast<const XT *>(v_init),
+                                     static_cast<const XT *>(w), static_cast<const XT *>(b),
+                                     static_cast<OT *>(out), static_cast<XT *>(v_out), T, N, C, HW, K, S, out_scale,
+                                     bias_mul, p);
+  if (e != cudaSuccess) return fail(SNNB_ERR_CUDA, "pool_linear: launch failed: %s", cudaGetErrorString(e));
+  return SNNB_OK;
+}
+
 template <typename XT, typename VT, bool NHWC, int VEC>
 int launch(const void *x, const void *v_init, const void *w, const void *b, void *out, void *v_out,
            int T, int N, int C, int HW, int K, const LifParams &p, cudaStream_t stream) {
@@ -416,6 +676,14 @@ int pick(const void *x, const void *v_init, const void *w, const void *b, void *
     {   // streaming form: the channels split evenly over the cluster into 16-byte vectors
       constexpr int V = 16 / (int)sizeof(XT);
       const int Cs = C / CL;
+      if constexpr (sizeof(XT) == 2 && std::is_same<XT, VT>::value) {
+        // 16-bit activations and membrane, counts exact as 16-bit floats: tensor-core mat-vec form
+        const int max_count = std::is_same<XT, __nv_bfloat16>::value ? 256 : 2048;
+        if (al && pool_linear_mma_ok(x, w, C) && (long long)T * HW <= max_count) {
+          const int mode = (p.mode == 1 && p.hard && p.v_reset == 0.f) ? kScanLifFast : kScanLif;
+          return launch_mma<XT, XT, false>(x, v_init, w, b, out, v_out, T, N, C, HW, K, mode, 1.0f / (float)HW, (float)T, p, stream);
+        }
+      }
       if (al && aligned16(w) && C % (CL * V) == 0 && C % 8 == 0 && NTF % (Cs / V) == 0 &&
           (size_t)C * sizeof(int) <= 48 * 1024 && (sizeof(VT) == sizeof(XT)))
         return launch_stream<XT, VT, V>(x, v_init, w, b, out, v_out, T, N, C, HW, K, p, stream);
@@ -429,6 +697,19 @@ int pick(const void *x, const void *v_init, const void *w, const void *b, void *
 }
 
 }  // namespace
+
+// Average pool + linear + mean over T of a channels-last bf16 sequence through the tensor-core form above (the
+// sums of arbitrary inputs are kept as two bf16 parts). Returns SNNB_OK with *taken = false when the shape is not
+// one it serves.
+int head_pool_linear_bf16(const void *x, const void *w, const void *b, float *out, int T, int N, int C, int HW, int K,
+                          cudaStream_t stream, bool *taken) {
+  *taken = pool_linear_mma_ok(x, w, C);
+  if (!*taken) return SNNB_OK;
+  LifParams p = make_lif_params(1.f, 0.f, 2.f);   // unused by the summing scan
+  return launch_mma<__nv_bfloat16, float, true>(x, nullptr, w, b, out, nullptr, T, N, C, HW, K, kScanSum,
+                                               1.0f / ((float)T * (float)HW), 1.0f, p, stream);
+}
+
 }  // namespace snnb
 
 extern "C" int snnb_lif_avgpool_linear(const void *x_seq, const void *v_init, const void *fc_w,
