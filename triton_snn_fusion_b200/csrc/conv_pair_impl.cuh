@@ -43,6 +43,7 @@ constexpr int kRowBytes = kPW * 128;                   // 1280
 constexpr int kHaloT = kPW * kPH * 128;                // 20480 bytes per timestep
 constexpr int kTileRows = 14;                          // valid output rows per tile
 constexpr int kPairRing = 3;                           // halo (pair) slots
+constexpr int kPairRingMax = 4;                        // ... four of the smaller halo-free tiles of 1x1 convs, which each feed one MMA group only
 constexpr int kIdentBytes = 192 * 128;                 // zero rows / 64x64 identity / zero rows, see the residual path
 constexpr int kWRingP = 5;                             // weight-tile slots (16 KB each): a load must cover ~1 us of L2 latency
 constexpr int kWSlot = 128 * 128;
@@ -376,7 +377,7 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
                     ST *__restrict__ spikes, VT *v_out, const PairGeom g, const LifParams p) {
   using R = Roles<TWIN>;
   extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t bars[2 * kPairRing + 2 * kWRingP + 4];
+  __shared__ __align__(8) uint64_t bars[2 * kPairRingMax + 2 * kWRingP + 4];
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_s;
 
@@ -391,11 +392,11 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
   const uint32_t slot_bytes = (uint32_t)(g.tq * g.halo_t);
   const uint32_t bar_base = umma::smem_u32(bars);
   auto hfull = [&](uint32_t s) { return bar_base + 8u * s; };
-  auto hempty = [&](uint32_t s) { return bar_base + 8u * ((uint32_t)kPairRing + s); };
-  auto wfull = [&](uint32_t s) { return bar_base + 8u * (2u * kPairRing + s); };
-  auto wempty = [&](uint32_t s) { return bar_base + 8u * (2u * kPairRing + kWRingP + s); };
-  auto accfull = [&](uint32_t s) { return bar_base + 8u * (2u * kPairRing + 2u * kWRingP + s); };
-  auto accempty = [&](uint32_t s) { return bar_base + 8u * (2u * kPairRing + 2u * kWRingP + 2u + s); };
+  auto hempty = [&](uint32_t s) { return bar_base + 8u * ((uint32_t)kPairRingMax + s); };
+  auto wfull = [&](uint32_t s) { return bar_base + 8u * (2u * kPairRingMax + s); };
+  auto wempty = [&](uint32_t s) { return bar_base + 8u * (2u * kPairRingMax + kWRingP + s); };
+  auto accfull = [&](uint32_t s) { return bar_base + 8u * (2u * kPairRingMax + 2u * kWRingP + s); };
+  auto accempty = [&](uint32_t s) { return bar_base + 8u * (2u * kPairRingMax + 2u * kWRingP + 2u + s); };
   volatile int *abort_flag = &abort_s;
   const long long wl = g.wait_limit;   // SM cycles after which a wait on an mbarrier gives up
 
@@ -954,7 +955,7 @@ int launch(const ConvArgs &a, cudaStream_t stream) {
     if (rc != SNNB_OK) return rc;
   }
   // [identity block] + weight ring + halo ring + room for the junk rows the last descriptor group reads past a slot
-  g.ring = kPairRing;
+  g.ring = g.flat ? kPairRingMax : kPairRing;
   const bool ident = g.has_res && !g.sc_slabs;
   g.wring = ident ? kWRingP - 1 : kWRingP;
   size_t smem = (ident ? (size_t)kIdentBytes : 0) + (size_t)g.wring * kWSlot + (size_t)g.ring * g.tq * g.halo_t +

@@ -497,19 +497,24 @@ pool_linear_mma_kernel(const XT *__restrict__ x, const XT *v_init, const XT *__r
   cluster.sync();
   {
     const int q4 = Cs / 4;  // float4 per (peer, sample)
-    for (int i = tid; i < CL * ns * q4; i += NTF) {
-      const int q = i / (ns * q4);
-      const int rem = i - q * (ns * q4);
-      const int smp = rem / q4, j = rem - smp * q4;
-      const float *peer = cluster.map_shared_rank(sums, q);
-      const float4 c4 = *reinterpret_cast<const float4 *>(&peer[smp * Cs + j * 4]);
-      const float cf[4] = {c4.x, c4.y, c4.z, c4.w};
-      XT *dst = amat + smp * AP + q * Cs + j * 4;
+    const float *peers[CL];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const XT hi = DT<XT>::from_f(cf[u]);
-        dst[u] = hi;
-        if (SPLIT) dst[S * AP + u] = DT<XT>::from_f(cf[u] - DT<XT>::to_f(hi));
+    for (int q = 0; q < CL; ++q) peers[q] = cluster.map_shared_rank(sums, q);
+    for (int i = tid; i < ns * q4; i += NTF) {   // the eight remote loads of an item are in flight together
+      const int smp = i / q4, j = i - smp * q4;
+      float4 c4[CL];
+#pragma unroll
+      for (int q = 0; q < CL; ++q) c4[q] = *reinterpret_cast<const float4 *>(&peers[q][smp * Cs + j * 4]);
+#pragma unroll
+      for (int q = 0; q < CL; ++q) {
+        const float cf[4] = {c4[q].x, c4[q].y, c4[q].z, c4[q].w};
+        XT *dst = amat + smp * AP + q * Cs + j * 4;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const XT hi = DT<XT>::from_f(cf[u]);
+          dst[u] = hi;
+          if (SPLIT) dst[S * AP + u] = DT<XT>::from_f(cf[u] - DT<XT>::to_f(hi));
+        }
       }
     }
     for (int part_i = 0; part_i < NP; ++part_i)   // unused sample rows
@@ -524,15 +529,20 @@ pool_linear_mma_kernel(const XT *__restrict__ x, const XT *v_init, const XT *__r
     const int warp = tid / 32, lane = tid % 32;
     const int g = lane >> 2, t4 = lane & 3;
     const XT *arow = amat + (g < S ? g : 0) * AP;   // sample g (rows past S never reach the output)
-    for (int k0 = ks + 8 * warp; k0 < ke; k0 += 8 * (NTF / 32)) {
-      const int kc = min(k0 + g, ke - 1);   // classes past the end repeat the last one and are not stored
-      const XT *wrow = fc_w + (int64_t)kc * C;
-      float d[4] = {0.f, 0.f, 0.f, 0.f};
-      for (int c0 = 0; c0 < C; c0 += 128) {   // four independent 16-byte weight loads per trip
-        int4 wv[4], av[4], al[4];
+    // two class tiles per trip: eight independent 16-byte weight loads in flight per thread
+    for (int k0 = ks + 16 * warp; k0 < ke; k0 += 16 * (NTF / 32)) {
+      const XT *wrow[2];
 #pragma unroll
-        for (int u = 0; u < 4; ++u)
-          if (c0 + u * 32 < C) wv[u] = __ldg(reinterpret_cast<const int4 *>(wrow + c0 + u * 32 + t4 * 8));
+      for (int h = 0; h < 2; ++h)   // classes past the end repeat the last one and are not stored
+        wrow[h] = fc_w + (int64_t)min(k0 + 8 * h + g, ke - 1) * C;
+      float d[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+      for (int c0 = 0; c0 < C; c0 += 128) {
+        int4 wv[2][4], av[4], al[4];
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            if (c0 + u * 32 < C) wv[h][u] = __ldg(reinterpret_cast<const int4 *>(wrow[h] + c0 + u * 32 + t4 * 8));
 #pragma unroll
         for (int u = 0; u < 4; ++u)
           if (c0 + u * 32 < C) {
@@ -540,25 +550,29 @@ pool_linear_mma_kernel(const XT *__restrict__ x, const XT *v_init, const XT *__r
             if (SPLIT) al[u] = *reinterpret_cast<const int4 *>(arow + S * AP + c0 + u * 32 + t4 * 8);
           }
 #pragma unroll
-        for (int u = 0; u < 4; ++u)
-          if (c0 + u * 32 < C) {
-            if (SPLIT) {   // the small parts first
-              Mma16<XT>::run(d, (uint32_t)al[u].x, (uint32_t)al[u].y, (uint32_t)wv[u].x, (uint32_t)wv[u].y);
-              Mma16<XT>::run(d, (uint32_t)al[u].z, (uint32_t)al[u].w, (uint32_t)wv[u].z, (uint32_t)wv[u].w);
-            }
-            Mma16<XT>::run(d, (uint32_t)av[u].x, (uint32_t)av[u].y, (uint32_t)wv[u].x, (uint32_t)wv[u].y);
-            Mma16<XT>::run(d, (uint32_t)av[u].z, (uint32_t)av[u].w, (uint32_t)wv[u].z, (uint32_t)wv[u].w);
-          }
-      }
-      // d[0], d[1]: sample g, classes k0 + 2 * t4, k0 + 2 * t4 + 1
+        for (int h = 0; h < 2; ++h)
 #pragma unroll
-      for (int j = 0; j < 2; ++j) {
-        const int k = k0 + 2 * t4 + j;
-        if (g < ns && k < ke) {
-          const float bk = fc_b != nullptr ? DT<XT>::to_f(fc_b[k]) * bias_mul : 0.f;
-          out[(int64_t)(n0 + g) * K + k] = DT<OT>::from_f(d[j] * out_scale + bk);
-        }
+          for (int u = 0; u < 4; ++u)
+            if (c0 + u * 32 < C) {
+              if (SPLIT) {   // the small parts first
+                Mma16<XT>::run(d[h], (uint32_t)al[u].x, (uint32_t)al[u].y, (uint32_t)wv[h][u].x, (uint32_t)wv[h][u].y);
+                Mma16<XT>::run(d[h], (uint32_t)al[u].z, (uint32_t)al[u].w, (uint32_t)wv[h][u].z, (uint32_t)wv[h][u].w);
+              }
+              Mma16<XT>::run(d[h], (uint32_t)av[u].x, (uint32_t)av[u].y, (uint32_t)wv[h][u].x, (uint32_t)wv[h][u].y);
+              Mma16<XT>::run(d[h], (uint32_t)av[u].z, (uint32_t)av[u].w, (uint32_t)wv[h][u].z, (uint32_t)wv[h][u].w);
+            }
       }
+      // d[h][0], d[h][1]: sample g, classes k0 + 8 * h + 2 * t4, + 1
+#pragma unroll
+      for (int h = 0; h < 2; ++h)
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const int k = k0 + 8 * h + 2 * t4 + j;
+          if (g < ns && k < ke) {
+            const float bk = fc_b != nullptr ? DT<XT>::to_f(fc_b[k]) * bias_mul : 0.f;
+            out[(int64_t)(n0 + g) * K + k] = DT<OT>::from_f(d[h][j] * out_scale + bk);
+          }
+        }
     }
   }
 }
