@@ -288,23 +288,18 @@ def run_ours(args):
         return
     peaks = _peaks()
     flops = conv_flops(spec, net.shapes, B, T_STEPS)
-    # which kernel serves which layer (mirrors the library's dispatch for this network)
+    # which kernel serves which layer: the library's own dispatch, asked through its query entry point
     def kernel_of(L):
         if L["op"] != "conv":
             return {"maxpool": "maxpool3x3s2", "head": "avgpool_linear_mean", "tail": "lif_avgpool_linear"}[L["op"]]
         if L["groups"] != 1:
             return "dwconv3x3_lif"
-        if L["cin"] == 3:
-            return "stem (s2d + stem_gemm_lif)" if L["k"] == 7 else "conv3x3_smallcin (3-channel stem)"
-        ho, wo, _ = net.shapes[L["dst"]]
-        if L["k"] == 1 and L["s"] == 1 and L["cin"] % 64 == 0 and ((ho >= 8 and wo >= 8) or (ho <= 7 and wo <= 8 and L["cout"] > 64)):
-            return "conv3x3_pair"   # 1x1 convs run through the same kernel (centre tap only)
-        if L["k"] == 3 and L["s"] == 1:
-            one_image, two_images = ho >= 8 and wo >= 8, ho <= 7 and wo <= 8 and L["cout"] > 64
-            return "conv3x3_pair" if one_image or two_images else "conv3x3_halo"
-        if L["k"] == 3 and L["s"] == 2 and L["cout"] > 64 and L["cin"] % 64 == 0:
-            return "conv3x3_pair"   # stride 2 through the four phase views
-        return "conv_lif_tc"
+        if L["cin"] == 3 and L["k"] == 7:
+            return "stem (s2d + stem_gemm_lif)"
+        hi, wi, _ = net.shapes[L["src"]]
+        name = _lib.conv_kernel_name(T_STEPS, B, L["cin"], hi, wi, L["cout"], L["k"], L["s"], L["p"], torch.bfloat16,
+                                     one_frame=(L["cin"] == 3), residual=bool(L.get("residual")))
+        return name + (" (3-channel stem)" if L["cin"] == 3 else "")
     by_kernel = {}
     fused_into = {D["name"]: consumer for consumer, D in net.fused_sc.items()}   # shortcut conv -> the launch it rides in
     by_name = {L["name"]: L for L in spec}

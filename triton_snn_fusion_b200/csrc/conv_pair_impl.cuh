@@ -817,6 +817,10 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
         if (g.lif && p.mode == 1 && p.hard && p.v_reset == 0.f && g.tq == 2 && full && rows_valid >= 6) {
           if (rows_valid == 8) pair_epilogue_lean_any<ST, 8>(p, taddr, bias_c, out, frame_out, pm, v);
           else pair_epilogue_lean_any<ST, 6>(p, taddr, bias_c, out, frame_out, pm, v);
+        } else if (g.lif && p.mode == 1 && p.hard && p.v_reset == 0.f && g.tq == 2 && full && g.Cout == 64) {
+          // duplicated weight rows (1x1 and strided convs with 64 outputs): four or two tile rows per thread
+          if (rows_valid == 4) pair_epilogue_lean<ST, 4, 64>(p, taddr, bias_c, out, frame_out, pm, v);
+          else pair_epilogue_lean<ST, 2, 64>(p, taddr, bias_c, out, frame_out, pm, v);
         } else if (g.lif && p.mode == 1 && p.hard && g.tq == 2 && full) {
           if (rows_valid == 8) pair_epilogue_full<XT, ST, 8>(p, taddr, bias_c, out, frame_out, pm, v);
           else if (rows_valid == 6) pair_epilogue_full<XT, ST, 6>(p, taddr, bias_c, out, frame_out, pm, v);

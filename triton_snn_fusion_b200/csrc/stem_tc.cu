@@ -75,9 +75,83 @@ __device__ __forceinline__ void staged_tile(const StemGeom &g, const LifParams &
                                             const float *bias_s, const VT *__restrict__ v_init, VT *__restrict__ v_out,
                                             int bx, int by, int b, long long pix, bool valid) {
   const int lane = threadIdx.x & 31;
-  float v[64];
   const bool alias = g.Tacc != g.T;
   const long long o0 = pix * 64;
+  if constexpr (std::is_same<ST, uint64_t>::value && KIND == 2) {
+    if (alias) {
+      // Direct encoding with bit-packed spikes: the conv output is the same at every step, so each half of the
+      // pixel's 64 channels is read from tensor memory ONCE (bias added once) and the T steps then run in
+      // registers. The accumulator stage is released after the second half's read, before any LIF arithmetic.
+      // Spikes are packed without shifts: 16 channels are collected as two fp32 sums of 4^k terms (even and odd
+      // channels, exact below 2^16) by packed multiply-adds and converted to an integer once.
+      uint32_t *dst32 = reinterpret_cast<uint32_t *>(spikes);
+      const long long frame_px = (long long)g.B * g.Ho * g.Wo;
+      const float2 it2 = make_float2(p.inv_tau, p.inv_tau), four2 = make_float2(4.f, 4.f);
+#pragma unroll 1
+      for (int hf = 0; hf < 2; ++hf) {
+        float2 y[16], v[16];
+        {
+          uint32_t a[16], c[16];
+          umma::tmem_ld_x16(acc_addr + (uint32_t)(hf * 32), a);
+          umma::tmem_ld_x16(acc_addr + (uint32_t)(hf * 32 + 16), c);
+          umma::tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            y[i] = __fadd2_rn(make_float2(__uint_as_float(a[2 * i]), __uint_as_float(a[2 * i + 1])),
+                              make_float2(bias_s[hf * 32 + 2 * i], bias_s[hf * 32 + 2 * i + 1]));
+            y[8 + i] = __fadd2_rn(make_float2(__uint_as_float(c[2 * i]), __uint_as_float(c[2 * i + 1])),
+                                  make_float2(bias_s[hf * 32 + 16 + 2 * i], bias_s[hf * 32 + 16 + 2 * i + 1]));
+          }
+        }
+        if (hf == 1) {   // last read of this accumulator stage: the MMA warp may overwrite it
+          umma::tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) umma::mbar_arrive(accempty_bar);
+        }
+        if (v_init != nullptr && valid) {
+#pragma unroll
+          for (int q = 0; q < 2; ++q) {
+            float tmp[16];
+            load_pack_stream<VT, 16>(v_init + o0 + hf * 32 + q * 16, tmp);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[q * 8 + i] = make_float2(tmp[2 * i], tmp[2 * i + 1]);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) v[i] = make_float2(0.f, 0.f);
+        }
+        for (int t = 0; t < g.T; ++t) {
+          uint32_t word = 0u;
+#pragma unroll
+          for (int grp = 0; grp < 2; ++grp) {
+            float2 bits = make_float2(0.f, 0.f);   // .x: even channels of the group, .y: odd ones; channel pair k -> 4^k
+#pragma unroll
+            for (int k = 7; k >= 0; --k) {
+              const int i = grp * 8 + k;
+              const float2 d = __fadd2_rn(y[i], make_float2(-v[i].x, -v[i].y));
+              const float2 h = __fadd2_rn(v[i], __fmul2_rn(d, it2));
+              const float2 sp = make_float2(h.x >= p.v_th ? 1.f : 0.f, h.y >= p.v_th ? 1.f : 0.f);
+              v[i] = __ffma2_rn(make_float2(-sp.x, -sp.y), h, h);
+              bits = __ffma2_rn(bits, four2, sp);
+            }
+            word |= (uint32_t)__fmaf_rn(bits.y, 2.f, bits.x) << (grp * 16);
+          }
+          if (valid) dst32[((long long)t * frame_px + pix) * 2 + hf] = word;
+        }
+        if (valid && v_out != nullptr) {
+#pragma unroll
+          for (int q = 0; q < 2; ++q) {
+            float tmp[16];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) { tmp[2 * i] = v[q * 8 + i].x; tmp[2 * i + 1] = v[q * 8 + i].y; }
+            store_pack<VT, 16, false>(v_out + o0 + hf * 32 + q * 16, tmp);
+          }
+        }
+      }
+      return;
+    }
+  }
+  float v[64];
   if (v_init != nullptr && valid) {
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
