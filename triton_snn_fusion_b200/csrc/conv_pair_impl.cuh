@@ -148,13 +148,13 @@ struct PixMap {
 // Converts one timestep pair for the 64 pixels of this thread's channel: TMEM -> + bias (+ residual)
 // -> LIF (membrane in v[]) -> spikes. TQ2: the pair holds two timesteps; RES: a residual is added.
 // General version: every pixel is predicated on the tile / image edges.
-template <typename XT, typename ST, int KIND, bool TQ2, bool RES>
+template <typename XT, typename ST, int KIND, bool TQ2, bool RES, int NV>
 __device__ __forceinline__ void pair_epilogue(const LifParams &p, uint32_t tmem_addr, float bias_c,
                                               const XT *__restrict__ res, ST *__restrict__ out, long long frame_out,
-                                              const PixMap &pm, float (&v)[64], int nchunks) {
+                                              const PixMap &pm, float (&v)[NV], int nchunks) {
   // out / res already point at (timestep t0 of the pair, this thread's first row, column w0, channel c)
 #pragma unroll
-  for (int chunk = 0; chunk < 4; ++chunk) {
+  for (int chunk = 0; chunk < NV / 16; ++chunk) {
     if (chunk < nchunks) {   // warp-uniform; written as a guard so that the loop stays fully unrolled
     uint32_t a0[16], a1[16];
     umma::tmem_ld_x16(tmem_addr + (uint32_t)(chunk * 16), a0);
@@ -198,10 +198,10 @@ __device__ __forceinline__ void pair_epilogue(const LifParams &p, uint32_t tmem_
 // fetch. So the loop over 16-pixel chunks stays a real loop. The membrane potentials must be
 // registers, which cannot be indexed by the loop counter: each trip works on v[0..15] and then
 // rotates the thread's NROWS * 8 potentials by 16, so they are back in place after the last trip.
-template <typename XT, typename ST, int NROWS>
+template <typename XT, typename ST, int NROWS, int NV>
 __device__ __forceinline__ void pair_epilogue_full(const LifParams &p, uint32_t tmem_addr, float bias_c,
                                                    ST *__restrict__ out, long long frame_out, const PixMap &pm,
-                                                   float (&v)[64]) {
+                                                   float (&v)[NV]) {
   constexpr int NPIX = NROWS * 8;
   ST *p0 = out + pm.row0_off;
   ST *p1 = p0 + frame_out;
@@ -254,10 +254,10 @@ __device__ __forceinline__ float2 lif_fast2(float2 y, float &vx, float &vy, floa
   return s;
 }
 
-template <typename ST, int NROWS, int COUT>
+template <typename ST, int NROWS, int COUT, int NV>
 __device__ __forceinline__ void pair_epilogue_lean(const LifParams &p, uint32_t tmem_addr, float bias_c,
                                                    ST *__restrict__ out, long long frame_out, const PixMap &pm,
-                                                   float (&v)[64]) {
+                                                   float (&v)[NV]) {
   constexpr int NCH = NROWS / 2;   // chunks of 16 pixels = two tile rows
   const float2 b2 = make_float2(bias_c, bias_c), it2 = make_float2(p.inv_tau, p.inv_tau);
   const float v_th = p.v_th;
@@ -289,13 +289,13 @@ __device__ __forceinline__ void pair_epilogue_lean(const LifParams &p, uint32_t 
   }
 }
 
-template <typename ST, int NROWS>
+template <typename ST, int NROWS, int NV>
 __device__ __forceinline__ void pair_epilogue_lean_any(const LifParams &p, uint32_t tmem_addr, float bias_c,
                                                        ST *__restrict__ out, long long frame_out, const PixMap &pm,
-                                                       float (&v)[64]) {
+                                                       float (&v)[NV]) {
   switch (pm.Cout) {
-    case 128: pair_epilogue_lean<ST, NROWS, 128>(p, tmem_addr, bias_c, out, frame_out, pm, v); break;
-    default: pair_epilogue_lean<ST, NROWS, 0>(p, tmem_addr, bias_c, out, frame_out, pm, v); break;
+    case 128: pair_epilogue_lean<ST, NROWS, 128, NV>(p, tmem_addr, bias_c, out, frame_out, pm, v); break;
+    default: pair_epilogue_lean<ST, NROWS, 0, NV>(p, tmem_addr, bias_c, out, frame_out, pm, v); break;
   }
 }
 
@@ -367,7 +367,9 @@ __device__ __forceinline__ void twin_step(const LifParams &p, uint32_t tmem_addr
   }
 }
 
-template <typename XT, typename ST, typename VT, bool S2, bool TWIN>
+// DUP: the instantiation for duplicated weight rows at stride 1 (a thread owns four tile rows, 32 membrane values);
+// strided convs with at most 64 outputs run the S2 instantiation, which handles that case at run time.
+template <typename XT, typename ST, typename VT, bool S2, bool TWIN, bool DUP>
 __global__ void __launch_bounds__(Roles<TWIN>::kThreads)
 conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap,
                     const __grid_constant__ CUtensorMap rmap, const __grid_constant__ CUtensorMap wmap64,
@@ -376,6 +378,7 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
                     const XT *__restrict__ bias, const XT *__restrict__ bias2, const VT *v_init,
                     ST *__restrict__ spikes, VT *v_out, const PairGeom g, const LifParams p) {
   using R = Roles<TWIN>;
+  const bool dup = DUP || (S2 && g.dup);
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bars[2 * kPairRingMax + 2 * kWRingP + 4];
   __shared__ uint32_t tmem_base_s;
@@ -449,10 +452,10 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
     const int ident_bytes = TWIN ? kTwinIdentBytes : kIdentBytes;
     for (int i = threadIdx.x; i < ident_bytes / 16; i += 32 * R::kEpi) blk[i] = make_uint4(0u, 0u, 0u, 0u);
     asm volatile("bar.sync 2, %0;" ::"r"(32 * R::kEpi) : "memory");
-    if (g.dup ? threadIdx.x < 128 : threadIdx.x < 64) {
+    if (dup ? threadIdx.x < 128 : threadIdx.x < 64) {
       // dup mode: rows 0..127 carry the identity twice (row r has its one in column r % 64); twin mode: the D1 row
       // of channel k (row k for k < 32, row k + 32 above) has its one in column k, the D2 rows stay zero
-      const int k = threadIdx.x & 63, r = g.dup ? (int)threadIdx.x : (TWIN ? (k < 32 ? k : k + 32) : 64 + k);
+      const int k = threadIdx.x & 63, r = dup ? (int)threadIdx.x : (TWIN ? (k < 32 ? k : k + 32) : 64 + k);
       uint8_t *row = smem_raw + (ident_base - umma::smem_u32(smem_raw)) + r * 128;
       *reinterpret_cast<XT *>(row + (((k >> 3) ^ (r & 7)) << 4) + (k & 7) * 2) = DT<XT>::from_f(1.0f);
     }
@@ -548,7 +551,7 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
                 umma::tma_load_2d(dst + 32u * 128u, &wmap64, wfull(ws), kx2, 0);
                 umma::tma_load_2d(dst + 64u * 128u, &wmap64, wfull(ws), kx, 32);
                 umma::tma_load_2d(dst + 96u * 128u, &wmap64, wfull(ws), kx2, 32);
-              } else if (g.dup) {   // the same 64 rows into both halves of the tile
+              } else if (dup) {   // the same 64 rows into both halves of the tile
                 umma::tma_load_2d(w_base + ws * (uint32_t)kWSlot, &wmap64, wfull(ws), tap * g.Cin + slab * 64, 0);
                 umma::tma_load_2d(w_base + ws * (uint32_t)kWSlot + 64u * 128u, &wmap64, wfull(ws), tap * g.Cin + slab * 64, 0);
               } else {
@@ -625,7 +628,7 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
               if (!ok) break;
               adesc = wdesc0 + (uint64_t)((ws * (uint32_t)kWSlot) >> 4);
             } else {
-              adesc = umma::make_sw128_kmajor_desc(ident_base + ((rs == 0 && !g.dup && !TWIN) ? 64u * 128u : 0u));
+              adesc = umma::make_sw128_kmajor_desc(ident_base + ((rs == 0 && !dup && !TWIN) ? 64u * 128u : 0u));
             }
             umma::tc_fence_after_sync();
             const uint64_t xdesc = hdesc0 + (uint64_t)((slot * slot_bytes + (g.flat ? 0u : (uint32_t)(kPW + 1) * 128u)) >> 4);
@@ -757,9 +760,10 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
     const int quarter = warp & 3;
     // Pixel split: normally the two warps of a lane quarter take tile rows 0..7 / 8..15. In dup mode lanes
     // 64..127 repeat lanes 0..63, so the four warps that see the same 32 channels take 4 rows each.
-    const int r_begin = g.dup ? ((quarter >> 1) * 2 + (warp >> 2)) * 4 : ((warp < 4) ? 0 : 8);
-    const int my_rows = g.dup ? 4 : 8;
-    const int ch_in_tile = g.dup ? (quarter & 1) * 32 + lane : quarter * 32 + lane;
+    const int r_begin = dup ? ((quarter >> 1) * 2 + (warp >> 2)) * 4 : ((warp < 4) ? 0 : 8);
+    const int my_rows = dup ? 4 : 8;
+    constexpr int NV = DUP ? 32 : 64;   // membrane values a thread keeps
+    const int ch_in_tile = dup ? (quarter & 1) * 32 + lane : quarter * 32 + lane;
     const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(r_begin * 8);
     const long long frame_out = (long long)g.B * g.Ho * g.Wo * g.Cout;
     bool ok = true;
@@ -789,12 +793,12 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
 #pragma unroll
       for (int j = 0; j < 8; ++j)
         if (w0 + j < g.Wo && w0 + j >= wlo) pm.cols_ok |= 1 << j;
-      float v[64];
+      float v[NV];
 #pragma unroll
-      for (int i = 0; i < 64; ++i) v[i] = 0.f;
+      for (int i = 0; i < NV; ++i) v[i] = 0.f;
       if (g.lif && v_init != nullptr) {
 #pragma unroll
-        for (int i = 0; i < 64; ++i)
+        for (int i = 0; i < NV; ++i)
           if (((pm.rows_ok >> (i >> 3)) & 1) && ((pm.cols_ok >> (i & 7)) & 1))
             v[i] = DT<VT>::to_f(v_init[pm.row0_off + (long long)(i >> 3) * pm.row_stride + (i & 7) * pm.Cout]);
       }
@@ -814,26 +818,41 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
         const int nchunks = (rows_valid + 1) / 2;
         // warp-uniform choice: the TMEM loads inside are warp-collective
         const bool full = __all_sync(0xffffffffu, pm.rows_ok == rows_want && pm.cols_ok == 0xFF);
-        if (g.lif && p.mode == 1 && p.hard && p.v_reset == 0.f && g.tq == 2 && full && rows_valid >= 6) {
-          if (rows_valid == 8) pair_epilogue_lean_any<ST, 8>(p, taddr, bias_c, out, frame_out, pm, v);
-          else pair_epilogue_lean_any<ST, 6>(p, taddr, bias_c, out, frame_out, pm, v);
-        } else if (g.lif && p.mode == 1 && p.hard && p.v_reset == 0.f && g.tq == 2 && full && g.Cout == 64) {
-          // duplicated weight rows (1x1 and strided convs with 64 outputs): four or two tile rows per thread
-          if (rows_valid == 4) pair_epilogue_lean<ST, 4, 64>(p, taddr, bias_c, out, frame_out, pm, v);
-          else pair_epilogue_lean<ST, 2, 64>(p, taddr, bias_c, out, frame_out, pm, v);
-        } else if (g.lif && p.mode == 1 && p.hard && g.tq == 2 && full) {
-          if (rows_valid == 8) pair_epilogue_full<XT, ST, 8>(p, taddr, bias_c, out, frame_out, pm, v);
-          else if (rows_valid == 6) pair_epilogue_full<XT, ST, 6>(p, taddr, bias_c, out, frame_out, pm, v);
-          else if (rows_valid == 4) pair_epilogue_full<XT, ST, 4>(p, taddr, bias_c, out, frame_out, pm, v);
-          else pair_epilogue_full<XT, ST, 2>(p, taddr, bias_c, out, frame_out, pm, v);
+        const bool fast = g.lif && p.mode == 1 && p.hard && g.tq == 2 && full;
+        const bool lean = fast && p.v_reset == 0.f;
+        bool done = false;
+        if constexpr (!DUP) {   // eight or six tile rows per thread
+          if (lean && rows_valid >= 6) {
+            if (rows_valid == 8) pair_epilogue_lean_any<ST, 8, NV>(p, taddr, bias_c, out, frame_out, pm, v);
+            else pair_epilogue_lean_any<ST, 6, NV>(p, taddr, bias_c, out, frame_out, pm, v);
+            done = true;
+          } else if (fast && rows_valid >= 6) {
+            if (rows_valid == 8) pair_epilogue_full<XT, ST, 8, NV>(p, taddr, bias_c, out, frame_out, pm, v);
+            else pair_epilogue_full<XT, ST, 6, NV>(p, taddr, bias_c, out, frame_out, pm, v);
+            done = true;
+          }
+        }
+        if constexpr (DUP) {   // duplicated weight rows at stride 1: four or two tile rows per thread (strided convs
+                               // with at most 64 outputs take the general body below)
+          if (!done && lean && g.Cout == 64 && rows_valid <= 4) {
+            if (rows_valid == 4) pair_epilogue_lean<ST, 4, 64, NV>(p, taddr, bias_c, out, frame_out, pm, v);
+            else pair_epilogue_lean<ST, 2, 64, NV>(p, taddr, bias_c, out, frame_out, pm, v);
+            done = true;
+          } else if (!done && fast && rows_valid <= 4) {
+            if (rows_valid == 4) pair_epilogue_full<XT, ST, 4, NV>(p, taddr, bias_c, out, frame_out, pm, v);
+            else pair_epilogue_full<XT, ST, 2, NV>(p, taddr, bias_c, out, frame_out, pm, v);
+            done = true;
+          }
+        }
+        if (done) {
         } else if (g.lif && p.mode == 1 && p.hard && g.tq == 2) {
-          pair_epilogue<XT, ST, kLifFast, true, false>(p, taddr, bias_c, rs, out, frame_out, pm, v, nchunks);
+          pair_epilogue<XT, ST, kLifFast, true, false, NV>(p, taddr, bias_c, rs, out, frame_out, pm, v, nchunks);
         } else if (g.lif) {
-          if (g.tq == 2) pair_epilogue<XT, ST, kLifAny, true, false>(p, taddr, bias_c, rs, out, frame_out, pm, v, nchunks);
-          else pair_epilogue<XT, ST, kLifAny, false, false>(p, taddr, bias_c, rs, out, frame_out, pm, v, nchunks);
+          if (g.tq == 2) pair_epilogue<XT, ST, kLifAny, true, false, NV>(p, taddr, bias_c, rs, out, frame_out, pm, v, nchunks);
+          else pair_epilogue<XT, ST, kLifAny, false, false, NV>(p, taddr, bias_c, rs, out, frame_out, pm, v, nchunks);
         } else {
-          if (g.tq == 2) pair_epilogue<XT, ST, kLifOff, true, false>(p, taddr, bias_c, rs, out, frame_out, pm, v, nchunks);
-          else pair_epilogue<XT, ST, kLifOff, false, false>(p, taddr, bias_c, rs, out, frame_out, pm, v, nchunks);
+          if (g.tq == 2) pair_epilogue<XT, ST, kLifOff, true, false, NV>(p, taddr, bias_c, rs, out, frame_out, pm, v, nchunks);
+          else pair_epilogue<XT, ST, kLifOff, false, false, NV>(p, taddr, bias_c, rs, out, frame_out, pm, v, nchunks);
         }
         // this accumulator may now be overwritten by the next tile's MMAs
         umma::tc_fence_before_sync();
@@ -842,7 +861,7 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
       }
       if (ok && g.lif && v_out != nullptr) {
 #pragma unroll
-        for (int i = 0; i < 64; ++i)
+        for (int i = 0; i < NV; ++i)
           if (((pm.rows_ok >> (i >> 3)) & 1) && ((pm.cols_ok >> (i & 7)) & 1))
             v_out[pm.row0_off + (long long)(i >> 3) * pm.row_stride + (i & 7) * pm.Cout] = DT<VT>::from_f(v[i]);
       }
@@ -972,15 +991,18 @@ int launch(const ConvArgs &a, cudaStream_t stream) {
     static_assert(kTwinIdentBytes + 3 * kWSlot + kPairRing * 2 * kHaloT + kXchgBytes + 1024 <= 225 * 1024, "twin mode: shared memory");
     static_assert(4 * kWSlot + kPairRing * 2 * kHaloT + kXchgBytes + 1024 <= 225 * 1024, "twin mode: shared memory");
   }
-  auto kern = g.s2 ? conv3x3_pair_kernel<XT, ST, VT, true, false>
-                   : (g.twin ? conv3x3_pair_kernel<XT, ST, VT, false, true> : conv3x3_pair_kernel<XT, ST, VT, false, false>);
+  auto kern = g.s2 ? conv3x3_pair_kernel<XT, ST, VT, true, false, false>
+              : g.twin ? conv3x3_pair_kernel<XT, ST, VT, false, true, false>
+              : g.dup  ? conv3x3_pair_kernel<XT, ST, VT, false, false, true>
+                       : conv3x3_pair_kernel<XT, ST, VT, false, false, false>;
+  const int kidx = g.s2 ? 1 : (g.twin ? 2 : (g.dup ? 3 : 0));
   {
     // once per kernel instantiation and device: allow the largest dynamic shared-memory size any call may ask for
-    static bool raised[3][64] = {};
-    if (dev < 0 || dev >= 64 || !raised[g.s2 + 2 * g.twin][dev]) {
+    static bool raised[4][64] = {};
+    if (dev < 0 || dev >= 64 || !raised[kidx][dev]) {
       const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 225 * 1024);
       if (e != cudaSuccess) return fail(SNNB_ERR_CUDA, "conv_lif: cannot raise the shared-memory limit: %s", cudaGetErrorString(e));
-      if (dev >= 0 && dev < 64) raised[g.s2 + 2 * g.twin][dev] = true;
+      if (dev >= 0 && dev < 64) raised[kidx][dev] = true;
     }
   }
   {

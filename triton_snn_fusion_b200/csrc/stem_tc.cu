@@ -36,9 +36,15 @@ constexpr int kChunkBytes = 16384;   // 128 pixels x 128 bytes: one K chunk of a
 constexpr int kMaxRing = 12;
 constexpr int kMaxAcc = 4;
 constexpr int kStage = 4;            // staged epilogue: 4 x 16 KB = two 4 KB slots of outgoing rows per epilogue warp
-constexpr int kEpiWarpsS = 8;
-constexpr int kProdWarpS = kEpiWarpsS, kMmaWarpS = kEpiWarpsS + 1;
-constexpr int kThreadsS = 32 * (kEpiWarpsS + 2);
+// Warp roles: epilogue warps first (groups of four, one group per tile in flight), then the producer, then the MMA
+// issuer. Bit-packed spikes need no staging memory and few registers, so that form runs three groups; its epilogue
+// waits more than it computes (tensor-memory loads, accumulator hand-over) and a third group hides part of that.
+template <typename ST> struct StemRoles {
+  static constexpr int kEpi = std::is_same<ST, uint64_t>::value ? 12 : 8;
+  static constexpr int kGroups = kEpi / 4;
+  static constexpr int kProd = kEpi, kMma = kEpi + 1;
+  static constexpr int kThreads = 32 * (kEpi + 2);
+};
 
 struct StemGeom {
   int T, Tacc, B, Ho, Wo, Cout;
@@ -287,11 +293,12 @@ __device__ __forceinline__ void staged_tile(const StemGeom &g, const LifParams &
 }
 
 template <typename XT, typename ST, typename VT>
-__global__ void __launch_bounds__(kThreadsS)
+__global__ void __launch_bounds__(StemRoles<ST>::kThreads)
 stem_gemm_lif_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap,
                      const __grid_constant__ CUtensorMap smap, const XT *__restrict__ bias,
                      const VT *__restrict__ v_init, ST *__restrict__ spikes, VT *__restrict__ v_out,
                      const StemGeom g, const LifParams p) {
+  using SR = StemRoles<ST>;
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bars[2 * kMaxRing + 1 + 2 * kMaxAcc];
   __shared__ uint32_t tmem_base_s;
@@ -324,14 +331,14 @@ stem_gemm_lif_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_cons
     abort_s = 0;
     for (int s = 0; s < g.ring; ++s) { umma::mbar_init(afull(s), 1); umma::mbar_init(aempty(s), 1); }
     umma::mbar_init(wfull, 1);
-    for (int s = 0; s < g.nacc; ++s) { umma::mbar_init(accfull(s), 1); umma::mbar_init(accempty(s), g.staged ? kEpiWarpsS / 2 : kEpiWarpsS); }
+    for (int s = 0; s < g.nacc; ++s) { umma::mbar_init(accfull(s), 1); umma::mbar_init(accempty(s), g.staged ? 4 : 8); }
     umma::fence_mbar_init();
   }
-  if (warp == kMmaWarpS) {
+  if (warp == SR::kMma) {
     umma::tmem_alloc(umma::smem_u32(&tmem_base_s), (uint32_t)g.tmem_cols);
     umma::tmem_relinquish();
   }
-  if (warp == kProdWarpS && lane == 0) {
+  if (warp == SR::kProd && lane == 0) {
     umma::prefetch_tensormap(&xmap);
     umma::prefetch_tensormap(&wmap);
     if (g.staged) umma::prefetch_tensormap(&smap);
@@ -341,7 +348,7 @@ stem_gemm_lif_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_cons
   umma::tc_fence_after_sync();
   const uint32_t tmem_base = tmem_base_s;
 
-  if (warp == kProdWarpS) {
+  if (warp == SR::kProd) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
       umma::mbar_expect_tx(wfull, 4u * (uint32_t)g.w_chunk_bytes);
@@ -362,7 +369,7 @@ stem_gemm_lif_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_cons
       }
     }
     __syncwarp();
-  } else if (warp == kMmaWarpS) {
+  } else if (warp == SR::kMma) {
     // -------------------------------------------------------------- MMA issuer
     if (lane == 0) {
       const uint32_t idesc = umma::make_idesc_f16(128, g.Cout, std::is_same<XT, __nv_bfloat16>::value);
@@ -408,8 +415,9 @@ stem_gemm_lif_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_cons
     bool ok = true;
     {
       if (g.staged) {
-        // Warps 0-3 take this CTA's even tiles, warps 4-7 the odd ones; a warp converts all 64 channels of
-        // its 32 pixels and sends them out by itself, so the epilogue has no block-wide synchronisation.
+        // The groups of four warps take this CTA's tiles in turn (two groups: even / odd tiles); a warp converts
+        // all 64 channels of its 32 pixels and sends them out by itself, so the epilogue has no block-wide
+        // synchronisation.
         const int group = warp >> 2;
         const uint32_t slots = stage_base + (uint32_t)warp * 8192u;   // two 4 KB slots per warp
         uint32_t sslot = 0;
@@ -417,7 +425,7 @@ stem_gemm_lif_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_cons
         const int bx_off = (g.BW >= 32) ? (quarter * 32) % g.BW : 0;
         const int by_off = (g.BW >= 32) ? (quarter * 32) / g.BW : quarter * (32 / g.BW);
         int it = group;
-        for (int tile = blockIdx.x + group * gridDim.x; tile < g.total_tiles && ok; tile += 2 * gridDim.x, it += 2) {
+        for (int tile = blockIdx.x + group * gridDim.x; tile < g.total_tiles && ok; tile += SR::kGroups * gridDim.x, it += SR::kGroups) {
           int w0, h0, b;
           decode(tile, w0, h0, b);
           const int wo = w0 + pw, ho = h0 + ph;
@@ -473,7 +481,7 @@ stem_gemm_lif_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_cons
   umma::tc_fence_before_sync();
   __syncthreads();
   if (abort_s && threadIdx.x == 0) atomicExch(&g_stem_status, 1);
-  if (warp == kMmaWarpS) {
+  if (warp == SR::kMma) {
     umma::tc_fence_after_sync();
     umma::tmem_dealloc(tmem_base, (uint32_t)g.tmem_cols);
   }
@@ -547,7 +555,7 @@ int launch(const StemGemmArgs &a, cudaStream_t stream) {
   auto kern = stem_gemm_lif_kernel<XT, ST, VT>;
   const cudaError_t e = raise_smem_limit_once<stem_gemm_lif_kernel<XT, ST, VT>>(225 * 1024);
   if (e != cudaSuccess) return fail(SNNB_ERR_CUDA, "stem7x7_lif: cannot raise the shared-memory limit: %s", cudaGetErrorString(e));
-  kern<<<(unsigned)grid, kThreadsS, smem, stream>>>(xm, wm, sm, static_cast<const XT *>(a.b), static_cast<const VT *>(a.v_init),
+  kern<<<(unsigned)grid, StemRoles<ST>::kThreads, smem, stream>>>(xm, wm, sm, static_cast<const XT *>(a.b), static_cast<const VT *>(a.v_init),
                                                     static_cast<ST *>(a.spikes), static_cast<VT *>(a.v_out), g, a.p);
   SNNB_CHECK_LAUNCH("stem_gemm_lif");
   return SNNB_OK;
