@@ -37,10 +37,10 @@ constexpr int kMaxRing = 12;
 constexpr int kMaxAcc = 4;
 constexpr int kStage = 4;            // staged epilogue: 4 x 16 KB = two 4 KB slots of outgoing rows per epilogue warp
 // Warp roles: epilogue warps first (groups of four, one group per tile in flight), then the producer, then the MMA
-// issuer. Bit-packed spikes need no staging memory and few registers, so that form runs three groups; its epilogue
-// waits more than it computes (tensor-memory loads, accumulator hand-over) and a third group hides part of that.
+// issuer. Two groups: a third one (tried for the bit-packed form, which has the registers for it) made the layer
+// 5 % slower, i.e. the epilogue warps are not what the tiles wait for.
 template <typename ST> struct StemRoles {
-  static constexpr int kEpi = std::is_same<ST, uint64_t>::value ? 12 : 8;
+  static constexpr int kEpi = 8;
   static constexpr int kGroups = kEpi / 4;
   static constexpr int kProd = kEpi, kMma = kEpi + 1;
   static constexpr int kThreads = 32 * (kEpi + 2);
