@@ -215,40 +215,47 @@ def run_ours(args):
 
     spec = nets.NETS[args.net](CLASSES)
     params = nets.make_params(spec, seed=2026, gain=args.weight_gain)
-    net = nets.CompiledNet(spec, params, batch=B, T=T_STEPS, in_hw=IN_HW, dtype=torch.bfloat16, device=dev,
-                           conv_path=args.path)
     # this rank's shard of the seeded global batch, channels-last bf16, in pinned host memory
     g = torch.Generator().manual_seed(2026 + rank)
     host_in = torch.randn(B, *IN_HW, 3, generator=g).to(torch.bfloat16).pin_memory()
-    host_out = torch.empty(B, CLASSES, dtype=torch.float32).pin_memory()
-    gathered = torch.empty(GLOBAL_BATCH, CLASSES, dtype=torch.float32, device=dev) if world > 1 else None
-    net.x_in.copy_(host_in)
-    net.run()
-    torch.cuda.synchronize()
-    if args.graph:
-        net.capture()
 
-    def step_resident():
-        gather_logits(net.run(), out=gathered)
+    def make_net():
+        n = nets.CompiledNet(spec, params, batch=B, T=T_STEPS, in_hw=IN_HW, dtype=torch.bfloat16, device=dev,
+                             conv_path=args.path)
+        n.x_in.copy_(host_in)
+        return n
 
-    def step_e2e():
+    # `--in-flight` copies of the network take turns (pass i on copy i % copies, each on its own stream): the SMs one
+    # pass leaves idle in the partly filled last wave of a layer run blocks of the other pass
+    passes = nets.OverlappedPasses(make_net, copies=max(1, args.in_flight), graph=args.graph)
+    net = passes.nets[0]
+    copies = len(passes)
+    host_out = [torch.empty(B, CLASSES, dtype=torch.float32).pin_memory() for _ in range(copies)]
+    gathered = [torch.empty(GLOBAL_BATCH, CLASSES, dtype=torch.float32, device=dev) if world > 1 else None
+                for _ in range(copies)]
+
+    def step_resident(i):
+        passes.run(i, then=lambda logits, k: gather_logits(logits, out=gathered[k]))
+
+    def step_e2e(i):
         # the user-facing call: pinned host batch in, fp32 logits out to pinned host memory. The copy of
-        # step i+1 (side stream, second staging buffer) overlaps the kernels of step i; every step's
-        # copies lie inside the timed region because the step's kernels wait for them.
-        logits = net.submit(host_in, host_out)
-        gather_logits(logits, out=gathered)
+        # a copy's next step (side stream, second staging buffer) overlaps the kernels of its current one; every
+        # step's copies lie inside the timed region because the step's kernels wait for them.
+        passes.submit(i, host_in, host_out[i % copies], then=lambda logits, k: gather_logits(logits, out=gathered[k]))
 
     def timed(step_fn):
-        for _ in range(Wm):
-            step_fn()
+        for i in range(max(Wm, copies)):
+            step_fn(i)
         torch.cuda.synchronize()
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        for _ in range(K):
-            step_fn()
+        passes.fork()          # the copies' streams start after e0 ...
+        for i in range(K):
+            step_fn(i)
+        passes.join()          # ... and e1 follows the last kernel of every copy
         e1.record()
         torch.cuda.synchronize()
         if world > 1:
@@ -362,11 +369,11 @@ def run_ours(args):
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": workload_name(T_STEPS, GLOBAL_BATCH, args.net),
                    "parallelism": f"batch-sharded x{world}", "per_gpu_batch": B, "cuda_graph": bool(args.graph),
-                   "conv_path": args.path,
+                   "passes_in_flight": copies, "conv_path": args.path,
                    "l2": "no flush needed: each step streams >3 GB of activations per GPU, far beyond the 126 MB L2"},
         "e2e": {"value": GLOBAL_BATCH / (ms_e2e * 1e-3), "unit": "images/s", "ms_per_step": ms_e2e,
                 "h2d_bytes_per_step": host_in.numel() * host_in.element_size() * world,
-                "d2h_bytes_per_step": host_out.numel() * host_out.element_size() * world},
+                "d2h_bytes_per_step": host_out[0].numel() * host_out[0].element_size() * world},
         "gpu_launches": net.launches_per_forward * K,
         "roofline": roofline,
         "clocks": clocks,
@@ -393,6 +400,8 @@ def main():
                     help="network (the headline is resnet18; mobilenet_v1 is the depthwise / pointwise workload)")
     ap.add_argument("--path", default="auto", choices=["auto", "simt", "tcgen05", "tcgen05_taps", "tcgen05_halo"])
     ap.add_argument("--no-graph", dest="graph", action="store_false")
+    ap.add_argument("--in-flight", type=int, default=2,
+                    help="forward passes in flight (copies of the network on their own streams that take turns)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--layers", action="store_true", help="also print every layer's device time to stderr")
     ap.add_argument("--weight-gain", type=float, default=1.0,

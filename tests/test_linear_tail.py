@@ -82,7 +82,8 @@ def test_tail_golden(name):
 
 @pytest.mark.parametrize("shape", [(4, 16, 256, 8, 8, 10), (4, 64, 1024, 7, 7, 1000), (4, 5, 512, 7, 7, 1000),
                                    (2, 3, 20, 3, 5, 7), (5, 9, 128, 4, 4, 33), (9, 2, 64, 2, 2, 5), (4, 40, 2048, 2, 2, 100),
-                                   (4, 300, 512, 7, 7, 100)])   # eight samples per cluster, last group partial
+                                   (4, 300, 512, 7, 7, 100),    # eight samples per cluster, last group partial
+                                   (8, 6, 512, 7, 7, 100)])     # 392 spikes per channel at most: counts kept as two 16-bit parts
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("nhwc", [False, True])
 def test_tail_seeded(shape, dtype, nhwc):

@@ -129,6 +129,39 @@ def test_pipelined_submit_matches_forward():
         assert torch.equal(w.cpu(), o)
 
 
+def test_overlapped_passes_give_the_same_logits():
+    """Two copies of the network that take turns on their own streams (OverlappedPasses): every pass returns what a
+    single network returns for that input, whatever the other copy is doing at the time."""
+    from triton_snn_fusion_b200 import nets
+    B, hw, dtype = 6, 96, torch.bfloat16
+    spec = nets.NETS["resnet18"](100)
+    params = nets.make_params(spec, seed=7, gain=4.0)
+    def make():
+        return nets.CompiledNet(spec, params, batch=B, T=4, in_hw=(hw, hw), dtype=dtype, device="cuda")
+    g = torch.Generator().manual_seed(3)
+    xs = [torch.randn(B, hw, hw, 3, generator=g).to(dtype).cuda() for _ in range(2)]
+    single = make()
+    want = []
+    for x in xs:
+        want.append(single.forward(x).clone())
+    torch.cuda.synchronize()
+    passes = nets.OverlappedPasses(make, copies=2)
+    for k in range(2):
+        passes.nets[k].x_in.copy_(xs[k])
+    torch.cuda.synchronize()
+    got = [[], []]
+    passes.fork()
+    for i in range(8):
+        passes.run(i, then=lambda logits, k: got[k].append(logits.clone()))
+    passes.join()
+    torch.cuda.synchronize()
+    for k in range(2):
+        assert len(got[k]) == 4
+        for out in got[k]:
+            assert torch.equal(out, want[k])
+    assert float(want[0].abs().max()) > 0 and not torch.equal(want[0], want[1])
+
+
 @pytest.mark.parametrize("hw", [64, 96, 224])
 def test_fused_shortcut_convs_match_the_two_op_sequence(hw):
     """conv2 + strided 1x1 shortcut in one launch (snnb_conv3x3_shortcut_lif) against shortcut conv -> residual

@@ -360,9 +360,9 @@ lif_avgpool_linear_stream_kernel(const XT *__restrict__ x, const VT *v_init, con
 //     the LIF and sums the inputs themselves (the network head: average pool + linear over spikes that exist
 //     already).
 //   * exchange: every CTA gathers the eight slices of sums through DSMEM and stores them as 16-bit floats.
-//     Spike counts are at most T * HW: exact in bf16 up to 256 and in fp16 up to 2048 (larger counts take the
-//     first streaming form). SPLIT stores a second 16-bit float with the rounding error of the first, for sums
-//     of arbitrary values (relative error 2^-16 instead of 2^-8).
+//     Spike counts are at most T * HW: exact in bf16 up to 256 and in fp16 up to 2048. SPLIT stores a second
+//     16-bit float with the rounding error of the first: exact for counts up to 2^16, and for sums of arbitrary
+//     values a relative error of 2^-16 instead of 2^-8.
 //   * linear: out[s][k] = sum_c sum[s][c] * w[k][c] as mma.sync m16n8k16 with the samples as the M rows
 //     (rows 8..15 are zero) and eight classes as N. A thread's 16-byte load of w[k][c .. c + 7] and its
 //     16-byte shared-memory read of sum[s][c .. c + 7] are the operands of two MMAs (the channel order
@@ -693,9 +693,12 @@ int pick(const void *x, const void *v_init, const void *w, const void *b, void *
       if constexpr (sizeof(XT) == 2 && std::is_same<XT, VT>::value) {
         // 16-bit activations and membrane, counts exact as 16-bit floats: tensor-core mat-vec form
         const int max_count = std::is_same<XT, __nv_bfloat16>::value ? 256 : 2048;
-        if (al && pool_linear_mma_ok(x, w, C) && (long long)T * HW <= max_count) {
+        if (al && pool_linear_mma_ok(x, w, C) && (long long)T * HW <= 65536) {
           const int mode = (p.mode == 1 && p.hard && p.v_reset == 0.f) ? kScanLifFast : kScanLif;
-          return launch_mma<XT, XT, false>(x, v_init, w, b, out, v_out, T, N, C, HW, K, mode, 1.0f / (float)HW, (float)T, p, stream);
+          if ((long long)T * HW <= max_count)
+            return launch_mma<XT, XT, false>(x, v_init, w, b, out, v_out, T, N, C, HW, K, mode, 1.0f / (float)HW, (float)T, p, stream);
+          // larger counts: two 16-bit parts (an integer below 2^16 is the sum of two bf16 / fp16 values exactly)
+          return launch_mma<XT, XT, true>(x, v_init, w, b, out, v_out, T, N, C, HW, K, mode, 1.0f / (float)HW, (float)T, p, stream);
         }
       }
       if (al && aligned16(w) && C % (CL * V) == 0 && C % 8 == 0 && NTF % (Cs / V) == 0 &&
