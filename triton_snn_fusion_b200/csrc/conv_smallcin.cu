@@ -15,14 +15,18 @@ namespace {
 
 constexpr int kMaxTaps = 36;
 
-template <typename XT, typename ST, typename VT>
+// CIN: the channel count as a compile-time constant, which unrolls the whole window (all 9 * CIN input loads are
+// issued before the first multiply-add and out-of-image taps become predicated zero loads); FAST: tau a power of
+// two with hard reset, evaluated without lif_step's run-time mode switch.
+template <typename XT, typename ST, typename VT, int CIN, bool FAST>
 __global__ void __launch_bounds__(256)
 conv3x3_smallcin_kernel(const XT *__restrict__ x, long long x_t_stride, const XT *__restrict__ w,
                         const XT *__restrict__ bias, const VT *v_init, ST *__restrict__ spikes, VT *v_out,
-                        int T, int B, int Cin, int H, int W, int Cout, int stride, int Ho, int Wo, int lif,
+                        int T, int B, int H, int W, int Cout, int stride, int Ho, int Wo, int lif,
                         LifParams p) {
   extern __shared__ __align__(16) float ws[];   // [9 * Cin][Cout]
-  const int ntaps = 9 * Cin;
+  constexpr int Cin = CIN;
+  constexpr int ntaps = 9 * Cin;
   for (int i = threadIdx.x; i < ntaps * Cout; i += blockDim.x) {
     const int tap = i / Cout, co = i - tap * Cout;
     ws[i] = DT<XT>::to_f(w[(size_t)co * ntaps + tap]);   // [Cout][3][3][Cin] -> [tap][Cout]
@@ -56,28 +60,30 @@ conv3x3_smallcin_kernel(const XT *__restrict__ x, long long x_t_stride, const XT
       const XT *xf = x + (size_t)t * (size_t)x_t_stride + (size_t)b * H * W * Cin;
 #pragma unroll
       for (int i = 0; i < 8; ++i) y[i] = bs[i];
-      for (int kh = 0; kh < 3; ++kh) {
-        const int h = h0 + kh;
-        if (h < 0 || h >= H) continue;
+      float xv[ntaps];
+#pragma unroll
+      for (int kh = 0; kh < 3; ++kh)
+#pragma unroll
         for (int kw = 0; kw < 3; ++kw) {
-          const int wi = w0 + kw;
-          if (wi < 0 || wi >= W) continue;
-          const XT *px = xf + ((size_t)h * W + wi) * Cin;
-          const float *wt = ws + (size_t)((kh * 3 + kw) * Cin) * Cout + c0;
-          for (int ci = 0; ci < Cin; ++ci) {
-            const float xv = DT<XT>::to_f(px[ci]);
-            const float4 wa = *reinterpret_cast<const float4 *>(wt + (size_t)ci * Cout);
-            const float4 wb = *reinterpret_cast<const float4 *>(wt + (size_t)ci * Cout + 4);
-            y[0] = fmaf(wa.x, xv, y[0]); y[1] = fmaf(wa.y, xv, y[1]); y[2] = fmaf(wa.z, xv, y[2]); y[3] = fmaf(wa.w, xv, y[3]);
-            y[4] = fmaf(wb.x, xv, y[4]); y[5] = fmaf(wb.y, xv, y[5]); y[6] = fmaf(wb.z, xv, y[6]); y[7] = fmaf(wb.w, xv, y[7]);
-          }
+          const int h = h0 + kh, wi = w0 + kw;
+          const bool in = h >= 0 && h < H && wi >= 0 && wi < W;
+          const XT *px = xf + ((size_t)(in ? h : 0) * W + (in ? wi : 0)) * Cin;
+#pragma unroll
+          for (int ci = 0; ci < Cin; ++ci) xv[(kh * 3 + kw) * Cin + ci] = in ? DT<XT>::to_f(px[ci]) : 0.f;
         }
+#pragma unroll
+      for (int tp = 0; tp < ntaps; ++tp) {
+        const float4 wa = *reinterpret_cast<const float4 *>(ws + (size_t)tp * Cout + c0);
+        const float4 wb = *reinterpret_cast<const float4 *>(ws + (size_t)tp * Cout + c0 + 4);
+        const float xt = xv[tp];
+        y[0] = fmaf(wa.x, xt, y[0]); y[1] = fmaf(wa.y, xt, y[1]); y[2] = fmaf(wa.z, xt, y[2]); y[3] = fmaf(wa.w, xt, y[3]);
+        y[4] = fmaf(wb.x, xt, y[4]); y[5] = fmaf(wb.y, xt, y[5]); y[6] = fmaf(wb.z, xt, y[6]); y[7] = fmaf(wb.w, xt, y[7]);
       }
     }
     if (lif) {
       float s[8];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) s[i] = lif_step(y[i], v[i], p);
+      for (int i = 0; i < 8; ++i) s[i] = FAST ? lif_step_t<1, true>(y[i], v[i], p) : lif_step(y[i], v[i], p);
       store_pack<ST, 8>(spikes + (size_t)t * frame_out + o0, s);
     } else {
       store_pack<XT, 8>(reinterpret_cast<XT *>(spikes) + (size_t)t * frame_out + o0, y);
@@ -86,18 +92,33 @@ conv3x3_smallcin_kernel(const XT *__restrict__ x, long long x_t_stride, const XT
   if (lif && v_out != nullptr) store_pack<VT, 8>(v_out + o0, v);
 }
 
-template <typename XT, typename ST, typename VT>
-int launch(const ConvArgs &a, cudaStream_t stream) {
+template <typename XT, typename ST, typename VT, int CIN, bool FAST>
+int launch_cin(const ConvArgs &a, cudaStream_t stream) {
   const long long total = (long long)a.B * a.Ho * a.Wo * (a.Cout / 8);
   const long long blocks = (total + 255) / 256;
   if (blocks > 0x7fffffffLL) return fail(SNNB_ERR_INVALID, "conv_lif: problem too large");
   const size_t smem = (size_t)9 * a.Cin * a.Cout * sizeof(float);
-  conv3x3_smallcin_kernel<XT, ST, VT><<<(unsigned)blocks, 256, smem, stream>>>(
+  conv3x3_smallcin_kernel<XT, ST, VT, CIN, FAST><<<(unsigned)blocks, 256, smem, stream>>>(
       static_cast<const XT *>(a.x), (long long)a.x_t_stride, static_cast<const XT *>(a.w), static_cast<const XT *>(a.b),
-      static_cast<const VT *>(a.v_init), static_cast<ST *>(a.spikes), static_cast<VT *>(a.v_out), a.T, a.B, a.Cin,
+      static_cast<const VT *>(a.v_init), static_cast<ST *>(a.spikes), static_cast<VT *>(a.v_out), a.T, a.B,
       a.H, a.W, a.Cout, a.stride, a.Ho, a.Wo, a.lif, a.p);
   SNNB_CHECK_LAUNCH("conv3x3_smallcin");
   return SNNB_OK;
+}
+
+template <typename XT, typename ST, typename VT>
+int launch(const ConvArgs &a, cudaStream_t stream) {
+  const bool fast = a.lif && a.p.mode == 1 && a.p.hard;
+  switch (a.Cin * 2 + (fast ? 1 : 0)) {
+    case 2: return launch_cin<XT, ST, VT, 1, false>(a, stream);
+    case 3: return launch_cin<XT, ST, VT, 1, true>(a, stream);
+    case 4: return launch_cin<XT, ST, VT, 2, false>(a, stream);
+    case 5: return launch_cin<XT, ST, VT, 2, true>(a, stream);
+    case 6: return launch_cin<XT, ST, VT, 3, false>(a, stream);
+    case 7: return launch_cin<XT, ST, VT, 3, true>(a, stream);
+    case 8: return launch_cin<XT, ST, VT, 4, false>(a, stream);
+    default: return launch_cin<XT, ST, VT, 4, true>(a, stream);
+  }
 }
 
 template <typename XT>
