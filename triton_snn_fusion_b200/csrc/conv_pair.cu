@@ -18,10 +18,14 @@ void consume_wait_selftest(long long *limit_cycles, int *drop_load) {
   }
 }
 
-int conv3x3_pair_bf16(const ConvArgs &a, cudaStream_t stream);
-int conv3x3_pair_f16(const ConvArgs &a, cudaStream_t stream);
-int pair_status_bf16(int *out);
-int pair_status_f16(int *out);
+// one translation unit per (activation, spike, membrane) type combination: s = the activation type, u = one-byte
+// spikes, f = fp32 membrane
+#define SNNB_PAIR_UNITS(X) X(bf16_ss) X(bf16_sf) X(bf16_us) X(bf16_uf) X(f16_ss) X(f16_sf) X(f16_us) X(f16_uf)
+#define SNNB_PAIR_DECL(tag)                                        \
+  int conv3x3_pair_##tag(const ConvArgs &a, cudaStream_t stream);  \
+  int pair_status_##tag(int *out);
+SNNB_PAIR_UNITS(SNNB_PAIR_DECL)
+#undef SNNB_PAIR_DECL
 
 bool conv3x3_pair_supported(const ConvArgs &a) {
   if (a.dtype != SNNB_BF16 && a.dtype != SNNB_F16) return false;
@@ -57,16 +61,28 @@ bool conv3x3_pair_supported(const ConvArgs &a) {
 }
 
 int conv3x3_pair(const ConvArgs &a, cudaStream_t stream) {
-  return a.dtype == SNNB_BF16 ? conv3x3_pair_bf16(a, stream) : conv3x3_pair_f16(a, stream);
+  const bool s_u8 = a.lif && a.spike_dtype == SNNB_U8;
+  const bool v_f32 = a.lif && a.v_dtype == SNNB_F32;
+  if (a.dtype == SNNB_BF16) {
+    if (s_u8) return v_f32 ? conv3x3_pair_bf16_uf(a, stream) : conv3x3_pair_bf16_us(a, stream);
+    return v_f32 ? conv3x3_pair_bf16_sf(a, stream) : conv3x3_pair_bf16_ss(a, stream);
+  }
+  if (s_u8) return v_f32 ? conv3x3_pair_f16_uf(a, stream) : conv3x3_pair_f16_us(a, stream);
+  return v_f32 ? conv3x3_pair_f16_sf(a, stream) : conv3x3_pair_f16_ss(a, stream);
 }
 
 int pair_device_status(int *out) {
-  int h1 = 0, h2 = 0;
-  int rc = pair_status_bf16(&h1);
-  if (rc != SNNB_OK) return rc;
-  rc = pair_status_f16(&h2);
-  if (rc != SNNB_OK) return rc;
-  *out = h1 | h2;
+  int all = 0;
+#define SNNB_PAIR_STATUS(tag)                   \
+  {                                             \
+    int h = 0;                                  \
+    const int rc = pair_status_##tag(&h);       \
+    if (rc != SNNB_OK) return rc;               \
+    all |= h;                                   \
+  }
+  SNNB_PAIR_UNITS(SNNB_PAIR_STATUS)
+#undef SNNB_PAIR_STATUS
+  *out = all;
   return SNNB_OK;
 }
 

@@ -1025,17 +1025,6 @@ int launch(const ConvArgs &a, cudaStream_t stream) {
   return SNNB_OK;
 }
 
-template <typename XT>
-int dispatch(const ConvArgs &a, cudaStream_t stream) {
-  const bool s_u8 = a.lif && a.spike_dtype == SNNB_U8;
-  const bool v_f32 = a.lif && a.v_dtype == SNNB_F32;
-  if (s_u8 && v_f32) return launch<XT, uint8_t, float>(a, stream);
-  if (s_u8) return launch<XT, uint8_t, XT>(a, stream);
-  if (v_f32) return launch<XT, XT, float>(a, stream);
-  return launch<XT, XT, XT>(a, stream);
-}
-
-
 // Reads and clears this translation unit's status word (set when a bounded wait gave up).
 int pair_tu_status(int *out) {
   int h = 0;
