@@ -62,6 +62,9 @@ def build(force: bool = False, verbose: bool = False, ptxas_v: bool = False) -> 
     nvcc = _nvcc()
     OBJ_DIR.mkdir(parents=True, exist_ok=True)
     hdr_m = _headers_mtime()
+    src_m = max((s.stat().st_mtime for s in _sources()), default=0.0)
+    if not force and not ptxas_v and LIB_PATH.exists() and LIB_PATH.stat().st_mtime >= max(src_m, hdr_m):
+        return LIB_PATH   # the library is newer than every source (object files may be absent: they need not travel)
     jobs = []
     objs = []
     for src in _sources():
