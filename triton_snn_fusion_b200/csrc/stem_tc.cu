@@ -515,7 +515,9 @@ int launch(const StemGemmArgs &a, cudaStream_t stream) {
   g.tmem_cols = cols;
   g.w_chunk_bytes = a.Cout * 128;
   g.staged = a.Cout == 64 ? 1 : 0;   // a pixel's spikes are one 128-byte (16-bit) or 64-byte (u8) row
-  const int budget = 224 * 1024 - 1024 - 4 * g.w_chunk_bytes - (g.staged ? kStage * kChunkBytes : 0);
+  // bit-packed spikes are stored by the threads themselves: no staging slots, more activation slots instead
+  const bool staging = g.staged && !std::is_same<ST, uint64_t>::value;
+  const int budget = 224 * 1024 - 1024 - 4 * g.w_chunk_bytes - (staging ? kStage * kChunkBytes : 0);
   g.ring = budget / kChunkBytes < kMaxRing ? budget / kChunkBytes : kMaxRing;
   int dev = 0, sms = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 1)
@@ -551,7 +553,7 @@ int launch(const StemGemmArgs &a, cudaStream_t stream) {
                                    : encode_tmap(&sm, a.dtype, 4, a.spikes, dims, strides, box);
     if (rc != SNNB_OK) return rc;
   }
-  const size_t smem = (size_t)4 * g.w_chunk_bytes + (size_t)g.ring * kChunkBytes + (g.staged ? (size_t)kStage * kChunkBytes : 0) + 1024;
+  const size_t smem = (size_t)4 * g.w_chunk_bytes + (size_t)g.ring * kChunkBytes + (staging ? (size_t)kStage * kChunkBytes : 0) + 1024;
   auto kern = stem_gemm_lif_kernel<XT, ST, VT>;
   const cudaError_t e = raise_smem_limit_once<stem_gemm_lif_kernel<XT, ST, VT>>(225 * 1024);
   if (e != cudaSuccess) return fail(SNNB_ERR_CUDA, "stem7x7_lif: cannot raise the shared-memory limit: %s", cudaGetErrorString(e));
