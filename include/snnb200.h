@@ -94,6 +94,15 @@ int snnb_device_status(int *status_out);
 int snnb_selftest_arm_wait_timeout(long long limit_cycles);
 
 /*
+ * Diagnostic (no counterpart in the reference): SM cycles that `ctas` thread blocks, one per SM, each need for
+ * 4 * reps tcgen05.mma instructions of shape M x N x 16 (bf16, fp32 accumulate, operands in shared memory, one
+ * accumulator), from the first issue to the completion of the last. cycles_out[ctas] (device memory) receives one
+ * figure per block, -1 where the bounded wait for completion gave up, in which case *status_out (device memory,
+ * zeroed by the caller) is set to 1. M is 64 or 128, N a multiple of 16 up to 256, reps at most 4096.
+ */
+int snnb_probe_mma_cycles(int M, int N, int reps, int ctas, long long *cycles_out, int *status_out, void *stream);
+
+/*
  * Standalone temporal LIF scan.
  * Replaces run_triton_fused_temporal_lif_state
  * (runtime/triton_temporal_lif_backend.py:57-117) and

@@ -153,3 +153,21 @@ def test_maxpool_of_bit_packed_spikes(shape, dtype):
     L.check(L.lib.snnb_maxpool3x3s2_bits(xd.data_ptr(), y.data_ptr(), frames, H, W, C, L.dtype_code(dtype), None), "pool bits")
     want = F.max_pool2d(spikes.float().permute(0, 3, 1, 2), 3, 2, 1).permute(0, 2, 3, 1)
     assert torch.equal(y.float().cpu(), want)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("M,N", [(128, 256), (128, 64), (64, 128)])
+def test_mma_probe_reports_cycles(M, N):
+    """The tcgen05.mma timing probe ends by itself and reports a positive cycle count for every block."""
+    L = _lib()
+    ctas, reps = 6, 32
+    cyc = torch.zeros(ctas, dtype=torch.int64, device=DEV)
+    st = torch.zeros(1, dtype=torch.int32, device=DEV)
+    L.check(L.lib.snnb_probe_mma_cycles(M, N, reps, ctas, cyc.data_ptr(), st.data_ptr(), None), "probe")
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    assert bool((cyc > 0).all())
+    per = float(cyc.double().mean()) / (4 * reps)
+    assert 8.0 < per < 5000.0, per
+    with pytest.raises(L.SnnbError):
+        L.check(L.lib.snnb_probe_mma_cycles(96, N, reps, ctas, cyc.data_ptr(), st.data_ptr(), None), "probe")

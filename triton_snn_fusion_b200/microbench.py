@@ -6,6 +6,7 @@
     python -m triton_snn_fusion_b200.microbench tail --B 256 --c 1024 --hw 7 --classes 1000
     python -m triton_snn_fusion_b200.microbench stem --B 128 --hw 224
     python -m triton_snn_fusion_b200.microbench linear --M 4096 --K 768 --N 3072
+    python -m triton_snn_fusion_b200.microbench mma                # cycles per tcgen05.mma for M x N shapes
 
 Each case builds seeded synthetic spikes/currents on the GPU (larger than L2 at the default sizes),
 warms the op up three times, times `--reps` launches with CUDA events and prints the algorithmic
@@ -198,6 +199,30 @@ def case_stem(a):
           f"{nbytes / ms / 1e6:.0f} GB/s  spike rate {rate:.3f}  device status {_lib.device_status()}")
 
 
+def case_mma(a):
+    """SM cycles per tcgen05.mma (K = 16, bf16, fp32 accumulate) for the shapes the tile layouts choose between,
+    with one block on the GPU and with one block on every SM."""
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    print(f"cycles per tcgen05.mma.kind::f16 M x N x 16 ({4 * a.reps_mma} instructions behind one commit); "
+          f"128 x 256 x 16 at the nominal dense rate is 128 cycles")
+    print(f"{'M':>4} {'N':>4}  {'1 block':>9}  {'%d blocks (mean / max)' % sms:>24}  useful MACs per cycle and SM (all blocks)")
+    for M in (128, 64):
+        for N in (64, 128, 256):
+            row = []
+            for ctas in (1, sms):
+                cyc = torch.zeros(ctas, dtype=torch.int64, device=DEV)
+                st = torch.zeros(1, dtype=torch.int32, device=DEV)
+                for _ in range(2):   # the first launch also pays for set-up
+                    _lib.check(_lib.lib.snnb_probe_mma_cycles(M, N, a.reps_mma, ctas, cyc.data_ptr(), st.data_ptr(), None), "probe")
+                torch.cuda.synchronize()
+                if int(st.item()) != 0 or int(cyc.min().item()) < 0:
+                    raise SystemExit(f"probe M={M} N={N}: a bounded wait gave up")
+                per = cyc.double() / (4 * a.reps_mma)
+                row.append((float(per.mean()), float(per.max())))
+            macs = M * N * 16 / row[1][0]
+            print(f"{M:>4} {N:>4}  {row[0][0]:9.1f}  {row[1][0]:11.1f} / {row[1][1]:<10.1f}  {macs:8.0f}")
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     sub = ap.add_subparsers(dest="case", required=True)
@@ -242,6 +267,9 @@ def main(argv=None):
     n.add_argument("--path", type=int, default=_lib.PATH_TCGEN05)
     n.add_argument("--dist", choices=["bernoulli", "normal"], default="bernoulli")
     n.set_defaults(fn=case_linear)
+    q = sub.add_parser("mma")
+    q.add_argument("--reps-mma", type=int, default=512, help="batches of four MMAs per measurement")
+    q.set_defaults(fn=case_mma)
     for p in (c, l, d, t, m, n):
         p.add_argument("--T", type=int, default=4)
         p.add_argument("--reps", type=int, default=10)
