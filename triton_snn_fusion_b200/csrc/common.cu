@@ -42,6 +42,14 @@ bool twin_enabled() {
   return on;
 }
 
+bool wres_enabled() {
+  static const bool on = [] {
+    const char *e = std::getenv("SNNB_WRES");
+    return e == nullptr || e[0] != '0';
+  }();
+  return on;
+}
+
 int sm_count() {
   static int cached[64] = {};
   int dev = 0;

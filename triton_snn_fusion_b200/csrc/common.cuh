@@ -39,6 +39,8 @@ int head_pool_linear_bf16(const void *x, const void *w, const void *b, float *ou
 // Whether 3x3 / stride 1 convs with at most 64 output channels use the two-kernel-rows-per-MMA form of the
 // timestep-pair kernel (default; SNNB_TWIN=0 in the environment selects the form that duplicates the weight rows).
 bool twin_enabled();
+// experiment switch: SNNB_WRES=0 keeps the weight ring in the twin form
+bool wres_enabled();
 
 // Number of SMs of the current device (queried once per device; 0 if the query fails).
 int sm_count();

@@ -46,6 +46,7 @@ constexpr int kPairRing = 3;                           // halo (pair) slots
 constexpr int kPairRingMax = 4;                        // ... four of the smaller halo-free tiles of 1x1 convs, which each feed one MMA group only
 constexpr int kIdentBytes = 192 * 128;                 // zero rows / 64x64 identity / zero rows, see the residual path
 constexpr int kWRingP = 5;                             // weight-tile slots (16 KB each): a load must cover ~1 us of L2 latency
+constexpr int kWBarsP = 8;                             // barrier pairs reserved for weight slots (the resident form uses six)
 constexpr int kWSlot = 128 * 128;
 constexpr int kEpiW = 8;
 // "twin" mode (3x3 / stride 1 conv with at most 64 output channels): see PairGeom::twin
@@ -78,7 +79,9 @@ struct PairGeom {
   int halo_t;     // bytes of one timestep's tile: pw * 16 * 128
   int tile_rows;  // output rows a tile produces: 14 (with halo) or 16 (flat)
   int ring;   // halo slots in use
-  int wring;  // weight slots in use (<= kWRingP)
+  int wring;  // weight slots in use (<= kWBarsP)
+  int wres;   // twin form without residual, one channel slab: the six weight tiles (96 KB) are loaded once per block and
+              // stay in shared memory for all its tiles (two halo slots instead of three make the room)
   int stack;  // maps of at most 7 x 8: two images per tile, image b in row groups 0.., image b + 1 in groups 8..
               // (halo rows 0..8 and 8..16 of a timestep's region: row 8 is the zero padding of both, row 16
               // is row 0 of the next region, which is the zero top padding of whatever is stored there)
@@ -380,7 +383,7 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
   using R = Roles<TWIN>;
   const bool dup = DUP || (S2 && g.dup);
   extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t bars[2 * kPairRingMax + 2 * kWRingP + 4];
+  __shared__ __align__(8) uint64_t bars[2 * kPairRingMax + 2 * kWBarsP + 4];
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_s;
 
@@ -397,9 +400,9 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
   auto hfull = [&](uint32_t s) { return bar_base + 8u * s; };
   auto hempty = [&](uint32_t s) { return bar_base + 8u * ((uint32_t)kPairRingMax + s); };
   auto wfull = [&](uint32_t s) { return bar_base + 8u * (2u * kPairRingMax + s); };
-  auto wempty = [&](uint32_t s) { return bar_base + 8u * (2u * kPairRingMax + kWRingP + s); };
-  auto accfull = [&](uint32_t s) { return bar_base + 8u * (2u * kPairRingMax + 2u * kWRingP + s); };
-  auto accempty = [&](uint32_t s) { return bar_base + 8u * (2u * kPairRingMax + 2u * kWRingP + 2u + s); };
+  auto wempty = [&](uint32_t s) { return bar_base + 8u * (2u * kPairRingMax + kWBarsP + s); };
+  auto accfull = [&](uint32_t s) { return bar_base + 8u * (2u * kPairRingMax + 2u * kWBarsP + s); };
+  auto accempty = [&](uint32_t s) { return bar_base + 8u * (2u * kPairRingMax + 2u * kWBarsP + 2u + s); };
   volatile int *abort_flag = &abort_s;
   const long long wl = g.wait_limit;   // SM cycles after which a wait on an mbarrier gives up
 
@@ -530,6 +533,7 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
       for (int tile = blockIdx.x; tile < g.total_tiles && ok; tile += gridDim.x) {
         const int n0 = (tile % g.n_tiles_n) * 128;
         for (int pair = 0; pair < g.npairs && ok; ++pair) {
+          if (TWIN && g.wres && (tile != (int)blockIdx.x || pair != 0)) continue;   // resident weights: loaded once
           for (int sp = 0; sp < g.kslabs * (S2 ? 4 : 1) && ok; ++sp) {
             const int slab = S2 ? sp >> 2 : sp, ph = S2 ? sp & 3 : 0;
             for (int j = 0; j < phase_ntaps<S2, TWIN>(g, ph); ++j) {
@@ -597,7 +601,8 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
             ok = umma::mbar_wait(hfull(slot), phase, abort_flag, wl);
             if (!ok) break;
             for (int tap = 0; tap < phase_ntaps<S2, TWIN>(g, ph); ++tap) {
-              ok = umma::mbar_wait(wfull(ws), wphase, abort_flag, wl);
+              // resident weights: slot = tap, complete after the first pass over the six slots
+              if (!(TWIN && g.wres) || (it == 0 && pair == 0)) ok = umma::mbar_wait(wfull(ws), wphase, abort_flag, wl);
               if (!ok) break;
               umma::tc_fence_after_sync();
               int wtap_unused, off;
@@ -983,6 +988,7 @@ int launch(const ConvArgs &a, cudaStream_t stream) {
   g.wring = ident ? kWRingP - 1 : kWRingP;
   size_t smem = (ident ? (size_t)kIdentBytes : 0) + (size_t)g.wring * kWSlot + (size_t)g.ring * g.tq * g.halo_t +
                 4 * kRowBytes + 1024;
+  g.wres = 0;
   if (g.twin) {   // a smaller identity block and weight ring make room for the exchange buffers
     g.wring = ident ? 3 : 4;
     // (the junk rows read past the last halo slot fall into the exchange buffers, which only the epilogue writes)
@@ -990,6 +996,15 @@ int launch(const ConvArgs &a, cudaStream_t stream) {
     smem = (size_t)g.stage_off + kXchgBytes + 1024;
     static_assert(kTwinIdentBytes + 3 * kWSlot + kPairRing * 2 * kHaloT + kXchgBytes + 1024 <= 225 * 1024, "twin mode: shared memory");
     static_assert(4 * kWSlot + kPairRing * 2 * kHaloT + kXchgBytes + 1024 <= 225 * 1024, "twin mode: shared memory");
+    if (!ident && g.kslabs == 1 && g.tq == 2 && wres_enabled()) {   // all six weight tiles stay resident
+      g.wres = 1;
+      g.wring = 6;
+      g.ring = 2;
+      g.stage_off = g.wring * kWSlot + g.ring * g.tq * g.halo_t;
+      smem = (size_t)g.stage_off + kXchgBytes + 1024;
+      static_assert(6 * kWSlot + 2 * 2 * kHaloT + kXchgBytes + 1024 <= 225 * 1024, "twin mode, resident weights: shared memory");
+      static_assert(6 <= kWBarsP, "twin mode, resident weights: barriers");
+    }
   }
   auto kern = g.s2 ? conv3x3_pair_kernel<XT, ST, VT, true, false, false>
               : g.twin ? conv3x3_pair_kernel<XT, ST, VT, false, true, false>

@@ -201,26 +201,41 @@ def case_stem(a):
 
 def case_mma(a):
     """SM cycles per tcgen05.mma (K = 16, bf16, fp32 accumulate) for the shapes the tile layouts choose between,
-    with one block on the GPU and with one block on every SM."""
+    with one block on the GPU and with one block on every SM; then the 128 x 256 shape on every SM for about 0.2 s
+    with zero and with random operands: cycles per instruction and the SM clock the blocks really ran at."""
     sms = torch.cuda.get_device_properties(0).multi_processor_count
+
+    def probe(M, N, reps, ctas, fill, commit_every=0):
+        cyc = torch.zeros(ctas, dtype=torch.int64, device=DEV)
+        ns = torch.zeros(ctas, dtype=torch.int64, device=DEV)
+        st = torch.zeros(1, dtype=torch.int32, device=DEV)
+        for _ in range(2):   # the first launch also pays for set-up
+            _lib.check(_lib.lib.snnb_probe_mma_cycles(M, N, reps, ctas, fill, commit_every, cyc.data_ptr(), ns.data_ptr(), st.data_ptr(), None), "probe")
+        torch.cuda.synchronize()
+        if int(st.item()) != 0 or int(cyc.min().item()) < 0:
+            raise SystemExit(f"probe M={M} N={N}: a bounded wait gave up")
+        return cyc.double(), ns.double()
+
     print(f"cycles per tcgen05.mma.kind::f16 M x N x 16 ({4 * a.reps_mma} instructions behind one commit); "
           f"128 x 256 x 16 at the nominal dense rate is 128 cycles")
     print(f"{'M':>4} {'N':>4}  {'1 block':>9}  {'%d blocks (mean / max)' % sms:>24}  useful MACs per cycle and SM (all blocks)")
     for M in (128, 64):
         for N in (64, 128, 256):
-            row = []
-            for ctas in (1, sms):
-                cyc = torch.zeros(ctas, dtype=torch.int64, device=DEV)
-                st = torch.zeros(1, dtype=torch.int32, device=DEV)
-                for _ in range(2):   # the first launch also pays for set-up
-                    _lib.check(_lib.lib.snnb_probe_mma_cycles(M, N, a.reps_mma, ctas, cyc.data_ptr(), st.data_ptr(), None), "probe")
-                torch.cuda.synchronize()
-                if int(st.item()) != 0 or int(cyc.min().item()) < 0:
-                    raise SystemExit(f"probe M={M} N={N}: a bounded wait gave up")
-                per = cyc.double() / (4 * a.reps_mma)
-                row.append((float(per.mean()), float(per.max())))
-            macs = M * N * 16 / row[1][0]
-            print(f"{M:>4} {N:>4}  {row[0][0]:9.1f}  {row[1][0]:11.1f} / {row[1][1]:<10.1f}  {macs:8.0f}")
+            one, _ = probe(M, N, a.reps_mma, 1, 0)
+            allc, _ = probe(M, N, a.reps_mma, sms, 0)
+            per1, per = one / (4 * a.reps_mma), allc / (4 * a.reps_mma)
+            print(f"{M:>4} {N:>4}  {float(per1.mean()):9.1f}  {float(per.mean()):11.1f} / {float(per.max()):<10.1f}  "
+                  f"{M * N * 16 / float(per.mean()):8.0f}")
+    for ce in (1, 2, 4):
+        c, _ = probe(128, 256, a.reps_mma, sms, 0, ce)
+        print(f" 128  256  with a tcgen05.commit after every {ce} batch(es) of four: {float(c.mean()) / (4 * a.reps_mma):7.1f} cycles per instruction")
+    long_reps = 1 << 18   # 2^20 instructions of 128 cycles: about 0.07 s at full clock
+    print(f"128 x 256 x 16 on {sms} blocks, {4 * long_reps} instructions each:")
+    for fill, name in ((0, "zero operands"), (1, "random operands")):
+        cyc, ns = probe(128, 256, long_reps, sms, fill)
+        mhz = float((cyc / ns).mean()) * 1e3
+        tflops = sms * 2 * 128 * 256 * 16 * 4 * long_reps / float(ns.mean()) * 1e9 / 1e12
+        print(f"  {name:16s} {float(cyc.mean()) / (4 * long_reps):7.1f} cycles per instruction, SM clock {mhz:6.0f} MHz, {tflops:7.1f} TFLOP/s")
 
 
 def main(argv=None):
