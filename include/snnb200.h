@@ -100,10 +100,11 @@ int snnb_selftest_arm_wait_timeout(long long limit_cycles);
  * figure per block, -1 where the bounded wait for completion gave up, in which case *status_out (device memory,
  * zeroed by the caller) is set to 1; nanos_out[ctas] (device memory, may be NULL) the global-timer nanoseconds of the
  * same span. random_fill != 0 fills the operand tiles with random bf16 values instead of zeros; commit_every = c > 0
- * adds a tcgen05.commit after every c-th batch of four instructions (as the conv kernels do per K slab). M is 64 or 128, N a
+ * adds a tcgen05.commit after every c-th batch of four instructions (as the conv kernels do per K slab); batch r reads
+ * operand tile pair r % nslots (1 to 4 pairs of 48 KB in shared memory). M is 64 or 128, N a
  * multiple of 16 up to 256, reps at most 2^20 (the wait for completion gives up after about two seconds).
  */
-int snnb_probe_mma_cycles(int M, int N, int reps, int ctas, int random_fill, int commit_every,
+int snnb_probe_mma_cycles(int M, int N, int reps, int ctas, int random_fill, int commit_every, int nslots,
                           long long *cycles_out, long long *nanos_out, int *status_out, void *stream);
 
 /*

@@ -164,11 +164,11 @@ def test_mma_probe_reports_cycles(M, N):
     cyc = torch.zeros(ctas, dtype=torch.int64, device=DEV)
     st = torch.zeros(1, dtype=torch.int32, device=DEV)
     ns = torch.zeros(ctas, dtype=torch.int64, device=DEV)
-    L.check(L.lib.snnb_probe_mma_cycles(M, N, reps, ctas, 1, 1, cyc.data_ptr(), ns.data_ptr(), st.data_ptr(), None), "probe")
+    L.check(L.lib.snnb_probe_mma_cycles(M, N, reps, ctas, 1, 1, 3, cyc.data_ptr(), ns.data_ptr(), st.data_ptr(), None), "probe")
     torch.cuda.synchronize()
     assert int(st.item()) == 0
     assert bool((cyc > 0).all()) and bool((ns > 0).all())
     per = float(cyc.double().mean()) / (4 * reps)
     assert 8.0 < per < 5000.0, per
     with pytest.raises(L.SnnbError):
-        L.check(L.lib.snnb_probe_mma_cycles(96, N, reps, ctas, 0, 0, cyc.data_ptr(), None, st.data_ptr(), None), "probe")
+        L.check(L.lib.snnb_probe_mma_cycles(96, N, reps, ctas, 0, 0, 1, cyc.data_ptr(), None, st.data_ptr(), None), "probe")

@@ -26,7 +26,7 @@ SIGNATURES = {
     "snnb_last_error": (c_char_p, []),
     "snnb_device_status": (c_int, [POINTER(c_int)]),
     "snnb_selftest_arm_wait_timeout": (c_int, [c_int64]),
-    "snnb_probe_mma_cycles": (c_int, [c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "snnb_probe_mma_cycles": (c_int, [c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
     "snnb_lif_scan": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int, c_int, c_int,
                               c_float, c_float, c_float, c_void_p]),
     "snnb_lif_avgpool_linear": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,

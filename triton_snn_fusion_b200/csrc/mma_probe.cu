@@ -17,15 +17,17 @@ namespace snnb {
 namespace {
 
 __global__ void __launch_bounds__(128)
-mma_probe_kernel(int M, int N, int reps, int random_fill, int commit_every, long long *cycles, long long *nanos, int *status) {
+mma_probe_kernel(int M, int N, int reps, int random_fill, int commit_every, int nslots, long long *cycles, long long *nanos, int *status) {
   extern __shared__ uint8_t probe_smem[];
   __shared__ __align__(8) uint64_t bar, side_bar;
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_s;
   const uint32_t base = (umma::smem_u32(probe_smem) + 1023u) & ~1023u;
+  // `nslots` operand tile pairs of 48 KB (A 16 KB, B 32 KB); batch r reads pair r % nslots
   const uint32_t a_base = base, b_base = base + 128u * 128u;
+  constexpr uint32_t kPairBytes = 128u * 128u + 256u * 128u;
   uint4 *z = reinterpret_cast<uint4 *>(probe_smem + (base - umma::smem_u32(probe_smem)));
-  for (int i = threadIdx.x; i < (128 * 128 + 256 * 128) / 16; i += blockDim.x) {
+  for (int i = threadIdx.x; i < nslots * (int)(kPairBytes / 16); i += blockDim.x) {
     uint4 v = make_uint4(0u, 0u, 0u, 0u);
     if (random_fill) {   // bf16 values in (-2, 2) with random mantissas: operands that toggle the datapath
       uint32_t h = (uint32_t)i * 2654435761u + blockIdx.x * 40503u + 12345u;
@@ -60,10 +62,13 @@ mma_probe_kernel(int M, int N, int reps, int random_fill, int commit_every, long
     long long n0, n1;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(n0));
     const long long t0 = clock64();
+    int sl = 0;
     for (int r = 0; r < reps; ++r) {
+      const uint64_t so = (uint64_t)((uint32_t)sl * kPairBytes >> 4);
 #pragma unroll
       for (int k = 0; k < 4; ++k)
-        umma::mma_f16_ss(tmem_base, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc, (r > 0 || k > 0) ? 1u : 0u);
+        umma::mma_f16_ss(tmem_base, adesc + so + (uint64_t)(2 * k), bdesc + so + (uint64_t)(2 * k), idesc, (r > 0 || k > 0) ? 1u : 0u);
+      if (++sl == nslots) sl = 0;
       // the conv kernels commit after every K slab (to release its weight slot); what does that cost?
       if (commit_every > 0 && (r + 1) % commit_every == 0) umma::mma_commit(umma::smem_u32(&side_bar));
     }
@@ -86,17 +91,18 @@ mma_probe_kernel(int M, int N, int reps, int random_fill, int commit_every, long
 }  // namespace
 }  // namespace snnb
 
-extern "C" int snnb_probe_mma_cycles(int M, int N, int reps, int ctas, int random_fill, int commit_every,
+extern "C" int snnb_probe_mma_cycles(int M, int N, int reps, int ctas, int random_fill, int commit_every, int nslots,
                                      long long *cycles_out, long long *nanos_out, int *status_out, void *stream) {
   using namespace snnb;
   SNNB_CHECK_ARG(cycles_out != nullptr && status_out != nullptr, "probe_mma_cycles: null pointer");
   SNNB_CHECK_ARG(M == 64 || M == 128, "probe_mma_cycles: M must be 64 or 128");
   SNNB_CHECK_ARG(N >= 16 && N <= 256 && N % 16 == 0, "probe_mma_cycles: N must be a multiple of 16 in [16, 256]");
   SNNB_CHECK_ARG(reps >= 1 && reps <= (1 << 20) && ctas >= 1 && ctas <= 1024, "probe_mma_cycles: reps in [1, 2^20], ctas in [1, 1024]");
-  const size_t smem = 128 * 128 + 256 * 128 + 1024;
-  const cudaError_t e = raise_smem_limit_once<mma_probe_kernel>(64 * 1024);
+  SNNB_CHECK_ARG(nslots >= 1 && nslots <= 4, "probe_mma_cycles: nslots in [1, 4]");
+  const size_t smem = (size_t)nslots * (128 * 128 + 256 * 128) + 1024;
+  const cudaError_t e = raise_smem_limit_once<mma_probe_kernel>(200 * 1024);
   if (e != cudaSuccess) return fail(SNNB_ERR_CUDA, "probe_mma_cycles: cannot raise the shared-memory limit: %s", cudaGetErrorString(e));
-  mma_probe_kernel<<<(unsigned)ctas, 128, smem, static_cast<cudaStream_t>(stream)>>>(M, N, reps, random_fill, commit_every, cycles_out, nanos_out, status_out);
+  mma_probe_kernel<<<(unsigned)ctas, 128, smem, static_cast<cudaStream_t>(stream)>>>(M, N, reps, random_fill, commit_every, nslots, cycles_out, nanos_out, status_out);
   SNNB_CHECK_LAUNCH("mma_probe");
   return SNNB_OK;
 }

@@ -205,12 +205,12 @@ def case_mma(a):
     with zero and with random operands: cycles per instruction and the SM clock the blocks really ran at."""
     sms = torch.cuda.get_device_properties(0).multi_processor_count
 
-    def probe(M, N, reps, ctas, fill, commit_every=0):
+    def probe(M, N, reps, ctas, fill, commit_every=0, nslots=1):
         cyc = torch.zeros(ctas, dtype=torch.int64, device=DEV)
         ns = torch.zeros(ctas, dtype=torch.int64, device=DEV)
         st = torch.zeros(1, dtype=torch.int32, device=DEV)
         for _ in range(2):   # the first launch also pays for set-up
-            _lib.check(_lib.lib.snnb_probe_mma_cycles(M, N, reps, ctas, fill, commit_every, cyc.data_ptr(), ns.data_ptr(), st.data_ptr(), None), "probe")
+            _lib.check(_lib.lib.snnb_probe_mma_cycles(M, N, reps, ctas, fill, commit_every, nslots, cyc.data_ptr(), ns.data_ptr(), st.data_ptr(), None), "probe")
         torch.cuda.synchronize()
         if int(st.item()) != 0 or int(cyc.min().item()) < 0:
             raise SystemExit(f"probe M={M} N={N}: a bounded wait gave up")
@@ -229,6 +229,11 @@ def case_mma(a):
     for ce in (1, 2, 4):
         c, _ = probe(128, 256, a.reps_mma, sms, 0, ce)
         print(f" 128  256  with a tcgen05.commit after every {ce} batch(es) of four: {float(c.mean()) / (4 * a.reps_mma):7.1f} cycles per instruction")
+    for ns in (2, 4):
+        for N in (128, 256):
+            c, _ = probe(128, N, a.reps_mma, sms, 1, 1, ns)
+            print(f" 128 {N:4d}  batches cycling through {ns} operand tile pairs (random values, commit per batch): "
+                  f"{float(c.mean()) / (4 * a.reps_mma):7.1f} cycles per instruction")
     long_reps = 1 << 18   # 2^20 instructions of 128 cycles: about 0.07 s at full clock
     print(f"128 x 256 x 16 on {sms} blocks, {4 * long_reps} instructions each:")
     for fill, name in ((0, "zero operands"), (1, "random operands")):
