@@ -266,12 +266,17 @@ __device__ __forceinline__ void pair_epilogue_lean(const LifParams &p, uint32_t 
   const float v_th = p.v_th;
   const int cs = COUT ? COUT : pm.Cout;
   ST *row = out + pm.row0_off;
+  uint32_t ab[2][2][16];   // [buffer][timestep][pixel]: the next 16 pixels travel while these are evaluated
+  umma::tmem_ld_x16(tmem_addr, ab[0][0]);
+  umma::tmem_ld_x16(tmem_addr + 128u, ab[0][1]);
 #pragma unroll
   for (int c = 0; c < NCH; ++c) {
-    uint32_t a[2][16];   // [timestep][pixel]
-    umma::tmem_ld_x16(tmem_addr + (uint32_t)(c * 16), a[0]);
-    umma::tmem_ld_x16(tmem_addr + (uint32_t)(128 + c * 16), a[1]);
     umma::tmem_ld_wait();
+    uint32_t (&a)[2][16] = ab[c & 1];
+    if (c + 1 < NCH) {
+      umma::tmem_ld_x16(tmem_addr + (uint32_t)((c + 1) * 16), ab[(c + 1) & 1][0]);
+      umma::tmem_ld_x16(tmem_addr + (uint32_t)(128 + (c + 1) * 16), ab[(c + 1) & 1][1]);
+    }
 #pragma unroll
     for (int rr = 0; rr < 2; ++rr) {
       ST *q0 = row, *q1 = row + frame_out;
