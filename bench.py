@@ -355,12 +355,12 @@ def run_ours(args):
     achieved = d["flop"] / (d["ms"] * 1e-3) / 1e12 if d["ms"] > 0 else 0.0
     top = sorted(layer_ms.items(), key=lambda kv: -kv[1])[:6]
     # DRAM traffic per launch of the dominant kernel: one ncu capture of a 128->128, 56x56, T=4, batch-32
-    # layer read 103.33 MB and wrote 78.29 MB (its ncu summary is committed with the other profiles). The kernel
+    # layer read 103.17 MB and wrote 78.43 MB (its ncu summary is committed with the other profiles). The kernel
     # moves each activation once, so the figure is scaled by the activation elements (in + out) of the
     # layers it serves here and averaged over its launches.
     traffic = None
     if dom == "conv3x3_pair":
-        cap_bytes, cap_elems = 181.62e6, 4 * 32 * 56 * 56 * (128 + 128)
+        cap_bytes, cap_elems = 181.60e6, 4 * 32 * 56 * 56 * (128 + 128)
         elems = 0
         for L in spec:
             if L["name"] not in fused_into and kernel_of(L) == dom:
