@@ -221,8 +221,8 @@ int snnb_conv3x3_shortcut_lif(const void *x_seq, int64_t x_t_stride, const void 
  * tensor cores. Same reference items as snnb_conv_lif (kernel key k7_s2_p3,
  * kernels/benchmark_conv_lif_temporal_general.py:561-710, runtime/triton_convlif_backend.py:393-430);
  * snnb_conv_lif runs this shape on CUDA cores, this entry is the fast path for 16-bit data.
- *   x_seq [T][B][H][W][3] (x_t_stride elements apart; 0 = one frame for every step, convolved once),
- *   H and W even; w_packed [Cout][4][4][16] produced once by snnb_stem7x7_pack_weight from the
+ *   x_seq [T][B][H][W][3] (x_t_stride elements apart; 0 = one frame for every step, convolved once;
+ *   4-byte aligned with an even stride: it is read in 32-bit words), H and W even; w_packed [Cout][4][4][16] produced once by snnb_stem7x7_pack_weight from the
  *   [Cout][7][7][3] channels-last weight; spikes [T][B][H/2][W/2][Cout]; v_init/v_out [B][H/2][W/2][Cout]
  *   (v_out may be NULL, as for snnb_conv_lif). With Cout == 64 spike_dtype may also be SNNB_B1 (bit-packed,
  *   [T][B][H/2][W/2] 64-bit words).

@@ -20,36 +20,36 @@ static __device__ __align__(256) unsigned char g_stem_static_scratch[SNNB_STEM_S
 namespace snnb {
 namespace {
 
-// x [B][H][W][3] -> s [B][H/2+3][W/2+3][16], zero padded. One thread per (block, 8-channel half).
+// x [B][H][W][3] -> s [B][H/2+3][W/2+3][16], zero padded. One thread per 2x2 block of pixels: the block's two image
+// rows are 12 contiguous bytes each (two pixels x three 16-bit channels, 4-byte aligned because W is even), read as
+// three 32-bit words, and leave as the block's 32 bytes: channel (dr * 2 + dc) * 3 + c for c < 3, four zero channels.
 template <typename XT>
 __global__ void __launch_bounds__(256)
 stem_s2d_kernel(const XT *__restrict__ x, XT *__restrict__ s, int B, int H, int W) {
   const int Hb = H / 2 + 3, Wb = W / 2 + 3;
-  const long long total = (long long)B * Hb * Wb * 2;
+  const long long total = (long long)B * Hb * Wb;
   long long idx = (long long)blockIdx.x * 256 + threadIdx.x;
   if (idx >= total) return;
-  const int half = (int)(idx & 1);
-  idx >>= 1;
+  const long long out_idx = idx;
   const int bw = (int)(idx % Wb);
   idx /= Wb;
   const int bh = (int)(idx % Hb);
   const long long b = idx / Hb;
-  Pack<XT, 8> out;
-#pragma unroll
-  for (int i = 0; i < 8; ++i) out.v[i] = DT<XT>::from_f(0.f);
+  uint32_t r0[3] = {0u, 0u, 0u}, r1[3] = {0u, 0u, 0u};
   const int ph = bh - 2, pw = bw - 2;  // block coordinates in the image
   if (ph >= 0 && ph < H / 2 && pw >= 0 && pw < W / 2) {
+    const uint32_t *p0 = reinterpret_cast<const uint32_t *>(x + ((b * H + 2 * ph) * W + 2 * pw) * 3);
+    const uint32_t *p1 = reinterpret_cast<const uint32_t *>(x + ((b * H + 2 * ph + 1) * W + 2 * pw) * 3);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int ch = half * 8 + i;  // (dr*2 + dc)*3 + c for ch < 12
-      if (ch < 12) {
-        const int q = ch / 3, c = ch - q * 3;
-        const int dr = q >> 1, dc = q & 1;
-        out.v[i] = x[((b * H + 2 * ph + dr) * W + 2 * pw + dc) * 3 + c];
-      }
+    for (int i = 0; i < 3; ++i) {
+      r0[i] = __ldg(p0 + i);
+      r1[i] = __ldg(p1 + i);
     }
   }
-  *reinterpret_cast<int4 *>(s + (((b * Hb + bh) * Wb + bw) * 16 + half * 8)) = *reinterpret_cast<const int4 *>(&out);
+  // 16-bit channels 0..5 = row 0 (pixel 0: c0 c1 c2, pixel 1: c0 c1 c2), 6..11 = row 1, 12..15 = 0
+  int4 *dst = reinterpret_cast<int4 *>(s + out_idx * 16);
+  dst[0] = make_int4((int)r0[0], (int)r0[1], (int)r0[2], (int)r1[0]);
+  dst[1] = make_int4((int)r1[1], (int)r1[2], 0, 0);
 }
 
 // w [Cout][7][7][3] -> wp [Cout][4 block-rows][4 block-cols][16]; tap (kh, kw) = (2i + dr - 1, 2j + dc - 1).
@@ -103,6 +103,8 @@ extern "C" int snnb_stem7x7_lif(const void *x_seq, int64_t x_t_stride, const voi
   SNNB_CHECK_ARG(v_dtype == dtype || v_dtype == SNNB_F32, "stem7x7_lif: v dtype must be the x dtype or f32");
   SNNB_CHECK_ARG(x_t_stride >= 0 && tau != 0.0f, "stem7x7_lif: bad frame stride or tau");
   SNNB_CHECK_ARG(aligned16(scratch) && aligned16(w_packed), "stem7x7_lif: scratch and weights must be 16-byte aligned");
+  SNNB_CHECK_ARG((reinterpret_cast<uintptr_t>(x_seq) & 3u) == 0 && x_t_stride % 2 == 0,
+                 "stem7x7_lif: the input must be 4-byte aligned and its frame stride even (it is read in 32-bit words)");
   const int frames = (x_t_stride == 0) ? 1 : T;  // one frame reused for all steps: re-laid (and convolved) once
   SNNB_CHECK_ARG((int64_t)frames * B <= 0x7fffffffLL, "stem7x7_lif: too many frames");
   const int64_t need = snnb_stem7x7_scratch_bytes(frames * B, H, W);
@@ -112,7 +114,7 @@ extern "C" int snnb_stem7x7_lif(const void *x_seq, int64_t x_t_stride, const voi
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int Hb = H / 2 + 3, Wb = W / 2 + 3;
   for (int f = 0; f < frames; ++f) {
-    const long long total = (long long)B * Hb * Wb * 2;
+    const long long total = (long long)B * Hb * Wb;
     const long long blocks = (total + 255) / 256;
     SNNB_CHECK_ARG(blocks <= 0x7fffffffLL, "stem7x7_lif: problem too large");
     if (dtype == SNNB_BF16)
